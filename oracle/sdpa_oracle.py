@@ -1,0 +1,160 @@
+"""ctypes front-end of the CPU oracle (``oracle/sdpa_ref.cpp``).
+
+TEST INFRASTRUCTURE ONLY: imported by the test-suite, by the smoke check and by the benchmark's CPU
+baseline leg.  The product package never imports this module.
+
+``sdpa`` takes numpy float32 arrays laid out ``[B,H,S,D]`` (any strides with a unit innermost stride)
+and mirrors the semantics of the reference CPU path restated in ``sdpa_ref.cpp``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from typing import Optional, Tuple
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "_ref", "libaidn_sdpa_oracle.so")
+
+MASK_NONE, MASK_KEEP_U8, MASK_KEEP_F32, MASK_ADD_F32 = 0, 1, 2, 3
+
+
+class _Args(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+        ("out", ctypes.c_void_p), ("lse", ctypes.c_void_p), ("weights", ctypes.c_void_p),
+        ("batch", ctypes.c_int64), ("q_heads", ctypes.c_int64), ("kv_heads", ctypes.c_int64),
+        ("seq_q", ctypes.c_int64), ("seq_kv", ctypes.c_int64),
+        ("head_dim", ctypes.c_int64), ("head_dim_v", ctypes.c_int64),
+        ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3),
+        ("v_stride", ctypes.c_int64 * 3), ("o_stride", ctypes.c_int64 * 3),
+        ("scale", ctypes.c_float), ("softcap", ctypes.c_float),
+        ("causal", ctypes.c_int32), ("causal_offset", ctypes.c_int64),
+        ("mask_kind", ctypes.c_int32), ("mask", ctypes.c_void_p),
+        ("mask_stride", ctypes.c_int64 * 4), ("kv_len", ctypes.c_void_p),
+        ("accumulate_f64", ctypes.c_int32), ("faithful", ctypes.c_int32), ("threads", ctypes.c_int32),
+    ]
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle into ``oracle/_ref`` (no-op when the library is already newer than its source)."""
+    src = os.path.join(_HERE, "sdpa_ref.cpp")
+    if (not force and os.path.exists(_LIB_PATH)
+            and os.path.getmtime(_LIB_PATH) >= os.path.getmtime(src)):
+        return _LIB_PATH
+    subprocess.check_call(["make", "-C", _HERE, "-B", "CXX=g++"], stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        _lib = ctypes.CDLL(_LIB_PATH)
+        _lib.aidn_oracle_sdpa.argtypes = [ctypes.POINTER(_Args)]
+        _lib.aidn_oracle_sdpa.restype = ctypes.c_int
+        _lib.aidn_oracle_max_threads.restype = ctypes.c_int
+        _lib.aidn_oracle_f32_to_bf16_array.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+        _lib.aidn_oracle_bf16_to_f32_array.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64]
+    return _lib
+
+
+def max_threads() -> int:
+    return int(lib().aidn_oracle_max_threads())
+
+
+def _strides3(a: np.ndarray) -> Tuple[int, int, int]:
+    assert a.dtype == np.float32 and a.ndim == 4
+    assert a.shape[3] == 1 or a.strides[3] == 4, "innermost stride must be 1 element"
+    return tuple(int(s // 4) for s in a.strides[:3])
+
+
+def sdpa(q: np.ndarray, k: np.ndarray, v: np.ndarray, *, scale: Optional[float] = None,
+         causal: bool = False, causal_offset: Optional[int] = None, softcap: float = 0.0,
+         mask: Optional[np.ndarray] = None, mask_kind: int = MASK_NONE,
+         kv_len: Optional[np.ndarray] = None, want_lse: bool = False, want_weights: bool = False,
+         f64: bool = False, faithful: bool = False, threads: int = 0):
+    """Reference attention.  Returns ``out`` or ``(out, lse, weights)`` when either extra is asked for.
+
+    ``mask`` is a 4-D array broadcastable to ``[B,Hq,Sq,Sk]`` (size-1 axes broadcast): ``bool``/``uint8`` with
+    ``MASK_KEEP_U8`` (true = attend), ``float32`` with ``MASK_KEEP_F32`` (0.0 = masked) or ``MASK_ADD_F32`` (bias).
+    ``causal_offset`` defaults to ``Sk - Sq`` (the SDPA / GQA entry points); pass 0 for the FlashAttention ones.
+    """
+    q = np.asarray(q, dtype=np.float32)
+    k = np.asarray(k, dtype=np.float32)
+    v = np.asarray(v, dtype=np.float32)
+    B, Hq, Sq, D = q.shape
+    Bk, Hkv, Sk, Dk = k.shape
+    Dv = v.shape[3]
+    assert Bk == B and Dk == D and v.shape[:3] == (B, Hkv, Sk)
+    if scale is None:
+        scale = 1.0 / np.sqrt(D)
+    if causal_offset is None:
+        causal_offset = Sk - Sq
+    out = np.empty((B, Hq, Sq, Dv), dtype=np.float32)
+    lse = np.empty((B, Hq, Sq), dtype=np.float32) if want_lse else None
+    weights = np.empty((B, Hq, Sq, Sk), dtype=np.float32) if want_weights else None
+
+    a = _Args()
+    a.q, a.k, a.v, a.out = q.ctypes.data, k.ctypes.data, v.ctypes.data, out.ctypes.data
+    a.lse = lse.ctypes.data if lse is not None else None
+    a.weights = weights.ctypes.data if weights is not None else None
+    a.batch, a.q_heads, a.kv_heads, a.seq_q, a.seq_kv, a.head_dim, a.head_dim_v = B, Hq, Hkv, Sq, Sk, D, Dv
+    a.q_stride = (ctypes.c_int64 * 3)(*_strides3(q))
+    a.k_stride = (ctypes.c_int64 * 3)(*_strides3(k))
+    a.v_stride = (ctypes.c_int64 * 3)(*_strides3(v))
+    a.o_stride = (ctypes.c_int64 * 3)(*_strides3(out))
+    a.scale, a.softcap = float(scale), float(softcap)
+    a.causal, a.causal_offset = int(bool(causal)), int(causal_offset)
+    keep = []
+    if mask is not None:
+        assert mask.ndim == 4
+        if mask_kind == MASK_NONE:
+            mask_kind = MASK_KEEP_U8 if mask.dtype in (np.bool_, np.uint8) else MASK_ADD_F32
+        m = np.ascontiguousarray(mask.astype(np.uint8 if mask_kind == MASK_KEEP_U8 else np.float32))
+        keep.append(m)
+        full = (B, Hq, Sq, Sk)
+        es = m.strides
+        item = m.itemsize
+        ms = []
+        for ax in range(4):
+            assert m.shape[ax] in (1, full[ax]), f"mask axis {ax} not broadcastable"
+            ms.append(0 if m.shape[ax] == 1 and full[ax] != 1 else es[ax] // item)
+        a.mask, a.mask_kind = m.ctypes.data, mask_kind
+        a.mask_stride = (ctypes.c_int64 * 4)(*ms)
+    else:
+        a.mask, a.mask_kind = None, MASK_NONE
+    if kv_len is not None:
+        kl = np.ascontiguousarray(kv_len, dtype=np.int32)
+        assert kl.shape == (B,)
+        keep.append(kl)
+        a.kv_len = kl.ctypes.data
+    else:
+        a.kv_len = None
+    a.accumulate_f64, a.faithful, a.threads = int(f64), int(faithful), int(threads)
+    rc = lib().aidn_oracle_sdpa(ctypes.byref(a))
+    if rc != 0:
+        raise ValueError("oracle rejected the arguments")
+    if want_lse or want_weights:
+        return out, lse, weights
+    return out
+
+
+def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty(x.shape, dtype=np.uint16)
+    lib().aidn_oracle_f32_to_bf16_array(x.ctypes.data, out.ctypes.data, x.size)
+    return out
+
+
+def bf16_bits_to_f32(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.uint16)
+    out = np.empty(x.shape, dtype=np.float32)
+    lib().aidn_oracle_bf16_to_f32_array(x.ctypes.data, out.ctypes.data, x.size)
+    return out

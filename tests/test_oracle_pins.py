@@ -1,0 +1,140 @@
+"""Pins the CPU oracle (oracle/sdpa_ref.cpp) before anything else trusts it.
+
+Every case replays a test of the reference project (file:line in each docstring, paths relative to
+tests/AiDotNet.Tensors.Tests/) against the stored float64 fixtures and closed forms.
+"""
+import numpy as np
+import pytest
+
+from oracle import sdpa_oracle as O
+
+
+def test_softcap_closed_form(golden):
+    """Engines/BatchMatMulAndAttentionTests.cs:287-317 — Q.K^T = [10,-10], cap 2 (4 decimals there)."""
+    out, _, w = O.sdpa(golden["softcap_q"], golden["softcap_k"], golden["softcap_v"], scale=1.0, softcap=2.0,
+                       want_weights=True)
+    assert np.allclose(w.ravel(), golden["softcap_w"], atol=1e-6)
+    assert np.allclose(out.ravel(), golden["softcap_out"], atol=1e-5)
+    _, _, wp = O.sdpa(golden["softcap_q"], golden["softcap_k"], golden["softcap_v"], scale=1.0, want_weights=True)
+    assert wp.ravel()[1] < 1e-3 and w.ravel()[1] > 100 * wp.ravel()[1]
+
+
+def test_cross_attention_sequences(golden):
+    """Engines/DirectGpu/GpuCpuConsistencyTests.cs:895-960 — Sq=2, Sk=3, D=3, scale 0.75 (2e-5 there)."""
+    out, _, w = O.sdpa(golden["cross_q"], golden["cross_k"], golden["cross_v"], scale=0.75, want_weights=True)
+    assert np.abs(out - golden["cross_out"]).max() <= 2e-6
+    assert np.abs(w - golden["cross_w"]).max() <= 2e-6
+
+
+def test_logit_softcap_sequences(golden):
+    """Engines/DirectGpu/GpuCpuConsistencyTests.cs:962-1003 — scale 1.5, softcap 2."""
+    out, _, w = O.sdpa(golden["capcross_q"], golden["capcross_k"], golden["capcross_v"], scale=1.5, softcap=2.0,
+                       want_weights=True)
+    assert np.abs(out - golden["capcross_out"]).max() <= 2e-6
+    assert np.abs(w - golden["capcross_w"]).max() <= 2e-6
+
+
+def test_full_boolean_mask(golden):
+    """Engines/DirectGpu/GpuCpuConsistencyTests.cs:1005-1061 — full [B,H,Sq,Sk] bool mask, true = attend."""
+    m = golden["boolmask_mask"]
+    out, _, w = O.sdpa(golden["cross_q"], golden["cross_k"], golden["cross_v"], scale=0.75, mask=m,
+                       mask_kind=O.MASK_KEEP_U8, want_weights=True)
+    assert np.abs(out - golden["boolmask_out"]).max() <= 2e-6
+    assert np.abs(w - golden["boolmask_w"]).max() <= 2e-6
+    # the float upload of the same mask (false -> 0.0f) must mean the same thing
+    out2 = O.sdpa(golden["cross_q"], golden["cross_k"], golden["cross_v"], scale=0.75, mask=m.astype(np.float32),
+                  mask_kind=O.MASK_KEEP_F32)
+    assert np.array_equal(out, out2)
+
+
+@pytest.mark.parametrize("mb,mh", [(1, 1), (2, 1), (1, 3), (2, 3)])
+def test_broadcast_mask(golden, mb, mh):
+    """Engines/SdpaMaskBroadcastTests.cs:61-114 — [1,1,S,S], [B,1,S,S], [1,H,S,S] masks == materialised mask."""
+    q, k, v = golden["bcast_q"], golden["bcast_k"], golden["bcast_v"]
+    S = q.shape[2]
+    mask = np.broadcast_to(np.tril(np.ones((S, S), np.uint8)), (mb, mh, S, S)).copy()
+    out = O.sdpa(q, k, v, mask=mask, mask_kind=O.MASK_KEEP_U8)
+    assert np.abs(out - golden["bcast_out"]).max() <= 1e-5
+    # the causal flag (bottom-right, Sq == Sk) is the same plane
+    assert np.array_equal(out, O.sdpa(q, k, v, causal=True))
+    # non-vacuity (SdpaMaskBroadcastTests.cs:124-143)
+    assert np.abs(O.sdpa(q, k, v) - golden["bcast_out_nomask"]).max() <= 1e-5
+    assert np.abs(out - golden["bcast_out_nomask"]).max() > 1e-3
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_gqa_reference(golden, causal):
+    """Engines/DirectGpu/RopeGqaOpenClTests.cs:200-279 — Hq 6, Hkv 2, kv = h / group (1e-4 there)."""
+    out = O.sdpa(golden["gqa_q"], golden["gqa_k"], golden["gqa_v"], causal=causal)
+    want = golden["gqa_out_causal"] if causal else golden["gqa_out_plain"]
+    assert np.abs(out - want).max() <= 1e-5
+
+
+def test_decode_shape_list(golden):
+    """Engines/DirectGpu/FlashDecodeCudaTests.cs:43-126 — K/V stored [seqLen, kvHeads, D]; tol 2e-3 + 2e-3|e|."""
+    for n, (h, hk, d, L) in enumerate(golden["decode_shapes"]):
+        q = golden[f"decode{n}_q"][None, :, None, :]
+        k = golden[f"decode{n}_k"].transpose(1, 0, 2)[None]   # strided view, unit inner stride
+        v = golden[f"decode{n}_v"].transpose(1, 0, 2)[None]
+        out = O.sdpa(q, k, v)[0, :, 0, :]
+        assert np.abs(out - golden[f"decode{n}_out"]).max() <= 1e-5
+
+
+def test_flash_attention_bias_and_lse(golden):
+    """Engines/FlashAttentionBiasTests.cs:31-274 — bias added after scale, 3-D bias broadcasts over batch,
+    top-left causal, stats = max + log(sum)  (CpuEngine.cs:29226-29263)."""
+    q, k, v = golden["bias_q"], golden["bias_k"], golden["bias_v"]
+    out, lse, _ = O.sdpa(q, k, v, mask=golden["bias3"][None], mask_kind=O.MASK_ADD_F32, want_lse=True)
+    assert np.abs(out - golden["bias3_out"]).max() <= 2e-5
+    assert np.abs(lse - golden["bias3_lse"]).max() <= 2e-5
+    out, lse, _ = O.sdpa(q, k, v, mask=golden["bias4"], mask_kind=O.MASK_ADD_F32, causal=True, causal_offset=0,
+                         want_lse=True)
+    assert np.abs(out - golden["bias4c_out"]).max() <= 2e-5
+    assert np.abs(lse - golden["bias4c_lse"]).max() <= 2e-5
+
+
+def test_fully_masked_rows_give_zero_and_minus_inf():
+    """CpuEngine.cs:27822-27827 and 29244-29250."""
+    rng = np.random.default_rng(3)
+    q, k, v = (rng.standard_normal((1, 2, 4, 8)).astype(np.float32) for _ in range(3))
+    mask = np.ones((1, 1, 4, 4), np.uint8)
+    mask[0, 0, 2, :] = 0
+    out, lse, w = O.sdpa(q, k, v, mask=mask, mask_kind=O.MASK_KEEP_U8, want_lse=True, want_weights=True)
+    assert np.all(out[:, :, 2, :] == 0) and np.all(w[:, :, 2, :] == 0) and np.all(np.isneginf(lse[:, :, 2]))
+    assert np.all(np.isfinite(lse[:, :, [0, 1, 3]]))
+    # padding mask: kv_len = 0 masks every key of that batch entry
+    out = O.sdpa(q, k, v, kv_len=np.array([0], np.int32))
+    assert np.all(out == 0)
+
+
+def test_bottom_right_vs_top_left_causal():
+    """SDPA/GQA entry points keep k <= q + (Sk - Sq) (CpuEngine.cs:27333-27340); FlashAttention keeps k <= q."""
+    rng = np.random.default_rng(5)
+    q = rng.standard_normal((1, 1, 3, 8)).astype(np.float32)
+    k = rng.standard_normal((1, 1, 7, 8)).astype(np.float32)
+    v = rng.standard_normal((1, 1, 7, 8)).astype(np.float32)
+    br = np.array([[j <= i + 4 for j in range(7)] for i in range(3)], np.uint8)[None, None]
+    tl = np.array([[j <= i for j in range(7)] for i in range(3)], np.uint8)[None, None]
+    assert np.array_equal(O.sdpa(q, k, v, causal=True), O.sdpa(q, k, v, mask=br, mask_kind=O.MASK_KEEP_U8))
+    assert np.array_equal(O.sdpa(q, k, v, causal=True, causal_offset=0), O.sdpa(q, k, v, mask=tl, mask_kind=O.MASK_KEEP_U8))
+
+
+def test_f64_mode_and_faithful_mode_agree():
+    rng = np.random.default_rng(11)
+    q = rng.standard_normal((2, 4, 70, 32)).astype(np.float32)
+    k = rng.standard_normal((2, 2, 130, 32)).astype(np.float32)
+    v = rng.standard_normal((2, 2, 130, 32)).astype(np.float32)
+    kv = np.array([130, 57], np.int32)
+    a = O.sdpa(q, k, v, causal=True, kv_len=kv)
+    b = O.sdpa(q, k, v, causal=True, kv_len=kv, faithful=True)
+    c = O.sdpa(q, k, v, causal=True, kv_len=kv, f64=True)
+    assert np.abs(a - b).max() <= 1e-6     # trimming masked columns does not change a row's arithmetic
+    assert np.abs(a - c).max() <= 5e-6
+
+
+def test_bf16_rounding_vectors(golden):
+    """NumericOperations/BFloat16.cs:65-84 — RNE, NaN keeps its payload top bits and gains the quiet bit."""
+    x = golden["bf16_in_bits"].view(np.float32)
+    assert np.array_equal(O.f32_to_bf16_bits(x), golden["bf16_out_bits"])
+    back = O.bf16_bits_to_f32(golden["bf16_out_bits"])
+    assert np.array_equal(back.view(np.uint32), golden["bf16_out_bits"].astype(np.uint32) << 16)
