@@ -1,0 +1,241 @@
+"""Host-side mirror of the attention methods of the reference's CUDA backend, routed to the sm_100a library.
+
+Method names, argument order, argument meaning and error behaviour follow
+``src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/CudaBackend.cs`` of the reference:
+
+    ScaledDotProductAttention  :8322-8379      FlashAttention      :8522-8538
+    FlashAttentionV2           :8540-8578      GroupedQueryAttention :8721-8759
+    FlashDecode                :2968-3021
+
+and the interface they implement (``Engines/DirectGpu/IDirectGpuBackend.cs:1421-1503``).  Buffers are
+``GpuBuffer`` objects (the mirror of ``IGpuBuffer``, ``IDirectGpuBackend.cs:3776-3803``): a device
+allocation with ``Size`` (element count), ``SizeInBytes`` and ``Handle`` (device address).  torch is used
+only to own device memory and streams.
+
+Differences from the reference methods, all deliberate:
+  * buffers may hold bf16 / fp16 as well as fp32 (``GpuBuffer.dtype``); the output buffer is fp32 or the input dtype;
+  * element counts are 64-bit (the reference's ``checked(int)`` products overflow from S = 8192 on);
+  * ``attentionWeights`` must be None: the weight-returning call stays on the reference's own kernel;
+  * a failure raises; nothing falls back to a CPU path.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import native as N
+
+_DTYPE = {torch.float32: N.F32, torch.float16: N.F16, torch.bfloat16: N.BF16}
+
+
+class GpuBuffer:
+    """Mirror of ``IGpuBuffer``: ``Size`` elements of ``dtype`` at device address ``Handle``."""
+
+    def __init__(self, tensor: torch.Tensor):
+        if not tensor.is_cuda:
+            raise ValueError("GpuBuffer needs a CUDA tensor")
+        if not tensor.is_contiguous():
+            raise ValueError("GpuBuffer needs a contiguous allocation")
+        self.tensor = tensor
+
+    @property
+    def Size(self) -> int:
+        return self.tensor.numel()
+
+    @property
+    def SizeInBytes(self) -> int:
+        return self.tensor.numel() * self.tensor.element_size()
+
+    @property
+    def Handle(self) -> int:
+        return self.tensor.data_ptr()
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.tensor.dtype
+
+
+class CudaBackend:
+    """The attention slice of ``CudaBackend``: one device, one stream (``CudaBackend.cs:371-375``)."""
+
+    def __init__(self, device: int = 0, stream: Optional[torch.cuda.Stream] = None, path: int = N.PATH_AUTO,
+                 decode_chunk: int = 0):
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device: this backend has no CPU path")
+        N.load()
+        self.device = device
+        torch.cuda.set_device(device)
+        self._stream = stream
+        self._path = path
+        self._decode_chunk = decode_chunk
+        self._handles: Dict[Tuple, N.Handle] = {}
+        self._scratch: Optional[torch.Tensor] = None
+        self.launch_count = 0  # kernels enqueued by this backend (the reference counts launches in GpuLaunchProbe)
+
+    # -- plumbing ---------------------------------------------------------------------------------------
+    @property
+    def stream(self) -> torch.cuda.Stream:
+        return self._stream if self._stream is not None else torch.cuda.current_stream(self.device)
+
+    def AllocateBuffer(self, size: int, dtype: torch.dtype = torch.float32) -> GpuBuffer:
+        return GpuBuffer(torch.empty(int(size), dtype=dtype, device=f"cuda:{self.device}"))
+
+    def AllocateByteBuffer(self, size: int) -> GpuBuffer:
+        return GpuBuffer(torch.empty(int(size), dtype=torch.uint8, device=f"cuda:{self.device}"))
+
+    def ConvertToFp16(self, src: GpuBuffer, dst: GpuBuffer, size: int) -> None:
+        N.cast("f32_to_f16", src.Handle, dst.Handle, size, self.stream.cuda_stream)
+
+    def ConvertToFp32(self, src: GpuBuffer, dst: GpuBuffer, size: int) -> None:
+        N.cast("f16_to_f32", src.Handle, dst.Handle, size, self.stream.cuda_stream)
+
+    def ConvertToBf16(self, src: GpuBuffer, dst: GpuBuffer, size: int) -> None:
+        N.cast("f32_to_bf16", src.Handle, dst.Handle, size, self.stream.cuda_stream)
+
+    def Synchronize(self) -> None:
+        self.stream.synchronize()
+
+    def _handle(self, **kw) -> N.Handle:
+        key = tuple(sorted(kw.items()))
+        h = self._handles.get(key)
+        if h is None:
+            h = N.Handle(device=self.device, path=self._path, decode_chunk=self._decode_chunk, **kw)
+            self._handles[key] = h
+        return h
+
+    def _workspace(self, nbytes: int) -> Tuple[Optional[int], int]:
+        if nbytes <= 0:
+            return None, 0
+        if self._scratch is None or self._scratch.numel() < nbytes:
+            self._scratch = torch.empty(nbytes, dtype=torch.uint8, device=f"cuda:{self.device}")
+        return self._scratch.data_ptr(), self._scratch.numel()
+
+    @staticmethod
+    def _check_dims(batch, numHeads, seqQ, seqK, headDim):
+        if batch <= 0 or numHeads <= 0 or seqQ <= 0 or seqK <= 0 or headDim <= 0:
+            raise ValueError("Attention dimensions must be positive.")  # ArgumentOutOfRangeException in the reference
+
+    def _run(self, h: N.Handle, *, query, key, value, output, batch, seqQ, seqK, scale, lse=None, mask=None,
+             mask_stride=(0, 0, 0, 0), kv_len=None, k_stride=None, v_stride=None):
+        ws, ws_bytes = self._workspace(h.workspace_bytes(batch, seqQ, seqK))
+        h.launch(q=query.Handle, k=key.Handle, v=value.Handle, out=output.Handle, batch=batch, seq_q=seqQ, seq_kv=seqK,
+                 stream=self.stream.cuda_stream, lse=lse.Handle if lse is not None else None,
+                 mask=mask.Handle if mask is not None else None, mask_stride=mask_stride,
+                 kv_len=kv_len.Handle if kv_len is not None else None, k_stride=k_stride, v_stride=v_stride,
+                 scale=scale, workspace=ws, workspace_bytes=ws_bytes)
+        self.launch_count += h.last_launch_count
+        self.last_path = h.last_path
+
+    # -- IDirectGpuBackend attention methods ----------------------------------------------------------------
+    def ScaledDotProductAttention(self, query: GpuBuffer, key: GpuBuffer, value: GpuBuffer, output: GpuBuffer,
+                                  attentionWeights: Optional[GpuBuffer], mask: Optional[GpuBuffer], batch: int,
+                                  numHeads: int, seqQ: int, seqK: int, headDim: int, scale: float, isCausal: bool,
+                                  softcap: float = 0.0, numKVHeads: int = 0, kvLengths: Optional[GpuBuffer] = None) -> None:
+        """softmax(Q K^T * scale [softcap] [mask]) V.  ``mask`` is the engine's float upload of a bool mask
+        (0.0 = masked) or a uint8 bool mask: shared [seqQ*seqK] when it holds fewer than batch*heads*seqQ*seqK
+        elements, full otherwise (``CudaBackend.cs:8355``).  Causal is bottom-right: key k is visible to query q
+        iff k <= q + (seqK - seqQ) (``CudaAttentionKernels.cs:66``).  ``kvLengths`` (extension) is an int32 [batch]
+        buffer of valid key counts: the padding mask of a batched decode step without materialising it."""
+        self._check_dims(batch, numHeads, seqQ, seqK, headDim)
+        kvHeads = numKVHeads if numKVHeads > 0 else numHeads
+        if numHeads % kvHeads != 0:
+            raise ValueError("numHeads must be an integer multiple of numKVHeads.")
+        querySize = batch * numHeads * seqQ * headDim
+        keyValueSize = batch * kvHeads * seqK * headDim
+        weightsSize = batch * numHeads * seqQ * seqK
+        if query.Size < querySize or key.Size < keyValueSize or value.Size < keyValueSize or output.Size < querySize:
+            raise ValueError("Attention tensor buffers are smaller than the requested dimensions.")
+        if attentionWeights is not None:
+            raise NotImplementedError("the weight-returning call is not served by the sm_100a library")
+        mask_kind, mask_stride = N.MASK_NONE, (0, 0, 0, 0)
+        if mask is not None:
+            if mask.Size < seqQ * seqK:
+                raise ValueError("The attention mask must contain at least seqQ * seqK elements.")
+            mask_kind = N.MASK_KEEP_U8 if mask.dtype in (torch.uint8, torch.bool) else N.MASK_KEEP_F32
+            full = mask.Size >= weightsSize
+            mask_stride = (numHeads * seqQ * seqK, seqQ * seqK, seqK, 1) if full else (0, 0, seqK, 1)
+        if query.dtype != key.dtype or query.dtype != value.dtype:
+            raise ValueError("query, key and value must share a dtype")
+        h = self._handle(qkv_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[output.dtype], head_dim=headDim,
+                         num_q_heads=numHeads, num_kv_heads=kvHeads, causal=bool(isCausal), causal_bottom_right=True,
+                         mask_kind=mask_kind, softcap=float(softcap))
+        self._run(h, query=query, key=key, value=value, output=output, batch=batch, seqQ=seqQ, seqK=seqK,
+                  scale=float(scale), mask=mask, mask_stride=mask_stride, kv_len=kvLengths)
+
+    def FlashAttention(self, query: GpuBuffer, key: GpuBuffer, value: GpuBuffer, output: GpuBuffer,
+                       mask: Optional[GpuBuffer], batch: int, numHeads: int, seqLen: int, headDim: int, scale: float,
+                       isCausal: bool) -> None:
+        if mask is not None:
+            self.ScaledDotProductAttention(query, key, value, output, None, mask, batch, numHeads, seqLen, seqLen,
+                                           headDim, scale, isCausal)
+            return
+        stats = self.AllocateBuffer(batch * numHeads * seqLen)
+        self.FlashAttentionV2(query, key, value, output, stats, batch, numHeads, seqLen, seqLen, headDim, scale, isCausal)
+
+    def FlashAttentionV2(self, query: GpuBuffer, key: GpuBuffer, value: GpuBuffer, output: GpuBuffer,
+                         softmaxStats: GpuBuffer, batch: int, numHeads: int, seqQ: int, seqK: int, headDim: int,
+                         scale: float, isCausal: bool, attentionBias: Optional[GpuBuffer] = None,
+                         biasBatchStride: int = 0) -> None:
+        """Attention with log-sum-exp statistics and an optional additive bias [B,H,Sq,Sk] (``biasBatchStride`` =
+        H*Sq*Sk) or [H,Sq,Sk] (``biasBatchStride`` = 0).  Causal is top-left: key k visible iff k <= q
+        (``CudaAttentionKernels.cs:197``)."""
+        self._check_dims(batch, numHeads, seqQ, seqK, headDim)
+        if softmaxStats.Size < batch * numHeads * seqQ or softmaxStats.dtype != torch.float32:
+            raise ValueError("softmaxStats must hold batch*heads*seqQ fp32 values")
+        mask_kind, mask_stride = N.MASK_NONE, (0, 0, 0, 0)
+        if attentionBias is not None:
+            mask_kind = N.MASK_ADD_F32
+            mask_stride = (int(biasBatchStride), seqQ * seqK, seqK, 1)
+        h = self._handle(qkv_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[output.dtype], head_dim=headDim,
+                         num_q_heads=numHeads, num_kv_heads=numHeads, causal=bool(isCausal), causal_bottom_right=False,
+                         causal_offset=0, mask_kind=mask_kind, emit_lse=True)
+        self._run(h, query=query, key=key, value=value, output=output, batch=batch, seqQ=seqQ, seqK=seqK,
+                  scale=float(scale), lse=softmaxStats, mask=attentionBias, mask_stride=mask_stride)
+
+    def GroupedQueryAttention(self, query: GpuBuffer, key: GpuBuffer, value: GpuBuffer, output: GpuBuffer,
+                              attentionWeights: Optional[GpuBuffer], batch: int, numQHeads: int, numKVHeads: int,
+                              seqQ: int, seqK: int, headDim: int, scale: float, isCausal: bool) -> None:
+        """GQA with top-left causal masking (``CudaAttentionKernels.cs:598``)."""
+        self._check_dims(batch, numQHeads, seqQ, seqK, headDim)
+        if numKVHeads <= 0 or numQHeads % numKVHeads != 0:
+            raise ValueError("numQHeads must be divisible by numKVHeads")
+        if attentionWeights is not None:
+            raise NotImplementedError("the weight-returning call is not served by the sm_100a library")
+        h = self._handle(qkv_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[output.dtype], head_dim=headDim,
+                         num_q_heads=numQHeads, num_kv_heads=numKVHeads, causal=bool(isCausal),
+                         causal_bottom_right=False, causal_offset=0)
+        self._run(h, query=query, key=key, value=value, output=output, batch=batch, seqQ=seqQ, seqK=seqK,
+                  scale=float(scale))
+
+    def FlashDecode(self, q: GpuBuffer, k: GpuBuffer, v: GpuBuffer, heads: int, kvHeads: int, headDim: int,
+                    seqLen: int, scale: float, splits: int = 0) -> GpuBuffer:
+        """Single-sequence decode over a cache stored [seqLen, kvHeads, headDim] (``CudaBackend.cs:2968-3021``).
+        ``splits`` > 0 fixes the number of KV splits; 0 lets the library choose."""
+        if heads <= 0 or kvHeads <= 0 or headDim <= 0 or heads % kvHeads != 0:
+            raise ValueError("heads must be a positive multiple of kvHeads")
+        if seqLen <= 0:
+            raise ValueError("seqLen must be positive")
+        if q.Size < heads * headDim or k.Size < seqLen * kvHeads * headDim or v.Size < seqLen * kvHeads * headDim:
+            raise ValueError("FlashDecode buffers are smaller than the requested dimensions.")
+        out = self.AllocateBuffer(heads * headDim)
+        chunk = 0
+        if splits > 0:
+            chunk = max(8, (math.ceil(seqLen / min(splits, seqLen)) + 7) // 8 * 8)
+        key = dict(qkv_dtype=_DTYPE[q.dtype], out_dtype=N.F32, head_dim=headDim, num_q_heads=heads,
+                   num_kv_heads=kvHeads, causal=False)
+        hkey = tuple(sorted(key.items())) + (("chunk", chunk),)
+        h = self._handles.get(hkey)
+        if h is None:
+            h = N.Handle(device=self.device, path=self._path, decode_chunk=chunk or self._decode_chunk, **key)
+            self._handles[hkey] = h
+        stride = (0, headDim, kvHeads * headDim)  # (B, H, S) element strides of the [S, Hkv, D] cache
+        self._run(h, query=q, key=k, value=v, output=out, batch=1, seqQ=1, seqK=seqLen, scale=float(scale),
+                  k_stride=stride, v_stride=stride)
+        return out
+
+    def Dispose(self) -> None:
+        for h in self._handles.values():
+            h.close()
+        self._handles.clear()

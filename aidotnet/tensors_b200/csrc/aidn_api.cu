@@ -1,0 +1,388 @@
+// C ABI of libaidotnet_sdpa_sm100 (declared in include/aidn_sdpa.h): argument validation, kernel selection
+// and launch.  No torch types, no allocation on the launch path, no CPU fallback: a request no CUDA kernel
+// of this build can serve is an error.
+#include <dlfcn.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+
+#include "common.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+  return fail(AIDN_ECUDA, "%s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+}
+
+inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+size_t elem_size(int dtype) { return dtype == AIDN_F32 ? 4 : 2; }
+
+// ---- NCCL, resolved lazily so that the library loads on machines without it --------------------------
+struct Nccl {
+  void* lib = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+  int (*GroupStart)() = nullptr;
+  int (*GroupEnd)() = nullptr;
+  int (*CommUserRank)(void*, int*) = nullptr;
+  int (*CommCount)(void*, int*) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  bool ok = false;
+};
+Nccl g_nccl;
+std::once_flag g_nccl_once;
+
+void load_nccl() {
+  const char* names[] = {"libnccl.so.2", "libnccl.so"};
+  for (const char* n : names) {
+    g_nccl.lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (g_nccl.lib) break;
+  }
+  if (!g_nccl.lib) return;
+  g_nccl.AllGather = (decltype(g_nccl.AllGather))dlsym(g_nccl.lib, "ncclAllGather");
+  g_nccl.GroupStart = (decltype(g_nccl.GroupStart))dlsym(g_nccl.lib, "ncclGroupStart");
+  g_nccl.GroupEnd = (decltype(g_nccl.GroupEnd))dlsym(g_nccl.lib, "ncclGroupEnd");
+  g_nccl.CommUserRank = (decltype(g_nccl.CommUserRank))dlsym(g_nccl.lib, "ncclCommUserRank");
+  g_nccl.CommCount = (decltype(g_nccl.CommCount))dlsym(g_nccl.lib, "ncclCommCount");
+  g_nccl.GetErrorString = (decltype(g_nccl.GetErrorString))dlsym(g_nccl.lib, "ncclGetErrorString");
+  g_nccl.ok = g_nccl.AllGather && g_nccl.GroupStart && g_nccl.GroupEnd && g_nccl.CommUserRank && g_nccl.CommCount;
+}
+
+constexpr int kNcclFloat32 = 7, kNcclFloat16 = 6, kNcclBfloat16 = 9;  // ncclDataType_t values (nccl.h)
+
+}  // namespace
+
+struct aidn_sdpa {
+  aidn_sdpa_desc d;
+  int group;
+  int head_count;
+  int32_t* status_dev;
+  void* scratch;
+  int64_t scratch_bytes;
+  int last_path;
+  int last_launches;
+  float* debug;
+};
+
+namespace {
+
+// Keys per split of the decode kernel.  Enough CTAs to fill 148 SMs several times over, but never more than
+// 512 keys per CTA so that ragged kv_len values balance, and never fewer than 64.
+int pick_chunk(const aidn_sdpa* h, int64_t batch, int64_t seq_kv) {
+  if (h->d.decode_chunk > 0) return h->d.decode_chunk;
+  const int gt = h->group <= 2 ? h->group : (h->group <= 4 ? 4 : 8);  // as the decode launcher picks
+  const int gchunks = (h->group + gt - 1) / gt;
+  const int64_t items = batch * (h->head_count / h->group) * gchunks;
+  const int64_t target = 148 * 8;
+  int64_t splits = (target + items - 1) / items;
+  if (splits < 1) splits = 1;
+  int64_t chunk = align_up((seq_kv + splits - 1) / splits, 64);
+  if (chunk > 512) chunk = 512;
+  if (chunk < 64) chunk = 64;
+  return (int)chunk;
+}
+
+int64_t decode_ws_bytes(const aidn_sdpa* h, int64_t batch, int64_t seq_kv, int* chunk_out, int* nchunks_out) {
+  const int chunk = pick_chunk(h, batch, seq_kv);
+  const int64_t nchunks = (seq_kv + chunk - 1) / chunk;
+  if (chunk_out) *chunk_out = chunk;
+  if (nchunks_out) *nchunks_out = (int)nchunks;
+  if (nchunks <= 1) return 0;
+  return align_up(batch * h->head_count * nchunks * (h->d.head_dim + 2) * (int64_t)sizeof(float), 256);
+}
+
+bool aligned16(const void* ptr, const int64_t* stride, size_t esz) {
+  if ((uintptr_t)ptr % 16 != 0) return false;
+  for (int i = 0; i < 3; ++i)
+    if ((stride[i] * (int64_t)esz) % 16 != 0) return false;
+  return true;
+}
+
+void dense_strides(int64_t* s, int64_t heads, int64_t seq, int64_t d) {
+  s[2] = d;
+  s[1] = seq * d;
+  s[0] = heads * seq * d;
+}
+
+bool all_zero(const int64_t* s) { return s[0] == 0 && s[1] == 0 && s[2] == 0; }
+
+}  // namespace
+
+extern "C" {
+
+const char* aidn_sdpa_last_error(void) { return g_err; }
+
+int aidn_sdpa_device_supported(int32_t device) {
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return prop.major == 10 ? 1 : 0;
+}
+
+int aidn_sdpa_create(const aidn_sdpa_desc* desc, aidn_sdpa_t* out) {
+  g_err[0] = 0;
+  if (!desc || !out) return fail(AIDN_EINVAL, "create: null argument");
+  *out = nullptr;
+  const aidn_sdpa_desc& d = *desc;
+  if (d.qkv_dtype < AIDN_F32 || d.qkv_dtype > AIDN_BF16) return fail(AIDN_EINVAL, "create: unknown qkv_dtype %d", d.qkv_dtype);
+  if (d.out_dtype != AIDN_F32 && d.out_dtype != d.qkv_dtype)
+    return fail(AIDN_EINVAL, "create: out_dtype must be fp32 or equal to qkv_dtype");
+  if (d.head_dim <= 0 || d.head_dim > 256) return fail(AIDN_EINVAL, "create: head_dim %d outside [1,256]", d.head_dim);
+  if (d.num_q_heads <= 0 || d.num_kv_heads <= 0 || d.num_q_heads % d.num_kv_heads != 0)
+    return fail(AIDN_EINVAL, "create: numHeads (%d) must be a positive multiple of numKVHeads (%d)", d.num_q_heads,
+                d.num_kv_heads);
+  if (d.mask_kind < AIDN_MASK_NONE || d.mask_kind > AIDN_MASK_ADD_F32) return fail(AIDN_EINVAL, "create: unknown mask_kind");
+  if (d.path < AIDN_PATH_AUTO || d.path > AIDN_PATH_PREFILL_SM100) return fail(AIDN_EINVAL, "create: unknown path");
+  if (!(d.softcap >= 0.f)) return fail(AIDN_EINVAL, "create: softcap must be >= 0");
+  const int group = d.num_q_heads / d.num_kv_heads;
+  const int head_count = d.head_count > 0 ? d.head_count : d.num_q_heads - d.head_begin;
+  if (d.head_begin < 0 || head_count <= 0 || d.head_begin + head_count > d.num_q_heads)
+    return fail(AIDN_EINVAL, "create: head shard [%d,%d) outside [0,%d)", d.head_begin, d.head_begin + head_count,
+                d.num_q_heads);
+  if (d.head_begin % group != 0 || head_count % group != 0)
+    return fail(AIDN_EINVAL, "create: a head shard must cover whole KV groups (group size %d)", group);
+  if (d.decode_chunk < 0 || (d.decode_chunk > 0 && d.decode_chunk % 8 != 0))
+    return fail(AIDN_EINVAL, "create: decode_chunk must be 0 or a positive multiple of 8");
+
+  int cur = -1;
+  cudaError_t e = cudaGetDevice(&cur);
+  if (e != cudaSuccess) return fail_cuda(e, "create: cudaGetDevice");
+  if (cur != d.device) return fail(AIDN_EINVAL, "create: desc.device (%d) is not the current device (%d)", d.device, cur);
+  if (!aidn_sdpa_device_supported(d.device))
+    return fail(AIDN_EUNSUPPORTED, "create: device %d is not compute capability 10.x (this library carries sm_100a code only)",
+                d.device);
+
+  aidn_sdpa* h = new (std::nothrow) aidn_sdpa();
+  if (!h) return fail(AIDN_ECUDA, "create: out of host memory");
+  h->d = d;
+  h->group = group;
+  h->head_count = head_count;
+  h->status_dev = nullptr;
+  h->scratch = nullptr;
+  h->scratch_bytes = 0;
+  h->last_path = AIDN_PATH_AUTO;
+  h->last_launches = 0;
+  h->debug = nullptr;
+  e = cudaMalloc(&h->status_dev, sizeof(int32_t));
+  if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, sizeof(int32_t));
+  if (e != cudaSuccess) {
+    if (h->status_dev) cudaFree(h->status_dev);
+    delete h;
+    return fail_cuda(e, "create: status word");
+  }
+  if (d.max_batch > 0 && d.max_seq_kv > 0) {
+    const int64_t bytes = decode_ws_bytes(h, d.max_batch, d.max_seq_kv, nullptr, nullptr);
+    if (bytes > 0) {
+      e = cudaMalloc(&h->scratch, (size_t)bytes);
+      if (e != cudaSuccess) {
+        cudaFree(h->status_dev);
+        delete h;
+        return fail_cuda(e, "create: decode scratch");
+      }
+      h->scratch_bytes = bytes;
+    }
+  }
+  *out = h;
+  return AIDN_OK;
+}
+
+int aidn_sdpa_destroy(aidn_sdpa_t h) {
+  if (!h) return AIDN_OK;
+  if (h->scratch) cudaFree(h->scratch);
+  if (h->status_dev) cudaFree(h->status_dev);
+  delete h;
+  return AIDN_OK;
+}
+
+int64_t aidn_sdpa_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq_q, int64_t seq_kv) {
+  if (!h || batch <= 0 || seq_q <= 0 || seq_kv <= 0) {
+    fail(AIDN_EINVAL, "workspace_bytes: bad argument");
+    return -1;
+  }
+  if (seq_q != 1 || h->d.path == AIDN_PATH_GENERIC || h->d.path == AIDN_PATH_PREFILL_SM100) return 0;
+  if (!aidn::decode_supported(h->d.qkv_dtype, h->d.head_dim)) return 0;
+  return decode_ws_bytes(h, batch, seq_kv, nullptr, nullptr);
+}
+
+int aidn_sdpa_last_path(aidn_sdpa_t h) { return h ? h->last_path : -1; }
+int aidn_sdpa_last_launch_count(aidn_sdpa_t h) { return h ? h->last_launches : -1; }
+
+// Diagnostic tap of the tcgen05 kernel (not part of the public header): CTA 0 writes its first score tile,
+// its un-normalised accumulator and the running (sum, max) into `buf`.
+AIDN_API int aidn_sdpa_debug_set(aidn_sdpa_t h, float* buf) {
+  if (!h) return AIDN_EINVAL;
+  h->debug = buf;
+  return AIDN_OK;
+}
+
+int aidn_sdpa_poll(aidn_sdpa_t h, void* cu_stream) {
+  g_err[0] = 0;
+  if (!h) return fail(AIDN_EINVAL, "poll: null handle");
+  cudaError_t e = cudaStreamSynchronize((cudaStream_t)cu_stream);
+  if (e != cudaSuccess) return fail_cuda(e, "poll: stream");
+  int32_t st = 0;
+  e = cudaMemcpy(&st, h->status_dev, sizeof(st), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail_cuda(e, "poll: status read");
+  if (st != 0) {
+    cudaMemset(h->status_dev, 0, sizeof(int32_t));
+    return fail(AIDN_ETIMEOUT, "poll: a kernel gave up a bounded wait (status word 0x%x)", st);
+  }
+  return AIDN_OK;
+}
+
+int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* a, void* cu_stream) {
+  g_err[0] = 0;
+  if (!h || !a) return fail(AIDN_EINVAL, "launch: null argument");
+  const aidn_sdpa_desc& d = h->d;
+  cudaStream_t stream = (cudaStream_t)cu_stream;
+  if (!a->q || !a->k || !a->v || !a->out) return fail(AIDN_EINVAL, "launch: null tensor pointer");
+  if (a->batch <= 0 || a->seq_q <= 0 || a->seq_kv <= 0)
+    return fail(AIDN_EINVAL, "launch: attention dimensions must be positive");
+  if (a->batch > 65535) return fail(AIDN_EINVAL, "launch: batch above 65535");
+  if (d.emit_lse && !a->lse) return fail(AIDN_EINVAL, "launch: emit_lse set but lse pointer is null");
+  if (d.mask_kind != AIDN_MASK_NONE && !a->mask) return fail(AIDN_EINVAL, "launch: mask_kind set but mask pointer is null");
+  if (a->scale < 0.f || std::isnan(a->scale)) return fail(AIDN_EINVAL, "launch: scale must be >= 0");
+
+  aidn::SdpaParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.q = a->q;
+  p.k = a->k;
+  p.v = a->v;
+  p.out = a->out;
+  p.lse = d.emit_lse ? a->lse : nullptr;
+  p.mask = d.mask_kind != AIDN_MASK_NONE ? a->mask : nullptr;
+  p.mask_kind = d.mask_kind;
+  p.kv_len = a->kv_len;
+  for (int i = 0; i < 4; ++i) p.mask_stride[i] = a->mask_stride[i];
+  p.seq_q = a->seq_q;
+  p.seq_kv = a->seq_kv;
+  p.batch = (int)a->batch;
+  p.num_q_heads = d.num_q_heads;
+  p.num_kv_heads = d.num_kv_heads;
+  p.group = h->group;
+  p.head_begin = d.head_begin;
+  p.head_count = h->head_count;
+  p.head_dim = d.head_dim;
+  p.causal = d.causal ? 1 : 0;
+  p.causal_offset = d.causal_bottom_right ? (a->seq_kv - a->seq_q) : d.causal_offset;
+  p.out_f32 = d.out_dtype == AIDN_F32 ? 1 : 0;
+  p.scale = a->scale > 0.f ? a->scale : 1.0f / std::sqrt((float)d.head_dim);
+  p.softcap = d.softcap;
+  p.status = h->status_dev;
+  const int64_t D = d.head_dim;
+  if (all_zero(a->q_stride)) dense_strides(p.qs, d.num_q_heads, a->seq_q, D);
+  else std::memcpy(p.qs, a->q_stride, sizeof(p.qs));
+  if (all_zero(a->k_stride)) dense_strides(p.ks, d.num_kv_heads, a->seq_kv, D);
+  else std::memcpy(p.ks, a->k_stride, sizeof(p.ks));
+  if (all_zero(a->v_stride)) dense_strides(p.vs, d.num_kv_heads, a->seq_kv, D);
+  else std::memcpy(p.vs, a->v_stride, sizeof(p.vs));
+  if (all_zero(a->o_stride)) dense_strides(p.os, d.num_q_heads, a->seq_q, D);
+  else std::memcpy(p.os, a->o_stride, sizeof(p.os));
+  for (int i = 0; i < 3; ++i)
+    if (p.qs[i] < 0 || p.ks[i] < 0 || p.vs[i] < 0 || p.os[i] < 0) return fail(AIDN_EINVAL, "launch: negative stride");
+  if (p.head_count > 65535) return fail(AIDN_EINVAL, "launch: more than 65535 heads in one shard");
+
+  const size_t esz = elem_size(d.qkv_dtype);
+  const bool vec_ok = aligned16(p.q, p.qs, esz) && aligned16(p.k, p.ks, esz) && aligned16(p.v, p.vs, esz);
+  const bool decode_ok = a->seq_q == 1 && aidn::decode_supported(d.qkv_dtype, d.head_dim) && vec_ok;
+  const char* why = "";
+  const bool prefill_ok = aidn::prefill_sm100_supported(p, d.qkv_dtype, &why);
+
+  int path = d.path;
+  if (path == AIDN_PATH_AUTO) path = decode_ok ? AIDN_PATH_DECODE : (prefill_ok ? AIDN_PATH_PREFILL_SM100 : AIDN_PATH_GENERIC);
+  if (path == AIDN_PATH_DECODE && !decode_ok)
+    return fail(AIDN_EUNSUPPORTED,
+                "launch: decode kernel needs seq_q == 1, head_dim 64/128 (256 for 16-bit) and 16-byte aligned Q/K/V rows");
+  if (path == AIDN_PATH_PREFILL_SM100 && !prefill_ok) return fail(AIDN_EUNSUPPORTED, "launch: %s", why);
+
+  cudaError_t e = cudaSuccess;
+  int launches = 0;
+  if (path == AIDN_PATH_DECODE) {
+    int chunk = 0, nchunks = 0;
+    const int64_t need = decode_ws_bytes(h, a->batch, a->seq_kv, &chunk, &nchunks);
+    float* ws = nullptr;
+    if (need > 0) {
+      if (a->workspace) {
+        if (a->workspace_bytes < need)
+          return fail(AIDN_EWORKSPACE, "launch: workspace of %lld bytes, need %lld", (long long)a->workspace_bytes,
+                      (long long)need);
+        if ((uintptr_t)a->workspace % 16 != 0) return fail(AIDN_EINVAL, "launch: workspace must be 16-byte aligned");
+        ws = static_cast<float*>(a->workspace);
+      } else if (h->scratch && h->scratch_bytes >= need) {
+        ws = static_cast<float*>(h->scratch);
+      } else {
+        return fail(AIDN_EWORKSPACE, "launch: decode needs %lld bytes of workspace and the handle owns %lld",
+                    (long long)need, (long long)h->scratch_bytes);
+      }
+    }
+    e = aidn::launch_decode(p, d.qkv_dtype, chunk, nchunks, ws, stream, &launches);
+  } else if (path == AIDN_PATH_PREFILL_SM100) {
+    e = aidn::launch_prefill_sm100(p, d.qkv_dtype, stream, h->debug, &why);
+    launches = 1;
+    if (e != cudaSuccess && why[0]) return fail(AIDN_ECUDA, "launch: %s (%s)", why, cudaGetErrorName(e));
+  } else {
+    e = aidn::launch_generic(p, d.qkv_dtype, stream);
+    launches = 1;
+  }
+  if (e != cudaSuccess) return fail_cuda(e, "launch");
+  h->last_path = path;
+  h->last_launches = launches;
+
+  if (a->gather_output) {
+    if (!d.nccl_comm) return fail(AIDN_ENCCL, "launch: gather_output needs desc.nccl_comm");
+    std::call_once(g_nccl_once, load_nccl);
+    if (!g_nccl.ok) return fail(AIDN_ENCCL, "launch: libnccl.so.2 could not be loaded");
+    int nranks = 0, rank = -1;
+    if (g_nccl.CommCount(d.nccl_comm, &nranks) != 0 || g_nccl.CommUserRank(d.nccl_comm, &rank) != 0)
+      return fail(AIDN_ENCCL, "launch: cannot query the communicator");
+    if (h->head_count * nranks != d.num_q_heads || d.head_begin != rank * h->head_count)
+      return fail(AIDN_EINVAL, "launch: gather needs %d equal consecutive head shards, rank r owning heads [r*n,(r+1)*n)", nranks);
+    if (p.os[2] != D || p.os[1] != a->seq_q * D)
+      return fail(AIDN_EINVAL, "launch: gather needs a dense [B,H,S,D] output");
+    const size_t osz = p.out_f32 ? 4 : 2;
+    const int dt = p.out_f32 ? kNcclFloat32 : (d.qkv_dtype == AIDN_F16 ? kNcclFloat16 : kNcclBfloat16);
+    const size_t count = (size_t)h->head_count * (size_t)a->seq_q * (size_t)D;
+    int rc = g_nccl.GroupStart();
+    for (int64_t b = 0; b < a->batch && rc == 0; ++b) {
+      char* recv = static_cast<char*>(a->out) + (size_t)b * p.os[0] * osz;
+      rc = g_nccl.AllGather(recv + (size_t)rank * count * osz, recv, count, dt, d.nccl_comm, stream);
+    }
+    const int rc2 = g_nccl.GroupEnd();
+    if (rc == 0) rc = rc2;
+    if (rc != 0)
+      return fail(AIDN_ENCCL, "launch: ncclAllGather failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?");
+    h->last_launches += 1;
+  }
+  return AIDN_OK;
+}
+
+static int cast_common(int kind, const void* src, void* dst, int64_t n, void* cu_stream) {
+  g_err[0] = 0;
+  if (n < 0 || (n > 0 && (!src || !dst))) return fail(AIDN_EINVAL, "cast: bad argument");
+  cudaError_t e = aidn::launch_cast(kind, src, dst, n, (cudaStream_t)cu_stream);
+  if (e != cudaSuccess) return fail_cuda(e, "cast");
+  return AIDN_OK;
+}
+
+int aidn_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* s) { return cast_common(0, src, dst, n, s); }
+int aidn_cast_f32_to_f16(const float* src, void* dst, int64_t n, void* s) { return cast_common(1, src, dst, n, s); }
+int aidn_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* s) { return cast_common(2, src, dst, n, s); }
+int aidn_cast_f16_to_f32(const void* src, float* dst, int64_t n, void* s) { return cast_common(3, src, dst, n, s); }
+
+}  // extern "C"

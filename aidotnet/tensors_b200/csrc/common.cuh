@@ -1,0 +1,127 @@
+// Shared definitions of the attention kernels: the flattened launch parameters, dtype helpers and the
+// mask evaluation that every kernel uses so that mask semantics are defined once.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../../include/aidn_sdpa.h"
+
+namespace aidn {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Device status word values (bit flags) written by kernels that give up a bounded wait.
+constexpr int kStatusTimeout = 1;
+
+struct SdpaParams {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse;
+  const void* mask;
+  const int32_t* kv_len;
+  int64_t mask_stride[4];
+  int64_t qs[3], ks[3], vs[3], os[3];  // element strides for (B, H, S)
+  int64_t seq_q, seq_kv;
+  int64_t causal_offset;
+  int32_t batch;
+  int32_t num_q_heads, num_kv_heads, group;  // group = Hq / Hkv
+  int32_t head_begin, head_count;            // q-head shard computed by this launch
+  int32_t head_dim;
+  int32_t mask_kind;
+  int32_t causal;
+  int32_t out_f32;  // 1: output is fp32, 0: output has the input dtype
+  float scale;
+  float softcap;
+  int32_t* status;  // device word, or null
+};
+
+template <typename T>
+__device__ __forceinline__ float to_float(T x);
+template <>
+__device__ __forceinline__ float to_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
+template <>
+__device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// Stores one output element either as fp32 or in the input dtype.
+template <typename T>
+__device__ __forceinline__ void store_out(void* base, int64_t idx, float x, int out_f32) {
+  if (out_f32) static_cast<float*>(base)[idx] = x;
+  else static_cast<T*>(base)[idx] = from_float<T>(x);
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// exp used by the softmax: exact expf for fp32 inputs (1e-5 relative contract), ex2.approx otherwise.
+template <typename T>
+__device__ __forceinline__ float softmax_exp(float x) {
+  if constexpr (sizeof(T) == 4) return expf(x);
+  else return ex2_approx(x * kLog2e);
+}
+
+// Applies softcap, additive bias and every mask to a scaled logit.
+// Order: scale (done by the caller) -> softcap -> bias -> keep masks / causal / padding,
+// as CpuEngine.cs:27807-27816 (SDPA) and :29218-29239 (FlashAttention) of the reference.
+// Returns -inf for a masked position.
+__device__ __forceinline__ float finish_logit(const SdpaParams& p, float s, int b, int h, int64_t qi, int64_t kj,
+                                              int64_t kv_limit) {
+  if (p.softcap > 0.f) s = p.softcap * tanhf(s / p.softcap);
+  if (kj >= kv_limit) return -INFINITY;
+  if (p.causal && kj > qi + p.causal_offset) return -INFINITY;
+  if (p.mask_kind != AIDN_MASK_NONE) {
+    const int64_t idx = b * p.mask_stride[0] + h * p.mask_stride[1] + qi * p.mask_stride[2] + kj * p.mask_stride[3];
+    if (p.mask_kind == AIDN_MASK_KEEP_U8) {
+      if (static_cast<const uint8_t*>(p.mask)[idx] == 0) return -INFINITY;
+    } else if (p.mask_kind == AIDN_MASK_KEEP_F32) {
+      if (static_cast<const float*>(p.mask)[idx] == 0.0f) return -INFINITY;
+    } else {
+      s += static_cast<const float*>(p.mask)[idx];
+    }
+  }
+  return s;
+}
+
+// Number of keys a batch entry can see before causal masking: min(seq_kv, kv_len[b]).
+__device__ __forceinline__ int64_t kv_limit_of(const SdpaParams& p, int b) {
+  int64_t lim = p.seq_kv;
+  if (p.kv_len) {
+    int64_t l = p.kv_len[b];
+    if (l < 0) l = 0;
+    if (l < lim) lim = l;
+  }
+  return lim;
+}
+
+// Host-side launchers (one per kernel family); each returns the CUDA error of its launch.
+cudaError_t launch_generic(const SdpaParams& p, int dtype, cudaStream_t stream);
+cudaError_t launch_decode(const SdpaParams& p, int dtype, int chunk, int nchunks, float* workspace, cudaStream_t stream,
+                          int* launches);
+bool decode_supported(int dtype, int head_dim);
+cudaError_t launch_cast(int kind, const void* src, void* dst, int64_t n, cudaStream_t stream);
+
+struct PrefillPlan;  // opaque to callers of the sm100 prefill launcher
+bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why);
+cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t stream, float* debug, const char** why);
+cudaError_t prefill_sm100_prepare();  // one-time per-process function attribute setup
+
+}  // namespace aidn

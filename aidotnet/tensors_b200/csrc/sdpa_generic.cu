@@ -1,0 +1,189 @@
+// Generic attention forward: fp32 FFMA arithmetic, online softmax, any head_dim <= 256, every mask kind.
+//
+// Serves (1) the fp32-input contract (<= 1e-5 relative against the fp32 CPU path), where tensor-core
+// rounding of the inputs is not admissible, and (2) shapes and mask kinds the tcgen05 prefill kernel does
+// not take.  Replaces the one-thread-per-row kernel of the reference
+// (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/CudaAttentionKernels.cs:28-112), which recomputes
+// q.k up to D+2 times per key; here K/V tiles are staged once in shared memory per 16 query rows.
+//
+// CTA = 4 warps, 16 query rows (4 per warp), key tiles of 32.  In the score phase lane j owns key j of the
+// tile; in the P.V phase lane l owns output dims l, l+32, ...
+#include "common.cuh"
+
+namespace aidn {
+namespace {
+
+constexpr int kRowsPerWarp = 4;
+constexpr int kWarps = 4;
+constexpr int kBM = kRowsPerWarp * kWarps;  // 16
+constexpr int kBN = 32;
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaParams p) {
+  constexpr int PITCH = DMAX + 4;  // floats; keeps float4 rows 16-byte aligned and bank-conflict free
+  constexpr int ND = DMAX / 32;
+  extern __shared__ __align__(16) float smem[];
+  float* Qs = smem;                       // [kBM][PITCH]
+  float* Ks = Qs + kBM * PITCH;           // [kBN][PITCH]
+  float* Vs = Ks + kBN * PITCH;           // [kBN][PITCH]
+  float* Ps = Vs + kBN * PITCH;           // [kWarps][kRowsPerWarp][kBN]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z;
+  const int h = p.head_begin + blockIdx.y;
+  const int kvh = h / p.group;
+  const int64_t row0 = (int64_t)blockIdx.x * kBM;
+  const int D = p.head_dim;
+
+  const T* qb = static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1];
+  const T* kb = static_cast<const T*>(p.k) + b * p.ks[0] + kvh * p.ks[1];
+  const T* vb = static_cast<const T*>(p.v) + b * p.vs[0] + kvh * p.vs[1];
+
+  for (int idx = tid; idx < kBM * DMAX; idx += kWarps * 32) {
+    const int r = idx / DMAX, d = idx - r * DMAX;
+    const int64_t row = row0 + r;
+    Qs[r * PITCH + d] = (row < p.seq_q && d < D) ? to_float<T>(qb[row * p.qs[2] + d]) : 0.f;
+  }
+
+  const int64_t kv_limit = kv_limit_of(p, b);
+  int64_t kend = kv_limit;
+  if (p.causal) {
+    int64_t last_row = row0 + kBM - 1;
+    if (last_row > p.seq_q - 1) last_row = p.seq_q - 1;
+    const int64_t c = last_row + p.causal_offset + 1;
+    if (c < kend) kend = c;
+  }
+
+  float m[kRowsPerWarp], l[kRowsPerWarp], acc[kRowsPerWarp][ND];
+#pragma unroll
+  for (int r = 0; r < kRowsPerWarp; ++r) {
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acc[r][i] = 0.f;
+  }
+
+  for (int64_t j0 = 0; j0 < kend; j0 += kBN) {
+    __syncthreads();  // previous tile fully consumed (also orders the Q stores before first use)
+    for (int idx = tid; idx < kBN * DMAX; idx += kWarps * 32) {
+      const int j = idx / DMAX, d = idx - j * DMAX;
+      const int64_t key = j0 + j;
+      const bool ok = key < p.seq_kv && d < D;
+      Ks[j * PITCH + d] = ok ? to_float<T>(kb[key * p.ks[2] + d]) : 0.f;
+      Vs[j * PITCH + d] = ok ? to_float<T>(vb[key * p.vs[2] + d]) : 0.f;
+    }
+    __syncthreads();
+
+    float s[kRowsPerWarp] = {0.f, 0.f, 0.f, 0.f};
+    const float4* krow = reinterpret_cast<const float4*>(Ks + lane * PITCH);
+#pragma unroll 4
+    for (int d4 = 0; d4 < DMAX / 4; ++d4) {
+      const float4 kv = krow[d4];
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) {
+        const float4 qv = reinterpret_cast<const float4*>(Qs + (warp * kRowsPerWarp + r) * PITCH)[d4];
+        s[r] = fmaf(qv.x, kv.x, s[r]);
+        s[r] = fmaf(qv.y, kv.y, s[r]);
+        s[r] = fmaf(qv.z, kv.z, s[r]);
+        s[r] = fmaf(qv.w, kv.w, s[r]);
+      }
+    }
+
+    const int64_t key = j0 + lane;
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) {
+      const int64_t row = row0 + warp * kRowsPerWarp + r;
+      float val = -INFINITY;
+      if (row < p.seq_q && key < p.seq_kv) val = finish_logit(p, s[r] * p.scale, b, h, row, key, kv_limit);
+      float mt = val;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));
+      const float m_new = fmaxf(m[r], mt);
+      float pj = 0.f, corr = 1.f;
+      if (m_new != -INFINITY) {
+        corr = (m[r] == -INFINITY) ? 0.f : softmax_exp<T>(m[r] - m_new);
+        pj = (val == -INFINITY) ? 0.f : softmax_exp<T>(val - m_new);
+      }
+      float ps = pj;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, o);
+      l[r] = l[r] * corr + ps;
+      m[r] = m_new;
+#pragma unroll
+      for (int i = 0; i < ND; ++i) acc[r][i] *= corr;
+      Ps[(warp * kRowsPerWarp + r) * kBN + lane] = pj;
+    }
+    __syncwarp();
+
+#pragma unroll 2
+    for (int j4 = 0; j4 < kBN / 4; ++j4) {
+      float4 pv[kRowsPerWarp];
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r)
+        pv[r] = reinterpret_cast<const float4*>(Ps + (warp * kRowsPerWarp + r) * kBN)[j4];
+#pragma unroll
+      for (int i = 0; i < ND; ++i) {
+        const float v0 = Vs[(j4 * 4 + 0) * PITCH + lane + 32 * i];
+        const float v1 = Vs[(j4 * 4 + 1) * PITCH + lane + 32 * i];
+        const float v2 = Vs[(j4 * 4 + 2) * PITCH + lane + 32 * i];
+        const float v3 = Vs[(j4 * 4 + 3) * PITCH + lane + 32 * i];
+#pragma unroll
+        for (int r = 0; r < kRowsPerWarp; ++r) {
+          acc[r][i] = fmaf(pv[r].x, v0, acc[r][i]);
+          acc[r][i] = fmaf(pv[r].y, v1, acc[r][i]);
+          acc[r][i] = fmaf(pv[r].z, v2, acc[r][i]);
+          acc[r][i] = fmaf(pv[r].w, v3, acc[r][i]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+
+#pragma unroll
+  for (int r = 0; r < kRowsPerWarp; ++r) {
+    const int64_t row = row0 + warp * kRowsPerWarp + r;
+    if (row >= p.seq_q) continue;
+    const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+    const int64_t obase = b * p.os[0] + h * p.os[1] + row * p.os[2];
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) store_out<T>(p.out, obase + d, acc[r][i] * inv, p.out_f32);
+    }
+    if (p.lse && lane == 0)
+      p.lse[((int64_t)b * p.num_q_heads + h) * p.seq_q + row] = (l[r] > 0.f) ? m[r] + logf(l[r]) : -INFINITY;
+  }
+}
+
+template <typename T, int DMAX>
+cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream) {
+  constexpr int PITCH = DMAX + 4;
+  const size_t smem = sizeof(float) * ((kBM + 2 * kBN) * PITCH + kWarps * kRowsPerWarp * kBN);
+  auto kern = sdpa_generic_kernel<T, DMAX>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  dim3 grid((unsigned)((p.seq_q + kBM - 1) / kBM), (unsigned)p.head_count, (unsigned)p.batch);
+  kern<<<grid, kWarps * 32, smem, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_d(const SdpaParams& p, cudaStream_t stream) {
+  if (p.head_dim <= 64) return launch_t<T, 64>(p, stream);
+  if (p.head_dim <= 128) return launch_t<T, 128>(p, stream);
+  return launch_t<T, 256>(p, stream);
+}
+
+}  // namespace
+
+cudaError_t launch_generic(const SdpaParams& p, int dtype, cudaStream_t stream) {
+  switch (dtype) {
+    case AIDN_F32: return launch_d<float>(p, stream);
+    case AIDN_F16: return launch_d<__half>(p, stream);
+    default: return launch_d<__nv_bfloat16>(p, stream);
+  }
+}
+
+}  // namespace aidn

@@ -1,0 +1,190 @@
+"""ctypes binding of the C ABI declared in ``include/aidn_sdpa.h``.
+
+This is the same surface a C# ``[DllImport]`` shim binds (see ``bindings/AidnSdpaNative.cs``); Python uses it
+for the tests, the smoke check and the benchmark.  There is no fallback: if the CUDA library is missing or a
+call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Optional, Sequence
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libaidotnet_sdpa_sm100.so")
+
+# aidn_status
+OK, EINVAL, EUNSUPPORTED, ECUDA, EWORKSPACE, ETIMEOUT, ENCCL = range(7)
+# aidn_dtype
+F32, F16, BF16 = 0, 1, 2
+# aidn_mask_kind
+MASK_NONE, MASK_KEEP_U8, MASK_KEEP_F32, MASK_ADD_F32 = 0, 1, 2, 3
+# aidn_path
+PATH_AUTO, PATH_GENERIC, PATH_DECODE, PATH_PREFILL_SM100 = 0, 1, 2, 3
+
+EXPORTS = (
+    "aidn_sdpa_create", "aidn_sdpa_workspace_bytes", "aidn_sdpa_launch", "aidn_sdpa_poll", "aidn_sdpa_last_path",
+    "aidn_sdpa_last_launch_count", "aidn_sdpa_destroy", "aidn_sdpa_last_error", "aidn_sdpa_device_supported",
+    "aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32",
+)
+
+
+class SdpaDesc(ctypes.Structure):
+    _fields_ = [
+        ("device", ctypes.c_int32), ("qkv_dtype", ctypes.c_int32), ("out_dtype", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32), ("num_q_heads", ctypes.c_int32), ("num_kv_heads", ctypes.c_int32),
+        ("causal", ctypes.c_int32), ("causal_bottom_right", ctypes.c_int32), ("causal_offset", ctypes.c_int64),
+        ("mask_kind", ctypes.c_int32), ("emit_lse", ctypes.c_int32), ("softcap", ctypes.c_float),
+        ("path", ctypes.c_int32), ("head_begin", ctypes.c_int32), ("head_count", ctypes.c_int32),
+        ("decode_chunk", ctypes.c_int32), ("max_batch", ctypes.c_int32), ("max_seq_q", ctypes.c_int64),
+        ("max_seq_kv", ctypes.c_int64), ("nccl_comm", ctypes.c_void_p),
+    ]
+
+
+class SdpaArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", ctypes.c_void_p), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("lse", ctypes.c_void_p), ("mask", ctypes.c_void_p), ("mask_stride", ctypes.c_int64 * 4),
+        ("kv_len", ctypes.c_void_p), ("batch", ctypes.c_int64), ("seq_q", ctypes.c_int64), ("seq_kv", ctypes.c_int64),
+        ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3), ("v_stride", ctypes.c_int64 * 3),
+        ("o_stride", ctypes.c_int64 * 3), ("scale", ctypes.c_float), ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_int64), ("gather_output", ctypes.c_int32),
+    ]
+
+
+class AidnError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"aidn_sdpa status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads the CUDA library.  Raises if it has not been built: there is no CPU path behind this API."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(
+            f"{LIB_PATH} is missing: build it with `python -m aidotnet.tensors_b200.build` (needs nvcc)")
+    lib = ctypes.CDLL(LIB_PATH)
+    lib.aidn_sdpa_create.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(ctypes.c_void_p)]
+    lib.aidn_sdpa_create.restype = ctypes.c_int
+    lib.aidn_sdpa_workspace_bytes.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64]
+    lib.aidn_sdpa_workspace_bytes.restype = ctypes.c_int64
+    lib.aidn_sdpa_launch.argtypes = [ctypes.c_void_p, ctypes.POINTER(SdpaArgs), ctypes.c_void_p]
+    lib.aidn_sdpa_launch.restype = ctypes.c_int
+    lib.aidn_sdpa_poll.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    lib.aidn_sdpa_poll.restype = ctypes.c_int
+    lib.aidn_sdpa_last_path.argtypes = [ctypes.c_void_p]
+    lib.aidn_sdpa_last_path.restype = ctypes.c_int
+    lib.aidn_sdpa_last_launch_count.argtypes = [ctypes.c_void_p]
+    lib.aidn_sdpa_last_launch_count.restype = ctypes.c_int
+    lib.aidn_sdpa_destroy.argtypes = [ctypes.c_void_p]
+    lib.aidn_sdpa_destroy.restype = ctypes.c_int
+    lib.aidn_sdpa_last_error.argtypes = []
+    lib.aidn_sdpa_last_error.restype = ctypes.c_char_p
+    lib.aidn_sdpa_device_supported.argtypes = [ctypes.c_int32]
+    lib.aidn_sdpa_device_supported.restype = ctypes.c_int
+    for name in ("aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32"):
+        fn = getattr(lib, name)
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+        fn.restype = ctypes.c_int
+    lib.aidn_sdpa_debug_set.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    lib.aidn_sdpa_debug_set.restype = ctypes.c_int
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    return load().aidn_sdpa_last_error().decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise AidnError(status, last_error())
+
+
+def _arr3(values: Optional[Sequence[int]]):
+    return (ctypes.c_int64 * 3)(*(values if values is not None else (0, 0, 0)))
+
+
+class Handle:
+    """Owns one ``aidn_sdpa_t``.  Pointers are raw device addresses (``int``); the stream is a ``cudaStream_t``."""
+
+    def __init__(self, *, device: int, qkv_dtype: int, out_dtype: int = F32, head_dim: int, num_q_heads: int,
+                 num_kv_heads: Optional[int] = None, causal: bool = False, causal_bottom_right: bool = True,
+                 causal_offset: int = 0, mask_kind: int = MASK_NONE, emit_lse: bool = False, softcap: float = 0.0,
+                 path: int = PATH_AUTO, head_begin: int = 0, head_count: int = 0, decode_chunk: int = 0,
+                 max_batch: int = 0, max_seq_q: int = 0, max_seq_kv: int = 0, nccl_comm: Optional[int] = None):
+        self._lib = load()
+        d = SdpaDesc()
+        d.device, d.qkv_dtype, d.out_dtype, d.head_dim = device, qkv_dtype, out_dtype, head_dim
+        d.num_q_heads = num_q_heads
+        d.num_kv_heads = num_kv_heads if num_kv_heads else num_q_heads
+        d.causal, d.causal_bottom_right, d.causal_offset = int(causal), int(causal_bottom_right), causal_offset
+        d.mask_kind, d.emit_lse, d.softcap, d.path = mask_kind, int(emit_lse), softcap, path
+        d.head_begin, d.head_count, d.decode_chunk = head_begin, head_count, decode_chunk
+        d.max_batch, d.max_seq_q, d.max_seq_kv = max_batch, max_seq_q, max_seq_kv
+        d.nccl_comm = nccl_comm
+        self.desc = d
+        h = ctypes.c_void_p()
+        check(self._lib.aidn_sdpa_create(ctypes.byref(d), ctypes.byref(h)))
+        self._h = h
+
+    def workspace_bytes(self, batch: int, seq_q: int, seq_kv: int) -> int:
+        n = self._lib.aidn_sdpa_workspace_bytes(self._h, batch, seq_q, seq_kv)
+        if n < 0:
+            raise AidnError(EINVAL, last_error())
+        return int(n)
+
+    def launch(self, *, q: int, k: int, v: int, out: int, batch: int, seq_q: int, seq_kv: int, stream: int,
+               lse: Optional[int] = None, mask: Optional[int] = None, mask_stride: Sequence[int] = (0, 0, 0, 0),
+               kv_len: Optional[int] = None, q_stride=None, k_stride=None, v_stride=None, o_stride=None,
+               scale: float = 0.0, workspace: Optional[int] = None, workspace_bytes: int = 0,
+               gather_output: bool = False) -> None:
+        a = SdpaArgs()
+        a.q, a.k, a.v, a.out, a.lse, a.mask, a.kv_len = q, k, v, out, lse, mask, kv_len
+        a.mask_stride = (ctypes.c_int64 * 4)(*mask_stride)
+        a.batch, a.seq_q, a.seq_kv = batch, seq_q, seq_kv
+        a.q_stride, a.k_stride, a.v_stride, a.o_stride = _arr3(q_stride), _arr3(k_stride), _arr3(v_stride), _arr3(o_stride)
+        a.scale, a.workspace, a.workspace_bytes, a.gather_output = scale, workspace, workspace_bytes, int(gather_output)
+        check(self._lib.aidn_sdpa_launch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
+
+    def poll(self, stream: int) -> None:
+        check(self._lib.aidn_sdpa_poll(self._h, ctypes.c_void_p(stream)))
+
+    @property
+    def last_path(self) -> int:
+        return int(self._lib.aidn_sdpa_last_path(self._h))
+
+    @property
+    def last_launch_count(self) -> int:
+        return int(self._lib.aidn_sdpa_last_launch_count(self._h))
+
+    def debug_set(self, ptr: Optional[int]) -> None:
+        self._lib.aidn_sdpa_debug_set(self._h, ctypes.c_void_p(ptr))
+
+    def close(self) -> None:
+        if getattr(self, "_h", None):
+            self._lib.aidn_sdpa_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+
+def cast(kind: str, src: int, dst: int, n: int, stream: int) -> None:
+    check(getattr(load(), f"aidn_cast_{kind}")(ctypes.c_void_p(src), ctypes.c_void_p(dst), n, ctypes.c_void_p(stream)))

@@ -1,0 +1,376 @@
+#!/usr/bin/env python
+"""Benchmark of the fused SDPA forward path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5shard] [--impl reference]
+
+One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
+default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
+configuration (B64 H32 D128, kv_len in [512,4096]) is measured in the same run and reported under "decode".
+With N > 1 every rank runs the same per-GPU workload on its own head/batch shard of an N-times larger job
+(no collective on the data path; weak scaling).  Prints ONE JSON line on rank 0.
+
+FLOPs are algorithmic: 4 * D * (visible query-key pairs), i.e. causal work is counted once, not doubled.
+Bytes for decode are the valid K and V rows plus Q and O, each once.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, Hq, Hkv, Sq, Sk, D, causal, dtype, kind)
+    "c2": dict(B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True, kind="prefill",
+               name="llama_prefill_B4_H32_S2048_D128_causal_bf16"),
+    "c3": dict(B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill",
+               name="gqa_prefill_B2_Hq32_Hkv8_S8192_D128_causal_bf16"),
+    "c5shard": dict(B=1, Hq=8, Hkv=1, Sq=32768, Sk=32768, D=128, causal=True, kind="prefill",
+                    name="long_context_shard_B1_Hq8_Hkv1_S32768_D128_causal_bf16"),
+    "c4": dict(B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
+               name="batched_decode_B64_H32_D128_kvlen512-4096_bf16"),
+}
+METRIC = "attention TFLOP/s/GPU & % bf16 peak (prefill); decode HBM GB/s; 1/2/4/8 GPUs"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm=float(p["hbm_gbs"]), bf16=float(p["bf16_tflops"]), bf16_sustained=float(p["bf16_tflops_sustained"]),
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+def visible_pairs(Sq, Sk, causal):
+    if not causal:
+        return Sq * Sk
+    off = Sk - Sq
+    return int(np.minimum(Sk, np.maximum(0, np.arange(Sq, dtype=np.int64) + off + 1)).sum())
+
+
+def algorithmic_flops(w, kv_len=None):
+    if w["kind"] == "decode":
+        return 4 * w["Hq"] * w["D"] * int(np.sum(kv_len))
+    return 4 * w["B"] * w["Hq"] * w["D"] * visible_pairs(w["Sq"], w["Sk"], w["causal"])
+
+
+def algorithmic_bytes(w, kv_len=None):
+    if w["kind"] == "decode":
+        kv = 2 * w["Hkv"] * w["D"] * 2 * int(np.sum(kv_len))
+        return kv + w["B"] * w["Hq"] * w["D"] * (2 + 4)
+    qo = w["B"] * w["Hq"] * w["Sq"] * w["D"] * (2 + 4)
+    return qo + 2 * w["B"] * w["Hkv"] * w["Sk"] * w["D"] * 2
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._window = [None, None]
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+                 0x80: "hw_power_brake_slowdown"}
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                self.samples.append((time.perf_counter(), mhz, r))
+                for bit, name in names.items():
+                    if r & bit and self._window[0] is not None and self._window[1] is None:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def mark_begin(self):
+        self._window[0] = time.perf_counter()
+
+    def mark_end(self):
+        self._window[1] = time.perf_counter()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=1.0)
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "note": "NVML unavailable"}
+        t0, t1 = self._window
+        inside = [m for (t, m, _) in self.samples if t0 is not None and t1 is not None and t0 <= t <= t1]
+        note = "sampled inside the timed region"
+        if not inside:
+            inside = [m for (_, m, _) in self.samples]
+            note = "timed region shorter than the sampling period; samples span warm-up + timed region"
+        return {"sm_mhz": float(np.median(inside)), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(inside), "note": note}
+
+
+def make_inputs(w, device, seed):
+    g = torch.Generator(device=device).manual_seed(seed)
+    mk = lambda *s: (torch.randn(s, generator=g, device=device) * 0.5).to(torch.bfloat16)
+    q = mk(w["B"], w["Hq"], w["Sq"], w["D"])
+    k = mk(w["B"], w["Hkv"], w["Sk"], w["D"])
+    v = mk(w["B"], w["Hkv"], w["Sk"], w["D"])
+    kv_len = None
+    if w["kind"] == "decode":
+        kv_len = np.random.Generator(np.random.Philox(seed)).integers(512, w["Sk"] + 1, w["B"]).astype(np.int32)
+    return q, k, v, kv_len
+
+
+class Runner:
+    """One workload bound to one handle of the C ABI; `step()` enqueues one forward pass."""
+
+    def __init__(self, w, device_index, seed):
+        from aidotnet.tensors_b200 import native as N
+        self.N = N
+        self.w = w
+        dev = torch.device("cuda", device_index)
+        self.q, self.k, self.v, self.kv_len_host = make_inputs(w, dev, seed)
+        self.kv_len = torch.from_numpy(self.kv_len_host).to(dev) if self.kv_len_host is not None else None
+        self.out = torch.empty((w["B"], w["Hq"], w["Sq"], w["D"]), dtype=torch.float32, device=dev)
+        self.h = N.Handle(device=device_index, qkv_dtype=N.BF16, out_dtype=N.F32, head_dim=w["D"], num_q_heads=w["Hq"],
+                          num_kv_heads=w["Hkv"], causal=w["causal"], causal_bottom_right=True,
+                          max_batch=w["B"], max_seq_q=w["Sq"], max_seq_kv=w["Sk"])
+        self.stream = torch.cuda.current_stream(dev).cuda_stream
+        self.launches = 0
+
+    def step(self, q=None, k=None, v=None):
+        q = self.q if q is None else q
+        k = self.k if k is None else k
+        v = self.v if v is None else v
+        self.h.launch(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=self.out.data_ptr(), batch=self.w["B"],
+                      seq_q=self.w["Sq"], seq_kv=self.w["Sk"], stream=self.stream,
+                      kv_len=self.kv_len.data_ptr() if self.kv_len is not None else None)
+        self.launches += self.h.last_launch_count
+
+    def time_steps(self, steps, warmup, sampler=None, dist=None):
+        for _ in range(warmup):
+            self.step()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        l0 = self.launches
+        if sampler:
+            sampler.mark_begin()
+        e0.record()
+        for _ in range(steps):
+            self.step()
+        e1.record()
+        torch.cuda.synchronize()
+        if sampler:
+            sampler.mark_end()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / 1e3, self.launches - l0
+
+    def time_e2e(self, steps, warmup):
+        """Same call with HOST buffers: pinned Q/K/V copied in and the output copied back inside the timed region."""
+        hq, hk, hv = (t.cpu().pin_memory() for t in (self.q, self.k, self.v))
+        dq, dk, dv = (torch.empty_like(t) for t in (self.q, self.k, self.v))
+        hout = torch.empty(self.out.shape, dtype=self.out.dtype).pin_memory()
+        def one():
+            dq.copy_(hq, non_blocking=True)
+            dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True)
+            self.step(dq, dk, dv)
+            hout.copy_(self.out, non_blocking=True)
+        for _ in range(max(1, warmup)):
+            one()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            one()
+        e1.record()
+        torch.cuda.synchronize()
+        h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv))
+        d2h = hout.numel() * hout.element_size()
+        return e0.elapsed_time(e1) / 1e3, h2d, d2h
+
+
+def cpu_reference_time(w, threads, passes=1, sample_batch=None):
+    """Times the CPU restatement of the reference path (faithful mode: full-width GEMMs, KV broadcast copy)."""
+    from oracle import sdpa_oracle as O
+    B = sample_batch or w["B"]
+    rng = np.random.Generator(np.random.Philox(7))
+    mk = lambda *s: (rng.standard_normal(s, dtype=np.float32) * np.float32(0.5))
+    q, k, v = mk(B, w["Hq"], w["Sq"], w["D"]), mk(B, w["Hkv"], w["Sk"], w["D"]), mk(B, w["Hkv"], w["Sk"], w["D"])
+    kv = None
+    if w["kind"] == "decode":
+        kv = np.random.Generator(np.random.Philox(7)).integers(512, w["Sk"] + 1, B).astype(np.int32)
+    t0 = time.perf_counter()
+    for _ in range(passes):
+        O.sdpa(q, k, v, causal=w["causal"], kv_len=kv, faithful=True, threads=threads)
+    dt = (time.perf_counter() - t0) / passes
+    ws = dict(w, B=B)
+    return dt, algorithmic_flops(ws, kv), algorithmic_bytes(ws, kv)
+
+
+def run_reference_arm(args, w):
+    """`--impl reference`: the reference's CPU attention path (C++ restatement; the .NET original cannot run here)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import sdpa_oracle as O
+    threads = O.max_threads()
+    sample_batch = 1
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, fl, by = cpu_reference_time(w, threads, 1, sample_batch)
+        if i >= args.warmup:
+            times.append(dt)
+    ms = float(np.mean(times)) * 1e3
+    value = (fl / 1e12) / (ms / 1e3) if w["kind"] == "prefill" else (by / 1e9) / (ms / 1e3)
+    unit = "TFLOP/s" if w["kind"] == "prefill" else "GB/s"
+    sample = f"batch entry 0 of the workload ({sample_batch} of {w['B']} batch entries) per step"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": {"workload": w["name"], "sample": sample},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference_arm(args, w)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist = dist_mod
+    pk = peaks()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+
+    runner = Runner(w, local, 0xA1D00000 + 2 + rank)
+    kvh = runner.kv_len_host
+    fl, by = algorithmic_flops(w, kvh), algorithmic_bytes(w, kvh)
+    secs, launches = runner.time_steps(args.steps, args.warmup, sampler, dist)
+    if dist is not None:
+        t = torch.tensor([secs], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        secs = float(t.item())
+    clocks = sampler.stop() if sampler else None
+    per_step = secs / args.steps
+    prefill = w["kind"] == "prefill"
+    per_gpu = (fl / 1e12 if prefill else by / 1e9) / per_step
+    value = per_gpu * world
+    peak = pk["bf16"] if prefill else pk["hbm"]
+
+    e2e_secs, h2d, d2h = runner.time_e2e(max(3, min(args.steps, 10)), 2)
+    e2e_steps = max(3, min(args.steps, 10))
+    if dist is not None:
+        t = torch.tensor([e2e_secs], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_secs = float(t.item())
+    e2e_value = (fl / 1e12 if prefill else by / 1e9) / (e2e_secs / e2e_steps) * world
+
+    decode_obj = None
+    if prefill and not args.no_decode:
+        wd = WORKLOADS["c4"]
+        rd = Runner(wd, local, 0xA1D00004 + rank)
+        dsecs, dl = rd.time_steps(max(10, args.steps // 2), 3, None, dist)
+        dsteps = max(10, args.steps // 2)
+        if dist is not None:
+            t = torch.tensor([dsecs], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dsecs = float(t.item())
+        dby = algorithmic_bytes(wd, rd.kv_len_host)
+        gbs = dby / 1e9 / (dsecs / dsteps)
+        decode_obj = {"workload": wd["name"], "value": gbs * world, "unit": "GB/s", "ms_per_step": dsecs / dsteps * 1e3,
+                      "tokens_per_s": wd["B"] * world / (dsecs / dsteps), "gpu_launches": dl,
+                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s",
+                                   "frac": gbs / pk["hbm"], "traffic": None, "peak_source": pk["source"]}}
+        del rd
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import sdpa_oracle as O
+        threads = O.max_threads()
+        dt, cfl, cby = cpu_reference_time(w, threads, 1, 1 if prefill else None)
+        cpu = {"value": (cfl / 1e12 if prefill else cby / 1e9) / dt, "unit": "TFLOP/s" if prefill else "GB/s",
+               "cores": threads, "kind": "port",
+               "sample": ("batch entry 0 of the workload (1 of %d batch entries), one pass" % w["B"]) if prefill
+               else "the full workload, one pass"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s" if prefill else "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "per_gpu": "one copy of the workload per GPU (batch x head shard of an N-fold job)",
+                       "l2": "inputs+outputs larger than the 126 MB L2; no flush",
+                       "flop_convention": "4*D*visible(q,k) pairs (causal counted once)"},
+            "per_gpu": per_gpu, "pct_of_measured_bf16_peak": (100.0 * per_gpu / pk["bf16"]) if prefill else None,
+            "tokens_per_s": w["B"] * w["Sq"] * world / per_step,
+            "roofline": {"bound": "tensor" if prefill else "hbm", "achieved": per_gpu, "peak": peak,
+                         "unit": "TFLOP/s" if prefill else "GB/s", "frac": per_gpu / peak, "traffic": None,
+                         "peak_source": pk["source"] + (" (burst)" if prefill else "")},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s" if prefill else "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_secs / e2e_steps * 1e3},
+            "gpu_launches": launches, "clocks": clocks, "decode": decode_obj,
+        }
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

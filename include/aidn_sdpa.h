@@ -1,0 +1,150 @@
+/*
+ * aidn_sdpa.h — C ABI of libaidotnet_sdpa_sm100: fused scaled-dot-product-attention forward for
+ * NVIDIA B200 (sm_100a).
+ *
+ * The library is a drop-in for the attention methods of the reference's CUDA backend.  File:line
+ * citations are relative to src/AiDotNet.Tensors/ of the reference project:
+ *
+ *   Engines/DirectGpu/IDirectGpuBackend.cs:1421-1424  ScaledDotProductAttention(query,key,value,output,
+ *        attentionWeights?,mask?,batch,numHeads,seqQ,seqK,headDim,scale,isCausal,softcap,numKVHeads)
+ *   Engines/DirectGpu/IDirectGpuBackend.cs:1448-1449  FlashAttention(...)
+ *   Engines/DirectGpu/IDirectGpuBackend.cs:1468-1471  FlashAttentionV2(...,softmaxStats,...,attentionBias?,biasBatchStride)
+ *   Engines/DirectGpu/IDirectGpuBackend.cs:1501-1503  GroupedQueryAttention(...)
+ *   Engines/DirectGpu/CUDA/CudaBackend.cs:2968-3021   FlashDecode(q,k,v,heads,kvHeads,headDim,seqLen,scale,splits)
+ *   Engines/DirectGpu/IDirectGpuBackend.cs:1890,1911  ConvertToFp16 / ConvertToFp32 (dtype staging)
+ *
+ * Conventions inherited from that caller (CudaBackend.cs:371-375, 546, 5253-5272, 5389-5403):
+ *   - every buffer is caller-owned device memory (IGpuBuffer.Handle, IDirectGpuBackend.cs:3776-3803);
+ *   - the caller's CUDA context is current on the calling thread and all work is enqueued on the
+ *     explicit stream argument; nothing here synchronises, creates a context or touches the default stream;
+ *   - a launch allocates nothing: scratch is either passed in (workspace) or owned by the handle;
+ *   - errors are status codes plus a thread-local message, never aborts.
+ *
+ * Tensor layout is [B, H, S, D] with a unit stride on D; the B, H and S strides are explicit so that
+ * permuted views ([B,S,H,D] storage, the single-sequence [S,Hkv,D] decode cache) need no copy.
+ */
+#ifndef AIDN_SDPA_H_
+#define AIDN_SDPA_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define AIDN_API __declspec(dllexport)
+#else
+#define AIDN_API __attribute__((visibility("default")))
+#endif
+
+typedef struct aidn_sdpa* aidn_sdpa_t;
+
+typedef enum {
+  AIDN_OK = 0,
+  AIDN_EINVAL = 1,       /* bad argument (shape, stride, null pointer, alignment)            */
+  AIDN_EUNSUPPORTED = 2, /* valid request that no kernel of this build serves               */
+  AIDN_ECUDA = 3,        /* a CUDA call failed; aidn_sdpa_last_error() carries its message   */
+  AIDN_EWORKSPACE = 4,   /* workspace missing or too small                                   */
+  AIDN_ETIMEOUT = 5,     /* a bounded device-side wait expired (reported by aidn_sdpa_poll)  */
+  AIDN_ENCCL = 6         /* NCCL missing or an NCCL call failed                              */
+} aidn_status;
+
+typedef enum { AIDN_F32 = 0, AIDN_F16 = 1, AIDN_BF16 = 2 } aidn_dtype;
+
+/* How args.mask is read.  Every kind broadcasts over axes whose mask_stride is 0
+ * (CpuEngine.MultiHeadAttention.cs:344 BroadcastMaskIndex). */
+typedef enum {
+  AIDN_MASK_NONE = 0,
+  AIDN_MASK_KEEP_U8 = 1,  /* Tensor<bool>: non-zero = attend (IEngine.cs:4133-4140)                       */
+  AIDN_MASK_KEEP_F32 = 2, /* the engine's float upload of a bool mask: 0.0f = masked
+                             (CUDA/Kernels/CudaAttentionKernels.cs:74)                                   */
+  AIDN_MASK_ADD_F32 = 3   /* additive bias, added after scale (CpuEngine.cs:29226-29233)                 */
+} aidn_mask_kind;
+
+/* Kernel selection.  AUTO picks: split-KV decode when seq_q == 1, the tcgen05 prefill kernel for 16-bit
+ * inputs with head_dim 64 or 128, the generic FFMA kernel otherwise.  The others force one kernel (tests). */
+typedef enum {
+  AIDN_PATH_AUTO = 0,
+  AIDN_PATH_GENERIC = 1,
+  AIDN_PATH_DECODE = 2,
+  AIDN_PATH_PREFILL_SM100 = 3
+} aidn_path;
+
+typedef struct {
+  int32_t device;       /* CUDA ordinal; must be the device of the current context                     */
+  int32_t qkv_dtype;    /* aidn_dtype of Q, K and V                                                    */
+  int32_t out_dtype;    /* AIDN_F32 (the reference's contract) or the same as qkv_dtype                */
+  int32_t head_dim;     /* D = Dv; 64 or 128 on the tcgen05 path, any multiple of 8 up to 256 elsewhere */
+  int32_t num_q_heads;  /* Hq of the full tensor                                                       */
+  int32_t num_kv_heads; /* Hkv; Hq % Hkv == 0; kv head of q head h is h / (Hq / Hkv)                   */
+  int32_t causal;       /* keep key k for query q iff k <= q + causal_offset                           */
+  int32_t causal_bottom_right; /* 1: causal_offset = seq_kv - seq_q per launch (SDPA / Gqa entry points,
+                                  CpuEngine.cs:27333-27340); 0: use causal_offset as given
+                                  (0 = top-left, the FlashAttention entry points, CpuEngine.cs:29235) */
+  int64_t causal_offset;
+  int32_t mask_kind;    /* aidn_mask_kind                                                              */
+  int32_t emit_lse;     /* 1: args.lse receives max + ln(sum) per row, -inf for a fully masked row      */
+  float softcap;        /* > 0: score = softcap * tanh(score * scale / softcap); 0 disables            */
+  int32_t path;         /* aidn_path                                                                   */
+  int32_t head_begin;   /* first q head this handle computes (head shard of a multi-GPU run)           */
+  int32_t head_count;   /* number of q heads it computes; 0 = all.  Must cover whole KV groups.        */
+  int32_t decode_chunk; /* keys per split of the decode kernel; 0 = choose from the shape              */
+  int32_t max_batch;    /* > 0 together with max_seq_kv: the handle allocates its own decode scratch   */
+  int64_t max_seq_q;    /*   for shapes up to these, so launch can be called with workspace == NULL    */
+  int64_t max_seq_kv;
+  void* nccl_comm;      /* ncclComm_t whose ranks hold consecutive head shards, or NULL                */
+} aidn_sdpa_desc;
+
+typedef struct {
+  const void* q;        /* device pointers; element (b,h,s,d) at base + b*stride[0] + h*stride[1] + s*stride[2] + d */
+  const void* k;
+  const void* v;
+  void* out;
+  float* lse;           /* [B, Hq, Sq] dense, fp32; required iff desc.emit_lse                          */
+  const void* mask;     /* per desc.mask_kind, or NULL                                                 */
+  int64_t mask_stride[4]; /* elements for (B, H, Sq, Sk); 0 = broadcast                                 */
+  const int32_t* kv_len;  /* [B] valid key count per batch entry (padding mask), or NULL                */
+  int64_t batch, seq_q, seq_kv;
+  int64_t q_stride[3];  /* elements for (B, H, S); all zero = dense [B,H,S,D]                           */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+  int64_t o_stride[3];
+  float scale;          /* 0 = 1/sqrt(head_dim)                                                        */
+  void* workspace;      /* device scratch of at least aidn_sdpa_workspace_bytes(), or NULL to use the handle's */
+  int64_t workspace_bytes;
+  int32_t gather_output;  /* 1: after the kernel, ncclAllGather the head shards of `out` in place on the same
+                             stream (batch == 1 or per-batch-entry group call); needs desc.nccl_comm      */
+} aidn_sdpa_args;
+
+/* Pointers passed with q/k/v/out index the FULL tensors: the handle offsets them by head_begin itself. */
+
+/* Validates the descriptor, resolves driver entry points, sizes and allocates handle-owned scratch. */
+AIDN_API int aidn_sdpa_create(const aidn_sdpa_desc* desc, aidn_sdpa_t* out);
+/* Bytes of caller workspace a launch of this shape needs (0 for the prefill kernels); < 0 on error. */
+AIDN_API int64_t aidn_sdpa_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq_q, int64_t seq_kv);
+/* Enqueues the attention forward on `cu_stream` (a CUstream / cudaStream_t).  Capture-safe, no allocation. */
+AIDN_API int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* args, void* cu_stream);
+/* Synchronises `cu_stream` and returns AIDN_ETIMEOUT if a kernel of this handle gave up a bounded wait,
+ * AIDN_ECUDA on a CUDA error, else AIDN_OK.  For tests and diagnostics; not needed on the hot path. */
+AIDN_API int aidn_sdpa_poll(aidn_sdpa_t h, void* cu_stream);
+/* Which kernel the last launch used (aidn_path value), and how many kernels it enqueued. */
+AIDN_API int aidn_sdpa_last_path(aidn_sdpa_t h);
+AIDN_API int aidn_sdpa_last_launch_count(aidn_sdpa_t h);
+AIDN_API int aidn_sdpa_destroy(aidn_sdpa_t h);
+/* Thread-local message of the last failing call on this thread ("" if none). */
+AIDN_API const char* aidn_sdpa_last_error(void);
+/* 1 when `device` is compute capability 10.x and this build carries sm_100a code, else 0. */
+AIDN_API int aidn_sdpa_device_supported(int32_t device);
+
+/* dtype staging (IDirectGpuBackend.cs:1890 ConvertToFp16, :1911 ConvertToFp32; bf16 rounding per
+ * NumericOperations/BFloat16.cs:65-84: round-to-nearest-even, NaN keeps its top payload bits plus the quiet bit). */
+AIDN_API int aidn_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* cu_stream);
+AIDN_API int aidn_cast_f32_to_f16(const float* src, void* dst, int64_t n, void* cu_stream);
+AIDN_API int aidn_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* cu_stream);
+AIDN_API int aidn_cast_f16_to_f32(const void* src, float* dst, int64_t n, void* cu_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AIDN_SDPA_H_ */

@@ -1,0 +1,355 @@
+"""GPU parity: every CUDA kernel, called through the C ABI, against the CPU oracle on the same seeded inputs,
+the committed golden fixtures, and size-independent properties at the full benchmark sizes.
+
+Case lists follow the reference's own attention tests (tests/AiDotNet.Tensors.Tests/Engines/...): odd sequence
+lengths, Sq != Sk, GQA ratios 1/2/3/4/8, MQA, fully masked rows, broadcast masks, additive bias with LSE.
+"""
+import numpy as np
+import pytest
+import torch
+
+from aidotnet.tensors_b200 import native as N
+from oracle import sdpa_oracle as O
+from tests._harness import compare, compare_lse, gen, oracle_rows, run_gpu
+
+pytestmark = pytest.mark.gpu
+
+
+def _t(x, dtype=torch.float32):
+    return torch.from_numpy(np.ascontiguousarray(x)).to(dtype).cuda()
+
+
+# ------------------------------------------------------------------------------------------------ generic / fp32
+def test_config1_fp32_noncausal():
+    """BASELINE config 1: fp32, B1 H8 S512 D64, no mask, scale 1/sqrt(D); <= 1e-5 relative."""
+    q, qf = gen((1, 8, 512, 64), "f32", 0xA1D00001, 1.0)
+    k, kf = gen((1, 8, 512, 64), "f32", 0xA1D00002, 1.0)
+    v, vf = gen((1, 8, 512, 64), "f32", 0xA1D00003, 1.0)
+    out, _, info = run_gpu(q, k, v, dtype="f32")
+    assert info["path"] == N.PATH_GENERIC
+    compare(out, O.sdpa(qf, kf, vf), "f32", "config1")
+
+
+def test_golden_cross_attention_and_masks(golden):
+    """GpuCpuConsistencyTests.cs:895-1061 (2e-5 there): D=3, Sq=2, Sk=3; full bool mask; logit softcap."""
+    q, k, v = (_t(golden[n]) for n in ("cross_q", "cross_k", "cross_v"))
+    out, _, _ = run_gpu(q, k, v, dtype="f32", scale=0.75)
+    assert np.abs(out.cpu().numpy() - golden["cross_out"]).max() <= 2e-5
+    m = golden["boolmask_mask"]
+    out, _, _ = run_gpu(q, k, v, dtype="f32", scale=0.75, mask=_t(m, torch.uint8), mask_kind=N.MASK_KEEP_U8)
+    assert np.abs(out.cpu().numpy() - golden["boolmask_out"]).max() <= 2e-5
+    out, _, _ = run_gpu(q, k, v, dtype="f32", scale=0.75, mask=_t(m.astype(np.float32)), mask_kind=N.MASK_KEEP_F32)
+    assert np.abs(out.cpu().numpy() - golden["boolmask_out"]).max() <= 2e-5
+    q, k, v = (_t(golden[n]) for n in ("capcross_q", "capcross_k", "capcross_v"))
+    out, _, _ = run_gpu(q, k, v, dtype="f32", scale=1.5, softcap=2.0)
+    assert np.abs(out.cpu().numpy() - golden["capcross_out"]).max() <= 2e-5
+
+
+def test_golden_softcap_closed_form(golden):
+    """BatchMatMulAndAttentionTests.cs:287-317: D=1, one query, two keys."""
+    out, _, _ = run_gpu(_t(golden["softcap_q"]), _t(golden["softcap_k"]), _t(golden["softcap_v"]), dtype="f32",
+                        scale=1.0, softcap=2.0)
+    assert abs(float(out.cpu().ravel()[0]) - float(golden["softcap_out"][0])) <= 1e-4
+
+
+@pytest.mark.parametrize("mb,mh", [(1, 1), (2, 1), (1, 3), (2, 3)])
+def test_golden_broadcast_masks(golden, mb, mh):
+    """SdpaMaskBroadcastTests.cs:61-114: size-1 mask axes broadcast."""
+    q, k, v = (_t(golden[n]) for n in ("bcast_q", "bcast_k", "bcast_v"))
+    S = q.shape[2]
+    mask = np.broadcast_to(np.tril(np.ones((S, S), np.uint8)), (mb, mh, S, S)).copy()
+    out, _, _ = run_gpu(q, k, v, dtype="f32", mask=_t(mask, torch.uint8), mask_kind=N.MASK_KEEP_U8)
+    assert np.abs(out.cpu().numpy() - golden["bcast_out"]).max() <= 1e-5
+    out2, _, _ = run_gpu(q, k, v, dtype="f32", causal=True)
+    assert np.abs(out2.cpu().numpy() - golden["bcast_out"]).max() <= 1e-5
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_golden_gqa(golden, causal):
+    """RopeGqaOpenClTests.cs:200-279: Hq 6 / Hkv 2 (ratio 3), D=8, S=5 (1e-4 there)."""
+    q, k, v = (_t(golden[n]) for n in ("gqa_q", "gqa_k", "gqa_v"))
+    out, _, _ = run_gpu(q, k, v, dtype="f32", causal=causal, bottom_right=False)
+    want = golden["gqa_out_causal"] if causal else golden["gqa_out_plain"]
+    assert np.abs(out.cpu().numpy() - want).max() <= 1e-5
+
+
+def test_golden_bias_and_lse(golden):
+    """FlashAttentionBiasTests.cs: 3-D (batch-broadcast) and 4-D bias, LSE = max + ln(sum), top-left causal."""
+    q, k, v = (_t(golden[n]) for n in ("bias_q", "bias_k", "bias_v"))
+    out, lse, _ = run_gpu(q, k, v, dtype="f32", mask=_t(golden["bias3"][None]), mask_kind=N.MASK_ADD_F32, want_lse=True)
+    assert np.abs(out.cpu().numpy() - golden["bias3_out"]).max() <= 2e-5
+    assert np.abs(lse.cpu().numpy() - golden["bias3_lse"]).max() <= 2e-5
+    out, lse, _ = run_gpu(q, k, v, dtype="f32", mask=_t(golden["bias4"]), mask_kind=N.MASK_ADD_F32, want_lse=True,
+                          causal=True, bottom_right=False)
+    assert np.abs(out.cpu().numpy() - golden["bias4c_out"]).max() <= 2e-5
+    assert np.abs(lse.cpu().numpy() - golden["bias4c_lse"]).max() <= 2e-5
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 37, 53, 40), (1, 8, 1, 130, 130, 128), (2, 3, 3, 65, 200, 256),
+                                   (1, 6, 2, 17, 300, 72)])
+def test_generic_kernel_shapes(dtype, shape):
+    """Odd lengths, Sq != Sk, GQA 2/8/1/3, head dims off the tensor-core path; causal + padding + LSE."""
+    B, Hq, Hkv, Sq, Sk, D = shape
+    q, qf = gen((B, Hq, Sq, D), dtype, 11)
+    k, kf = gen((B, Hkv, Sk, D), dtype, 12)
+    v, vf = gen((B, Hkv, Sk, D), dtype, 13)
+    kv = np.array([Sk, max(1, Sk // 3)][:B], np.int32)
+    out, lse, info = run_gpu(q, k, v, dtype=dtype, causal=True, kv_len=_t(kv, torch.int32), want_lse=True,
+                             path=N.PATH_GENERIC)
+    ref, rlse, _ = O.sdpa(qf, kf, vf, causal=True, kv_len=kv, want_lse=True)
+    compare(out, ref, dtype, f"generic {shape}")
+    compare_lse(lse, rlse, dtype)
+
+
+def test_fully_masked_rows_and_negative_offset():
+    """A fully masked row gives zeros and LSE -inf (CpuEngine.cs:27822-27827, 29244-29250)."""
+    q, qf = gen((1, 2, 40, 64), "f32", 21)
+    k, kf = gen((1, 2, 24, 64), "f32", 22)
+    v, vf = gen((1, 2, 24, 64), "f32", 23)
+    # bottom-right causal with Sq > Sk: the first Sq - Sk rows see nothing
+    out, lse, _ = run_gpu(q, k, v, dtype="f32", causal=True, want_lse=True)
+    ref, rlse, _ = O.sdpa(qf, kf, vf, causal=True, want_lse=True)
+    assert np.all(ref[:, :, :15] == 0) and np.all(out.cpu().numpy()[:, :, :15] == 0)
+    compare(out, ref, "f32")
+    compare_lse(lse, rlse, "f32")
+    out, _, _ = run_gpu(q, k, v, dtype="f32", kv_len=_t(np.array([0], np.int32), torch.int32))
+    assert np.all(out.cpu().numpy() == 0)
+
+
+def test_output_in_input_dtype():
+    q, qf = gen((1, 2, 33, 64), "bf16", 31)
+    k, kf = gen((1, 2, 70, 64), "bf16", 32)
+    v, vf = gen((1, 2, 70, 64), "bf16", 33)
+    out, _, _ = run_gpu(q, k, v, dtype="bf16", out_dtype="bf16", path=N.PATH_GENERIC)
+    assert out.dtype == torch.bfloat16
+    compare(out, O.sdpa(qf, kf, vf), "bf16")
+
+
+# ------------------------------------------------------------------------------------------------ decode
+def test_golden_flash_decode_shapes(golden):
+    """FlashDecodeCudaTests.cs:43-126 through the backend mirror: cache stored [seqLen, kvHeads, D]."""
+    from aidotnet.tensors_b200.backend import CudaBackend, GpuBuffer
+    be = CudaBackend(0)
+    for n, (h, hk, d, L) in enumerate(golden["decode_shapes"]):
+        qb, kb, vb = (GpuBuffer(_t(golden[f"decode{n}_{x}"]).reshape(-1)) for x in "qkv")
+        for splits in (0, 1, 8):
+            ob = be.FlashDecode(qb, kb, vb, int(h), int(hk), int(d), int(L), 1.0 / np.sqrt(np.float32(d)), splits)
+            be.Synchronize()
+            got = ob.tensor.cpu().numpy().reshape(h, d)
+            e = golden[f"decode{n}_out"]
+            assert np.all(np.abs(got - e) <= 2e-5 + 2e-5 * np.abs(e)), (n, splits)
+    be.Dispose()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16", "f32"])
+@pytest.mark.parametrize("shape", [(3, 8, 8, 700, 128), (2, 8, 2, 1000, 64), (2, 16, 2, 333, 128), (1, 6, 2, 129, 64),
+                                   (2, 4, 4, 513, 256), (1, 12, 1, 64, 128)])
+@pytest.mark.parametrize("chunk", [0, 64])
+def test_decode_kernel_shapes(dtype, shape, chunk):
+    """Ragged kv_len per batch entry, GQA ratios 1/4/8/3/12 (MQA), every dtype, forced small splits."""
+    B, Hq, Hkv, L, D = shape
+    if dtype == "f32" and D == 256:
+        pytest.skip("fp32 D=256 is served by the generic kernel")
+    q, qf = gen((B, Hq, 1, D), dtype, 41)
+    k, kf = gen((B, Hkv, L, D), dtype, 42)
+    v, vf = gen((B, Hkv, L, D), dtype, 43)
+    kv = np.array([L, L // 2 + 1, 7][:B], np.int32)
+    out, lse, info = run_gpu(q, k, v, dtype=dtype, kv_len=_t(kv, torch.int32), want_lse=True, decode_chunk=chunk)
+    assert info["path"] == N.PATH_DECODE
+    ref, rlse, _ = O.sdpa(qf, kf, vf, kv_len=kv, want_lse=True)
+    compare(out, ref, dtype, f"decode {shape}")
+    compare_lse(lse, rlse, dtype)
+
+
+def test_decode_with_masks_and_softcap():
+    B, Hq, Hkv, L, D = 2, 8, 4, 300, 128
+    q, qf = gen((B, Hq, 1, D), "bf16", 51)
+    k, kf = gen((B, Hkv, L, D), "bf16", 52)
+    v, vf = gen((B, Hkv, L, D), "bf16", 53)
+    rng = np.random.default_rng(5)
+    keep = (rng.random((B, 1, 1, L)) > 0.3).astype(np.uint8)
+    keep[1] = 0  # batch entry 1 sees nothing
+    out, _, _ = run_gpu(q, k, v, dtype="bf16", mask=_t(keep, torch.uint8), mask_kind=N.MASK_KEEP_U8, softcap=5.0,
+                        decode_chunk=64)
+    ref = O.sdpa(qf, kf, vf, mask=keep, mask_kind=O.MASK_KEEP_U8, softcap=5.0)
+    compare(out, ref, "bf16")
+    assert np.all(out[1].cpu().numpy() == 0)
+    bias = rng.standard_normal((B, Hq, 1, L)).astype(np.float32)
+    out, _, _ = run_gpu(q, k, v, dtype="bf16", mask=_t(bias), mask_kind=N.MASK_ADD_F32)
+    compare(out, O.sdpa(qf, kf, vf, mask=bias, mask_kind=O.MASK_ADD_F32), "bf16")
+
+
+def test_config4_batched_decode_full_size():
+    """BASELINE config 4: B64 H32 D128 bf16, kv_len uniform in [512, 4096], padded cache [64,32,4096,128]."""
+    B, H, L, D = 64, 32, 4096, 128
+    g = torch.Generator(device="cuda").manual_seed(0xA1D00004)
+    q = (torch.randn((B, H, 1, D), generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    k = (torch.randn((B, H, L, D), generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    v = (torch.randn((B, H, L, D), generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    kv = np.random.Generator(np.random.Philox(0xA1D00004)).integers(512, 4097, B).astype(np.int32)
+    out, _, info = run_gpu(q, k, v, dtype="bf16", kv_len=_t(kv, torch.int32))
+    assert info["path"] == N.PATH_DECODE
+    ref = O.sdpa(q.float().cpu().numpy(), k.float().cpu().numpy(), v.float().cpu().numpy(), kv_len=kv)
+    compare(out, ref, "bf16", "config4")
+    # determinism: fixed split count => fixed reduction order => identical bits
+    out2, _, _ = run_gpu(q, k, v, dtype="bf16", kv_len=_t(kv, torch.int32))
+    assert torch.equal(out, out2)
+
+
+# ------------------------------------------------------------------------------------------------ tcgen05 prefill
+PREFILL_SHAPES = [
+    # B, Hq, Hkv, Sq, Sk, D, causal
+    (1, 1, 1, 128, 128, 128, False),   # one tile, one KV tile
+    (1, 1, 1, 256, 128, 128, False),   # both tiles of a CTA
+    (1, 1, 1, 128, 384, 128, False),   # three KV tiles: accumulation, ring reuse, rescale
+    (1, 2, 1, 256, 256, 128, True),    # head pair (GQA 2), causal diagonal
+    (2, 4, 4, 300, 300, 128, True),    # ragged rows, row-tile pairs with an odd tile count
+    (1, 8, 2, 200, 456, 128, True),    # GQA 4, Sq != Sk (bottom-right causal)
+    (2, 3, 1, 129, 1025, 128, False),  # odd group (3): row-pair mode under GQA
+    (1, 4, 2, 640, 640, 64, True),     # head_dim 64
+    (1, 2, 2, 1024, 1024, 128, True),  # longer causal
+]
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("shape", PREFILL_SHAPES)
+def test_prefill_sm100_shapes(dtype, shape):
+    B, Hq, Hkv, Sq, Sk, D, causal = shape
+    q, qf = gen((B, Hq, Sq, D), dtype, 61)
+    k, kf = gen((B, Hkv, Sk, D), dtype, 62)
+    v, vf = gen((B, Hkv, Sk, D), dtype, 63)
+    out, lse, info = run_gpu(q, k, v, dtype=dtype, causal=causal, want_lse=True, path=N.PATH_PREFILL_SM100)
+    assert info["path"] == N.PATH_PREFILL_SM100
+    ref, rlse, _ = O.sdpa(qf, kf, vf, causal=causal, want_lse=True)
+    compare(out, ref, dtype, f"prefill {shape}")
+    compare_lse(lse, rlse, dtype)
+
+
+def test_prefill_sm100_padding_and_dtype_out():
+    B, Hq, Hkv, Sq, Sk, D = 2, 4, 2, 260, 700, 128
+    q, qf = gen((B, Hq, Sq, D), "bf16", 71)
+    k, kf = gen((B, Hkv, Sk, D), "bf16", 72)
+    v, vf = gen((B, Hkv, Sk, D), "bf16", 73)
+    kv = np.array([700, 131], np.int32)
+    out, _, _ = run_gpu(q, k, v, dtype="bf16", out_dtype="bf16", causal=True, kv_len=_t(kv, torch.int32),
+                        path=N.PATH_PREFILL_SM100)
+    compare(out, O.sdpa(qf, kf, vf, causal=True, kv_len=kv), "bf16")
+    # top-left causal with Sq < Sk and large values that force the lazy rescale to fire
+    q2, q2f = gen((B, Hq, Sq, D), "bf16", 74, 2.0)
+    out, _, _ = run_gpu(q2, k, v, dtype="bf16", causal=True, bottom_right=False, path=N.PATH_PREFILL_SM100)
+    compare(out, O.sdpa(q2f, kf, vf, causal=True, causal_offset=0), "bf16")
+
+
+def test_prefill_sm100_head_shard_matches_full():
+    """A head shard (multi-GPU partition) computes exactly the rows of the full call."""
+    B, Hq, Hkv, S, D = 1, 8, 4, 384, 128
+    q, _ = gen((B, Hq, S, D), "bf16", 81)
+    k, _ = gen((B, Hkv, S, D), "bf16", 82)
+    v, _ = gen((B, Hkv, S, D), "bf16", 83)
+    full, _, _ = run_gpu(q, k, v, dtype="bf16", causal=True, path=N.PATH_PREFILL_SM100)
+    out = torch.zeros_like(full)
+    for hb in (0, 4):
+        run_gpu(q, k, v, dtype="bf16", causal=True, path=N.PATH_PREFILL_SM100, head_begin=hb, head_count=4, out=out)
+    assert torch.equal(out, full)
+
+
+def test_config2_llama_prefill_full_size():
+    """BASELINE config 2: B4 H32 S2048 D128 causal bf16 -> fp32; full tensor against the oracle."""
+    B, H, S, D = 4, 32, 2048, 128
+    q, qf = gen((B, H, S, D), "bf16", 0xA1D00021)
+    k, kf = gen((B, H, S, D), "bf16", 0xA1D00022)
+    v, vf = gen((B, H, S, D), "bf16", 0xA1D00023)
+    out, _, info = run_gpu(q, k, v, dtype="bf16", causal=True)
+    assert info["path"] == N.PATH_PREFILL_SM100
+    compare(out, O.sdpa(qf, kf, vf, causal=True), "bf16", "config2")
+    out2, _, _ = run_gpu(q, k, v, dtype="bf16", causal=True)
+    assert torch.equal(out, out2), "prefill must be bit-reproducible"
+
+
+def test_config3_gqa_prefill_full_size_sampled_rows_and_properties():
+    """BASELINE config 3: B2 Hq32/Hkv8 S8192 D128 causal bf16.  Oracle on sampled row blocks (the full tensor
+    is 1.1 TFLOP on the CPU) plus two size-independent properties on the whole output."""
+    B, Hq, Hkv, S, D = 2, 32, 8, 8192, 128
+    q, qf = gen((B, Hq, S, D), "bf16", 0xA1D00031)
+    k, kf = gen((B, Hkv, S, D), "bf16", 0xA1D00032)
+    v, vf = gen((B, Hkv, S, D), "bf16", 0xA1D00033)
+    out, _, info = run_gpu(q, k, v, dtype="bf16", causal=True)
+    assert info["path"] == N.PATH_PREFILL_SM100
+    for r0 in (0, 127, 4096 - 32, 8192 - 64):
+        ref = oracle_rows(qf, kf, vf, r0, r0 + 64, causal=True, causal_offset=0)
+        compare(out[:, :, r0:r0 + 64], ref, "bf16", f"config3 rows {r0}")
+    # (a) softmax weights sum to one: with V == 1 every output element is 1
+    ones = torch.ones_like(v)
+    o1, _, _ = run_gpu(q, k, ones, dtype="bf16", causal=True)
+    assert float((o1 - 1).abs().max()) <= 4e-3
+    # (b) linearity in V: out(V) + out(V2) == out(V + V2) up to bf16 rounding of the summed V
+    v2, _ = gen((B, Hkv, S, D), "bf16", 0xA1D00034)
+    vs = (v.float() + v2.float()).to(torch.bfloat16)
+    o2, _, _ = run_gpu(q, k, v2, dtype="bf16", causal=True)
+    os_, _, _ = run_gpu(q, k, vs, dtype="bf16", causal=True)
+    assert float((out + o2 - os_).abs().max()) <= 2e-2
+
+
+def test_config5_long_context_shard_sampled_rows():
+    """BASELINE config 5, the shard one GPU owns: 8 q heads sharing kv head g of B1 Hq64/Hkv8 S32768 D128."""
+    Hq, Hkv, S, D = 64, 8, 32768, 128
+    g = 3
+    q, qf = gen((1, 8, S, D), "bf16", 0xA1D00051)      # only this shard's heads are materialised
+    k, kf = gen((1, 1, S, D), "bf16", 0xA1D00052)
+    v, vf = gen((1, 1, S, D), "bf16", 0xA1D00053)
+    out, _, info = run_gpu(q, k, v, dtype="bf16", causal=True)
+    assert info["path"] == N.PATH_PREFILL_SM100
+    for r0 in (0, 16384 - 16, 32768 - 32):
+        ref = oracle_rows(qf, kf, vf, r0, r0 + 32, causal=True, causal_offset=0)
+        compare(out[:, :, r0:r0 + 32], ref, "bf16", f"config5 rows {r0}")
+    del Hq, Hkv, g
+
+
+# ------------------------------------------------------------------------------------------------ casts, errors
+def test_cast_kernels_bit_exact(golden):
+    """BFloat16.cs:65-84 bit for bit, NaN payloads included; round trip through fp32 is lossless."""
+    x = torch.from_numpy(golden["bf16_in_bits"].view(np.int32).copy()).cuda()
+    dst = torch.zeros(x.numel(), dtype=torch.int16, device="cuda")
+    s = torch.cuda.current_stream().cuda_stream
+    N.cast("f32_to_bf16", x.data_ptr(), dst.data_ptr(), x.numel(), s)
+    torch.cuda.synchronize()
+    assert np.array_equal(dst.cpu().numpy().view(np.uint16), golden["bf16_out_bits"])
+    big = torch.randn(1 << 20, device="cuda") * 3
+    b16 = torch.empty(1 << 20, dtype=torch.bfloat16, device="cuda")
+    N.cast("f32_to_bf16", big.data_ptr(), b16.data_ptr(), big.numel(), s)
+    back = torch.empty_like(big)
+    N.cast("bf16_to_f32", b16.data_ptr(), back.data_ptr(), big.numel(), s)
+    torch.cuda.synchronize()
+    assert np.array_equal(b16.view(torch.int16).cpu().numpy().view(np.uint16), O.f32_to_bf16_bits(big.cpu().numpy()))
+    assert torch.equal(back, b16.float())
+    h16 = torch.empty(1 << 20, dtype=torch.float16, device="cuda")
+    N.cast("f32_to_f16", big.data_ptr(), h16.data_ptr(), big.numel(), s)
+    torch.cuda.synchronize()
+    assert torch.equal(h16, big.half())
+
+
+def test_error_codes_no_fallback():
+    """Bad requests are status codes with a message; nothing is silently rerouted to another path."""
+    with pytest.raises(N.AidnError) as e:
+        N.Handle(device=0, qkv_dtype=N.BF16, head_dim=128, num_q_heads=6, num_kv_heads=4)
+    assert e.value.status == N.EINVAL
+    q, _ = gen((1, 2, 16, 72), "bf16", 1)
+    with pytest.raises(N.AidnError) as e:
+        run_gpu(q, q, q, dtype="bf16", path=N.PATH_PREFILL_SM100)      # head_dim 72 is not a tensor-core shape
+    assert e.value.status == N.EUNSUPPORTED
+    with pytest.raises(N.AidnError) as e:
+        run_gpu(q, q, q, dtype="bf16", path=N.PATH_DECODE)             # seq_q != 1
+    assert e.value.status == N.EUNSUPPORTED
+    h = N.Handle(device=0, qkv_dtype=N.BF16, head_dim=128, num_q_heads=2)
+    with pytest.raises(N.AidnError) as e:
+        h.launch(q=0, k=0, v=0, out=0, batch=1, seq_q=1, seq_kv=1, stream=0)
+    assert e.value.status == N.EINVAL
+    qd, _ = gen((4, 2, 1, 128), "bf16", 2)
+    kd, _ = gen((4, 2, 2048, 128), "bf16", 3)
+    o = torch.empty((4, 2, 1, 128), device="cuda")
+    with pytest.raises(N.AidnError) as e:   # decode needs scratch and none was given
+        h.launch(q=qd.data_ptr(), k=kd.data_ptr(), v=kd.data_ptr(), out=o.data_ptr(), batch=4, seq_q=1, seq_kv=2048,
+                 stream=torch.cuda.current_stream().cuda_stream)
+    assert e.value.status == N.EWORKSPACE
+    h.close()
