@@ -1,0 +1,83 @@
+// P/Invoke binding of libaidotnet_sdpa_sm100 (C ABI: include/aidn_sdpa.h) for the reference's CUDA backend.
+// Drop into src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/ next to CuBlasNative.cs.  Source only: it has not been
+// compiled in the environment this repository was built in (no .NET toolchain there); field order, sizes and
+// entry points mirror the header one to one, and the same layout is checked from Python (ctypes) in the tests.
+using System;
+using System.Runtime.InteropServices;
+
+namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
+{
+    internal enum AidnStatus { Ok = 0, Inval = 1, Unsupported = 2, Cuda = 3, Workspace = 4, Timeout = 5, Nccl = 6 }
+    internal enum AidnDtype { F32 = 0, F16 = 1, BF16 = 2 }
+    internal enum AidnMaskKind { None = 0, KeepU8 = 1, KeepF32 = 2, AddF32 = 3 }
+    internal enum AidnPath { Auto = 0, Generic = 1, Decode = 2, PrefillSm100 = 3 }
+
+    [StructLayout(LayoutKind.Sequential)]
+    internal struct AidnSdpaDesc
+    {
+        public int device, qkv_dtype, out_dtype, head_dim, num_q_heads, num_kv_heads, causal, causal_bottom_right;
+        public long causal_offset;
+        public int mask_kind, emit_lse;
+        public float softcap;
+        public int path, head_begin, head_count, decode_chunk, max_batch;
+        public long max_seq_q, max_seq_kv;
+        public IntPtr nccl_comm;
+    }
+
+    [StructLayout(LayoutKind.Sequential)]
+    internal unsafe struct AidnSdpaArgs
+    {
+        public IntPtr q, k, v, @out, lse, mask;
+        public fixed long mask_stride[4];
+        public IntPtr kv_len;
+        public long batch, seq_q, seq_kv;
+        public fixed long q_stride[3];
+        public fixed long k_stride[3];
+        public fixed long v_stride[3];
+        public fixed long o_stride[3];
+        public float scale;
+        public IntPtr workspace;
+        public long workspace_bytes;
+        public int gather_output;
+    }
+
+    internal static class AidnSdpaNative
+    {
+        private const string Lib = "aidotnet_sdpa_sm100";
+
+        static AidnSdpaNative()
+        {
+            // Same resolver mechanism as the cuBLAS / NVRTC bindings (Engines/NativeLibraryResolverRegistry.cs:35).
+            NativeLibraryResolverRegistry.Register(Lib, new[] { "libaidotnet_sdpa_sm100.so", "aidotnet_sdpa_sm100.dll" });
+        }
+
+        /// <summary>Master switch, read once: AIDOTNET_SDPA_SM100=0 keeps the NVRTC kernels.</summary>
+        public static readonly bool Enabled =
+            Environment.GetEnvironmentVariable("AIDOTNET_SDPA_SM100") != "0";
+
+        [DllImport(Lib)] public static extern int aidn_sdpa_create(ref AidnSdpaDesc desc, out IntPtr handle);
+        [DllImport(Lib)] public static extern long aidn_sdpa_workspace_bytes(IntPtr handle, long batch, long seqQ, long seqKv);
+        [DllImport(Lib)] public static extern int aidn_sdpa_launch(IntPtr handle, ref AidnSdpaArgs args, IntPtr cuStream);
+        [DllImport(Lib)] public static extern int aidn_sdpa_poll(IntPtr handle, IntPtr cuStream);
+        [DllImport(Lib)] public static extern int aidn_sdpa_last_path(IntPtr handle);
+        [DllImport(Lib)] public static extern int aidn_sdpa_last_launch_count(IntPtr handle);
+        [DllImport(Lib)] public static extern int aidn_sdpa_destroy(IntPtr handle);
+        [DllImport(Lib)] private static extern IntPtr aidn_sdpa_last_error();
+        [DllImport(Lib)] public static extern int aidn_sdpa_device_supported(int device);
+        [DllImport(Lib)] public static extern int aidn_cast_f32_to_bf16(IntPtr src, IntPtr dst, long n, IntPtr cuStream);
+        [DllImport(Lib)] public static extern int aidn_cast_f32_to_f16(IntPtr src, IntPtr dst, long n, IntPtr cuStream);
+        [DllImport(Lib)] public static extern int aidn_cast_bf16_to_f32(IntPtr src, IntPtr dst, long n, IntPtr cuStream);
+        [DllImport(Lib)] public static extern int aidn_cast_f16_to_f32(IntPtr src, IntPtr dst, long n, IntPtr cuStream);
+
+        public static string LastError() => Marshal.PtrToStringAnsi(aidn_sdpa_last_error()) ?? string.Empty;
+
+        /// <summary>Non-zero status becomes an exception; the sm_100a route has no CPU fallback.</summary>
+        public static void Check(int status)
+        {
+            if (status == (int)AidnStatus.Ok) return;
+            string message = $"aidn_sdpa status {(AidnStatus)status}: {LastError()}";
+            if (status == (int)AidnStatus.Inval) throw new ArgumentException(message);
+            throw new InvalidOperationException(message);
+        }
+    }
+}

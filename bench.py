@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5shard] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c4q|c5shard] [--impl reference]
 
 One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
 default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
@@ -35,6 +35,8 @@ WORKLOADS = {
                name="gqa_prefill_B2_Hq32_Hkv8_S8192_D128_causal_bf16"),
     "c5shard": dict(B=1, Hq=8, Hkv=1, Sq=32768, Sk=32768, D=128, causal=True, kind="prefill",
                     name="long_context_shard_B1_Hq8_Hkv1_S32768_D128_causal_bf16"),
+    "c4q": dict(B=16, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
+                name="batched_decode_quarter_B16_H32_D128_kvlen512-4096_bf16"),
     "c4": dict(B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
                name="batched_decode_B64_H32_D128_kvlen512-4096_bf16"),
 }
