@@ -372,6 +372,85 @@ int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* a, void* cu_stream) {
   return AIDN_OK;
 }
 
+// Decode for callers that cannot allocate device memory (no handle, no workspace): see include/aidn_sdpa.h.
+int aidn_sdpa_decode_noalloc(const aidn_sdpa_desc* desc, const aidn_sdpa_args* a, void* cu_stream) {
+  g_err[0] = 0;
+  if (!desc || !a) return fail(AIDN_EINVAL, "decode_noalloc: null argument");
+  const aidn_sdpa_desc& d = *desc;
+  if (d.qkv_dtype < AIDN_F32 || d.qkv_dtype > AIDN_BF16) return fail(AIDN_EINVAL, "decode_noalloc: unknown qkv_dtype");
+  if (d.out_dtype != AIDN_F32 && d.out_dtype != d.qkv_dtype)
+    return fail(AIDN_EINVAL, "decode_noalloc: out_dtype must be fp32 or equal to qkv_dtype");
+  if (d.num_q_heads <= 0 || d.num_kv_heads <= 0 || d.num_q_heads % d.num_kv_heads != 0)
+    return fail(AIDN_EINVAL, "decode_noalloc: numHeads must be a positive multiple of numKVHeads");
+  if (d.mask_kind < AIDN_MASK_NONE || d.mask_kind > AIDN_MASK_ADD_F32) return fail(AIDN_EINVAL, "decode_noalloc: unknown mask_kind");
+  if (!(d.softcap >= 0.f)) return fail(AIDN_EINVAL, "decode_noalloc: softcap must be >= 0");
+  if (d.decode_chunk < 0 || (d.decode_chunk > 0 && d.decode_chunk % 8 != 0))
+    return fail(AIDN_EINVAL, "decode_noalloc: decode_chunk must be 0 or a positive multiple of 8");
+  aidn_sdpa tmp;  // on the stack: only the fields the chunk heuristic reads
+  std::memset(&tmp, 0, sizeof(tmp));
+  tmp.d = d;
+  tmp.group = d.num_q_heads / d.num_kv_heads;
+  tmp.head_count = d.head_count > 0 ? d.head_count : d.num_q_heads - d.head_begin;
+  if (d.head_begin < 0 || tmp.head_count <= 0 || d.head_begin + tmp.head_count > d.num_q_heads ||
+      d.head_begin % tmp.group != 0 || tmp.head_count % tmp.group != 0)
+    return fail(AIDN_EINVAL, "decode_noalloc: the head shard must lie inside the tensor and cover whole KV groups");
+  if (!a->q || !a->k || !a->v || !a->out) return fail(AIDN_EINVAL, "decode_noalloc: null tensor pointer");
+  if (a->batch <= 0 || a->batch > 65535 || a->seq_kv <= 0) return fail(AIDN_EINVAL, "decode_noalloc: bad batch or seq_kv");
+  if (a->seq_q != 1) return fail(AIDN_EUNSUPPORTED, "decode_noalloc: seq_q must be 1");
+  if (d.emit_lse && !a->lse) return fail(AIDN_EINVAL, "decode_noalloc: emit_lse set but lse pointer is null");
+  if (d.mask_kind != AIDN_MASK_NONE && !a->mask) return fail(AIDN_EINVAL, "decode_noalloc: mask_kind set but mask pointer is null");
+  if (a->scale < 0.f || std::isnan(a->scale)) return fail(AIDN_EINVAL, "decode_noalloc: scale must be >= 0");
+  if (!aidn::decode_supported(d.qkv_dtype, d.head_dim))
+    return fail(AIDN_EUNSUPPORTED, "decode_noalloc: head_dim must be 64 or 128 (256 for 16-bit inputs)");
+
+  aidn::SdpaParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.q = a->q; p.k = a->k; p.v = a->v; p.out = a->out;
+  p.lse = d.emit_lse ? a->lse : nullptr;
+  p.mask = d.mask_kind != AIDN_MASK_NONE ? a->mask : nullptr;
+  p.mask_kind = d.mask_kind;
+  p.kv_len = a->kv_len;
+  for (int i = 0; i < 4; ++i) p.mask_stride[i] = a->mask_stride[i];
+  p.seq_q = 1;
+  p.seq_kv = a->seq_kv;
+  p.batch = (int)a->batch;
+  p.num_q_heads = d.num_q_heads;
+  p.num_kv_heads = d.num_kv_heads;
+  p.group = tmp.group;
+  p.head_begin = d.head_begin;
+  p.head_count = tmp.head_count;
+  p.head_dim = d.head_dim;
+  p.causal = d.causal ? 1 : 0;
+  p.causal_offset = d.causal_bottom_right ? (a->seq_kv - 1) : d.causal_offset;
+  p.out_f32 = d.out_dtype == AIDN_F32 ? 1 : 0;
+  p.scale = a->scale > 0.f ? a->scale : 1.0f / std::sqrt((float)d.head_dim);
+  p.softcap = d.softcap;
+  p.status = nullptr;
+  const int64_t D = d.head_dim;
+  if (all_zero(a->q_stride)) dense_strides(p.qs, d.num_q_heads, 1, D); else std::memcpy(p.qs, a->q_stride, sizeof(p.qs));
+  if (all_zero(a->k_stride)) dense_strides(p.ks, d.num_kv_heads, a->seq_kv, D); else std::memcpy(p.ks, a->k_stride, sizeof(p.ks));
+  if (all_zero(a->v_stride)) dense_strides(p.vs, d.num_kv_heads, a->seq_kv, D); else std::memcpy(p.vs, a->v_stride, sizeof(p.vs));
+  if (all_zero(a->o_stride)) dense_strides(p.os, d.num_q_heads, 1, D); else std::memcpy(p.os, a->o_stride, sizeof(p.os));
+  for (int i = 0; i < 3; ++i)
+    if (p.qs[i] < 0 || p.ks[i] < 0 || p.vs[i] < 0 || p.os[i] < 0) return fail(AIDN_EINVAL, "decode_noalloc: negative stride");
+  const size_t esz = elem_size(d.qkv_dtype);
+  if (!(aligned16(p.q, p.qs, esz) && aligned16(p.k, p.ks, esz) && aligned16(p.v, p.vs, esz)))
+    return fail(AIDN_EUNSUPPORTED, "decode_noalloc: Q/K/V rows must be 16-byte aligned");
+
+  int chunk = 0, nchunks = 0;
+  const int64_t need = decode_ws_bytes(&tmp, a->batch, a->seq_kv, &chunk, &nchunks);
+  const int64_t have = aidn::decode_static_scratch_bytes();
+  if (need > have)
+    return fail(AIDN_EWORKSPACE,
+                "decode_noalloc: this shape needs %lld bytes of split-KV scratch but the library's static array holds %lld; "
+                "lower batch*heads*ceil(seq_kv/chunk) (a larger decode_chunk helps) or use aidn_sdpa_launch with a workspace",
+                (long long)need, (long long)have);
+  int launches = 0;
+  cudaError_t e = aidn::launch_decode_static(p, d.qkv_dtype, chunk, nchunks, (cudaStream_t)cu_stream, &launches);
+  if (e != cudaSuccess) return fail_cuda(e, "decode_noalloc");
+  return AIDN_OK;
+}
+
 static int cast_common(int kind, const void* src, void* dst, int64_t n, void* cu_stream) {
   g_err[0] = 0;
   if (n < 0 || (n > 0 && (!src || !dst))) return fail(AIDN_EINVAL, "cast: bad argument");

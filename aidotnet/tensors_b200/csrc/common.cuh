@@ -117,6 +117,9 @@ cudaError_t launch_generic(const SdpaParams& p, int dtype, cudaStream_t stream);
 cudaError_t launch_decode(const SdpaParams& p, int dtype, int chunk, int nchunks, float* workspace, cudaStream_t stream,
                           int* launches);
 bool decode_supported(int dtype, int head_dim);
+int64_t decode_static_scratch_bytes();
+cudaError_t launch_decode_static(const SdpaParams& p, int dtype, int chunk, int nchunks, cudaStream_t stream,
+                                 int* launches);
 cudaError_t launch_cast(int kind, const void* src, void* dst, int64_t n, cudaStream_t stream);
 
 struct PrefillPlan;  // opaque to callers of the sm100 prefill launcher

@@ -11,6 +11,8 @@
 // thread per (head, split) with a serial, uncoalesced walk over the cache and take a single sequence.
 //
 // Scratch layout (fp32): acc[B][Hc][nchunks][D] followed by ml[B][Hc][nchunks][2], Hc = heads of the shard.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace aidn {
@@ -334,6 +336,37 @@ cudaError_t launch_decode_t(const SdpaParams& p, int chunk, int nchunks, float* 
   return cudaGetLastError();
 }
 
+
+// ---- decode with library-owned static scratch ---------------------------------------------------------------
+// Some callers may not allocate device memory at the point where they decode: code running inside a CUDA-graph
+// capture or a real-time serving loop where cudaMalloc (which can synchronise the device) is forbidden, or a
+// host whose memory budget was handed out up front.  For them the split-KV partials live in this fixed array
+// instead of a caller or handle allocation.  Every GPU that loads the library holds the array until exit.
+constexpr int64_t kStaticScratchFloats = 4ll * 1024 * 1024;  // 16 MiB
+static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+// In host code the array's name is only a stand-in; the device address has to be asked for, per device, with
+// that device current.
+cudaError_t static_scratch_address(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (!g_static_scratch_ptr[dev]) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_static_scratch);
+    if (e != cudaSuccess) return e;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return cudaSuccess;
+}
+
 }  // namespace
 
 bool decode_supported(int dtype, int head_dim) {
@@ -348,6 +381,22 @@ cudaError_t launch_decode(const SdpaParams& p, int dtype, int chunk, int nchunks
     case AIDN_F16: return launch_decode_t<__half>(p, chunk, nchunks, workspace, stream, launches);
     default: return launch_decode_t<__nv_bfloat16>(p, chunk, nchunks, workspace, stream, launches);
   }
+}
+
+}  // namespace aidn
+
+namespace aidn {
+
+int64_t decode_static_scratch_bytes() { return kStaticScratchFloats * (int64_t)sizeof(float); }
+
+// Same two kernels as launch_decode, with the partials in the library's static array.  `need_bytes` is what the
+// shape requires; the caller has already checked it against decode_static_scratch_bytes().
+cudaError_t launch_decode_static(const SdpaParams& p, int dtype, int chunk, int nchunks, cudaStream_t stream,
+                                 int* launches) {
+  float* scratch = nullptr;
+  cudaError_t e = static_scratch_address(&scratch);
+  if (e != cudaSuccess) return e;
+  return launch_decode(p, dtype, chunk, nchunks, scratch, stream, launches);
 }
 
 }  // namespace aidn

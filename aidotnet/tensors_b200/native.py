@@ -26,6 +26,7 @@ EXPORTS = (
     "aidn_sdpa_create", "aidn_sdpa_workspace_bytes", "aidn_sdpa_launch", "aidn_sdpa_poll", "aidn_sdpa_last_path",
     "aidn_sdpa_last_launch_count", "aidn_sdpa_destroy", "aidn_sdpa_last_error", "aidn_sdpa_device_supported",
     "aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32",
+    "aidn_sdpa_decode_noalloc",
 )
 
 
@@ -93,6 +94,8 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
         fn.restype = ctypes.c_int
+    lib.aidn_sdpa_decode_noalloc.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(SdpaArgs), ctypes.c_void_p]
+    lib.aidn_sdpa_decode_noalloc.restype = ctypes.c_int
     lib.aidn_sdpa_debug_set.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.aidn_sdpa_debug_set.restype = ctypes.c_int
     _lib = lib
@@ -188,3 +191,10 @@ class Handle:
 
 def cast(kind: str, src: int, dst: int, n: int, stream: int) -> None:
     check(getattr(load(), f"aidn_cast_{kind}")(ctypes.c_void_p(src), ctypes.c_void_p(dst), n, ctypes.c_void_p(stream)))
+
+
+def decode_noalloc(desc: SdpaDesc, args: SdpaArgs, stream: int) -> None:
+    """Batched decode through the entry point that allocates nothing (split-KV partials in the library's static
+    16 MiB array).  For hosts that may not allocate device memory where they decode; calls that overlap on the GPU
+    race on the shared array, so keep them on one stream."""
+    check(load().aidn_sdpa_decode_noalloc(ctypes.byref(desc), ctypes.byref(args), ctypes.c_void_p(stream)))

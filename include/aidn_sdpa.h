@@ -137,6 +137,26 @@ AIDN_API const char* aidn_sdpa_last_error(void);
 /* 1 when `device` is compute capability 10.x and this build carries sm_100a code, else 0. */
 AIDN_API int aidn_sdpa_device_supported(int32_t device);
 
+/* Batched decode (seq_q == 1) that allocates nothing, for callers that are not allowed to: a serving loop or a
+ * CUDA-graph-replaying runtime that fixed its device memory up front, or a host (such as a managed runtime whose GPU
+ * buffers all come from one pre-sized pool) that cannot call cudaMalloc at the point where it decodes.  It needs no
+ * handle and no workspace: the split-KV partials go to a fixed 16 MiB array that is part of the library image, so
+ * every GPU that loads the library keeps those 16 MiB until the process exits.  The caller still passes Q, K, V,
+ * out (and lse / mask / kv_len) exactly as for aidn_sdpa_launch; `desc` is read on every call (path, max_*, nccl_comm
+ * are ignored) and `args.workspace` is ignored.
+ *   - Limit: batch * heads_in_shard * ceil(seq_kv / chunk) * (head_dim + 2) * 4 bytes must fit in 16 MiB, where
+ *     chunk is desc.decode_chunk or the library's choice (at most 512 keys); a larger request returns
+ *     AIDN_EWORKSPACE with the two sizes in aidn_sdpa_last_error().
+ *   - The first call on each device looks up the array's device address (with that device current); make that
+ *     first call outside any stream capture.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.  Nothing has to be
+ *     cleared between calls, because the combine kernel reads only the slots the partial kernel of the same call
+ *     wrote, but two calls whose kernels overlap on the GPU (different streams, or two host threads) race on it:
+ *     run them on one stream or order them yourself.
+ * No counterpart in the reference: its FlashDecode allocates three scratch buffers per call
+ * (CudaBackend.cs:2994-2996). */
+AIDN_API int aidn_sdpa_decode_noalloc(const aidn_sdpa_desc* desc, const aidn_sdpa_args* args, void* cu_stream);
+
 /* dtype staging (IDirectGpuBackend.cs:1890 ConvertToFp16, :1911 ConvertToFp32; bf16 rounding per
  * NumericOperations/BFloat16.cs:65-84: round-to-nearest-even, NaN keeps its top payload bits plus the quiet bit). */
 AIDN_API int aidn_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* cu_stream);
