@@ -76,6 +76,7 @@ struct aidn_sdpa {
   int last_path;
   int last_launches;
   float* debug;
+  int debug_mode;
 };
 
 namespace {
@@ -179,6 +180,7 @@ int aidn_sdpa_create(const aidn_sdpa_desc* desc, aidn_sdpa_t* out) {
   h->last_path = AIDN_PATH_AUTO;
   h->last_launches = 0;
   h->debug = nullptr;
+  h->debug_mode = 0;
   e = cudaMalloc(&h->status_dev, sizeof(int32_t));
   if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, sizeof(int32_t));
   if (e != cudaSuccess) {
@@ -223,11 +225,13 @@ int64_t aidn_sdpa_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq_q, i
 int aidn_sdpa_last_path(aidn_sdpa_t h) { return h ? h->last_path : -1; }
 int aidn_sdpa_last_launch_count(aidn_sdpa_t h) { return h ? h->last_launches : -1; }
 
-// Diagnostic tap of the tcgen05 kernel (not part of the public header): CTA 0 writes its first score tile,
-// its un-normalised accumulator and the running (sum, max) into `buf`.
-AIDN_API int aidn_sdpa_debug_set(aidn_sdpa_t h, float* buf) {
+// Diagnostic tap of the tcgen05 kernel (not part of the public header).  mode 1: CTA 0 writes its first score
+// tile, its un-normalised accumulator and the running (sum, max) into `buf`; mode 2: every CTA writes a timeline
+// of 16 globaltimer stamps.
+AIDN_API int aidn_sdpa_debug_set(aidn_sdpa_t h, float* buf, int mode) {
   if (!h) return AIDN_EINVAL;
   h->debug = buf;
+  h->debug_mode = buf ? mode : 0;
   return AIDN_OK;
 }
 
@@ -333,7 +337,7 @@ int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* a, void* cu_stream) {
     }
     e = aidn::launch_decode(p, d.qkv_dtype, chunk, nchunks, ws, stream, &launches);
   } else if (path == AIDN_PATH_PREFILL_SM100) {
-    e = aidn::launch_prefill_sm100(p, d.qkv_dtype, stream, h->debug, &why);
+    e = aidn::launch_prefill_sm100(p, d.qkv_dtype, stream, h->debug, h->debug_mode, &why);
     launches = 1;
     if (e != cudaSuccess && why[0]) return fail(AIDN_ECUDA, "launch: %s (%s)", why, cudaGetErrorName(e));
   } else {

@@ -64,6 +64,7 @@ struct PrefillParams {
   int32_t items_per_rank;  // batch * work items per rank
   int32_t per_batch;       // work items per rank per batch entry
   float* debug;            // optional tap: scores of CTA 0 at j == 0, un-normalised O, l, m
+  int32_t debug_mode;      // 1: value tap of CTA 0; 2: per-CTA timeline (16 x u64 per CTA)
 };
 
 struct TileInfo {
@@ -97,6 +98,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_ptr_smem + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Timeline tap (debug_mode 2): slot k of this CTA's 16-entry record receives a globaltimer stamp.
+  unsigned long long* trace = pp.debug_mode == 2 ? reinterpret_cast<unsigned long long*>(pp.debug) + (size_t)blockIdx.x * 16 : nullptr;
+  auto stamp = [&](int slot) { if (trace) trace[slot] = globaltimer_ns(); };
+  if (threadIdx.x == 0) stamp(0);
 
   // ---- work item ---------------------------------------------------------------------------------
   const int item = blockIdx.x;
@@ -167,6 +172,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
+  if (threadIdx.x == 0) {
+    stamp(1);
+    if (trace) {
+      unsigned smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      trace[15] = ((unsigned long long)smid << 32) | (unsigned)n_max;
+    }
+  }
 
   const float sl2 = p.scale * kLog2e;
 
@@ -194,6 +207,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { alive = false; break; }
       tc_fence_after();
+      if (j == 0 && row_in_tile == 0) stamp(2 + 4 * i);
 
       uint32_t sr[128];
       tmem_ld32(t_s + 0, sr + 0);
@@ -203,7 +217,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_wait_ld();
       float* s = reinterpret_cast<float*>(sr);
 
-      if (pp.debug && blockIdx.x == 0 && j == 0) {
+      if (pp.debug_mode == 1 && blockIdx.x == 0 && j == 0) {
         float* dbg = pp.debug + (size_t)(i * kBM + row_in_tile) * kBN;
 #pragma unroll
         for (int c = 0; c < kBN; ++c) dbg[c] = s[c];
@@ -278,6 +292,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_arrive(bar_p_full + 8 * i);
     }
 
+    if (row_in_tile == 0) stamp(3 + 4 * i);
     // ---- epilogue: O / l -> global -----------------------------------------------------------------
     if (alive && ti.valid) {
       bool have_o = ti.n > 0;
@@ -288,6 +303,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (alive) {
         tc_fence_after();
+        if (row_in_tile == 0) stamp(4 + 4 * i);
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const int64_t obase = b * p.os[0] + (int64_t)ti.h * p.os[1] + qrow * p.os[2];
 #pragma unroll
@@ -300,7 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int c = 0; c < 32; ++c) orr[c] = 0u;
           }
-          if (pp.debug && blockIdx.x == 0) {
+          if (pp.debug_mode == 1 && blockIdx.x == 0) {
             float* dbg = pp.debug + 2 * kBM * kBN + (size_t)(i * kBM + row_in_tile) * HD + c0;
 #pragma unroll
             for (int c = 0; c < 32; ++c) dbg[c] = __uint_as_float(orr[c]);
@@ -329,11 +345,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (row_valid && p.lse)
           p.lse[((int64_t)b * p.num_q_heads + ti.h) * p.seq_q + qrow] =
               (l > 0.f) ? m * p.scale + logf(l) : -INFINITY;
-        if (pp.debug && blockIdx.x == 0) {
+        if (pp.debug_mode == 1 && blockIdx.x == 0) {
           float* dbg = pp.debug + 2 * kBM * kBN + 2 * kBM * HD + (size_t)(i * kBM + row_in_tile) * 2;
           dbg[0] = l;
           dbg[1] = m;
         }
+        if (row_in_tile == 0) stamp(5 + 4 * i);
       }
     }
   } else {
@@ -443,9 +460,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (threadIdx.x == 0 && p.status) atomicOr(p.status, kStatusTimeout);
     __syncthreads();
   }
+  if (threadIdx.x == 0) stamp(10);
   if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+    if (lane == 0) stamp(11);
   }
 }
 
@@ -496,7 +515,7 @@ bool tma_ok(const void* base, const int64_t* stride, int64_t S, int64_t H, int64
 }
 
 template <typename T, int HD>
-cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, float* debug, const char** why) {
+cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, float* debug, int debug_mode, const char** why) {
   using C = Cfg<HD>;
   cudaError_t e = resolve_encode();
   if (e != cudaSuccess) { *why = "cuTensorMapEncodeTiled is not available from the driver"; return e; }
@@ -511,6 +530,7 @@ cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, float* debug, con
   PrefillParams pp;
   pp.p = p;
   pp.debug = debug;
+  pp.debug_mode = debug ? debug_mode : 0;
   pp.row_tiles = (int)((p.seq_q + kBM - 1) / kBM);
   pp.pair_heads = (p.group % 2 == 0) ? 1 : 0;
   if (pp.pair_heads) {
@@ -552,13 +572,14 @@ bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why) {
   return true;
 }
 
-cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t stream, float* debug, const char** why) {
+cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t stream, float* debug, int debug_mode,
+                                 const char** why) {
   if (dtype == AIDN_BF16) {
-    if (p.head_dim == 128) return launch_t<__nv_bfloat16, 128>(p, stream, debug, why);
-    return launch_t<__nv_bfloat16, 64>(p, stream, debug, why);
+    if (p.head_dim == 128) return launch_t<__nv_bfloat16, 128>(p, stream, debug, debug_mode, why);
+    return launch_t<__nv_bfloat16, 64>(p, stream, debug, debug_mode, why);
   }
-  if (p.head_dim == 128) return launch_t<__half, 128>(p, stream, debug, why);
-  return launch_t<__half, 64>(p, stream, debug, why);
+  if (p.head_dim == 128) return launch_t<__half, 128>(p, stream, debug, debug_mode, why);
+  return launch_t<__half, 64>(p, stream, debug, debug_mode, why);
 }
 
 }  // namespace aidn

@@ -96,7 +96,7 @@ def load() -> ctypes.CDLL:
         fn.restype = ctypes.c_int
     lib.aidn_sdpa_decode_noalloc.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(SdpaArgs), ctypes.c_void_p]
     lib.aidn_sdpa_decode_noalloc.restype = ctypes.c_int
-    lib.aidn_sdpa_debug_set.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    lib.aidn_sdpa_debug_set.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
     lib.aidn_sdpa_debug_set.restype = ctypes.c_int
     _lib = lib
     return lib
@@ -168,8 +168,8 @@ class Handle:
     def last_launch_count(self) -> int:
         return int(self._lib.aidn_sdpa_last_launch_count(self._h))
 
-    def debug_set(self, ptr: Optional[int]) -> None:
-        self._lib.aidn_sdpa_debug_set(self._h, ctypes.c_void_p(ptr))
+    def debug_set(self, ptr: Optional[int], mode: int = 1) -> None:
+        self._lib.aidn_sdpa_debug_set(self._h, ctypes.c_void_p(ptr), mode)
 
     def close(self) -> None:
         if getattr(self, "_h", None):
