@@ -70,7 +70,8 @@ struct aidn_sdpa {
   aidn_sdpa_desc d;
   int group;
   int head_count;
-  int32_t* status_dev;
+  int32_t* status_dev;   // [0] status word, [1..2] scheduler counters of the persistent prefill kernel
+  int num_sms;
   void* scratch;
   int64_t scratch_bytes;
   int last_path;
@@ -181,8 +182,10 @@ int aidn_sdpa_create(const aidn_sdpa_desc* desc, aidn_sdpa_t* out) {
   h->last_launches = 0;
   h->debug = nullptr;
   h->debug_mode = 0;
-  e = cudaMalloc(&h->status_dev, sizeof(int32_t));
-  if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, sizeof(int32_t));
+  h->num_sms = 0;
+  e = cudaDeviceGetAttribute(&h->num_sms, cudaDevAttrMultiProcessorCount, d.device);
+  if (e == cudaSuccess) e = cudaMalloc(&h->status_dev, 4 * sizeof(int32_t));
+  if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t));
   if (e != cudaSuccess) {
     if (h->status_dev) cudaFree(h->status_dev);
     delete h;
@@ -244,7 +247,7 @@ int aidn_sdpa_poll(aidn_sdpa_t h, void* cu_stream) {
   e = cudaMemcpy(&st, h->status_dev, sizeof(st), cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return fail_cuda(e, "poll: status read");
   if (st != 0) {
-    cudaMemset(h->status_dev, 0, sizeof(int32_t));
+    cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t));
     return fail(AIDN_ETIMEOUT, "poll: a kernel gave up a bounded wait (status word 0x%x)", st);
   }
   return AIDN_OK;
@@ -337,7 +340,7 @@ int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* a, void* cu_stream) {
     }
     e = aidn::launch_decode(p, d.qkv_dtype, chunk, nchunks, ws, stream, &launches);
   } else if (path == AIDN_PATH_PREFILL_SM100) {
-    e = aidn::launch_prefill_sm100(p, d.qkv_dtype, stream, h->debug, h->debug_mode, &why);
+    e = aidn::launch_prefill_sm100(p, d.qkv_dtype, stream, h->status_dev + 1, h->num_sms, h->debug, h->debug_mode, &why);
     launches = 1;
     if (e != cudaSuccess && why[0]) return fail(AIDN_ECUDA, "launch: %s (%s)", why, cudaGetErrorName(e));
   } else {

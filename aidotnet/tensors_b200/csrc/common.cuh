@@ -124,8 +124,8 @@ cudaError_t launch_cast(int kind, const void* src, void* dst, int64_t n, cudaStr
 
 struct PrefillPlan;  // opaque to callers of the sm100 prefill launcher
 bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why);
-cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t stream, float* debug, int debug_mode,
-                                 const char** why);
+cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t stream, int32_t* sched, int num_sms,
+                                 float* debug, int debug_mode, const char** why);
 cudaError_t prefill_sm100_prepare();  // one-time per-process function attribute setup
 
 }  // namespace aidn
