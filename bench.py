@@ -40,6 +40,9 @@ WORKLOADS = {
     "c4": dict(B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
                name="batched_decode_B64_H32_D128_kvlen512-4096_bf16"),
 }
+# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each,
+# see profiles/): prefill C2 measured directly; decode C4 measured on the B=16 quarter and scaled by 4.
+NCU_TRAFFIC_BYTES = {"c2": 651.0e6, "c4": 4 * 527.4e6, "c4q": 527.4e6}
 METRIC = "attention TFLOP/s/GPU & % bf16 peak (prefill); decode HBM GB/s; 1/2/4/8 GPUs"
 
 
@@ -240,13 +243,20 @@ def cpu_reference_time(w, threads, passes=1, sample_batch=None):
     return dt, algorithmic_flops(ws, kv), algorithmic_bytes(ws, kv)
 
 
+def host_threads():
+    """All host cores this process may use (torchrun exports OMP_NUM_THREADS=1, which is not what is wanted here)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
 def run_reference_arm(args, w):
     """`--impl reference`: the reference's CPU attention path (C++ restatement; the .NET original cannot run here)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import sdpa_oracle as O
-    threads = O.max_threads()
+    threads = host_threads()
     sample_batch = 1
     times = []
     for i in range(args.warmup + args.steps):
@@ -338,13 +348,14 @@ def main():
         decode_obj = {"workload": wd["name"], "value": gbs * world, "unit": "GB/s", "ms_per_step": dsecs / dsteps * 1e3,
                       "tokens_per_s": wd["B"] * world / (dsecs / dsteps), "gpu_launches": dl,
                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s",
-                                   "frac": gbs / pk["hbm"], "traffic": None, "peak_source": pk["source"]}}
+                                   "frac": gbs / pk["hbm"], "traffic": NCU_TRAFFIC_BYTES["c4"],
+                                   "traffic_unit": "bytes per launch (ncu, B=16 capture x 4)", "algorithmic": dby,
+                                   "algorithmic_unit": "bytes per launch", "peak_source": pk["source"]}}
         del rd
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        from oracle import sdpa_oracle as O
-        threads = O.max_threads()
+        threads = host_threads()
         dt, cfl, cby = cpu_reference_time(w, threads, 1, 1 if prefill else None)
         cpu = {"value": (cfl / 1e12 if prefill else cby / 1e9) / dt, "unit": "TFLOP/s" if prefill else "GB/s",
                "cores": threads, "kind": "port",
@@ -362,7 +373,9 @@ def main():
             "per_gpu": per_gpu, "pct_of_measured_bf16_peak": (100.0 * per_gpu / pk["bf16"]) if prefill else None,
             "tokens_per_s": w["B"] * w["Sq"] * world / per_step,
             "roofline": {"bound": "tensor" if prefill else "hbm", "achieved": per_gpu, "peak": peak,
-                         "unit": "TFLOP/s" if prefill else "GB/s", "frac": per_gpu / peak, "traffic": None,
+                         "unit": "TFLOP/s" if prefill else "GB/s", "frac": per_gpu / peak,
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "traffic_unit": "bytes per launch (ncu)",
+                         "algorithmic": fl if prefill else by, "algorithmic_unit": "FLOP per launch" if prefill else "bytes per launch",
                          "peak_source": pk["source"] + (" (burst)" if prefill else "")},
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s" if prefill else "GB/s", "h2d_bytes_per_step": h2d,
