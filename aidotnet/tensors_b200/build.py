@@ -72,5 +72,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+HOST_TEST_BIN = os.path.join(BUILD, "backend_tests")
+
+
+def build_host_tests(force: bool = False) -> str:
+    """Compiles the C++ host mirror (csrc/host) together with its test program (tests/cpp) against the library."""
+    root = os.path.dirname(os.path.dirname(HERE))
+    srcs = [os.path.join(root, "tests", "cpp", "backend_tests.cpp"), os.path.join(CSRC, "host", "direct_gpu_backend.cpp")]
+    deps = srcs + [os.path.join(CSRC, "host", "direct_gpu_backend.hpp"), build(force)]
+    if not force and os.path.exists(HOST_TEST_BIN) and os.path.getmtime(HOST_TEST_BIN) >= max(os.path.getmtime(f) for f in deps):
+        return HOST_TEST_BIN
+    cmd = [_nvcc(), "-O2", "-std=c++17", *ARCH, "-ccbin", _host_cxx(), "-o", HOST_TEST_BIN, *srcs, "-L", LIBDIR,
+           "-laidotnet_sdpa_sm100", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"host test build failed:\n{r.stdout}\n{r.stderr}")
+    return HOST_TEST_BIN
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_host_tests(force="--force" in sys.argv))

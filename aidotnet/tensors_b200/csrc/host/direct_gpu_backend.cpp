@@ -1,0 +1,207 @@
+#include "direct_gpu_backend.hpp"
+
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstring>
+
+namespace aidn {
+namespace host {
+
+void CudaBackend::Check(int status, const char* where) {
+  if (status == AIDN_OK) return;
+  const std::string msg = std::string(where) + ": " + aidn_sdpa_last_error();
+  if (status == AIDN_EINVAL) throw std::invalid_argument(msg);
+  throw std::runtime_error(msg);
+}
+
+CudaBackend::CudaBackend(int device, void* stream) : device_(device), stream_(stream) {
+  if (cudaSetDevice(device) != cudaSuccess) throw std::runtime_error("CudaBackend: cannot select the device");
+  if (!aidn_sdpa_device_supported(device))
+    throw std::runtime_error("CudaBackend: the device is not compute capability 10.x; there is no other path");
+}
+
+CudaBackend::~CudaBackend() {
+  for (auto& kv : handles_) aidn_sdpa_destroy(kv.second);
+  if (workspace_) cudaFree(workspace_);
+}
+
+aidn_sdpa_t CudaBackend::Handle(const aidn_sdpa_desc& d) {
+  const Key key{d.qkv_dtype, d.out_dtype, d.head_dim, d.num_q_heads, d.num_kv_heads, d.causal, d.causal_bottom_right,
+                d.mask_kind, d.emit_lse, d.softcap, d.decode_chunk};
+  auto it = handles_.find(key);
+  if (it != handles_.end()) return it->second;
+  aidn_sdpa_t h = nullptr;
+  Check(aidn_sdpa_create(&d, &h), "aidn_sdpa_create");
+  handles_[key] = h;
+  return h;
+}
+
+void CudaBackend::Run(aidn_sdpa_t h, aidn_sdpa_args& a) {
+  const int64_t need = aidn_sdpa_workspace_bytes(h, a.batch, a.seq_q, a.seq_kv);
+  if (need < 0) Check(AIDN_EINVAL, "aidn_sdpa_workspace_bytes");
+  if (need > workspace_bytes_) {   // grown outside of launch, like the reference's pooled scratch buffers
+    if (workspace_) cudaFree(workspace_);
+    workspace_ = nullptr;
+    workspace_bytes_ = 0;
+    if (cudaMalloc(&workspace_, (size_t)need) != cudaSuccess) throw std::runtime_error("CudaBackend: out of device memory");
+    workspace_bytes_ = need;
+  }
+  a.workspace = need > 0 ? workspace_ : nullptr;
+  a.workspace_bytes = need > 0 ? workspace_bytes_ : 0;
+  Check(aidn_sdpa_launch(h, &a, stream_), "aidn_sdpa_launch");
+  launch_count_ += aidn_sdpa_last_launch_count(h);
+  last_path_ = aidn_sdpa_last_path(h);
+}
+
+void CudaBackend::Synchronize() {
+  if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream_)) != cudaSuccess)
+    throw std::runtime_error("CudaBackend: stream synchronisation failed");
+}
+
+static aidn_sdpa_desc base_desc(int device, const GpuBuffer& q, const GpuBuffer& out, int headDim, int heads, int kvHeads) {
+  aidn_sdpa_desc d;
+  std::memset(&d, 0, sizeof(d));
+  d.device = device;
+  d.qkv_dtype = q.Dtype;
+  d.out_dtype = out.Dtype;
+  d.head_dim = headDim;
+  d.num_q_heads = heads;
+  d.num_kv_heads = kvHeads;
+  return d;
+}
+
+void CudaBackend::ScaledDotProductAttention(const GpuBuffer& query, const GpuBuffer& key, const GpuBuffer& value,
+                                            const GpuBuffer& output, const GpuBuffer* attentionWeights,
+                                            const GpuBuffer* mask, int batch, int numHeads, int seqQ, int seqK,
+                                            int headDim, float scale, bool isCausal, float softcap, int numKVHeads) {
+  if (batch <= 0 || numHeads <= 0 || seqQ <= 0 || seqK <= 0 || headDim <= 0)
+    throw std::invalid_argument("Attention dimensions must be positive.");
+  const int kvHeads = numKVHeads > 0 ? numKVHeads : numHeads;
+  if (numHeads % kvHeads != 0) throw std::invalid_argument("numHeads must be an integer multiple of numKVHeads.");
+  const int64_t querySize = (int64_t)batch * numHeads * seqQ * headDim;
+  const int64_t keyValueSize = (int64_t)batch * kvHeads * seqK * headDim;
+  const int64_t weightsSize = (int64_t)batch * numHeads * seqQ * seqK;
+  if (query.Size < querySize || key.Size < keyValueSize || value.Size < keyValueSize || output.Size < querySize)
+    throw std::invalid_argument("Attention tensor buffers are smaller than the requested dimensions.");
+  if (attentionWeights) throw std::runtime_error("the weight-returning call is not served by the sm_100a library");
+  if (mask && mask->Size < (int64_t)seqQ * seqK)
+    throw std::invalid_argument("The attention mask must contain at least seqQ * seqK elements.");
+  aidn_sdpa_desc d = base_desc(device_, query, output, headDim, numHeads, kvHeads);
+  d.causal = isCausal ? 1 : 0;
+  d.causal_bottom_right = 1;                 // CudaAttentionKernels.cs:66: qPos = qi + (seqK - seqQ)
+  d.softcap = softcap;
+  d.mask_kind = mask ? AIDN_MASK_KEEP_F32 : AIDN_MASK_NONE;   // the engine uploads bool masks as floats, 0.0f = masked
+  aidn_sdpa_args a;
+  std::memset(&a, 0, sizeof(a));
+  a.q = query.Handle; a.k = key.Handle; a.v = value.Handle; a.out = output.Handle;
+  a.batch = batch; a.seq_q = seqQ; a.seq_kv = seqK; a.scale = scale;
+  if (mask) {
+    a.mask = mask->Handle;
+    const bool full = mask->Size >= weightsSize;   // maskMode rule, CudaBackend.cs:8355
+    a.mask_stride[0] = full ? (int64_t)numHeads * seqQ * seqK : 0;
+    a.mask_stride[1] = full ? (int64_t)seqQ * seqK : 0;
+    a.mask_stride[2] = seqK;
+    a.mask_stride[3] = 1;
+  }
+  Run(Handle(d), a);
+}
+
+void CudaBackend::FlashAttentionV2(const GpuBuffer& query, const GpuBuffer& key, const GpuBuffer& value,
+                                   const GpuBuffer& output, const GpuBuffer& softmaxStats, int batch, int numHeads,
+                                   int seqQ, int seqK, int headDim, float scale, bool isCausal,
+                                   const GpuBuffer* attentionBias, int biasBatchStride) {
+  if (batch <= 0 || numHeads <= 0 || seqQ <= 0 || seqK <= 0 || headDim <= 0)
+    throw std::invalid_argument("Attention dimensions must be positive.");
+  if (softmaxStats.Size < (int64_t)batch * numHeads * seqQ || softmaxStats.Dtype != AIDN_F32)
+    throw std::invalid_argument("softmaxStats must hold batch*heads*seqQ fp32 values");
+  aidn_sdpa_desc d = base_desc(device_, query, output, headDim, numHeads, numHeads);
+  d.causal = isCausal ? 1 : 0;
+  d.causal_bottom_right = 0;                 // CudaAttentionKernels.cs:197: ki > qi masked (top-left)
+  d.causal_offset = 0;
+  d.emit_lse = 1;
+  d.mask_kind = attentionBias ? AIDN_MASK_ADD_F32 : AIDN_MASK_NONE;
+  aidn_sdpa_args a;
+  std::memset(&a, 0, sizeof(a));
+  a.q = query.Handle; a.k = key.Handle; a.v = value.Handle; a.out = output.Handle;
+  a.lse = static_cast<float*>(softmaxStats.Handle);
+  a.batch = batch; a.seq_q = seqQ; a.seq_kv = seqK; a.scale = scale;
+  if (attentionBias) {
+    a.mask = attentionBias->Handle;
+    a.mask_stride[0] = biasBatchStride;      // 0 broadcasts a [H,Sq,Sk] bias over the batch
+    a.mask_stride[1] = (int64_t)seqQ * seqK;
+    a.mask_stride[2] = seqK;
+    a.mask_stride[3] = 1;
+  }
+  Run(Handle(d), a);
+}
+
+void CudaBackend::FlashAttention(const GpuBuffer& query, const GpuBuffer& key, const GpuBuffer& value,
+                                 const GpuBuffer& output, const GpuBuffer* mask, int batch, int numHeads, int seqLen,
+                                 int headDim, float scale, bool isCausal) {
+  if (mask) {
+    ScaledDotProductAttention(query, key, value, output, nullptr, mask, batch, numHeads, seqLen, seqLen, headDim, scale,
+                              isCausal);
+    return;
+  }
+  GpuBuffer stats;
+  stats.Size = (int64_t)batch * numHeads * seqLen;
+  stats.Dtype = AIDN_F32;
+  if (cudaMalloc(&stats.Handle, (size_t)stats.SizeInBytes()) != cudaSuccess)
+    throw std::runtime_error("CudaBackend: out of device memory");
+  try {
+    FlashAttentionV2(query, key, value, output, stats, batch, numHeads, seqLen, seqLen, headDim, scale, isCausal);
+  } catch (...) {
+    cudaFree(stats.Handle);
+    throw;
+  }
+  Synchronize();
+  cudaFree(stats.Handle);
+}
+
+void CudaBackend::GroupedQueryAttention(const GpuBuffer& query, const GpuBuffer& key, const GpuBuffer& value,
+                                        const GpuBuffer& output, const GpuBuffer* attentionWeights, int batch,
+                                        int numQHeads, int numKVHeads, int seqQ, int seqK, int headDim, float scale,
+                                        bool isCausal) {
+  if (batch <= 0 || numQHeads <= 0 || seqQ <= 0 || seqK <= 0 || headDim <= 0)
+    throw std::invalid_argument("Attention dimensions must be positive.");
+  if (numKVHeads <= 0 || numQHeads % numKVHeads != 0)
+    throw std::invalid_argument("numQHeads must be divisible by numKVHeads");
+  if (attentionWeights) throw std::runtime_error("the weight-returning call is not served by the sm_100a library");
+  aidn_sdpa_desc d = base_desc(device_, query, output, headDim, numQHeads, numKVHeads);
+  d.causal = isCausal ? 1 : 0;
+  d.causal_bottom_right = 0;                 // CudaAttentionKernels.cs:598 (top-left)
+  aidn_sdpa_args a;
+  std::memset(&a, 0, sizeof(a));
+  a.q = query.Handle; a.k = key.Handle; a.v = value.Handle; a.out = output.Handle;
+  a.batch = batch; a.seq_q = seqQ; a.seq_kv = seqK; a.scale = scale;
+  Run(Handle(d), a);
+}
+
+void CudaBackend::FlashDecode(const GpuBuffer& q, const GpuBuffer& k, const GpuBuffer& v, const GpuBuffer& output,
+                              int heads, int kvHeads, int headDim, int seqLen, float scale, int splits) {
+  if (heads <= 0 || kvHeads <= 0 || headDim <= 0 || heads % kvHeads != 0)
+    throw std::invalid_argument("heads must be a positive multiple of kvHeads");
+  if (seqLen <= 0) throw std::invalid_argument("seqLen must be positive");
+  const int64_t kvSize = (int64_t)seqLen * kvHeads * headDim;
+  if (q.Size < (int64_t)heads * headDim || k.Size < kvSize || v.Size < kvSize || output.Size < (int64_t)heads * headDim)
+    throw std::invalid_argument("FlashDecode buffers are smaller than the requested dimensions.");
+  aidn_sdpa_desc d = base_desc(device_, q, output, headDim, heads, kvHeads);
+  if (splits > 0) {
+    const int s = splits < seqLen ? splits : seqLen;
+    int chunk = (seqLen + s - 1) / s;
+    chunk = (chunk + 7) / 8 * 8;
+    d.decode_chunk = chunk < 8 ? 8 : chunk;
+  }
+  aidn_sdpa_args a;
+  std::memset(&a, 0, sizeof(a));
+  a.q = q.Handle; a.k = k.Handle; a.v = v.Handle; a.out = output.Handle;
+  a.batch = 1; a.seq_q = 1; a.seq_kv = seqLen; a.scale = scale;
+  // the cache is stored [seqLen, kvHeads, headDim] (CudaFlashDecodeKernels.cs): (B, H, S) strides in elements
+  a.k_stride[0] = 0; a.k_stride[1] = headDim; a.k_stride[2] = (int64_t)kvHeads * headDim;
+  a.v_stride[0] = 0; a.v_stride[1] = headDim; a.v_stride[2] = (int64_t)kvHeads * headDim;
+  Run(Handle(d), a);
+}
+
+}  // namespace host
+}  // namespace aidn

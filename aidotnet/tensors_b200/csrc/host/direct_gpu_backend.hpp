@@ -1,0 +1,78 @@
+// C++ host-side mirror of the attention slice of the reference's CUDA backend, on top of the C ABI
+// (include/aidn_sdpa.h).  The reference host is C# (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/CudaBackend.cs);
+// this class keeps its method names, argument order, argument meaning and error behaviour so that a port of the
+// reference's backend tests reads the same:
+//
+//   ScaledDotProductAttention  CudaBackend.cs:8322-8379     FlashAttention        CudaBackend.cs:8522-8538
+//   FlashAttentionV2           CudaBackend.cs:8540-8578     GroupedQueryAttention CudaBackend.cs:8721-8759
+//   FlashDecode                CudaBackend.cs:2968-3021
+//
+// ArgumentException / ArgumentOutOfRangeException map to std::invalid_argument, InvalidOperationException to
+// std::runtime_error.  There is no CPU fallback: a failing call throws.
+#pragma once
+
+#include <cstdint>
+#include <map>
+#include <stdexcept>
+#include <string>
+#include <tuple>
+
+#include "../../../../include/aidn_sdpa.h"
+
+namespace aidn {
+namespace host {
+
+// Mirror of IGpuBuffer (Engines/DirectGpu/IDirectGpuBackend.cs:3776-3803): Size is an element count.
+struct GpuBuffer {
+  void* Handle = nullptr;
+  int64_t Size = 0;
+  aidn_dtype Dtype = AIDN_F32;
+  int64_t SizeInBytes() const { return Size * (Dtype == AIDN_F32 ? 4 : 2); }
+};
+
+class CudaBackend {
+ public:
+  // `stream` is the backend's single CUstream / cudaStream_t (CudaBackend.cs:371-375).
+  CudaBackend(int device, void* stream);
+  ~CudaBackend();
+  CudaBackend(const CudaBackend&) = delete;
+  CudaBackend& operator=(const CudaBackend&) = delete;
+
+  void ScaledDotProductAttention(const GpuBuffer& query, const GpuBuffer& key, const GpuBuffer& value,
+                                 const GpuBuffer& output, const GpuBuffer* attentionWeights, const GpuBuffer* mask,
+                                 int batch, int numHeads, int seqQ, int seqK, int headDim, float scale, bool isCausal,
+                                 float softcap = 0.0f, int numKVHeads = 0);
+  void FlashAttention(const GpuBuffer& query, const GpuBuffer& key, const GpuBuffer& value, const GpuBuffer& output,
+                      const GpuBuffer* mask, int batch, int numHeads, int seqLen, int headDim, float scale,
+                      bool isCausal);
+  void FlashAttentionV2(const GpuBuffer& query, const GpuBuffer& key, const GpuBuffer& value, const GpuBuffer& output,
+                        const GpuBuffer& softmaxStats, int batch, int numHeads, int seqQ, int seqK, int headDim,
+                        float scale, bool isCausal, const GpuBuffer* attentionBias = nullptr, int biasBatchStride = 0);
+  void GroupedQueryAttention(const GpuBuffer& query, const GpuBuffer& key, const GpuBuffer& value,
+                             const GpuBuffer& output, const GpuBuffer* attentionWeights, int batch, int numQHeads,
+                             int numKVHeads, int seqQ, int seqK, int headDim, float scale, bool isCausal);
+  // The reference allocates and returns the output buffer; here the caller passes it (heads * headDim elements).
+  void FlashDecode(const GpuBuffer& q, const GpuBuffer& k, const GpuBuffer& v, const GpuBuffer& output, int heads,
+                   int kvHeads, int headDim, int seqLen, float scale, int splits = 0);
+
+  void Synchronize();
+  int64_t LaunchCount() const { return launch_count_; }   // kernels enqueued (GpuLaunchProbe, CudaBackend.cs:5407)
+  int LastPath() const { return last_path_; }             // aidn_path of the last call
+
+ private:
+  using Key = std::tuple<int, int, int, int, int, int, int, int, int, float, int>;
+  aidn_sdpa_t Handle(const aidn_sdpa_desc& d);
+  void Run(aidn_sdpa_t h, aidn_sdpa_args& a);
+  static void Check(int status, const char* where);
+
+  int device_;
+  void* stream_;
+  std::map<Key, aidn_sdpa_t> handles_;
+  void* workspace_ = nullptr;
+  int64_t workspace_bytes_ = 0;
+  int64_t launch_count_ = 0;
+  int last_path_ = 0;
+};
+
+}  // namespace host
+}  // namespace aidn

@@ -1,0 +1,242 @@
+// Port of the reference's CUDA-backend attention tests to the C++ host mirror (csrc/host/direct_gpu_backend.hpp).
+// Each case names the reference test it replays (paths relative to tests/AiDotNet.Tensors.Tests/Engines/) and, as
+// those tests do, recomputes its expectation with an in-test scalar reference.  Exit code 0 = all cases passed.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <functional>
+#include <limits>
+#include <string>
+#include <vector>
+
+#include "../../aidotnet/tensors_b200/csrc/host/direct_gpu_backend.hpp"
+
+using aidn::host::CudaBackend;
+using aidn::host::GpuBuffer;
+
+static int g_failed = 0;
+#define EXPECT(cond, ...)                                  \
+  do {                                                     \
+    if (!(cond)) {                                         \
+      std::printf("  FAILED %s:%d: ", __FILE__, __LINE__); \
+      std::printf(__VA_ARGS__);                            \
+      std::printf("\n");                                   \
+      ++g_failed;                                          \
+    }                                                      \
+  } while (0)
+
+struct DeviceArray {
+  GpuBuffer buf;
+  DeviceArray(const std::vector<float>& host, aidn_dtype dt = AIDN_F32) {
+    buf.Size = (int64_t)host.size();
+    buf.Dtype = dt;
+    cudaMalloc(&buf.Handle, (size_t)buf.SizeInBytes());
+    if (dt == AIDN_F32) {
+      cudaMemcpy(buf.Handle, host.data(), host.size() * 4, cudaMemcpyHostToDevice);
+    } else {
+      std::vector<__nv_bfloat16> h(host.size());
+      for (size_t i = 0; i < host.size(); ++i) h[i] = __float2bfloat16_rn(host[i]);
+      cudaMemcpy(buf.Handle, h.data(), h.size() * 2, cudaMemcpyHostToDevice);
+    }
+  }
+  explicit DeviceArray(int64_t n) {
+    buf.Size = n;
+    cudaMalloc(&buf.Handle, (size_t)n * 4);
+    cudaMemset(buf.Handle, 0xff, (size_t)n * 4);
+  }
+  ~DeviceArray() { cudaFree(buf.Handle); }
+  std::vector<float> download() const {
+    std::vector<float> h((size_t)buf.Size);
+    cudaMemcpy(h.data(), buf.Handle, h.size() * 4, cudaMemcpyDeviceToHost);
+    return h;
+  }
+};
+
+// Scalar reference in double: softmax(q k^T * scale [softcap] [+bias] [mask]) v, with the reference's conventions.
+struct RefOpts {
+  double scale = 1, softcap = 0;
+  bool causal = false;
+  long causal_offset = 0;
+  const std::vector<float>* keep = nullptr;   // [B,H,Sq,Sk] float mask, 0 = masked
+  const std::vector<float>* bias = nullptr;   // [B or 1,H,Sq,Sk]
+  bool bias_has_batch = true;
+};
+static void reference(const std::vector<float>& q, const std::vector<float>& k, const std::vector<float>& v, int B,
+                      int Hq, int Hkv, int Sq, int Sk, int D, const RefOpts& o, std::vector<double>& out,
+                      std::vector<double>& lse, std::function<size_t(int, int, int, int)> kv_index = nullptr) {
+  out.assign((size_t)B * Hq * Sq * D, 0.0);
+  lse.assign((size_t)B * Hq * Sq, 0.0);
+  const int g = Hq / Hkv;
+  if (!kv_index) kv_index = [=](int b, int kh, int j, int d) { return (((size_t)b * Hkv + kh) * Sk + j) * D + d; };
+  std::vector<double> s(Sk);
+  for (int b = 0; b < B; ++b)
+    for (int h = 0; h < Hq; ++h)
+      for (int i = 0; i < Sq; ++i) {
+        double mx = -std::numeric_limits<double>::infinity();
+        for (int j = 0; j < Sk; ++j) {
+          double dot = 0;
+          for (int d = 0; d < D; ++d) dot += (double)q[(((size_t)b * Hq + h) * Sq + i) * D + d] * k[kv_index(b, h / g, j, d)];
+          double val = dot * o.scale;
+          if (o.softcap > 0) val = o.softcap * std::tanh(val / o.softcap);
+          const size_t mi = (((size_t)b * Hq + h) * Sq + i) * Sk + j;
+          if (o.bias) val += (*o.bias)[o.bias_has_batch ? mi : (((size_t)h) * Sq + i) * Sk + j];
+          if (o.keep && (*o.keep)[mi] == 0.0f) val = -std::numeric_limits<double>::infinity();
+          if (o.causal && j > i + o.causal_offset) val = -std::numeric_limits<double>::infinity();
+          s[j] = val;
+          mx = std::max(mx, val);
+        }
+        double sum = 0;
+        if (std::isinf(mx)) {
+          lse[((size_t)b * Hq + h) * Sq + i] = mx;
+          continue;
+        }
+        for (int j = 0; j < Sk; ++j) { s[j] = std::exp(s[j] - mx); sum += s[j]; }
+        lse[((size_t)b * Hq + h) * Sq + i] = mx + std::log(sum);
+        for (int d = 0; d < D; ++d) {
+          double acc = 0;
+          for (int j = 0; j < Sk; ++j) acc += s[j] / sum * v[kv_index(b, h / g, j, d)];
+          out[(((size_t)b * Hq + h) * Sq + i) * D + d] = acc;
+        }
+      }
+}
+
+static std::vector<float> sequence(int n, float a, float b) {
+  std::vector<float> r(n);
+  for (int i = 0; i < n; ++i) r[i] = a + b * i;
+  return r;
+}
+static std::vector<float> uniform(int n, unsigned seed) {   // LCG, U(-1, 1)
+  std::vector<float> r(n);
+  unsigned s = seed * 2654435761u + 12345u;
+  for (int i = 0; i < n; ++i) { s = s * 1664525u + 1013904223u; r[i] = (float)((s >> 8) * (2.0 / 16777216.0) - 1.0); }
+  return r;
+}
+static double max_abs_diff(const std::vector<float>& a, const std::vector<double>& b) {
+  double m = 0;
+  for (size_t i = 0; i < a.size(); ++i) m = std::max(m, std::fabs((double)a[i] - b[i]));
+  return m;
+}
+
+int main() {
+  cudaStream_t stream;
+  cudaSetDevice(0);
+  cudaStreamCreate(&stream);
+  CudaBackend backend(0, stream);
+  std::vector<double> ref, lse;
+
+  {  // DirectGpu/GpuCpuConsistencyTests.cs:895-960  ScaledDotProductAttention_CrossAttention..., tolerance 2e-5
+    std::printf("cross attention (Sq=2, Sk=3, D=3)\n");
+    const int B = 2, H = 2, Sq = 2, Sk = 3, D = 3;
+    auto q = sequence(B * H * Sq * D, -0.2f, 0.03f), k = sequence(B * H * Sk * D, 0.5f, -0.025f), v = sequence(B * H * Sk * D, -0.1f, 0.04f);
+    DeviceArray dq(q), dk(k), dv(v), dout((int64_t)B * H * Sq * D);
+    backend.ScaledDotProductAttention(dq.buf, dk.buf, dv.buf, dout.buf, nullptr, nullptr, B, H, Sq, Sk, D, 0.75f, false);
+    backend.Synchronize();
+    RefOpts o; o.scale = 0.75;
+    reference(q, k, v, B, H, H, Sq, Sk, D, o, ref, lse);
+    EXPECT(max_abs_diff(dout.download(), ref) <= 2e-5, "output mismatch %g", max_abs_diff(dout.download(), ref));
+
+    // :1005-1061 full boolean mask, uploaded as floats (false -> 0.0f)
+    std::printf("full boolean mask\n");
+    std::vector<float> mask = {1,0,1,0,1,1, 1,1,0,1,0,0, 0,1,1,1,1,0, 1,0,0,0,1,0};
+    DeviceArray dm(mask);
+    backend.ScaledDotProductAttention(dq.buf, dk.buf, dv.buf, dout.buf, nullptr, &dm.buf, B, H, Sq, Sk, D, 0.75f, false);
+    backend.Synchronize();
+    o.keep = &mask;
+    reference(q, k, v, B, H, H, Sq, Sk, D, o, ref, lse);
+    EXPECT(max_abs_diff(dout.download(), ref) <= 2e-5, "masked output mismatch %g", max_abs_diff(dout.download(), ref));
+  }
+  {  // :962-1003 ScaledDotProductAttention_LogitSoftcap_MatchesCpu
+    std::printf("logit softcap\n");
+    const int B = 2, H = 2, Sq = 2, Sk = 3, D = 3;
+    auto q = sequence(B * H * Sq * D, -0.9f, 0.17f), k = sequence(B * H * Sk * D, 1.3f, -0.11f), v = sequence(B * H * Sk * D, -0.4f, 0.09f);
+    DeviceArray dq(q), dk(k), dv(v), dout((int64_t)B * H * Sq * D);
+    backend.ScaledDotProductAttention(dq.buf, dk.buf, dv.buf, dout.buf, nullptr, nullptr, B, H, Sq, Sk, D, 1.5f, false, 2.0f);
+    backend.Synchronize();
+    RefOpts o; o.scale = 1.5; o.softcap = 2.0;
+    reference(q, k, v, B, H, H, Sq, Sk, D, o, ref, lse);
+    EXPECT(max_abs_diff(dout.download(), ref) <= 2e-5, "softcap output mismatch %g", max_abs_diff(dout.download(), ref));
+  }
+  {  // DirectGpu/FlashDecodeCudaTests.cs:43-126  MhaDecode / GqaDecode, tolerance 2e-3 + 2e-3|e|
+    std::printf("flash decode shape list\n");
+    const int shapes[][5] = {{4, 4, 64, 40, 8}, {8, 8, 32, 100, 8}, {4, 4, 64, 7, 8}, {4, 4, 64, 64, 1}, {6, 6, 48, 77, 0},
+                             {8, 2, 64, 50, 8}, {8, 1, 64, 40, 8}};
+    for (auto& sh : shapes) {
+      const int heads = sh[0], kvh = sh[1], D = sh[2], L = sh[3], splits = sh[4];
+      auto k = uniform(L * kvh * D, 0xFDE + heads + kvh + L), v = uniform(L * kvh * D, 77 + L), q = uniform(heads * D, 5 + heads);
+      DeviceArray dq(q), dk(k), dv(v), dout((int64_t)heads * D);
+      const float scale = 1.0f / std::sqrt((float)D);
+      backend.FlashDecode(dq.buf, dk.buf, dv.buf, dout.buf, heads, kvh, D, L, scale, splits);
+      backend.Synchronize();
+      RefOpts o; o.scale = scale;
+      reference(q, k, v, 1, heads, kvh, 1, L, D, o, ref, lse,
+                [=](int, int kh, int j, int d) { return ((size_t)j * kvh + kh) * D + d; });
+      auto got = dout.download();
+      bool ok = true;
+      for (size_t i = 0; i < got.size(); ++i) ok = ok && std::fabs(got[i] - ref[i]) <= 2e-3 + 2e-3 * std::fabs(ref[i]);
+      EXPECT(ok, "decode heads=%d kv=%d D=%d L=%d splits=%d", heads, kvh, D, L, splits);
+    }
+  }
+  {  // DirectGpu/RopeGqaOpenClTests.cs:200-279  GroupedQueryAttention vs GqaReference (top-left causal), 1e-4
+    std::printf("grouped query attention\n");
+    const int B = 1, Hq = 6, Hkv = 2, S = 5, D = 8;
+    auto q = uniform(B * Hq * S * D, 23), k = uniform(B * Hkv * S * D, 24), v = uniform(B * Hkv * S * D, 25);
+    DeviceArray dq(q), dk(k), dv(v), dout((int64_t)B * Hq * S * D);
+    for (int causal = 0; causal < 2; ++causal) {
+      backend.GroupedQueryAttention(dq.buf, dk.buf, dv.buf, dout.buf, nullptr, B, Hq, Hkv, S, S, D, 1.0f / std::sqrt(8.0f), causal != 0);
+      backend.Synchronize();
+      RefOpts o; o.scale = 1.0 / std::sqrt(8.0); o.causal = causal != 0;
+      reference(q, k, v, B, Hq, Hkv, S, S, D, o, ref, lse);
+      EXPECT(max_abs_diff(dout.download(), ref) <= 1e-4, "gqa causal=%d mismatch", causal);
+    }
+  }
+  {  // FlashAttentionBiasTests.cs: 3-D (batch-broadcast) and 4-D additive bias, stats = max + log(sum)
+    std::printf("flash attention v2 with bias and statistics\n");
+    const int B = 2, H = 3, S = 9, D = 16;
+    auto q = uniform(B * H * S * D, 31), k = uniform(B * H * S * D, 32), v = uniform(B * H * S * D, 33);
+    auto bias3 = uniform(H * S * S, 34), bias4 = uniform(B * H * S * S, 35);
+    DeviceArray dq(q), dk(k), dv(v), db3(bias3), db4(bias4), dout((int64_t)B * H * S * D), dstats((int64_t)B * H * S);
+    backend.FlashAttentionV2(dq.buf, dk.buf, dv.buf, dout.buf, dstats.buf, B, H, S, S, D, 0.25f, false, &db3.buf, 0);
+    backend.Synchronize();
+    RefOpts o; o.scale = 0.25; o.bias = &bias3; o.bias_has_batch = false;
+    reference(q, k, v, B, H, H, S, S, D, o, ref, lse);
+    EXPECT(max_abs_diff(dout.download(), ref) <= 2e-5 && max_abs_diff(dstats.download(), lse) <= 2e-5, "3-D bias mismatch");
+    backend.FlashAttentionV2(dq.buf, dk.buf, dv.buf, dout.buf, dstats.buf, B, H, S, S, D, 0.25f, true, &db4.buf, H * S * S);
+    backend.Synchronize();
+    o.bias = &bias4; o.bias_has_batch = true; o.causal = true;
+    reference(q, k, v, B, H, H, S, S, D, o, ref, lse);
+    EXPECT(max_abs_diff(dout.download(), ref) <= 2e-5 && max_abs_diff(dstats.download(), lse) <= 2e-5, "4-D bias mismatch");
+  }
+  {  // bf16 prefill on the tcgen05 kernel (half-precision bar of DirectPtxWmmaTests.cs:474-477: 0.012 / LSE 0.02)
+    std::printf("bf16 causal GQA prefill on the tensor-core kernel\n");
+    const int B = 1, Hq = 4, Hkv = 2, S = 320, D = 128;
+    auto round_bf16 = [](std::vector<float> x) { for (auto& f : x) f = __bfloat162float(__float2bfloat16_rn(f * 0.5f)); return x; };
+    auto q = round_bf16(uniform(B * Hq * S * D, 41)), k = round_bf16(uniform(B * Hkv * S * D, 42)), v = round_bf16(uniform(B * Hkv * S * D, 43));
+    DeviceArray dq(q, AIDN_BF16), dk(k, AIDN_BF16), dv(v, AIDN_BF16), dout((int64_t)B * Hq * S * D);
+    backend.ScaledDotProductAttention(dq.buf, dk.buf, dv.buf, dout.buf, nullptr, nullptr, B, Hq, S, S, D, 1.0f / std::sqrt(128.0f), true, 0.0f, Hkv);
+    backend.Synchronize();
+    EXPECT(backend.LastPath() == AIDN_PATH_PREFILL_SM100, "expected the tcgen05 path, got %d", backend.LastPath());
+    RefOpts o; o.scale = 1.0 / std::sqrt(128.0); o.causal = true;
+    reference(q, k, v, B, Hq, Hkv, S, S, D, o, ref, lse);
+    EXPECT(max_abs_diff(dout.download(), ref) <= 0.012, "bf16 prefill mismatch %g", max_abs_diff(dout.download(), ref));
+  }
+  {  // argument errors throw, as ArgumentOutOfRangeException / ArgumentException do in the reference
+    std::printf("argument errors\n");
+    std::vector<float> z(64, 0.f);
+    DeviceArray a(z), out(64);
+    bool threw = false;
+    try { backend.ScaledDotProductAttention(a.buf, a.buf, a.buf, out.buf, nullptr, nullptr, 0, 1, 1, 1, 8, 1.f, false); } catch (const std::invalid_argument&) { threw = true; }
+    EXPECT(threw, "batch = 0 must throw");
+    threw = false;
+    try { backend.ScaledDotProductAttention(a.buf, a.buf, a.buf, out.buf, nullptr, nullptr, 1, 6, 1, 1, 8, 1.f, false, 0.f, 4); } catch (const std::invalid_argument&) { threw = true; }
+    EXPECT(threw, "numHeads %% numKVHeads != 0 must throw");
+    threw = false;
+    try { backend.ScaledDotProductAttention(a.buf, a.buf, a.buf, out.buf, nullptr, nullptr, 4, 4, 4, 4, 8, 1.f, false); } catch (const std::invalid_argument&) { threw = true; }
+    EXPECT(threw, "undersized buffers must throw");
+  }
+  std::printf(g_failed ? "%d case(s) FAILED\n" : "all cases passed (%d failures)\n", g_failed);
+  cudaStreamDestroy(stream);
+  return g_failed ? 1 : 0;
+}
