@@ -72,6 +72,12 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // exp used by the softmax: exact expf for fp32 inputs (1e-5 relative contract), ex2.approx otherwise.
 template <typename T>
 __device__ __forceinline__ float softmax_exp(float x) {

@@ -1,5 +1,6 @@
 // FlashAttention-style prefill forward for sm_100a: TMA + mbarrier pipeline, tcgen05 UMMA with TMEM
-// accumulators, warp-specialised roles, online softmax in registers, persistent CTAs.
+// accumulators, warp-specialised roles, online softmax in registers, persistent CTAs.  Causal / padding masks are
+// arithmetic; a second instantiation adds softcap, additive bias and keep-masks read by the softmax warps.
 //
 // A work item is TWO 128-row query tiles that share one KV head, so every K/V tile fetched into shared
 // memory feeds two score MMAs and two P.V MMAs.  The two tiles are two query heads of the same GQA group at
@@ -134,7 +135,9 @@ __device__ __forceinline__ Item decode_item(const PrefillParams& pp, int item) {
   return it;
 }
 
-template <typename T, int HD>
+// MASKED: the softmax warps also apply softcap, an additive bias or a keep-mask read from global memory (one row
+// per thread); the plain variant carries none of that code.
+template <typename T, int HD, bool MASKED>
 __global__ void __launch_bounds__(kThreads, 1)
     sdpa_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -198,7 +201,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  const float sl2 = p.scale * kLog2e;
+  // Plain: scores stay raw and the scale is folded into the exponent (one FMA).  Masked: scores are scaled first
+  // (softcap and bias act on scaled logits), so the exponent only needs log2(e).
+  const float sl2 = MASKED ? kLog2e : p.scale * kLog2e;
+  const float lse_scale = MASKED ? 1.f : p.scale;
 
   if (warp < kSoftmaxWarps) {
     // =================================== softmax / epilogue ===================================
@@ -276,6 +282,74 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
 
         const int64_t col0 = (int64_t)j * kBN;
+        if constexpr (MASKED) {
+          // scale -> softcap -> bias -> keep-mask, the order of the reference (CpuEngine.cs:27807-27816, 29218-29239)
+          const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
+          const int64_t mrow = qrow < p.seq_q ? qrow : p.seq_q - 1;   // rows past the end read a valid row
+          const int64_t mbase = (int64_t)b * p.mask_stride[0] + (int64_t)ti.h * p.mask_stride[1] + mrow * p.mask_stride[2];
+          const int64_t ms3 = p.mask_stride[3];
+          const bool full_tile = col0 + kBN <= p.seq_kv;
+          const int kind = p.mask_kind;
+          if (kind == AIDN_MASK_NONE) {
+#pragma unroll
+            for (int c = 0; c < kBN; ++c) {
+              float val = s[c] * p.scale;
+              if (p.softcap > 0.f) val = p.softcap * tanh_approx(val * inv_cap);
+              s[c] = val;
+            }
+          } else if (kind == AIDN_MASK_KEEP_U8) {
+            const uint8_t* mp = static_cast<const uint8_t*>(p.mask) + mbase + col0 * ms3;
+            const bool vec = ms3 == 1 && full_tile && ((reinterpret_cast<uintptr_t>(mp) & 15) == 0);
+#pragma unroll
+            for (int c0 = 0; c0 < kBN; c0 += 16) {
+              uint32_t w[4];
+              if (vec) {
+                const uint4 u = *reinterpret_cast<const uint4*>(mp + c0);
+                w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+              } else {
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                  w[q4] = 0;
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const int c = c0 + q4 * 4 + e;
+                    const uint32_t byte = (col0 + c < p.seq_kv) ? mp[(int64_t)c * ms3] : 0u;
+                    w[q4] |= (byte != 0 ? 1u : 0u) << (8 * e);
+                  }
+                }
+              }
+#pragma unroll
+              for (int c = 0; c < 16; ++c) {
+                float val = s[c0 + c] * p.scale;
+                if (p.softcap > 0.f) val = p.softcap * tanh_approx(val * inv_cap);
+                if (((w[c >> 2] >> (8 * (c & 3))) & 0xffu) == 0u) val = -INFINITY;
+                s[c0 + c] = val;
+              }
+            }
+          } else {
+            const float* mp = static_cast<const float*>(p.mask) + mbase + col0 * ms3;
+            const bool vec = ms3 == 1 && full_tile && ((reinterpret_cast<uintptr_t>(mp) & 15) == 0);
+#pragma unroll
+            for (int c0 = 0; c0 < kBN; c0 += 4) {
+              float mv[4];
+              if (vec) {
+                const float4 u = *reinterpret_cast<const float4*>(mp + c0);
+                mv[0] = u.x; mv[1] = u.y; mv[2] = u.z; mv[3] = u.w;
+              } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) mv[e] = (col0 + c0 + e < p.seq_kv) ? mp[(int64_t)(c0 + e) * ms3] : 0.f;
+              }
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                float val = s[c0 + e] * p.scale;
+                if (p.softcap > 0.f) val = p.softcap * tanh_approx(val * inv_cap);
+                if (kind == AIDN_MASK_ADD_F32) val += mv[e];
+                else if (mv[e] == 0.0f) val = -INFINITY;
+                s[c0 + e] = val;
+              }
+            }
+          }
+        }
         if (col0 + kBN - 1 > kmax_row) {
           const int64_t lim = kmax_row - col0;  // columns > lim are masked (lim may be negative)
 #pragma unroll
@@ -412,7 +486,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         if (row_valid && p.lse)
           p.lse[((int64_t)b * p.num_q_heads + ti.h) * p.seq_q + qrow] =
-              (inv > 0.f) ? m * p.scale + logf(l) : -INFINITY;
+              (inv > 0.f) ? m * lse_scale + logf(l) : -INFINITY;
         if (tap) {
           float* dbg = pp.debug + 2 * kBM * kBN + 2 * kBM * HD + (size_t)(i * kBM + row_in_tile) * 2;
           dbg[0] = l;
@@ -633,7 +707,7 @@ bool aligned_bhs(const void* base, const int64_t* stride, int64_t H, int64_t B, 
   return true;
 }
 
-template <typename T, int HD>
+template <typename T, int HD, bool MASKED>
 cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, int num_sms, float* debug,
                      int debug_mode, const char** why) {
   using C = Cfg<HD>;
@@ -671,7 +745,7 @@ cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
   const int64_t total = (int64_t)pp.ranks * pp.items_per_rank;
   if (total <= 0 || total > 0x3fffffff) { *why = "work item count out of range"; return cudaErrorInvalidValue; }
   pp.total_items = (int)total;
-  auto kern = sdpa_prefill_sm100_kernel<T, HD>;
+  auto kern = sdpa_prefill_sm100_kernel<T, HD, MASKED>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) { *why = "cannot raise the dynamic shared memory limit"; return e; }
   const unsigned grid = (unsigned)(total < num_sms ? total : num_sms);
@@ -684,8 +758,6 @@ cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
 bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why) {
   if (dtype != AIDN_BF16 && dtype != AIDN_F16) { *why = "tcgen05 prefill takes fp16 or bf16 inputs"; return false; }
   if (p.head_dim != 64 && p.head_dim != 128) { *why = "tcgen05 prefill takes head_dim 64 or 128"; return false; }
-  if (p.mask_kind != AIDN_MASK_NONE) { *why = "tcgen05 prefill takes no explicit mask (causal and kv_len only)"; return false; }
-  if (p.softcap > 0.f) { *why = "tcgen05 prefill has no softcap"; return false; }
   if (!aligned_bhs(p.q, p.qs, p.num_q_heads, p.batch, 2, 16) || !aligned_bhs(p.k, p.ks, p.num_kv_heads, p.batch, 2, 16) ||
       !aligned_bhs(p.v, p.vs, p.num_kv_heads, p.batch, 2, 16)) {
     *why = "Q/K/V base must be 16-byte aligned and strides multiples of 8 elements for TMA";
@@ -699,14 +771,22 @@ bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why) {
   return true;
 }
 
+template <typename T, int HD>
+cudaError_t launch_m(const SdpaParams& p, cudaStream_t stream, int32_t* sched, int num_sms, float* debug, int debug_mode,
+                     const char** why) {
+  if (p.mask_kind != AIDN_MASK_NONE || p.softcap > 0.f)
+    return launch_t<T, HD, true>(p, stream, sched, num_sms, debug, debug_mode, why);
+  return launch_t<T, HD, false>(p, stream, sched, num_sms, debug, debug_mode, why);
+}
+
 cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t stream, int32_t* sched, int num_sms,
                                  float* debug, int debug_mode, const char** why) {
   if (dtype == AIDN_BF16) {
-    if (p.head_dim == 128) return launch_t<__nv_bfloat16, 128>(p, stream, sched, num_sms, debug, debug_mode, why);
-    return launch_t<__nv_bfloat16, 64>(p, stream, sched, num_sms, debug, debug_mode, why);
+    if (p.head_dim == 128) return launch_m<__nv_bfloat16, 128>(p, stream, sched, num_sms, debug, debug_mode, why);
+    return launch_m<__nv_bfloat16, 64>(p, stream, sched, num_sms, debug, debug_mode, why);
   }
-  if (p.head_dim == 128) return launch_t<__half, 128>(p, stream, sched, num_sms, debug, debug_mode, why);
-  return launch_t<__half, 64>(p, stream, sched, num_sms, debug, debug_mode, why);
+  if (p.head_dim == 128) return launch_m<__half, 128>(p, stream, sched, num_sms, debug, debug_mode, why);
+  return launch_m<__half, 64>(p, stream, sched, num_sms, debug, debug_mode, why);
 }
 
 }  // namespace aidn

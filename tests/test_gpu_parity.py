@@ -254,6 +254,66 @@ def test_prefill_sm100_head_shard_matches_full():
     assert torch.equal(out, full)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("kind", ["keep_u8", "keep_f32", "bias", "bias_causal_lse", "softcap", "softcap_bias"])
+@pytest.mark.parametrize("shape", [(2, 4, 2, 256, 384, 128), (1, 3, 3, 200, 333, 64), (2, 2, 1, 130, 129, 128)])
+def test_prefill_sm100_masks_bias_softcap(dtype, kind, shape):
+    """Explicit masks on the tensor-core kernel: bool / float keep-masks with broadcast axes, additive bias
+    (3-D batch-broadcast and 4-D) with top-left causal and LSE, logit softcap; aligned and ragged key counts."""
+    B, Hq, Hkv, Sq, Sk, D = shape
+    q, qf = gen((B, Hq, Sq, D), dtype, 91)
+    k, kf = gen((B, Hkv, Sk, D), dtype, 92)
+    v, vf = gen((B, Hkv, Sk, D), dtype, 93)
+    rng = np.random.default_rng(17)
+    kw_gpu, kw_ref = {}, {}
+    if kind == "keep_u8":
+        m = (rng.random((B, 1, Sq, Sk)) > 0.4).astype(np.uint8)       # broadcast over heads
+        m[0, 0, 5, :] = 0                                              # a fully masked row
+        kw_gpu = dict(mask=_t(m, torch.uint8), mask_kind=N.MASK_KEEP_U8)
+        kw_ref = dict(mask=m, mask_kind=O.MASK_KEEP_U8)
+    elif kind == "keep_f32":
+        m = (rng.random((1, Hq, Sq, Sk)) > 0.5).astype(np.float32)    # broadcast over batch
+        kw_gpu = dict(mask=_t(m), mask_kind=N.MASK_KEEP_F32)
+        kw_ref = dict(mask=m, mask_kind=O.MASK_KEEP_F32)
+    elif kind == "bias":
+        m = rng.standard_normal((1, Hq, Sq, Sk)).astype(np.float32)   # [H,Sq,Sk] bias broadcast over batch
+        kw_gpu = dict(mask=_t(m), mask_kind=N.MASK_ADD_F32)
+        kw_ref = dict(mask=m, mask_kind=O.MASK_ADD_F32)
+    elif kind == "bias_causal_lse":
+        m = rng.standard_normal((B, Hq, Sq, Sk)).astype(np.float32)
+        kw_gpu = dict(mask=_t(m), mask_kind=N.MASK_ADD_F32, causal=True, bottom_right=False)
+        kw_ref = dict(mask=m, mask_kind=O.MASK_ADD_F32, causal=True, causal_offset=0)
+    elif kind == "softcap":
+        kw_gpu = dict(softcap=1.5, causal=True)
+        kw_ref = dict(softcap=1.5, causal=True)
+    else:
+        m = rng.standard_normal((B, Hq, Sq, Sk)).astype(np.float32)
+        kw_gpu = dict(softcap=2.0, mask=_t(m), mask_kind=N.MASK_ADD_F32)
+        kw_ref = dict(softcap=2.0, mask=m, mask_kind=O.MASK_ADD_F32)
+    out, lse, info = run_gpu(q, k, v, dtype=dtype, want_lse=True, path=N.PATH_PREFILL_SM100, **kw_gpu)
+    assert info["path"] == N.PATH_PREFILL_SM100
+    ref, rlse, _ = O.sdpa(qf, kf, vf, want_lse=True, **kw_ref)
+    compare(out, ref, dtype, f"masked prefill {kind} {shape}")
+    compare_lse(lse, rlse, dtype)
+
+
+def test_prefill_sm100_bias_at_scale_matches_generic_kernel():
+    """FlashAttention-style call with a full 4-D bias at B2 H8 S1024 D128: tensor-core kernel vs the fp32-arithmetic
+    generic kernel (the oracle at this size is covered above on smaller shapes)."""
+    B, H, S, D = 2, 8, 1024, 128
+    q, _ = gen((B, H, S, D), "bf16", 95)
+    k, _ = gen((B, H, S, D), "bf16", 96)
+    v, _ = gen((B, H, S, D), "bf16", 97)
+    bias = torch.randn((B, H, S, S), device="cuda", generator=torch.Generator(device="cuda").manual_seed(5))
+    a, la, ia = run_gpu(q, k, v, dtype="bf16", mask=bias, mask_kind=N.MASK_ADD_F32, causal=True, bottom_right=False,
+                        want_lse=True)
+    b_, lb, ib = run_gpu(q, k, v, dtype="bf16", mask=bias, mask_kind=N.MASK_ADD_F32, causal=True, bottom_right=False,
+                         want_lse=True, path=N.PATH_GENERIC)
+    assert ia["path"] == N.PATH_PREFILL_SM100 and ib["path"] == N.PATH_GENERIC
+    assert float((a - b_).abs().max()) <= 2e-2 and float((a - b_).abs().mean()) <= 2e-3
+    assert float((la - lb).abs().max()) <= 2e-2
+
+
 def test_config2_llama_prefill_full_size():
     """BASELINE config 2: B4 H32 S2048 D128 causal bf16 -> fp32; full tensor against the oracle."""
     B, H, S, D = 4, 32, 2048, 128
