@@ -549,7 +549,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == kMmaWarp) {
     // ========================================== UMMA issuer ==========================================
-    if (lane == 0) {
+    // The whole warp runs this role in lockstep and only the tcgen05 instructions themselves are issued by one
+    // elected lane: descriptors and addresses then stay warp-uniform (uniform registers), which a branch on
+    // lane == 0 around the role would prevent - every UMMA would first move its operands lane -> uniform.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_qk = make_idesc(kBM, kBN, kBf16, false);
       constexpr uint32_t idesc_pv = make_idesc(kBM, HD, kBf16, true);
       bool alive = true;
@@ -562,7 +566,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int slot = seq & 1;
           if (!mbar_wait(bar_sched_full + 8 * slot, (uint32_t)((seq >> 1) & 1), abort_flag)) break;
           item = sched_item[slot];
-          mbar_arrive(bar_sched_empty + 8 * slot);
+          __syncwarp();
+          if (leader) mbar_arrive(bar_sched_empty + 8 * slot);
         }
         if (item >= pp.total_items) break;
         const Item it = decode_item(pp, item);
@@ -573,26 +578,29 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (!mbar_wait(bar_kv_full + 8 * s, (t / C::kStages) & 1u, abort_flag)) alive = false;
           return kv_smem + s * C::kTileBytes;
         };
-        auto kv_release = [&](uint32_t t) { tc_commit(bar_kv_empty + 8 * kv_slot(t)); };
+        auto kv_release = [&](uint32_t t) { if (leader) tc_commit(bar_kv_empty + 8 * kv_slot(t)); };
         auto issue_qk = [&](int i, uint32_t kaddr, bool last_for_item) {
           const uint32_t qaddr = q_smem + i * C::kTileBytes;
           const uint32_t d = tmem_base + (uint32_t)(i * kBN);
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk) {
             const uint32_t off = (uint32_t)((kk >> 2) * C::kHalfBytes + (kk & 3) * 32);
-            mma_ss(d, make_smem_desc(qaddr + off, 16, 1024), make_smem_desc(kaddr + off, 16, 1024), idesc_qk,
-                   kk > 0 ? 1u : 0u);
+            const uint64_t ad = make_smem_desc(qaddr + off, 16, 1024), bd = make_smem_desc(kaddr + off, 16, 1024);
+            if (leader) mma_ss(d, ad, bd, idesc_qk, kk > 0 ? 1u : 0u);
           }
-          tc_commit(bar_s_full + 8 * i);
-          if (last_for_item) tc_commit(bar_q_empty + 8 * i);   // the Q tile may be overwritten by the next item
+          if (leader) {
+            tc_commit(bar_s_full + 8 * i);
+            if (last_for_item) tc_commit(bar_q_empty + 8 * i);   // the Q tile may be overwritten by the next item
+          }
         };
         auto issue_pv = [&](int i, uint32_t vaddr, bool accumulate) {
           const uint32_t d = tmem_base + (uint32_t)(C::kOCol + i * HD);
           const uint32_t a = tmem_base + (uint32_t)(i * kBN);
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk)
-            mma_ts(d, a + (uint32_t)(kk * 8), make_smem_desc(vaddr + (uint32_t)(kk * 2048), C::kHalfBytes, 1024),
-                   idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < kBN / 16; ++kk) {
+            const uint64_t bd = make_smem_desc(vaddr + (uint32_t)(kk * 2048), C::kHalfBytes, 1024);
+            if (leader) mma_ts(d, a + (uint32_t)(kk * 8), bd, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
+          }
         };
 
         // S_i(0) = Q_i K_0^T
@@ -620,7 +628,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             tc_fence_after();
             issue_pv(i, vaddr, j > 0);
             if (j + 1 < it.tile[i].n) issue_qk(i, knext, j + 2 == it.tile[i].n);
-            else tc_commit(bar_o_full + 8 * i);
+            else if (leader) tc_commit(bar_o_full + 8 * i);
           }
           if (alive) {
             kv_release(t0 + 2 * j + 1);
