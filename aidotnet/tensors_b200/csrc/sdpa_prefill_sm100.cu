@@ -504,7 +504,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp == kProducerWarp) {
     // ==================================== TMA producer + scheduler ====================================
-    if (lane == 0) {
+    // warp-uniform like the UMMA issuer: one elected lane issues the TMA loads and barrier operations
+    {
+      const bool leader = elect_one();
       bool alive = true;
       uint32_t t_load = 0;          // K/V tiles loaded so far (ring position)
       uint32_t q_uses[2] = {0, 0};  // loads of each Q tile so far
@@ -512,15 +514,19 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int seq = 0; alive; ++seq) {
         const int slot = seq & 1;
         if (!mbar_wait(bar_sched_empty + 8 * slot, (uint32_t)(((seq >> 1) & 1) ^ 1), abort_flag)) break;
-        sched_item[slot] = item;
-        mbar_arrive(bar_sched_full + 8 * slot);
+        if (leader) {
+          sched_item[slot] = item;
+          mbar_arrive(bar_sched_full + 8 * slot);
+        }
         if (item >= pp.total_items) break;
         const Item it = decode_item(pp, item);
         auto load_tile = [&](const CUtensorMap* tm, uint32_t dst, uint32_t bar, int row, int head) {
-          mbar_expect_tx(bar, (uint32_t)C::kTileBytes);
+          if (leader) {
+            mbar_expect_tx(bar, (uint32_t)C::kTileBytes);
 #pragma unroll
-          for (int hf = 0; hf < C::kHalves; ++hf)
-            tma_load_4d(dst + hf * C::kHalfBytes, tm, bar, hf * 64, row, head, it.b);
+            for (int hf = 0; hf < C::kHalves; ++hf)
+              tma_load_4d(dst + hf * C::kHalfBytes, tm, bar, hf * 64, row, head, it.b);
+          }
         };
         auto load_q = [&](int i) {
           if (it.tile[i].n == 0) return;
@@ -544,7 +550,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (alive && j + 1 < it.n_max) load_kv(&tm_k, j + 1);
           }
         }
-        item = atomicAdd(pp.sched, 1) + (int)gridDim.x;
+        {
+          int next = 0;
+          if (leader) next = atomicAdd(pp.sched, 1) + (int)gridDim.x;
+          item = __shfl_sync(0xffffffffu, next, 0);   // elect.sync picks the lowest lane of the full warp
+        }
       }
     }
   } else if (warp == kMmaWarp) {
