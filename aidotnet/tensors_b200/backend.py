@@ -5,7 +5,7 @@ Method names, argument order, argument meaning and error behaviour follow
 
     ScaledDotProductAttention  :8322-8379      FlashAttention      :8522-8538
     FlashAttentionV2           :8540-8578      GroupedQueryAttention :8721-8759
-    FlashDecode                :2968-3021
+    FlashDecode                :2968-3021      PagedAttentionDecode/Prefill{,Gqa} :2845-2966
 
 and the interface they implement (``Engines/DirectGpu/IDirectGpuBackend.cs:1421-1503``).  Buffers are
 ``GpuBuffer`` objects (the mirror of ``IGpuBuffer``, ``IDirectGpuBackend.cs:3776-3803``): a device
@@ -101,6 +101,8 @@ class CudaBackend:
         key = tuple(sorted(kw.items()))
         h = self._handles.get(key)
         if h is None:
+            if len(self._handles) >= 128:  # e.g. one handle per startPos of a long chunked prefill: drop the oldest
+                self._handles.pop(next(iter(self._handles))).close()
             h = N.Handle(device=self.device, path=self._path, decode_chunk=self._decode_chunk, **kw)
             self._handles[key] = h
         return h
@@ -118,13 +120,16 @@ class CudaBackend:
             raise ValueError("Attention dimensions must be positive.")  # ArgumentOutOfRangeException in the reference
 
     def _run(self, h: N.Handle, *, query, key, value, output, batch, seqQ, seqK, scale, lse=None, mask=None,
-             mask_stride=(0, 0, 0, 0), kv_len=None, k_stride=None, v_stride=None):
+             mask_stride=(0, 0, 0, 0), kv_len=None, q_stride=None, k_stride=None, v_stride=None, o_stride=None,
+             block_table=None, block_table_stride=0, block_size=0, num_blocks=0):
         ws, ws_bytes = self._workspace(h.workspace_bytes(batch, seqQ, seqK))
         h.launch(q=query.Handle, k=key.Handle, v=value.Handle, out=output.Handle, batch=batch, seq_q=seqQ, seq_kv=seqK,
                  stream=self.stream.cuda_stream, lse=lse.Handle if lse is not None else None,
                  mask=mask.Handle if mask is not None else None, mask_stride=mask_stride,
-                 kv_len=kv_len.Handle if kv_len is not None else None, k_stride=k_stride, v_stride=v_stride,
-                 scale=scale, workspace=ws, workspace_bytes=ws_bytes)
+                 kv_len=kv_len.Handle if kv_len is not None else None, q_stride=q_stride, k_stride=k_stride,
+                 v_stride=v_stride, o_stride=o_stride, scale=scale, workspace=ws, workspace_bytes=ws_bytes,
+                 block_table=block_table.Handle if block_table is not None else None,
+                 block_table_stride=block_table_stride, block_size=block_size, num_blocks=num_blocks)
         self.launch_count += h.last_launch_count
         self.last_path = h.last_path
 
@@ -234,6 +239,99 @@ class CudaBackend:
         self._run(h, query=q, key=k, value=v, output=out, batch=1, seqQ=1, seqK=seqLen, scale=float(scale),
                   k_stride=stride, v_stride=stride)
         return out
+
+    # -- paged K/V (IDirectGpuBackend.cs:3619-3632) ---------------------------------------------------------
+    MaxHeadDim = 256  # GpuKernelGuards.MaxHeadDim
+
+    def _paged_guards(self, op, q, kcache, vcache, blockTable, heads, kvHeads, headDim, blockSize, keyLen, qRows):
+        """``GpuKernelGuards.Attention`` / ``Gqa`` / ``PagedAttentionBuffers`` (``GpuKernelGuards.cs:15-35, 83-99``)."""
+        if heads <= 0:
+            raise ValueError(f"{op}: heads must be > 0 (got {heads}).")
+        if headDim <= 0 or headDim > self.MaxHeadDim:
+            raise ValueError(f"{op}: headDim must be in [1, {self.MaxHeadDim}] (got {headDim}).")
+        if blockSize <= 0:
+            raise ValueError(f"{op}: blockSize must be > 0 (got {blockSize}).")
+        if qRows <= 0 or keyLen <= 0:
+            raise ValueError(f"{op}: sequence/query count must be > 0.")
+        if kvHeads <= 0 or kvHeads > heads or heads % kvHeads != 0:
+            raise ValueError(f"{op}: kvHeads must satisfy 1 <= kvHeads <= heads and heads % kvHeads == 0 "
+                             f"(heads={heads}, kvHeads={kvHeads}).")
+        if q.Size < qRows * heads * headDim:
+            raise ValueError(f"{op}: q holds fewer than {qRows * heads * headDim} elements.")
+        if blockTable.Size < (keyLen + blockSize - 1) // blockSize:
+            raise ValueError(f"{op}: blockTable holds fewer than {(keyLen + blockSize - 1) // blockSize} entries.")
+        if blockTable.dtype != torch.int32:
+            raise ValueError(f"{op}: blockTable must be an int32 buffer.")
+        if kcache is None or vcache is None:
+            raise ValueError(f"{op}: K/V pools must not be null.")
+        if kcache.Size <= 0 or kcache.Size != vcache.Size:
+            raise ValueError(f"{op}: kcache/vcache must be equal-sized, non-empty K/V pools.")
+        perBlock = blockSize * kvHeads * headDim
+        if kcache.Size % perBlock != 0:
+            raise ValueError(f"{op}: K/V pool size {kcache.Size} is not a whole number of blocks.")
+        return kcache.Size // perBlock
+
+    def _paged(self, op, q, kcache, vcache, blockTable, heads, kvHeads, headDim, blockSize, numQueries, keyLen,
+               startPos, scale, batch=1, seqLens=None, tableStride=0):
+        numBlocks = self._paged_guards(op, q, kcache, vcache, blockTable, heads, kvHeads, headDim, blockSize, keyLen,
+                                       numQueries * batch)
+        out = self.AllocateBuffer(batch * numQueries * heads * headDim,
+                                  torch.float32 if q.dtype == torch.float32 else q.dtype)
+        causal = numQueries > 1
+        h = self._handle(qkv_dtype=_DTYPE[q.dtype], out_dtype=_DTYPE[out.dtype], head_dim=headDim, num_q_heads=heads,
+                         num_kv_heads=kvHeads, causal=causal, causal_bottom_right=False, causal_offset=int(startPos))
+        # q / out are [batch, numQueries, heads, headDim]: (B, H, S) strides of that storage
+        qo = (numQueries * heads * headDim, headDim, heads * headDim)
+        self._run(h, query=q, key=kcache, value=vcache, output=out, batch=batch, seqQ=numQueries, seqK=keyLen,
+                  scale=float(scale), kv_len=seqLens, q_stride=qo, o_stride=qo, block_table=blockTable,
+                  block_table_stride=tableStride, block_size=blockSize, num_blocks=numBlocks)
+        return out
+
+    def PagedAttentionDecode(self, q: GpuBuffer, kcache: GpuBuffer, vcache: GpuBuffer, blockTable: GpuBuffer,
+                             heads: int, headDim: int, blockSize: int, seqLen: int, scale: float) -> GpuBuffer:
+        """out[h] = softmax(scale * q[h] . K[., h]) V[., h] over a pool [MaxBlocks, blockSize, heads, headDim] read
+        through ``blockTable`` (``CudaBackend.cs:2845-2870``).  Returns a new [heads * headDim] buffer."""
+        return self._paged("PagedAttentionDecode", q, kcache, vcache, blockTable, heads, heads, headDim, blockSize, 1,
+                           seqLen, 0, scale)
+
+    def PagedAttentionDecodeGqa(self, q: GpuBuffer, kcache: GpuBuffer, vcache: GpuBuffer, blockTable: GpuBuffer,
+                                heads: int, kvHeads: int, headDim: int, blockSize: int, seqLen: int,
+                                scale: float) -> GpuBuffer:
+        """Grouped-query variant: the pool is [MaxBlocks, blockSize, kvHeads, headDim] (``CudaBackend.cs:2905-2933``)."""
+        return self._paged("PagedAttentionDecodeGqa", q, kcache, vcache, blockTable, heads, kvHeads, headDim, blockSize,
+                           1, seqLen, 0, scale)
+
+    def PagedAttentionPrefill(self, q: GpuBuffer, kcache: GpuBuffer, vcache: GpuBuffer, blockTable: GpuBuffer,
+                              heads: int, headDim: int, blockSize: int, numQueries: int, startPos: int,
+                              scale: float) -> GpuBuffer:
+        """Causal multi-query paged attention: query qi (q is [numQueries, heads, headDim]) attends to keys
+        0..startPos+qi (``CudaBackend.cs:2875-2903``)."""
+        if startPos < 0:
+            raise ValueError("startPos must be >= 0")
+        return self._paged("PagedAttentionPrefill", q, kcache, vcache, blockTable, heads, heads, headDim, blockSize,
+                           numQueries, startPos + numQueries, startPos, scale)
+
+    def PagedAttentionPrefillGqa(self, q: GpuBuffer, kcache: GpuBuffer, vcache: GpuBuffer, blockTable: GpuBuffer,
+                                 heads: int, kvHeads: int, headDim: int, blockSize: int, numQueries: int, startPos: int,
+                                 scale: float) -> GpuBuffer:
+        """Grouped-query variant of ``PagedAttentionPrefill`` (``CudaBackend.cs:2935-2966``)."""
+        if startPos < 0:
+            raise ValueError("startPos must be >= 0")
+        return self._paged("PagedAttentionPrefillGqa", q, kcache, vcache, blockTable, heads, kvHeads, headDim,
+                           blockSize, numQueries, startPos + numQueries, startPos, scale)
+
+    def PagedAttentionDecodeBatched(self, q: GpuBuffer, kcache: GpuBuffer, vcache: GpuBuffer, blockTables: GpuBuffer,
+                                    seqLens: GpuBuffer, batch: int, heads: int, kvHeads: int, headDim: int,
+                                    blockSize: int, maxSeqLen: int, blocksPerSeq: int, scale: float) -> GpuBuffer:
+        """Extension with no reference counterpart (its paged calls take one sequence): one launch decodes ``batch``
+        sequences that share a pool.  ``q`` is [batch, heads, headDim], ``blockTables`` int32 [batch, blocksPerSeq],
+        ``seqLens`` int32 [batch] (each <= maxSeqLen <= blocksPerSeq * blockSize)."""
+        if batch <= 0 or blocksPerSeq * blockSize < maxSeqLen:
+            raise ValueError("PagedAttentionDecodeBatched: batch must be > 0 and blocksPerSeq * blockSize >= maxSeqLen")
+        if blockTables.Size < batch * blocksPerSeq or seqLens.Size < batch or seqLens.dtype != torch.int32:
+            raise ValueError("PagedAttentionDecodeBatched: blockTables / seqLens are too small or not int32")
+        return self._paged("PagedAttentionDecodeBatched", q, kcache, vcache, blockTables, heads, kvHeads, headDim,
+                           blockSize, 1, maxSeqLen, 0, scale, batch=batch, seqLens=seqLens, tableStride=blocksPerSeq)
 
     def Dispose(self) -> None:
         for h in self._handles.values():

@@ -234,7 +234,7 @@ int aidn_sdpa_last_launch_count(aidn_sdpa_t h) { return h ? h->last_launches : -
 AIDN_API int aidn_sdpa_debug_set(aidn_sdpa_t h, float* buf, int mode) {
   if (!h) return AIDN_EINVAL;
   h->debug = buf;
-  h->debug_mode = buf ? mode : 0;
+  h->debug_mode = (buf || mode == 3) ? mode : 0;
   return AIDN_OK;
 }
 
@@ -248,12 +248,19 @@ int aidn_sdpa_poll(aidn_sdpa_t h, void* cu_stream) {
   if (e != cudaSuccess) return fail_cuda(e, "poll: status read");
   if (st != 0) {
     cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t));
-    return fail(AIDN_ETIMEOUT, "poll: a kernel gave up a bounded wait (status word 0x%x)", st);
+    if (st & aidn::kStatusTimeout)
+      return fail(AIDN_ETIMEOUT, "poll: a kernel gave up a bounded wait (status word 0x%x)", st);
+    return fail(AIDN_EINVAL, "poll: a block-table entry outside [0, num_blocks) was skipped (status word 0x%x)", st);
   }
   return AIDN_OK;
 }
 
-int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* a, void* cu_stream) {
+}  // extern "C"
+
+namespace {
+
+// The launch shared by aidn_sdpa_launch (pg == nullptr) and aidn_sdpa_launch_paged.
+int launch_common(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* pg, void* cu_stream) {
   g_err[0] = 0;
   if (!h || !a) return fail(AIDN_EINVAL, "launch: null argument");
   const aidn_sdpa_desc& d = h->d;
@@ -295,10 +302,31 @@ int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* a, void* cu_stream) {
   const int64_t D = d.head_dim;
   if (all_zero(a->q_stride)) dense_strides(p.qs, d.num_q_heads, a->seq_q, D);
   else std::memcpy(p.qs, a->q_stride, sizeof(p.qs));
-  if (all_zero(a->k_stride)) dense_strides(p.ks, d.num_kv_heads, a->seq_kv, D);
-  else std::memcpy(p.ks, a->k_stride, sizeof(p.ks));
-  if (all_zero(a->v_stride)) dense_strides(p.vs, d.num_kv_heads, a->seq_kv, D);
-  else std::memcpy(p.vs, a->v_stride, sizeof(p.vs));
+  if (pg) {
+    if (!pg->block_table) return fail(AIDN_EINVAL, "launch_paged: null block table");
+    if (pg->block_size <= 0) return fail(AIDN_EINVAL, "launch_paged: block_size must be positive");
+    if (pg->num_blocks < 0 || pg->block_table_stride < 0) return fail(AIDN_EINVAL, "launch_paged: negative num_blocks or stride");
+    if (a->seq_kv > 0x7fffffffll) return fail(AIDN_EINVAL, "launch_paged: seq_kv above 2^31-1");
+    if (a->batch > 1 && pg->block_table_stride * pg->block_size < a->seq_kv && !a->kv_len)
+      return fail(AIDN_EINVAL, "launch_paged: block_table_stride (%lld) holds fewer than seq_kv keys",
+                  (long long)pg->block_table_stride);
+    p.block_table = pg->block_table;
+    p.bt_stride = pg->block_table_stride;
+    p.block_size = pg->block_size;
+    p.block_shift = -1;
+    for (int sft = 0; sft < 31; ++sft)
+      if ((1 << sft) == pg->block_size) p.block_shift = sft;
+    p.num_blocks = pg->num_blocks;
+    const int64_t pool_dense[3] = {0, D, (int64_t)d.num_kv_heads * D};
+    std::memcpy(p.ks, all_zero(a->k_stride) ? pool_dense : a->k_stride, sizeof(p.ks));
+    std::memcpy(p.vs, all_zero(a->v_stride) ? pool_dense : a->v_stride, sizeof(p.vs));
+    p.ks[0] = p.vs[0] = 0;
+  } else {
+    if (all_zero(a->k_stride)) dense_strides(p.ks, d.num_kv_heads, a->seq_kv, D);
+    else std::memcpy(p.ks, a->k_stride, sizeof(p.ks));
+    if (all_zero(a->v_stride)) dense_strides(p.vs, d.num_kv_heads, a->seq_kv, D);
+    else std::memcpy(p.vs, a->v_stride, sizeof(p.vs));
+  }
   if (all_zero(a->o_stride)) dense_strides(p.os, d.num_q_heads, a->seq_q, D);
   else std::memcpy(p.os, a->o_stride, sizeof(p.os));
   for (int i = 0; i < 3; ++i)
@@ -377,6 +405,22 @@ int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* a, void* cu_stream) {
     h->last_launches += 1;
   }
   return AIDN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* a, void* cu_stream) {
+  return launch_common(h, a, nullptr, cu_stream);
+}
+
+int aidn_sdpa_launch_paged(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* paged, void* cu_stream) {
+  if (!paged) {
+    g_err[0] = 0;
+    return fail(AIDN_EINVAL, "launch_paged: null aidn_paged_kv");
+  }
+  return launch_common(h, a, paged, cu_stream);
 }
 
 // Decode for callers that cannot allocate device memory (no handle, no workspace): see include/aidn_sdpa.h.

@@ -16,6 +16,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 
 // Device status word values (bit flags) written by kernels that give up a bounded wait.
 constexpr int kStatusTimeout = 1;
+constexpr int kStatusBadBlock = 2;  // a block-table entry outside [0, num_blocks) was met (the key is skipped)
 
 struct SdpaParams {
   const void* q;
@@ -39,6 +40,14 @@ struct SdpaParams {
   float scale;
   float softcap;
   int32_t* status;  // device word, or null
+  // Paged K/V (null block_table = contiguous): key t of batch entry b lives in row
+  // block_table[b * bt_stride + t / block_size] * block_size + t % block_size of the pool, and that row index
+  // takes the place of the key index in the K/V address (ks[2] / vs[2] = token stride, ks[0] / vs[0] unused).
+  const int32_t* block_table;
+  int64_t bt_stride;
+  int32_t block_size;
+  int32_t block_shift;  // log2(block_size) when it is a power of two, else -1
+  int32_t num_blocks;   // > 0: entries are range-checked against it
 };
 
 template <typename T>
@@ -116,6 +125,19 @@ __device__ __forceinline__ int64_t kv_limit_of(const SdpaParams& p, int b) {
     if (l < lim) lim = l;
   }
   return lim;
+}
+
+// Pool row of key `key` of batch entry b (the key itself without a block table); -1 for an entry outside the pool.
+__device__ __forceinline__ int64_t kv_row_of(const SdpaParams& p, int b, int64_t key) {
+  if (!p.block_table) return key;
+  const uint32_t k32 = (uint32_t)key;
+  const uint32_t blk = p.block_shift >= 0 ? (k32 >> p.block_shift) : (k32 / (uint32_t)p.block_size);
+  const int32_t phys = __ldg(p.block_table + (int64_t)b * p.bt_stride + blk);
+  if (phys < 0 || (p.num_blocks > 0 && phys >= p.num_blocks)) {
+    if (p.status) atomicOr(p.status, kStatusBadBlock);
+    return -1;
+  }
+  return (int64_t)phys * p.block_size + (k32 - blk * (uint32_t)p.block_size);
 }
 
 // Host-side launchers (one per kernel family); each returns the CUDA error of its launch.

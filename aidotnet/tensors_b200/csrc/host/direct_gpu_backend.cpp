@@ -28,7 +28,7 @@ CudaBackend::~CudaBackend() {
 
 aidn_sdpa_t CudaBackend::Handle(const aidn_sdpa_desc& d) {
   const Key key{d.qkv_dtype, d.out_dtype, d.head_dim, d.num_q_heads, d.num_kv_heads, d.causal, d.causal_bottom_right,
-                d.mask_kind, d.emit_lse, d.softcap, d.decode_chunk};
+                d.mask_kind, d.emit_lse, d.softcap, d.decode_chunk, d.causal_offset};
   auto it = handles_.find(key);
   if (it != handles_.end()) return it->second;
   aidn_sdpa_t h = nullptr;
@@ -37,7 +37,7 @@ aidn_sdpa_t CudaBackend::Handle(const aidn_sdpa_desc& d) {
   return h;
 }
 
-void CudaBackend::Run(aidn_sdpa_t h, aidn_sdpa_args& a) {
+void CudaBackend::Run(aidn_sdpa_t h, aidn_sdpa_args& a, const aidn_paged_kv* paged) {
   const int64_t need = aidn_sdpa_workspace_bytes(h, a.batch, a.seq_q, a.seq_kv);
   if (need < 0) Check(AIDN_EINVAL, "aidn_sdpa_workspace_bytes");
   if (need > workspace_bytes_) {   // grown outside of launch, like the reference's pooled scratch buffers
@@ -49,7 +49,8 @@ void CudaBackend::Run(aidn_sdpa_t h, aidn_sdpa_args& a) {
   }
   a.workspace = need > 0 ? workspace_ : nullptr;
   a.workspace_bytes = need > 0 ? workspace_bytes_ : 0;
-  Check(aidn_sdpa_launch(h, &a, stream_), "aidn_sdpa_launch");
+  if (paged) Check(aidn_sdpa_launch_paged(h, &a, paged, stream_), "aidn_sdpa_launch_paged");
+  else Check(aidn_sdpa_launch(h, &a, stream_), "aidn_sdpa_launch");
   launch_count_ += aidn_sdpa_last_launch_count(h);
   last_path_ = aidn_sdpa_last_path(h);
 }
@@ -201,6 +202,75 @@ void CudaBackend::FlashDecode(const GpuBuffer& q, const GpuBuffer& k, const GpuB
   a.k_stride[0] = 0; a.k_stride[1] = headDim; a.k_stride[2] = (int64_t)kvHeads * headDim;
   a.v_stride[0] = 0; a.v_stride[1] = headDim; a.v_stride[2] = (int64_t)kvHeads * headDim;
   Run(Handle(d), a);
+}
+
+// ---- paged K/V ------------------------------------------------------------------------------------------------
+// Guards as GpuKernelGuards.Attention / Gqa / PagedAttentionBuffers (Engines/DirectGpu/GpuKernelGuards.cs:15-35, 83-99).
+void CudaBackend::Paged(const char* op, const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+                        const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int kvHeads, int headDim,
+                        int blockSize, int numQueries, int64_t keyLen, int startPos, float scale) {
+  const std::string o(op);
+  if (heads <= 0) throw std::invalid_argument(o + ": heads must be > 0.");
+  if (headDim <= 0 || headDim > 256) throw std::invalid_argument(o + ": headDim must be in [1, 256].");
+  if (blockSize <= 0) throw std::invalid_argument(o + ": blockSize must be > 0.");
+  if (numQueries <= 0 || keyLen <= 0) throw std::invalid_argument(o + ": sequence/query count must be > 0.");
+  if (kvHeads <= 0 || kvHeads > heads || heads % kvHeads != 0)
+    throw std::invalid_argument(o + ": kvHeads must satisfy 1 <= kvHeads <= heads and heads % kvHeads == 0.");
+  const int64_t qSize = (int64_t)numQueries * heads * headDim;
+  if (q.Size < qSize || output.Size < qSize) throw std::invalid_argument(o + ": q / output are smaller than numQueries*heads*headDim.");
+  if (blockTable.Size < (keyLen + blockSize - 1) / blockSize) throw std::invalid_argument(o + ": blockTable is too short.");
+  if (!kcache.Handle || !vcache.Handle) throw std::invalid_argument(o + ": K/V pools must not be null.");
+  if (kcache.Size <= 0 || kcache.Size != vcache.Size)
+    throw std::invalid_argument(o + ": kcache/vcache must be equal-sized, non-empty K/V pools.");
+  const int64_t perBlock = (int64_t)blockSize * kvHeads * headDim;
+  if (kcache.Size % perBlock != 0) throw std::invalid_argument(o + ": K/V pool size is not a whole number of blocks.");
+  aidn_sdpa_desc d = base_desc(device_, q, output, headDim, heads, kvHeads);
+  d.causal = numQueries > 1 ? 1 : 0;
+  d.causal_bottom_right = 0;
+  d.causal_offset = startPos;    // query qi sees keys 0..startPos+qi (CudaPagedAttentionKernels.cs:67)
+  aidn_sdpa_args a;
+  std::memset(&a, 0, sizeof(a));
+  a.q = q.Handle; a.k = kcache.Handle; a.v = vcache.Handle; a.out = output.Handle;
+  a.batch = 1; a.seq_q = numQueries; a.seq_kv = keyLen; a.scale = scale;
+  // q / output are [numQueries, heads, headDim]: (B, H, S) strides in elements
+  a.q_stride[0] = a.o_stride[0] = qSize;
+  a.q_stride[1] = a.o_stride[1] = headDim;
+  a.q_stride[2] = a.o_stride[2] = (int64_t)heads * headDim;
+  aidn_paged_kv pg;
+  std::memset(&pg, 0, sizeof(pg));
+  pg.block_table = static_cast<const int32_t*>(blockTable.Handle);
+  pg.block_size = blockSize;
+  pg.num_blocks = (int32_t)(kcache.Size / perBlock);
+  Run(Handle(d), a, &pg);
+}
+
+void CudaBackend::PagedAttentionDecode(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+                                       const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int headDim,
+                                       int blockSize, int seqLen, float scale) {
+  Paged("PagedAttentionDecode", q, kcache, vcache, blockTable, output, heads, heads, headDim, blockSize, 1, seqLen, 0, scale);
+}
+
+void CudaBackend::PagedAttentionDecodeGqa(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+                                          const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int kvHeads,
+                                          int headDim, int blockSize, int seqLen, float scale) {
+  Paged("PagedAttentionDecodeGqa", q, kcache, vcache, blockTable, output, heads, kvHeads, headDim, blockSize, 1, seqLen, 0,
+        scale);
+}
+
+void CudaBackend::PagedAttentionPrefill(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+                                        const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int headDim,
+                                        int blockSize, int numQueries, int startPos, float scale) {
+  if (startPos < 0) throw std::invalid_argument("PagedAttentionPrefill: startPos must be >= 0.");
+  Paged("PagedAttentionPrefill", q, kcache, vcache, blockTable, output, heads, heads, headDim, blockSize, numQueries,
+        (int64_t)startPos + numQueries, startPos, scale);
+}
+
+void CudaBackend::PagedAttentionPrefillGqa(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+                                           const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int kvHeads,
+                                           int headDim, int blockSize, int numQueries, int startPos, float scale) {
+  if (startPos < 0) throw std::invalid_argument("PagedAttentionPrefillGqa: startPos must be >= 0.");
+  Paged("PagedAttentionPrefillGqa", q, kcache, vcache, blockTable, output, heads, kvHeads, headDim, blockSize, numQueries,
+        (int64_t)startPos + numQueries, startPos, scale);
 }
 
 }  // namespace host

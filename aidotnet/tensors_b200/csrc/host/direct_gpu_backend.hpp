@@ -5,7 +5,7 @@
 //
 //   ScaledDotProductAttention  CudaBackend.cs:8322-8379     FlashAttention        CudaBackend.cs:8522-8538
 //   FlashAttentionV2           CudaBackend.cs:8540-8578     GroupedQueryAttention CudaBackend.cs:8721-8759
-//   FlashDecode                CudaBackend.cs:2968-3021
+//   FlashDecode                CudaBackend.cs:2968-3021     PagedAttention{Decode,Prefill}{,Gqa} CudaBackend.cs:2845-2966
 //
 // ArgumentException / ArgumentOutOfRangeException map to std::invalid_argument, InvalidOperationException to
 // std::runtime_error.  There is no CPU fallback: a failing call throws.
@@ -55,14 +55,32 @@ class CudaBackend {
   void FlashDecode(const GpuBuffer& q, const GpuBuffer& k, const GpuBuffer& v, const GpuBuffer& output, int heads,
                    int kvHeads, int headDim, int seqLen, float scale, int splits = 0);
 
+  // Paged K/V (IDirectGpuBackend.cs:3619-3632): pools [MaxBlocks, blockSize, kvHeads, headDim], int32 block table,
+  // q / output [numQueries, heads, headDim].  The reference returns a new buffer; here the caller passes `output`.
+  void PagedAttentionDecode(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+                            const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int headDim, int blockSize,
+                            int seqLen, float scale);
+  void PagedAttentionPrefill(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+                             const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int headDim,
+                             int blockSize, int numQueries, int startPos, float scale);
+  void PagedAttentionDecodeGqa(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+                               const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int kvHeads,
+                               int headDim, int blockSize, int seqLen, float scale);
+  void PagedAttentionPrefillGqa(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+                                const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int kvHeads,
+                                int headDim, int blockSize, int numQueries, int startPos, float scale);
+
   void Synchronize();
   int64_t LaunchCount() const { return launch_count_; }   // kernels enqueued (GpuLaunchProbe, CudaBackend.cs:5407)
   int LastPath() const { return last_path_; }             // aidn_path of the last call
 
  private:
-  using Key = std::tuple<int, int, int, int, int, int, int, int, int, float, int>;
+  using Key = std::tuple<int, int, int, int, int, int, int, int, int, float, int, int64_t>;
   aidn_sdpa_t Handle(const aidn_sdpa_desc& d);
-  void Run(aidn_sdpa_t h, aidn_sdpa_args& a);
+  void Run(aidn_sdpa_t h, aidn_sdpa_args& a, const aidn_paged_kv* paged = nullptr);
+  void Paged(const char* op, const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
+             const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int kvHeads, int headDim, int blockSize,
+             int numQueries, int64_t keyLen, int startPos, float scale);
   static void Check(int status, const char* where);
 
   int device_;

@@ -9,6 +9,9 @@
 // Supersedes flash_decode_partial / flash_decode_reduce of the reference
 // (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/CudaFlashDecodeKernels.cs:19-81), which run one
 // thread per (head, split) with a serial, uncoalesced walk over the cache and take a single sequence.
+// The PAGED instantiation reads K/V through a block table and supersedes paged_attention_decode{,_gqa}
+// (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/CudaPagedAttentionKernels.cs:23-55, :97-124), which run
+// one thread per head over the whole sequence.
 //
 // Scratch layout (fp32): acc[B][Hc][nchunks][D] followed by ml[B][Hc][nchunks][2], Hc = heads of the shard.
 #include <mutex>
@@ -74,7 +77,7 @@ __device__ __forceinline__ int64_t decode_len(const SdpaParams& p, int b) {
   return L;
 }
 
-template <typename T, int D, int GT>
+template <typename T, int D, int GT, bool PAGED>
 __global__ void __launch_bounds__(kDecWarps * 32)
     sdpa_decode_partial_kernel(const SdpaParams p, const int chunk, const int nchunks, float* __restrict__ ws,
                                const int direct) {
@@ -122,8 +125,8 @@ __global__ void __launch_bounds__(kDecWarps * 32)
     const uint4 u = *reinterpret_cast<const uint4*>(qp);
     unpack16<T>(u, qf[g]);
   }
-  const T* kbase = static_cast<const T*>(p.k) + b * p.ks[0] + (int64_t)kvh * p.ks[1] + d0;
-  const T* vbase = static_cast<const T*>(p.v) + b * p.vs[0] + (int64_t)kvh * p.vs[1] + d0;
+  const T* kbase = static_cast<const T*>(p.k) + (PAGED ? 0 : b * p.ks[0]) + (int64_t)kvh * p.ks[1] + d0;
+  const T* vbase = static_cast<const T*>(p.v) + (PAGED ? 0 : b * p.vs[0]) + (int64_t)kvh * p.vs[1] + d0;
 
   float m[GT], l[GT], acc[GT][EPL];
 #pragma unroll
@@ -138,17 +141,21 @@ __global__ void __launch_bounds__(kDecWarps * 32)
   for (int64_t kb = start + warp * KPW; kb < end; kb += kDecWarps * KPW) {
     uint4 kv[kUnroll], vv[kUnroll];
     bool ok[kUnroll];
+    int64_t row[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const int64_t key = kb + u * KPI + grp;
       ok[u] = key < end;
-      kv[u] = ok[u] ? ld_stream16(kbase + key * p.ks[2]) : make_uint4(0, 0, 0, 0);
+      row[u] = key;
+      if constexpr (PAGED) {  // one block-table read per key, then the same 16-byte row loads
+        row[u] = ok[u] ? kv_row_of(p, b, key) : -1;
+        ok[u] = row[u] >= 0;
+      }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t key = kb + u * KPI + grp;
-      vv[u] = ok[u] ? ld_stream16(vbase + key * p.vs[2]) : make_uint4(0, 0, 0, 0);
-    }
+    for (int u = 0; u < kUnroll; ++u) kv[u] = ok[u] ? ld_stream16(kbase + row[u] * p.ks[2]) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) vv[u] = ok[u] ? ld_stream16(vbase + row[u] * p.vs[2]) : make_uint4(0, 0, 0, 0);
 
     float s[GT][kUnroll];
 #pragma unroll
@@ -300,7 +307,8 @@ template <typename T, int D, int GT>
 cudaError_t launch_partial(const SdpaParams& p, int chunk, int nchunks, float* ws, int direct, cudaStream_t stream) {
   const int gchunks = (p.group + GT - 1) / GT;
   dim3 grid((unsigned)nchunks, (unsigned)((p.head_count / p.group) * gchunks), (unsigned)p.batch);
-  sdpa_decode_partial_kernel<T, D, GT><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct);
+  if (p.block_table) sdpa_decode_partial_kernel<T, D, GT, true><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct);
+  else sdpa_decode_partial_kernel<T, D, GT, false><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct);
   return cudaGetLastError();
 }
 

@@ -27,6 +27,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaPar
   float* Ks = Qs + kBM * PITCH;           // [kBN][PITCH]
   float* Vs = Ks + kBN * PITCH;           // [kBN][PITCH]
   float* Ps = Vs + kBN * PITCH;           // [kWarps][kRowsPerWarp][kBN]
+  __shared__ int64_t kv_rows[kBN];        // pool rows of the tile's keys (paged K/V only)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.z;
@@ -36,8 +37,9 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaPar
   const int D = p.head_dim;
 
   const T* qb = static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1];
-  const T* kb = static_cast<const T*>(p.k) + b * p.ks[0] + kvh * p.ks[1];
-  const T* vb = static_cast<const T*>(p.v) + b * p.vs[0] + kvh * p.vs[1];
+  const bool paged = p.block_table != nullptr;
+  const T* kb = static_cast<const T*>(p.k) + (paged ? 0 : b * p.ks[0]) + kvh * p.ks[1];
+  const T* vb = static_cast<const T*>(p.v) + (paged ? 0 : b * p.vs[0]) + kvh * p.vs[1];
 
   for (int idx = tid; idx < kBM * DMAX; idx += kWarps * 32) {
     const int r = idx / DMAX, d = idx - r * DMAX;
@@ -65,12 +67,17 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaPar
 
   for (int64_t j0 = 0; j0 < kend; j0 += kBN) {
     __syncthreads();  // previous tile fully consumed (also orders the Q stores before first use)
+    if (paged) {
+      if (tid < kBN) kv_rows[tid] = (j0 + tid < kend) ? kv_row_of(p, b, j0 + tid) : -1;
+      __syncthreads();
+    }
     for (int idx = tid; idx < kBN * DMAX; idx += kWarps * 32) {
       const int j = idx / DMAX, d = idx - j * DMAX;
       const int64_t key = j0 + j;
-      const bool ok = key < p.seq_kv && d < D;
-      Ks[j * PITCH + d] = ok ? to_float<T>(kb[key * p.ks[2] + d]) : 0.f;
-      Vs[j * PITCH + d] = ok ? to_float<T>(vb[key * p.vs[2] + d]) : 0.f;
+      const int64_t row = paged ? kv_rows[j] : key;
+      const bool ok = key < p.seq_kv && d < D && row >= 0;
+      Ks[j * PITCH + d] = ok ? to_float<T>(kb[row * p.ks[2] + d]) : 0.f;
+      Vs[j * PITCH + d] = ok ? to_float<T>(vb[row * p.vs[2] + d]) : 0.f;
     }
     __syncthreads();
 
@@ -94,7 +101,8 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaPar
     for (int r = 0; r < kRowsPerWarp; ++r) {
       const int64_t row = row0 + warp * kRowsPerWarp + r;
       float val = -INFINITY;
-      if (row < p.seq_q && key < p.seq_kv) val = finish_logit(p, s[r] * p.scale, b, h, row, key, kv_limit);
+      if (row < p.seq_q && key < p.seq_kv && !(paged && kv_rows[lane] < 0))
+        val = finish_logit(p, s[r] * p.scale, b, h, row, key, kv_limit);
       float mt = val;
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, o));

@@ -78,7 +78,9 @@ struct PrefillParams {
   int32_t total_items;
   int32_t* sched;          // [0] next-item counter, [1] finished-CTA counter; both zero between launches
   float* debug;            // optional tap
-  int32_t debug_mode;      // 1: values of the first work item of CTA 0; 2: per-item timeline (16 x u64 per item)
+  int32_t debug_mode;      // 1: values of the first work item of CTA 0; 2: per-item timeline (16 x u64 per item);
+                           // 3: the producer withholds the Q tiles, so that the bounded waits run out (test hook)
+  uint64_t wait_budget_ns; // longest single wait before the CTA gives up
 };
 
 struct TileInfo {
@@ -167,6 +169,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kMiscOff + 12);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint64_t wait_ns = pp.wait_budget_ns;
 
   // ---- setup ---------------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
@@ -228,7 +231,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       int item;
       {
         const int slot = seq & 1;
-        bool ok = mbar_wait(bar_sched_full + 8 * slot, (uint32_t)((seq >> 1) & 1), abort_flag);
+        bool ok = mbar_wait(bar_sched_full + 8 * slot, (uint32_t)((seq >> 1) & 1), abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
         item = sched_item[slot];
@@ -261,7 +264,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       float m = -INFINITY, l = 0.f;
 
       for (int j = 0; j < ti.n; ++j) {
-        bool ok = mbar_wait(bar_s_full + 8 * i, s_cnt & 1u, abort_flag);
+        bool ok = mbar_wait(bar_s_full + 8 * i, s_cnt & 1u, abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
         tc_fence_after();
@@ -425,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       {
         const bool have_o = ti.n > 0;
         if (have_o) {
-          bool ok = mbar_wait(bar_o_full + 8 * i, o_cnt & 1u, abort_flag);
+          bool ok = mbar_wait(bar_o_full + 8 * i, o_cnt & 1u, abort_flag, wait_ns);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) { alive = false; break; }
           ++o_cnt;
@@ -513,7 +516,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       int item = blockIdx.x;
       for (int seq = 0; alive; ++seq) {
         const int slot = seq & 1;
-        if (!mbar_wait(bar_sched_empty + 8 * slot, (uint32_t)(((seq >> 1) & 1) ^ 1), abort_flag)) break;
+        if (!mbar_wait(bar_sched_empty + 8 * slot, (uint32_t)(((seq >> 1) & 1) ^ 1), abort_flag, wait_ns)) break;
         if (leader) {
           sched_item[slot] = item;
           mbar_arrive(bar_sched_full + 8 * slot);
@@ -529,15 +532,15 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         };
         auto load_q = [&](int i) {
-          if (it.tile[i].n == 0) return;
-          if (!mbar_wait(bar_q_empty + 8 * i, (q_uses[i] & 1u) ^ 1u, abort_flag)) { alive = false; return; }
+          if (it.tile[i].n == 0 || pp.debug_mode == 3) return;
+          if (!mbar_wait(bar_q_empty + 8 * i, (q_uses[i] & 1u) ^ 1u, abort_flag, wait_ns)) { alive = false; return; }
           load_tile(&tm_q, q_smem + i * C::kTileBytes, bar_q_full + 8 * i, it.tile[i].t * kBM, it.tile[i].h);
           ++q_uses[i];
         };
         auto load_kv = [&](const CUtensorMap* tm, int key_tile) {
           const int s = (int)(t_load % C::kStages);
           const uint32_t phase = (t_load / C::kStages) & 1u;
-          if (!mbar_wait(bar_kv_empty + 8 * s, phase ^ 1u, abort_flag)) { alive = false; return; }
+          if (!mbar_wait(bar_kv_empty + 8 * s, phase ^ 1u, abort_flag, wait_ns)) { alive = false; return; }
           load_tile(tm, kv_smem + s * C::kTileBytes, bar_kv_full + 8 * s, key_tile * kBN, it.kvh);
           ++t_load;
         };
@@ -574,7 +577,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         int item;
         {
           const int slot = seq & 1;
-          if (!mbar_wait(bar_sched_full + 8 * slot, (uint32_t)((seq >> 1) & 1), abort_flag)) break;
+          if (!mbar_wait(bar_sched_full + 8 * slot, (uint32_t)((seq >> 1) & 1), abort_flag, wait_ns)) break;
           item = sched_item[slot];
           __syncwarp();
           if (leader) mbar_arrive(bar_sched_empty + 8 * slot);
@@ -585,7 +588,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         auto kv_slot = [&](uint32_t t) { return (int)(t % C::kStages); };
         auto kv_wait = [&](uint32_t t) {
           const int s = kv_slot(t);
-          if (!mbar_wait(bar_kv_full + 8 * s, (t / C::kStages) & 1u, abort_flag)) alive = false;
+          if (!mbar_wait(bar_kv_full + 8 * s, (t / C::kStages) & 1u, abort_flag, wait_ns)) alive = false;
           return kv_smem + s * C::kTileBytes;
         };
         auto kv_release = [&](uint32_t t) { if (leader) tc_commit(bar_kv_empty + 8 * kv_slot(t)); };
@@ -618,7 +621,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t kaddr = kv_wait(t0);
         for (int i = 0; i < 2 && alive; ++i) {
           if (it.tile[i].n == 0) continue;
-          if (!mbar_wait(bar_q_full + 8 * i, q_uses[i] & 1u, abort_flag)) { alive = false; break; }
+          if (!mbar_wait(bar_q_full + 8 * i, q_uses[i] & 1u, abort_flag, wait_ns)) { alive = false; break; }
           ++q_uses[i];
           tc_fence_after();
           issue_qk(i, kaddr, it.tile[i].n == 1);
@@ -633,7 +636,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (alive && has_next) knext = kv_wait(t0 + 2 * j + 2);
           for (int i = 0; i < 2 && alive; ++i) {
             if (j >= it.tile[i].n) continue;
-            if (!mbar_wait(bar_p_full + 8 * i, p_cnt[i] & 1u, abort_flag)) { alive = false; break; }
+            if (!mbar_wait(bar_p_full + 8 * i, p_cnt[i] & 1u, abort_flag, wait_ns)) { alive = false; break; }
             ++p_cnt[i];
             tc_fence_after();
             issue_pv(i, vaddr, j > 0);
@@ -748,7 +751,8 @@ cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
   PrefillParams pp;
   pp.p = p;
   pp.debug = debug;
-  pp.debug_mode = debug ? debug_mode : 0;
+  pp.debug_mode = (debug || debug_mode == 3) ? debug_mode : 0;
+  pp.wait_budget_ns = debug_mode == 3 ? 20000000ull : kWaitBudgetNs;   // 20 ms in the time-out test
   pp.sched = sched;
   pp.row_tiles = (int)((p.seq_q + kBM - 1) / kBM);
   pp.pair_heads = (p.group % 2 == 0) ? 1 : 0;
@@ -776,6 +780,7 @@ cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
 bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why) {
   if (dtype != AIDN_BF16 && dtype != AIDN_F16) { *why = "tcgen05 prefill takes fp16 or bf16 inputs"; return false; }
   if (p.head_dim != 64 && p.head_dim != 128) { *why = "tcgen05 prefill takes head_dim 64 or 128"; return false; }
+  if (p.block_table) { *why = "tcgen05 prefill does not read paged K/V"; return false; }
   if (!aligned_bhs(p.q, p.qs, p.num_q_heads, p.batch, 2, 16) || !aligned_bhs(p.k, p.ks, p.num_kv_heads, p.batch, 2, 16) ||
       !aligned_bhs(p.v, p.vs, p.num_kv_heads, p.batch, 2, 16)) {
     *why = "Q/K/V base must be 16-byte aligned and strides multiples of 8 elements for TMA";

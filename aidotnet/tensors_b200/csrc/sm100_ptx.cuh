@@ -67,14 +67,15 @@ constexpr uint64_t kWaitBudgetNs = 2000000000ull;
 
 // Bounded wait.  Returns false when the budget expired or another thread of the CTA already gave up;
 // the caller then unwinds to the common teardown instead of spinning forever.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t budget_ns = kWaitBudgetNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63u) == 0u) {
+    if ((++spins & 7u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitBudgetNs) {
+      if (globaltimer_ns() - t0 > budget_ns) {
         *abort_flag = 1;
         return false;
       }

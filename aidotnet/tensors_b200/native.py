@@ -26,7 +26,7 @@ EXPORTS = (
     "aidn_sdpa_create", "aidn_sdpa_workspace_bytes", "aidn_sdpa_launch", "aidn_sdpa_poll", "aidn_sdpa_last_path",
     "aidn_sdpa_last_launch_count", "aidn_sdpa_destroy", "aidn_sdpa_last_error", "aidn_sdpa_device_supported",
     "aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32",
-    "aidn_sdpa_decode_noalloc",
+    "aidn_sdpa_decode_noalloc", "aidn_sdpa_launch_paged",
 )
 
 
@@ -50,6 +50,13 @@ class SdpaArgs(ctypes.Structure):
         ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3), ("v_stride", ctypes.c_int64 * 3),
         ("o_stride", ctypes.c_int64 * 3), ("scale", ctypes.c_float), ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_int64), ("gather_output", ctypes.c_int32),
+    ]
+
+
+class PagedKv(ctypes.Structure):
+    _fields_ = [
+        ("block_table", ctypes.c_void_p), ("block_table_stride", ctypes.c_int64), ("block_size", ctypes.c_int32),
+        ("num_blocks", ctypes.c_int32),
     ]
 
 
@@ -96,6 +103,9 @@ def load() -> ctypes.CDLL:
         fn.restype = ctypes.c_int
     lib.aidn_sdpa_decode_noalloc.argtypes = [ctypes.POINTER(SdpaDesc), ctypes.POINTER(SdpaArgs), ctypes.c_void_p]
     lib.aidn_sdpa_decode_noalloc.restype = ctypes.c_int
+    lib.aidn_sdpa_launch_paged.argtypes = [ctypes.c_void_p, ctypes.POINTER(SdpaArgs), ctypes.POINTER(PagedKv),
+                                           ctypes.c_void_p]
+    lib.aidn_sdpa_launch_paged.restype = ctypes.c_int
     lib.aidn_sdpa_debug_set.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
     lib.aidn_sdpa_debug_set.restype = ctypes.c_int
     _lib = lib
@@ -148,13 +158,22 @@ class Handle:
                lse: Optional[int] = None, mask: Optional[int] = None, mask_stride: Sequence[int] = (0, 0, 0, 0),
                kv_len: Optional[int] = None, q_stride=None, k_stride=None, v_stride=None, o_stride=None,
                scale: float = 0.0, workspace: Optional[int] = None, workspace_bytes: int = 0,
-               gather_output: bool = False) -> None:
+               gather_output: bool = False, block_table: Optional[int] = None, block_table_stride: int = 0,
+               block_size: int = 0, num_blocks: int = 0) -> None:
+        """Enqueues one forward.  With ``block_table`` (a device int32 array) ``k`` / ``v`` are the paged pools
+        ``[num_blocks, block_size, Hkv, D]`` and the call goes through ``aidn_sdpa_launch_paged``."""
         a = SdpaArgs()
         a.q, a.k, a.v, a.out, a.lse, a.mask, a.kv_len = q, k, v, out, lse, mask, kv_len
         a.mask_stride = (ctypes.c_int64 * 4)(*mask_stride)
         a.batch, a.seq_q, a.seq_kv = batch, seq_q, seq_kv
         a.q_stride, a.k_stride, a.v_stride, a.o_stride = _arr3(q_stride), _arr3(k_stride), _arr3(v_stride), _arr3(o_stride)
         a.scale, a.workspace, a.workspace_bytes, a.gather_output = scale, workspace, workspace_bytes, int(gather_output)
+        if block_table is not None:
+            pg = PagedKv()
+            pg.block_table, pg.block_table_stride = block_table, block_table_stride
+            pg.block_size, pg.num_blocks = block_size, num_blocks
+            check(self._lib.aidn_sdpa_launch_paged(self._h, ctypes.byref(a), ctypes.byref(pg), ctypes.c_void_p(stream)))
+            return
         check(self._lib.aidn_sdpa_launch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
 
     def poll(self, stream: int) -> None:

@@ -12,6 +12,8 @@
  *   Engines/DirectGpu/IDirectGpuBackend.cs:1501-1503  GroupedQueryAttention(...)
  *   Engines/DirectGpu/CUDA/CudaBackend.cs:2968-3021   FlashDecode(q,k,v,heads,kvHeads,headDim,seqLen,scale,splits)
  *   Engines/DirectGpu/IDirectGpuBackend.cs:1890,1911  ConvertToFp16 / ConvertToFp32 (dtype staging)
+ *   Engines/DirectGpu/IDirectGpuBackend.cs:3619-3632  PagedAttentionDecode / PagedAttentionPrefill and their Gqa
+ *        variants (q,kcache,vcache,blockTable,heads[,kvHeads],headDim,blockSize,seqLen | numQueries,startPos,scale)
  *
  * Conventions inherited from that caller (CudaBackend.cs:371-375, 546, 5253-5272, 5389-5403):
  *   - every buffer is caller-owned device memory (IGpuBuffer.Handle, IDirectGpuBackend.cs:3776-3803);
@@ -117,6 +119,20 @@ typedef struct {
                              stream (batch == 1 or per-batch-entry group call); needs desc.nccl_comm      */
 } aidn_sdpa_args;
 
+/* Paged K/V (the vLLM-style pool of Engines/DirectGpu/DevicePagedKVCache.cs:10-18): args.k / args.v are the key and
+ * value pools [num_blocks, block_size, Hkv, D]; key t of batch entry b is row
+ * block_table[b * block_table_stride + t / block_size] * block_size + t % block_size of the pool.  In this mode
+ * k_stride / v_stride mean: [0] unused, [1] head stride, [2] stride between pool rows; all zero = the dense pool
+ * layout above (head stride D, row stride Hkv * D).  The table must hold ceil(n / block_size) entries per sequence,
+ * n = the keys that sequence can see (kv_len[b] when given, else seq_kv). */
+typedef struct {
+  const int32_t* block_table; /* device, int32 (AllocateIntBuffer, CudaBackend.cs:5216-5234 convention)        */
+  int64_t block_table_stride; /* entries between consecutive sequences; unused for batch == 1                  */
+  int32_t block_size;         /* tokens per block, > 0; a multiple of 8 dividing 128 for the tcgen05 kernel    */
+  int32_t num_blocks;         /* blocks in the pool; > 0 makes the kernels skip entries outside [0,num_blocks)
+                                 and report them through aidn_sdpa_poll (AIDN_EINVAL); 0 = trust the table      */
+} aidn_paged_kv;
+
 /* Pointers passed with q/k/v/out index the FULL tensors: the handle offsets them by head_begin itself. */
 
 /* Validates the descriptor, resolves driver entry points, sizes and allocates handle-owned scratch. */
@@ -125,8 +141,14 @@ AIDN_API int aidn_sdpa_create(const aidn_sdpa_desc* desc, aidn_sdpa_t* out);
 AIDN_API int64_t aidn_sdpa_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq_q, int64_t seq_kv);
 /* Enqueues the attention forward on `cu_stream` (a CUstream / cudaStream_t).  Capture-safe, no allocation. */
 AIDN_API int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* args, void* cu_stream);
+/* The same forward with K and V read through a block table (see aidn_paged_kv).  Decode (seq_q == 1, any batch,
+ * per-sequence kv_len) is PagedAttentionDecode{,Gqa}; seq_q > 1 with desc.causal and causal_bottom_right = 0,
+ * causal_offset = startPos is PagedAttentionPrefill{,Gqa} — the reference's [numQueries, heads, D] query and output
+ * are q_stride = o_stride = {0, D, heads * D}. */
+AIDN_API int aidn_sdpa_launch_paged(aidn_sdpa_t h, const aidn_sdpa_args* args, const aidn_paged_kv* paged,
+                                    void* cu_stream);
 /* Synchronises `cu_stream` and returns AIDN_ETIMEOUT if a kernel of this handle gave up a bounded wait,
- * AIDN_ECUDA on a CUDA error, else AIDN_OK.  For tests and diagnostics; not needed on the hot path. */
+ * AIDN_EINVAL if a paged launch met a block-table entry outside the pool, AIDN_ECUDA on a CUDA error, else AIDN_OK.  For tests and diagnostics; not needed on the hot path. */
 AIDN_API int aidn_sdpa_poll(aidn_sdpa_t h, void* cu_stream);
 /* Which kernel the last launch used (aidn_path value), and how many kernels it enqueued. */
 AIDN_API int aidn_sdpa_last_path(aidn_sdpa_t h);

@@ -158,3 +158,62 @@ def bf16_bits_to_f32(x: np.ndarray) -> np.ndarray:
     out = np.empty(x.shape, dtype=np.float32)
     lib().aidn_oracle_bf16_to_f32_array(x.ctypes.data, out.ctypes.data, x.size)
     return out
+
+
+# ---- paged K/V ------------------------------------------------------------------------------------------------
+# The reference's CPU side of a paged cache is "materialise, then attend": PagedKVCache<T>.Materialize
+# (src/AiDotNet.Tensors/Engines/Autodiff/PagedKVCache.cs:127-153) gathers a sequence's blocks into contiguous
+# [len, heads, headDim] tensors, and the expected values of the GPU tests are standard attention over keys read as
+# pool[(blockTable[t / blockSize] * blockSize + t % blockSize), head, :]
+# (tests/AiDotNet.Tensors.Tests/Engines/DirectGpu/PagedAttentionCudaTests.cs:70-95, :150-181).
+
+def materialize(cache: np.ndarray, block_table: np.ndarray, block_size: int, seq_kv: int,
+                kv_len: Optional[np.ndarray] = None) -> np.ndarray:
+    """Gathers ``cache`` [num_blocks, block_size, Hkv, D] through ``block_table`` [B, blocks_per_seq] into a
+    contiguous [B, Hkv, seq_kv, D] array.  Positions at or beyond ``kv_len[b]`` are zero (their table entries are
+    not read, as a cache only fills the entries a sequence uses)."""
+    cache = np.asarray(cache, dtype=np.float32)
+    bt = np.asarray(block_table, dtype=np.int64)
+    assert cache.ndim == 4 and cache.shape[1] == block_size and bt.ndim == 2
+    B = bt.shape[0]
+    out = np.zeros((B, cache.shape[2], seq_kv, cache.shape[3]), dtype=np.float32)
+    t = np.arange(seq_kv)
+    for b in range(B):
+        n = seq_kv if kv_len is None else int(min(max(int(kv_len[b]), 0), seq_kv))
+        rows = bt[b, t[:n] // block_size] * block_size + t[:n] % block_size
+        flat = cache.reshape(-1, cache.shape[2], cache.shape[3])
+        out[b, :, :n, :] = flat[rows].transpose(1, 0, 2)
+    return out
+
+
+def paged_sdpa(q: np.ndarray, kcache: np.ndarray, vcache: np.ndarray, block_table: np.ndarray, *, block_size: int,
+               seq_kv: int, kv_len: Optional[np.ndarray] = None, **kw):
+    """``sdpa`` over K/V materialised from the paged pools; ``q`` is [B, Hq, Sq, D], every keyword of ``sdpa`` applies."""
+    k = materialize(kcache, block_table, block_size, seq_kv, kv_len)
+    v = materialize(vcache, block_table, block_size, seq_kv, kv_len)
+    return sdpa(q, k, v, kv_len=kv_len, **kw)
+
+
+def paged_attention_rows(q: np.ndarray, kcache: np.ndarray, vcache: np.ndarray, block_table: np.ndarray, heads: int,
+                         kv_heads: int, head_dim: int, block_size: int, num_queries: int, start_pos: int,
+                         scale: float, decode_len: Optional[int] = None) -> np.ndarray:
+    """Direct restatement (float64 numpy, small cases) of the four reference kernels paged_attention_decode,
+    _prefill, _decode_gqa and _prefill_gqa (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/
+    CudaPagedAttentionKernels.cs:23-160): flat ``q`` [num_queries, heads, head_dim], flat pools, flat block table;
+    query qi sees keys 0..start_pos+qi (prefill) or 0..decode_len-1 (decode, num_queries == 1).  Independent of
+    ``sdpa`` and ``materialize``: it pins them."""
+    q = np.asarray(q, dtype=np.float64).reshape(num_queries, heads, head_dim)
+    kc = np.asarray(kcache, dtype=np.float64).reshape(-1, kv_heads, head_dim)
+    vc = np.asarray(vcache, dtype=np.float64).reshape(-1, kv_heads, head_dim)
+    bt = np.asarray(block_table, dtype=np.int64).reshape(-1)
+    out = np.zeros((num_queries, heads, head_dim))
+    for qi in range(num_queries):
+        key_len = decode_len if decode_len is not None else start_pos + qi + 1
+        t = np.arange(key_len)
+        rows = bt[t // block_size] * block_size + t % block_size
+        for h in range(heads):
+            kvh = h // (heads // kv_heads)
+            logits = kc[rows, kvh, :] @ q[qi, h] * scale
+            w = np.exp(logits - logits.max())
+            out[qi, h] = (w / w.sum()) @ vc[rows, kvh, :]
+    return out.astype(np.float32)

@@ -222,6 +222,59 @@ int main() {
     reference(q, k, v, B, Hq, Hkv, S, S, D, o, ref, lse);
     EXPECT(max_abs_diff(dout.download(), ref) <= 0.012, "bf16 prefill mismatch %g", max_abs_diff(dout.download(), ref));
   }
+  {  // DirectGpu/PagedAttentionCudaTests.cs:43-205: scattered block table over a pool with spare blocks; decode,
+     // prefill (query qi sees keys 0..startPos+qi) and their Gqa variants against a scalar reference in double
+    std::printf("paged attention decode / prefill (+Gqa)\n");
+    struct Case { int heads, kvHeads, D, bs, nq, start; };
+    const Case cases[] = {{4, 4, 64, 16, 1, 39}, {2, 2, 128, 8, 1, 19}, {8, 8, 32, 32, 1, 99}, {4, 4, 64, 16, 8, 0},
+                          {2, 2, 128, 8, 12, 5}, {8, 8, 32, 32, 20, 40}, {8, 2, 64, 16, 1, 51}, {8, 2, 64, 16, 9, 30}};
+    for (const Case& c : cases) {
+      const int keyLen = c.start + c.nq, nLogical = (keyLen + c.bs - 1) / c.bs, maxBlocks = nLogical + 5;
+      const int pool = maxBlocks * c.bs * c.kvHeads * c.D;
+      auto kc = uniform(pool, 51 + c.heads), vc = uniform(pool, 52 + c.heads), q = uniform(c.nq * c.heads * c.D, 53 + c.nq);
+      std::vector<int> table(nLogical);
+      for (int i = 0; i < nLogical; ++i) table[i] = (i * 5 + 3) % maxBlocks;   // 5 is coprime to every maxBlocks used (6..9)
+      for (int i = 0; i < nLogical; ++i) for (int j = 0; j < i; ++j) if (table[i] == table[j]) table[i] = -1;
+      bool distinct = true; for (int t : table) distinct = distinct && t >= 0;
+      EXPECT(distinct, "test bug: block table has a repeated entry");
+      const double scale = 1.0 / std::sqrt((double)c.D);
+      std::vector<double> want((size_t)c.nq * c.heads * c.D, 0.0);
+      for (int qi = 0; qi < c.nq; ++qi)
+        for (int h = 0; h < c.heads; ++h) {
+          const int kvh = h / (c.heads / c.kvHeads), len = c.start + qi + 1;
+          std::vector<double> w(len);
+          double mx = -1e300, sum = 0;
+          for (int t = 0; t < len; ++t) {
+            const size_t base = (((size_t)table[t / c.bs] * c.bs + t % c.bs) * c.kvHeads + kvh) * c.D;
+            double dot = 0;
+            for (int d = 0; d < c.D; ++d) dot += (double)q[((size_t)qi * c.heads + h) * c.D + d] * kc[base + d];
+            w[t] = dot * scale; mx = std::max(mx, w[t]);
+          }
+          for (int t = 0; t < len; ++t) { w[t] = std::exp(w[t] - mx); sum += w[t]; }
+          for (int t = 0; t < len; ++t) {
+            const size_t base = (((size_t)table[t / c.bs] * c.bs + t % c.bs) * c.kvHeads + kvh) * c.D;
+            for (int d = 0; d < c.D; ++d) want[((size_t)qi * c.heads + h) * c.D + d] += w[t] / sum * vc[base + d];
+          }
+        }
+      DeviceArray dq(q), dk(kc), dv(vc), dout((int64_t)c.nq * c.heads * c.D);
+      GpuBuffer bt; bt.Size = nLogical; bt.Dtype = AIDN_F32;   // 4-byte elements; holds int32 (AllocateIntBuffer)
+      cudaMalloc(&bt.Handle, (size_t)nLogical * 4);
+      cudaMemcpy(bt.Handle, table.data(), (size_t)nLogical * 4, cudaMemcpyHostToDevice);
+      const bool gqa = c.kvHeads != c.heads;
+      if (c.nq == 1 && !gqa) backend.PagedAttentionDecode(dq.buf, dk.buf, dv.buf, bt, dout.buf, c.heads, c.D, c.bs, keyLen, (float)scale);
+      else if (c.nq == 1) backend.PagedAttentionDecodeGqa(dq.buf, dk.buf, dv.buf, bt, dout.buf, c.heads, c.kvHeads, c.D, c.bs, keyLen, (float)scale);
+      else if (!gqa) backend.PagedAttentionPrefill(dq.buf, dk.buf, dv.buf, bt, dout.buf, c.heads, c.D, c.bs, c.nq, c.start, (float)scale);
+      else backend.PagedAttentionPrefillGqa(dq.buf, dk.buf, dv.buf, bt, dout.buf, c.heads, c.kvHeads, c.D, c.bs, c.nq, c.start, (float)scale);
+      backend.Synchronize();
+      EXPECT(max_abs_diff(dout.download(), want) <= 2e-5, "paged heads=%d kv=%d D=%d bs=%d nq=%d start=%d: %g", c.heads,
+             c.kvHeads, c.D, c.bs, c.nq, c.start, max_abs_diff(dout.download(), want));
+      bool threw = false;
+      try { backend.PagedAttentionDecode(dq.buf, dk.buf, dv.buf, bt, dout.buf, c.heads, c.D, c.bs, nLogical * c.bs + 1, (float)scale); }
+      catch (const std::invalid_argument&) { threw = true; }
+      EXPECT(threw, "a block table shorter than the sequence must throw");
+      cudaFree(bt.Handle);
+    }
+  }
   {  // argument errors throw, as ArgumentOutOfRangeException / ArgumentException do in the reference
     std::printf("argument errors\n");
     std::vector<float> z(64, 0.f);

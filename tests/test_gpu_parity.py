@@ -366,6 +366,32 @@ def test_config5_long_context_shard_sampled_rows():
     del Hq, Hkv, g
 
 
+def test_prefill_bounded_wait_expires_cleanly():
+    """Failure detection without a fault: a test hook makes the producer withhold the Q tiles, so the UMMA warp's
+    bounded wait (20 ms in this mode) runs out.  The kernel must unwind (every role leaves its loop, TMEM is freed,
+    the scheduler counters are reset), poll() must report AIDN_ETIMEOUT, and the very next launch on the same handle
+    must be correct."""
+    q, qf = gen((1, 4, 512, 128), "bf16", 201)
+    k, kf = gen((1, 2, 512, 128), "bf16", 202)
+    v, vf = gen((1, 2, 512, 128), "bf16", 203)
+    out = torch.zeros((1, 4, 512, 128), device="cuda")
+    h = N.Handle(device=0, qkv_dtype=N.BF16, head_dim=128, num_q_heads=4, num_kv_heads=2, causal=True,
+                 path=N.PATH_PREFILL_SM100)
+    stream = torch.cuda.current_stream().cuda_stream
+    launch = lambda: h.launch(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), batch=1, seq_q=512,
+                              seq_kv=512, stream=stream)
+    h.debug_set(None, 3)
+    launch()
+    with pytest.raises(N.AidnError) as e:
+        h.poll(stream)
+    assert e.value.status == N.ETIMEOUT
+    h.debug_set(None, 0)
+    launch()
+    h.poll(stream)
+    compare(out, O.sdpa(qf, kf, vf, causal=True), "bf16", "launch after a timed-out launch")
+    h.close()
+
+
 # ------------------------------------------------------------------------------------------------ casts, errors
 def test_cast_kernels_bit_exact(golden):
     """BFloat16.cs:65-84 bit for bit, NaN payloads included; round trip through fp32 is lossless."""

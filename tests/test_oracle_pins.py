@@ -138,3 +138,56 @@ def test_bf16_rounding_vectors(golden):
     assert np.array_equal(O.f32_to_bf16_bits(x), golden["bf16_out_bits"])
     back = O.bf16_bits_to_f32(golden["bf16_out_bits"])
     assert np.array_equal(back.view(np.uint32), golden["bf16_out_bits"].astype(np.uint32) << 16)
+
+
+# ---- paged K/V ----------------------------------------------------------------------------------------------
+def _paged_case(rng, heads, kv_heads, head_dim, block_size, key_len, n_q):
+    n_logical = (key_len + block_size - 1) // block_size
+    max_blocks = n_logical + 5                      # spare blocks, as the reference's tests allocate
+    kc = rng.uniform(-1, 1, (max_blocks, block_size, kv_heads, head_dim)).astype(np.float32)
+    vc = rng.uniform(-1, 1, (max_blocks, block_size, kv_heads, head_dim)).astype(np.float32)
+    q = rng.uniform(-1, 1, (n_q, heads, head_dim)).astype(np.float32)
+    bt = rng.permutation(max_blocks)[:n_logical].astype(np.int32)   # a scattered, non-monotonic table
+    return q, kc, vc, bt
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size,seq_len", [
+    (4, 4, 64, 16, 40), (2, 2, 128, 8, 20), (8, 8, 32, 32, 100),      # PagedAttentionCudaTests.cs:44-46
+    (8, 2, 64, 16, 40), (4, 1, 128, 8, 33)])                           # grouped-query shapes
+def test_paged_decode_materialised_equals_kernel_restatement(heads, kv_heads, head_dim, block_size, seq_len):
+    """materialize + sdpa (the form the GPU parity tests use) against the line-by-line restatement of
+    paged_attention_decode{,_gqa}, within the reference tests' own tolerance 2e-3 + 2e-3|e| (…CudaTests.cs:118)."""
+    rng = np.random.default_rng(0xA77 + heads + seq_len)
+    q, kc, vc, bt = _paged_case(rng, heads, kv_heads, head_dim, block_size, seq_len, 1)
+    scale = 1.0 / np.sqrt(head_dim)
+    want = O.paged_attention_rows(q, kc, vc, bt, heads, kv_heads, head_dim, block_size, 1, 0, scale, decode_len=seq_len)
+    got = O.paged_sdpa(q.transpose(1, 0, 2)[None], kc, vc, bt[None], block_size=block_size, seq_kv=seq_len, scale=scale)
+    got = got[0].transpose(1, 0, 2)
+    assert np.all(np.abs(got - want) <= 1e-5 + 1e-5 * np.abs(want))
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,block_size,num_queries,start_pos", [
+    (4, 4, 64, 16, 8, 0), (2, 2, 128, 8, 12, 5), (8, 8, 32, 32, 20, 40),   # PagedAttentionCudaTests.cs:125-127
+    (8, 2, 64, 16, 8, 3)])
+def test_paged_prefill_materialised_equals_kernel_restatement(heads, kv_heads, head_dim, block_size, num_queries,
+                                                              start_pos):
+    """Query qi sees keys 0..start_pos+qi: causal with causal_offset = start_pos over start_pos+num_queries keys."""
+    rng = np.random.default_rng(0xB99 + heads + num_queries + start_pos)
+    q, kc, vc, bt = _paged_case(rng, heads, kv_heads, head_dim, block_size, start_pos + num_queries, num_queries)
+    scale = 1.0 / np.sqrt(head_dim)
+    want = O.paged_attention_rows(q, kc, vc, bt, heads, kv_heads, head_dim, block_size, num_queries, start_pos, scale)
+    got = O.paged_sdpa(q.transpose(1, 0, 2)[None], kc, vc, bt[None], block_size=block_size,
+                       seq_kv=start_pos + num_queries, causal=True, causal_offset=start_pos, scale=scale)
+    got = got[0].transpose(1, 0, 2)
+    assert np.all(np.abs(got - want) <= 1e-5 + 1e-5 * np.abs(want))
+
+
+def test_materialize_respects_kv_len_and_unused_entries():
+    """Entries of the table beyond a sequence's length are never read (a cache leaves them unset)."""
+    rng = np.random.default_rng(3)
+    kc = rng.standard_normal((6, 4, 2, 8)).astype(np.float32)
+    bt = np.array([[2, 5, -7], [1, 0, 3]], np.int32)
+    out = O.materialize(kc, bt, 4, 12, kv_len=np.array([7, 12], np.int32))
+    assert np.array_equal(out[0, :, :4], kc[2].transpose(1, 0, 2)) and np.array_equal(out[0, :, 4:7], kc[5, :3].transpose(1, 0, 2))
+    assert np.all(out[0, :, 7:] == 0)
+    assert np.array_equal(out[1, :, 8:12], kc[3].transpose(1, 0, 2))
