@@ -537,20 +537,54 @@ __global__ void __launch_bounds__(kThreads, 1)
           load_tile(&tm_q, q_smem + i * C::kTileBytes, bar_q_full + 8 * i, it.tile[i].t * kBM, it.tile[i].h);
           ++q_uses[i];
         };
-        auto load_kv = [&](const CUtensorMap* tm, int key_tile) {
+        // Paged K/V: a key tile is 128 / block_size pool blocks, each fetched by its own TMA box (block_size rows)
+        // into its slice of the ring slot; the 128-byte swizzle is a function of the shared-memory address, so the
+        // slices compose into the same tile image as one 128-row box.  Lane i holds the pool block of slice i.
+        const bool paged = p.block_table != nullptr;
+        int32_t blk_cur = 0;
+        int64_t last_blk = 0;
+        if (paged) last_blk = (kv_limit_of(p, it.b) - 1) >> p.block_shift;
+        auto load_kv = [&](const CUtensorMap* tm, int key_tile, bool is_k) {
           const int s = (int)(t_load % C::kStages);
           const uint32_t phase = (t_load / C::kStages) & 1u;
           if (!mbar_wait(bar_kv_empty + 8 * s, phase ^ 1u, abort_flag, wait_ns)) { alive = false; return; }
-          load_tile(tm, kv_smem + s * C::kTileBytes, bar_kv_full + 8 * s, key_tile * kBN, it.kvh);
+          if (!paged) {
+            load_tile(tm, kv_smem + s * C::kTileBytes, bar_kv_full + 8 * s, key_tile * kBN, it.kvh);
+          } else {
+            const int parts = kBN >> p.block_shift;
+            if (is_k) {   // the V tile of the same keys follows and reuses the entries
+              // Logical blocks past the sequence's last one repeat it: their keys are masked, the table has no entry
+              // for them, and what lands in shared memory only has to be finite.
+              int64_t lb = (int64_t)key_tile * parts + lane;
+              if (lb > last_blk) lb = last_blk;
+              blk_cur = 0;
+              if (lane < parts) {
+                blk_cur = __ldg(p.block_table + (int64_t)it.b * p.bt_stride + lb);
+                if ((blk_cur < 0 || blk_cur >= p.num_blocks) && p.status) atomicOr(p.status, kStatusBadBlock);
+              }
+            }
+            const uint32_t dst = kv_smem + s * C::kTileBytes, bar = bar_kv_full + 8 * s;
+            if (leader) mbar_expect_tx(bar, (uint32_t)C::kTileBytes);
+            for (int part = 0; part < parts; ++part) {
+              // an entry outside the pool gives an out-of-range coordinate, which TMA fills with zeros
+              const int32_t phys = __shfl_sync(0xffffffffu, blk_cur, part);
+              if (leader) {
+#pragma unroll
+                for (int hf = 0; hf < C::kHalves; ++hf)
+                  tma_load_4d(dst + hf * C::kHalfBytes + part * (p.block_size * 128), tm, bar, hf * 64,
+                              phys * p.block_size, it.kvh, 0);
+              }
+            }
+          }
           ++t_load;
         };
         if (it.n_max > 0) {
           load_q(0);
-          if (alive) load_kv(&tm_k, 0);
+          if (alive) load_kv(&tm_k, 0, true);
           if (alive) load_q(1);
           for (int j = 0; j < it.n_max && alive; ++j) {
-            load_kv(&tm_v, j);
-            if (alive && j + 1 < it.n_max) load_kv(&tm_k, j + 1);
+            load_kv(&tm_v, j, false);
+            if (alive && j + 1 < it.n_max) load_kv(&tm_k, j + 1, true);
           }
         }
         {
@@ -742,9 +776,13 @@ cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
   const bool ok_o = p.out_f32
       ? encode_bhsd(&to, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, s128, p.out, HD, p.seq_q, p.num_q_heads, p.batch, p.os, 32, 32)
       : encode_bhsd(&to, dt16, 2, s128, p.out, HD, p.seq_q, p.num_q_heads, p.batch, p.os, 64, 32);
+  // Paged pools are one "sequence" of num_blocks * block_size rows, fetched one block (box of block_size rows) at a time.
+  const int64_t kv_rows = p.block_table ? (int64_t)p.num_blocks * p.block_size : p.seq_kv;
+  const int kv_batch = p.block_table ? 1 : p.batch;
+  const int kv_box = p.block_table ? p.block_size : kBN;
   if (!encode_bhsd(&tq, dt16, 2, s128, p.q, HD, p.seq_q, p.num_q_heads, p.batch, p.qs, 64, kBM) ||
-      !encode_bhsd(&tk, dt16, 2, s128, p.k, HD, p.seq_kv, p.num_kv_heads, p.batch, p.ks, 64, kBN) ||
-      !encode_bhsd(&tv, dt16, 2, s128, p.v, HD, p.seq_kv, p.num_kv_heads, p.batch, p.vs, 64, kBN) || !ok_o) {
+      !encode_bhsd(&tk, dt16, 2, s128, p.k, HD, kv_rows, p.num_kv_heads, kv_batch, p.ks, 64, kv_box) ||
+      !encode_bhsd(&tv, dt16, 2, s128, p.v, HD, kv_rows, p.num_kv_heads, kv_batch, p.vs, 64, kv_box) || !ok_o) {
     *why = "cuTensorMapEncodeTiled rejected a tensor (address or stride alignment)";
     return cudaErrorInvalidValue;
   }
@@ -780,9 +818,19 @@ cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
 bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why) {
   if (dtype != AIDN_BF16 && dtype != AIDN_F16) { *why = "tcgen05 prefill takes fp16 or bf16 inputs"; return false; }
   if (p.head_dim != 64 && p.head_dim != 128) { *why = "tcgen05 prefill takes head_dim 64 or 128"; return false; }
-  if (p.block_table) { *why = "tcgen05 prefill does not read paged K/V"; return false; }
-  if (!aligned_bhs(p.q, p.qs, p.num_q_heads, p.batch, 2, 16) || !aligned_bhs(p.k, p.ks, p.num_kv_heads, p.batch, 2, 16) ||
-      !aligned_bhs(p.v, p.vs, p.num_kv_heads, p.batch, 2, 16)) {
+  const int kv_batch = p.block_table ? 1 : p.batch;
+  if (p.block_table) {
+    if (p.block_shift < 3 || p.block_size > kBN) {
+      *why = "tcgen05 prefill reads paged K/V in blocks of 8, 16, 32, 64 or 128 tokens";
+      return false;
+    }
+    if (p.num_blocks <= 0 || (int64_t)p.num_blocks * p.block_size > 0x7fffff00ll) {
+      *why = "tcgen05 prefill needs aidn_paged_kv.num_blocks (pool rows below 2^31)";
+      return false;
+    }
+  }
+  if (!aligned_bhs(p.q, p.qs, p.num_q_heads, p.batch, 2, 16) || !aligned_bhs(p.k, p.ks, p.num_kv_heads, kv_batch, 2, 16) ||
+      !aligned_bhs(p.v, p.vs, p.num_kv_heads, kv_batch, 2, 16)) {
     *why = "Q/K/V base must be 16-byte aligned and strides multiples of 8 elements for TMA";
     return false;
   }

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c4q|c5shard] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqapaged|c5shard] [--impl reference]
 
 One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
 default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
@@ -35,10 +35,19 @@ WORKLOADS = {
                name="gqa_prefill_B2_Hq32_Hkv8_S8192_D128_causal_bf16"),
     "c5shard": dict(B=1, Hq=8, Hkv=1, Sq=32768, Sk=32768, D=128, causal=True, kind="prefill",
                     name="long_context_shard_B1_Hq8_Hkv1_S32768_D128_causal_bf16"),
+    "c3paged": dict(B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill", block_size=16,
+                    name="paged_gqa_prefill_B2_Hq32_Hkv8_S8192_D128_block16_causal_bf16"),
     "c4q": dict(B=16, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
                 name="batched_decode_quarter_B16_H32_D128_kvlen512-4096_bf16"),
     "c4": dict(B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
                name="batched_decode_B64_H32_D128_kvlen512-4096_bf16"),
+    # the same decode step over a paged pool [blocks, 16, Hkv, D] with a shuffled block table (the serving layout)
+    "c4paged": dict(B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode", block_size=16,
+                    name="paged_decode_B64_H32_D128_block16_kvlen512-4096_bf16"),
+    "c4gqa": dict(B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
+                  name="gqa_decode_B64_Hq32_Hkv8_D128_kvlen512-4096_bf16"),
+    "c4gqapaged": dict(B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode", block_size=16,
+                       name="paged_gqa_decode_B64_Hq32_Hkv8_D128_block16_kvlen512-4096_bf16"),
 }
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each,
 # see profiles/): prefill C2 measured directly; decode C4 measured on the B=16 quarter and scaled by 4.
@@ -167,6 +176,20 @@ class Runner:
                           max_batch=w["B"], max_seq_q=w["Sq"], max_seq_kv=w["Sk"])
         self.stream = torch.cuda.current_stream(dev).cuda_stream
         self.launches = 0
+        self.paged = {}
+        bs = w.get("block_size")
+        if bs:
+            # Scatter the logical blocks of every sequence over one shared pool [blocks, bs, Hkv, D].
+            nb = w["B"] * w["Sk"] // bs
+            perm = torch.randperm(nb, generator=torch.Generator().manual_seed(seed & 0x7fffffff))
+            for name in ("k", "v"):
+                logical = getattr(self, name).permute(0, 2, 1, 3).reshape(nb, bs, w["Hkv"], w["D"])
+                pool = torch.empty_like(logical)
+                pool[perm.to(dev)] = logical
+                setattr(self, name, pool)
+            self.table = perm.to(torch.int32).reshape(w["B"], w["Sk"] // bs).to(dev)
+            self.paged = dict(block_table=self.table.data_ptr(), block_table_stride=w["Sk"] // bs, block_size=bs,
+                              num_blocks=nb)
 
     def step(self, q=None, k=None, v=None):
         q = self.q if q is None else q
@@ -174,7 +197,7 @@ class Runner:
         v = self.v if v is None else v
         self.h.launch(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=self.out.data_ptr(), batch=self.w["B"],
                       seq_q=self.w["Sq"], seq_kv=self.w["Sk"], stream=self.stream,
-                      kv_len=self.kv_len.data_ptr() if self.kv_len is not None else None)
+                      kv_len=self.kv_len.data_ptr() if self.kv_len is not None else None, **self.paged)
         self.launches += self.h.last_launch_count
 
     def time_steps(self, steps, warmup, sampler=None, dist=None):

@@ -208,6 +208,55 @@ def test_paged_prefill_batched(dtype, shape):
     compare(out, ref.transpose(0, 2, 1, 3), dtype, f"paged prefill {shape}")
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("shape", [(2, 8, 2, 128, 16, 300, 77), (1, 4, 4, 64, 32, 130, 0), (3, 6, 2, 128, 8, 64, 500),
+                                   (2, 3, 3, 128, 128, 257, 130), (1, 8, 1, 64, 64, 513, 1000), (2, 2, 1, 128, 16, 1, 300)])
+def test_paged_prefill_on_the_tcgen05_kernel(dtype, shape):
+    """Chunked prefill through the tensor-core kernel: every supported block size (8..128), head pairs and row pairs,
+    ragged kv_len (a sequence shorter than the launch's seq_kv: its trailing table entries are poison), a start
+    offset that is not a multiple of the block or the tile, and seq_q = 1 forced onto this kernel."""
+    B, heads, kv_heads, D, bs, nq, start = shape
+    rng = np.random.default_rng(1300 + nq + bs)
+    L = start + nq
+    lens = np.array([L, max(1, L - 37), max(1, L // 2)][:B], np.int32)
+    bps = (L + bs - 1) // bs
+    nblocks = int(sum((int(x) + bs - 1) // bs for x in lens)) + 3
+    k, kf, v, vf = _pool(nblocks, bs, kv_heads, D, dtype, 650)
+    q, qf = gen((B, nq, heads, D), dtype, 652)
+    bt = _tables(rng, B, bps, nblocks, lens, bs)
+    out, info = _launch_paged(q, k, v, bt, dtype=dtype, block_size=bs, seq_q=nq, seq_kv=L, heads=heads,
+                              kv_heads=kv_heads, head_dim=D, causal=True, causal_offset=start, kv_len=lens,
+                              path=N.PATH_PREFILL_SM100)
+    assert info["path"] == N.PATH_PREFILL_SM100
+    ref = O.paged_sdpa(qf.transpose(0, 2, 1, 3), kf, vf, np.where(bt == 0x3fffffff, 0, bt), block_size=bs, seq_kv=L,
+                       kv_len=lens, causal=True, causal_offset=start)
+    compare(out, ref.transpose(0, 2, 1, 3), dtype, f"paged tcgen05 prefill {shape}")
+
+
+def test_paged_prefill_identity_table_equals_contiguous_prefill():
+    """Size-independent property at a benchmark-sized shape: an identity block table must reproduce the contiguous
+    tensor-core prefill bit for bit (same tiles in shared memory, fetched by 8 boxes instead of 1)."""
+    B, heads, kv_heads, D, bs, S = 2, 8, 2, 128, 16, 4096
+    k, _, v, _ = _pool(B * S // bs, bs, kv_heads, D, "bf16", 720)     # == a [B, S, Hkv, D] cache
+    q, _ = gen((B, S, heads, D), "bf16", 722)
+    bt = np.arange(B * S // bs, dtype=np.int32).reshape(B, S // bs)
+    paged, info = _launch_paged(q, k, v, bt, dtype="bf16", block_size=bs, seq_q=S, seq_kv=S, heads=heads,
+                                kv_heads=kv_heads, head_dim=D, causal=True, causal_offset=0)
+    assert info["path"] == N.PATH_PREFILL_SM100
+    out = torch.full(q.shape, float("nan"), dtype=torch.float32, device="cuda")
+    h = N.Handle(device=0, qkv_dtype=N.BF16, head_dim=D, num_q_heads=heads, num_kv_heads=kv_heads, causal=True,
+                 causal_bottom_right=False, causal_offset=0)
+    stream = torch.cuda.current_stream().cuda_stream
+    qo = (S * heads * D, D, heads * D)
+    st = (S * kv_heads * D, D, kv_heads * D)
+    h.launch(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), batch=B, seq_q=S, seq_kv=S,
+             stream=stream, q_stride=qo, o_stride=qo, k_stride=st, v_stride=st)
+    h.poll(stream)
+    assert h.last_path == N.PATH_PREFILL_SM100
+    h.close()
+    assert torch.equal(paged, out)
+
+
 def test_paged_equals_contiguous_when_table_is_identity():
     """Size-independent property at a serving shape: with block_table = identity the paged launch must reproduce
     the contiguous launch bit for bit (same kernel arithmetic, different addressing)."""
