@@ -87,7 +87,10 @@ namespace {
 int pick_chunk(const aidn_sdpa* h, int64_t batch, int64_t seq_kv) {
   if (h->d.decode_chunk > 0) return h->d.decode_chunk;
   const int gt = h->group <= 2 ? h->group : (h->group <= 4 ? 4 : 8);  // as the decode launcher picks
-  const int gchunks = (h->group + gt - 1) / gt;
+  int gchunks = (h->group + gt - 1) / gt;
+  // 16-bit inputs with 2..16 query heads per KV head run the tensor-core decode kernel: one CTA per KV head and split
+  if (h->d.qkv_dtype != AIDN_F32 && (h->d.head_dim == 64 || h->d.head_dim == 128) && h->group >= 2 && h->group <= 16)
+    gchunks = 1;
   const int64_t items = batch * (h->head_count / h->group) * gchunks;
   const int64_t target = 148 * 8;
   int64_t splits = (target + items - 1) / items;

@@ -77,7 +77,7 @@ __device__ __forceinline__ int64_t decode_len(const SdpaParams& p, int b) {
   return L;
 }
 
-template <typename T, int D, int GT, bool PAGED>
+template <typename T, int D, int GT, bool PAGED, bool HEAD_FAST>
 __global__ void __launch_bounds__(kDecWarps * 32)
     sdpa_decode_partial_kernel(const SdpaParams p, const int chunk, const int nchunks, float* __restrict__ ws,
                                const int direct) {
@@ -95,11 +95,14 @@ __global__ void __launch_bounds__(kDecWarps * 32)
   const int grp = lane / LPK, gl = lane % LPK, d0 = gl * EPL;
   const int gchunks = (p.group + GT - 1) / GT;
   const int b = blockIdx.z;
-  const int kvh = p.head_begin / p.group + (int)blockIdx.y / gchunks;
-  const int gc = (int)blockIdx.y % gchunks;
+  // Token-major caches ([S, Hkv, D] and the paged pool) interleave the heads of one token: there the grid's fast
+  // axis is the head, so that CTAs running together read neighbouring 256-byte pieces of the same DRAM pages.
+  const int by = HEAD_FAST ? blockIdx.x : blockIdx.y;
+  const int kvh = p.head_begin / p.group + by / gchunks;
+  const int gc = by % gchunks;
   const int h0 = kvh * p.group + gc * GT;
   const int nheads = min(GT, p.group - gc * GT);
-  const int c = blockIdx.x;
+  const int c = HEAD_FAST ? blockIdx.y : blockIdx.x;
 
   const int64_t L = decode_len(p, b);
   const int64_t start = (int64_t)c * chunk;
@@ -267,6 +270,312 @@ __global__ void __launch_bounds__(kDecWarps * 32)
   }
 }
 
+// ---- grouped-query decode on the warp-level tensor-core path ---------------------------------------------------
+// With several query heads per KV head the FFMA kernel above is bound by its shuffle reductions (one per head and
+// key), not by HBM.  Here the heads of one KV head are the M dimension of mma.sync.m16n8k16 (up to 16, zero padded):
+// a warp takes 16 keys per step, S[16 heads x 16 keys] = Q K^T and O[16 heads x D] += P V run on the tensor
+// cores, and K and V still stream from global memory exactly once with 16-byte loads straight into the fragment
+// registers.  That works without shared memory or ldmatrix because a dot product does not care about the order of
+// its terms: the d index is assigned to the MMA's k slots (for Q K^T) and to its n columns (for P V) in whatever
+// order the coalesced 16-byte loads deliver it, Q is loaded once in the matching order, and the output columns are
+// un-permuted when the accumulators are written out.  The one re-arrangement needed, pairing two keys of the same
+// d in one 32-bit B register for P V, is a byte permute of two loaded registers.
+//
+// Fragment geometry (g = lane / 4, c = lane % 4), per 16-key step starting at key kb:
+//   K: thread loads rows kb + g and kb + 8 + g, 16-byte chunks i*4 + c (i < D/32); chunk register pair h supplies
+//      k-step 2i + h: slots (2c, 2c+1) <- d = (i*4+c)*8 + 4h + {0,1}, slots (2c+8, 2c+9) <- d = ... + 2 + {0,1}.
+//   V: thread loads rows kb + {2c, 2c+1, 2c+8, 2c+9}, chunks g + 8x (x < D/64); n-tile j = 8x + 2w + hh has its
+//      column n at d = (n + 8x)*8 + 2w + hh.
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1);
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                        uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                 uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__nv_bfloat16>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+template <>
+__device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// NH16: more than 8 query heads per KV head (rows 8..15 of the tile are live).
+template <typename T, int D, bool NH16, bool PAGED, bool HEAD_FAST>
+__global__ void __launch_bounds__(kDecWarps * 32, 2)
+    sdpa_decode_gqa_kernel(const SdpaParams p, const int chunk, const int nchunks, float* __restrict__ ws,
+                           const int direct) {
+  static_assert(sizeof(T) == 2 && (D == 64 || D == 128), "16-bit inputs, head_dim 64 or 128");
+  constexpr int KI = D / 32;      // 16-byte K chunks per thread and row
+  constexpr int VX = D / 64;      // 16-byte V chunks per thread and row
+  constexpr int NT = D / 8;       // n-tiles of the P V product
+  constexpr int ROWS = NH16 ? 16 : 8;
+  constexpr int NG = kDecWarps;
+
+  __shared__ float sm_m[NG][ROWS];
+  __shared__ float sm_l[NG][ROWS];
+  __shared__ __align__(16) float sm_acc[NG][ROWS][D];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int b = blockIdx.z;
+  const int kvh = p.head_begin / p.group + (HEAD_FAST ? (int)blockIdx.x : (int)blockIdx.y);
+  const int h0 = kvh * p.group;
+  const int nheads = p.group;
+  const int cidx = HEAD_FAST ? blockIdx.y : blockIdx.x;
+
+  const int64_t L = decode_len(p, b);
+  const int64_t start = (int64_t)cidx * chunk;
+  const int Hc = p.head_count;
+
+  if (start >= L) {
+    if (direct && cidx == 0) {
+      for (int idx = tid; idx < nheads * D; idx += kDecWarps * 32) {
+        const int hh = idx / D, d = idx - hh * D;
+        store_out<T>(p.out, b * p.os[0] + (int64_t)(h0 + hh) * p.os[1] + d, 0.f, p.out_f32);
+        if (p.lse && d == 0) p.lse[((int64_t)b * p.num_q_heads + h0 + hh) * p.seq_q] = -INFINITY;
+      }
+    }
+    return;
+  }
+  const int64_t end = (start + chunk < L) ? start + chunk : L;
+
+  // Q in fragment order: qa[i][0..3] = chunk i*4+c of head g, qb = head g+8 (zero rows beyond the group).
+  uint32_t qa[KI][4], qb[KI][4];
+#pragma unroll
+  for (int i = 0; i < KI; ++i) {
+    uint4 u = make_uint4(0, 0, 0, 0), w = make_uint4(0, 0, 0, 0);
+    if (g < nheads)
+      u = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + b * p.qs[0] + (int64_t)(h0 + g) * p.qs[1] + (i * 4 + c) * 8);
+    if (NH16 && g + 8 < nheads)
+      w = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + b * p.qs[0] + (int64_t)(h0 + g + 8) * p.qs[1] + (i * 4 + c) * 8);
+    qa[i][0] = u.x; qa[i][1] = u.y; qa[i][2] = u.z; qa[i][3] = u.w;
+    qb[i][0] = w.x; qb[i][1] = w.y; qb[i][2] = w.z; qb[i][3] = w.w;
+  }
+  const T* kbase = static_cast<const T*>(p.k) + (PAGED ? 0 : b * p.ks[0]) + (int64_t)kvh * p.ks[1];
+  const T* vbase = static_cast<const T*>(p.v) + (PAGED ? 0 : b * p.vs[0]) + (int64_t)kvh * p.vs[1];
+
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8; l is this thread's share of the sum
+
+  // Pool row of key kb + idx (idx < 16), or -1 beyond the chunk.
+  auto rows_of = [&](int64_t kb) -> int32_t {
+    if constexpr (PAGED) {
+      const int64_t key = kb + (lane & 15);
+      return key < end ? (int32_t)kv_row_of(p, b, key) : -1;
+    } else {
+      return 0;
+    }
+  };
+  auto row_at = [&](int32_t rows, int64_t kb, int idx) -> int64_t {
+    if constexpr (PAGED) {
+      return __shfl_sync(0xffffffffu, rows, idx);
+    } else {
+      return kb + idx < end ? kb + idx : -1;
+    }
+  };
+  uint4 kreg[2][KI], vreg[4][VX];
+  auto load_k = [&](int32_t rows, int64_t kb) {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int64_t r = row_at(rows, kb, t * 8 + g);
+#pragma unroll
+      for (int i = 0; i < KI; ++i)
+        kreg[t][i] = r >= 0 ? ld_stream16(kbase + r * p.ks[2] + (i * 4 + c) * 8) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  auto load_v = [&](int32_t rows, int64_t kb) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int64_t r = row_at(rows, kb, 2 * c + (e & 1) + (e >> 1) * 8);
+#pragma unroll
+      for (int x = 0; x < VX; ++x)
+        vreg[e][x] = r >= 0 ? ld_stream16(vbase + r * p.vs[2] + (g + 8 * x) * 8) : make_uint4(0, 0, 0, 0);
+    }
+  };
+
+  constexpr int kStep = 16;
+  int64_t kb = start + warp * kStep;
+  int32_t rows = rows_of(kb);
+  if (kb < end) {
+    load_k(rows, kb);
+    load_v(rows, kb);
+  }
+  for (; kb < end; kb += NG * kStep) {
+    // ---- S = Q K^T ------------------------------------------------------------------------------------
+    float sacc[2][4];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      sacc[t][0] = sacc[t][1] = sacc[t][2] = sacc[t][3] = 0.f;
+#pragma unroll
+      for (int i = 0; i < KI; ++i) {
+        const uint32_t kw[4] = {kreg[t][i].x, kreg[t][i].y, kreg[t][i].z, kreg[t][i].w};
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          mma16816<T>(sacc[t], qa[i][2 * h], qb[i][2 * h], qa[i][2 * h + 1], qb[i][2 * h + 1], kw[2 * h], kw[2 * h + 1]);
+      }
+    }
+    // the next step's keys are requested while this step's softmax and P V run
+    const int64_t kb_next = kb + NG * kStep;
+    const int32_t rows_next = rows_of(kb_next);
+    if (kb_next < end) load_k(rows_next, kb_next);
+
+    // ---- online softmax over the step's 16 keys ---------------------------------------------------------
+    float pr[2][4];   // probabilities in the S fragment layout
+    {
+      float mt0 = -INFINITY, mt1 = -INFINITY;
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int64_t key = kb + t * 8 + 2 * c + e;
+          bool ok = key < end;
+          if constexpr (PAGED) {   // every lane takes part in the shuffle, whatever its own key is
+            const int32_t key_row = __shfl_sync(0xffffffffu, rows, t * 8 + 2 * c + e);
+            ok = ok && key_row >= 0;
+          }
+          float v0 = -INFINITY, v1 = -INFINITY;
+          if (ok && g < nheads) v0 = finish_logit(p, sacc[t][e] * p.scale, b, h0 + g, 0, key, L);
+          if (NH16 && ok && g + 8 < nheads) v1 = finish_logit(p, sacc[t][2 + e] * p.scale, b, h0 + g + 8, 0, key, L);
+          sacc[t][e] = v0;
+          sacc[t][2 + e] = v1;
+          mt0 = fmaxf(mt0, v0);
+          mt1 = fmaxf(mt1, v1);
+        }
+      mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 1));
+      mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 2));
+      if (NH16) {
+        mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 1));
+        mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 2));
+      }
+      const float n0 = fmaxf(m0, mt0), n1 = fmaxf(m1, mt1);
+      const float c0 = (m0 == -INFINITY) ? 0.f : softmax_exp<T>(m0 - n0);   // n0 == -inf only if m0 is, too
+      const float c1 = (m1 == -INFINITY) ? 0.f : softmax_exp<T>(m1 - n1);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          pr[t][e] = (sacc[t][e] == -INFINITY) ? 0.f : softmax_exp<T>(sacc[t][e] - n0);
+          pr[t][2 + e] = (!NH16 || sacc[t][2 + e] == -INFINITY) ? 0.f : softmax_exp<T>(sacc[t][2 + e] - n1);
+          s0 += pr[t][e];
+          s1 += pr[t][2 + e];
+        }
+      l0 = l0 * c0 + s0;
+      l1 = l1 * c1 + s1;
+      m0 = n0;
+      m1 = n1;
+      if (c0 != 1.f || (NH16 && c1 != 1.f)) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          acc[j][0] *= c0;
+          acc[j][1] *= c0;
+          if (NH16) {
+            acc[j][2] *= c1;
+            acc[j][3] *= c1;
+          }
+        }
+      }
+    }
+    const uint32_t pa0 = pack_pair<T>(pr[0][0], pr[0][1]), pa1 = pack_pair<T>(pr[0][2], pr[0][3]);
+    const uint32_t pa2 = pack_pair<T>(pr[1][0], pr[1][1]), pa3 = pack_pair<T>(pr[1][2], pr[1][3]);
+
+    // ---- O += P V ----------------------------------------------------------------------------------------
+#pragma unroll
+    for (int x = 0; x < VX; ++x) {
+      const uint32_t r0[4] = {vreg[0][x].x, vreg[0][x].y, vreg[0][x].z, vreg[0][x].w};
+      const uint32_t r1[4] = {vreg[1][x].x, vreg[1][x].y, vreg[1][x].z, vreg[1][x].w};
+      const uint32_t r2[4] = {vreg[2][x].x, vreg[2][x].y, vreg[2][x].z, vreg[2][x].w};
+      const uint32_t r3[4] = {vreg[3][x].x, vreg[3][x].y, vreg[3][x].z, vreg[3][x].w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        // low halves: d = 2w, high halves: d = 2w + 1 of the chunk; two keys of one d share a register
+        mma16816<T>(acc[x * 8 + 2 * w], pa0, pa1, pa2, pa3, __byte_perm(r0[w], r1[w], 0x5410), __byte_perm(r2[w], r3[w], 0x5410));
+        mma16816<T>(acc[x * 8 + 2 * w + 1], pa0, pa1, pa2, pa3, __byte_perm(r0[w], r1[w], 0x7632), __byte_perm(r2[w], r3[w], 0x7632));
+      }
+    }
+    if (kb_next < end) load_v(rows_next, kb_next);
+    rows = rows_next;
+  }
+
+  // ---- merge the warps of the CTA ---------------------------------------------------------------------------
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (c == 0) {
+    sm_m[warp][g] = m0;
+    sm_l[warp][g] = l0;
+    if (NH16) {
+      sm_m[warp][g + 8] = m1;
+      sm_l[warp][g + 8] = l1;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const int x = j >> 3, w = (j >> 1) & 3, hh = j & 1;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int d = ((2 * c + e) + 8 * x) * 8 + 2 * w + hh;
+      sm_acc[warp][g][d] = acc[j][e];
+      if (NH16) sm_acc[warp][g + 8][d] = acc[j][2 + e];
+    }
+  }
+  __syncthreads();
+
+  for (int idx = tid; idx < nheads * D; idx += kDecWarps * 32) {
+    const int hh = idx / D, d = idx - hh * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < NG; ++n) M = fmaxf(M, sm_m[n][hh]);
+    float a = 0.f, lsum = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int n = 0; n < NG; ++n) {
+        const float mn = sm_m[n][hh];
+        const float wgt = (mn == -INFINITY) ? 0.f : softmax_exp<T>(mn - M);
+        a = fmaf(wgt, sm_acc[n][hh][d], a);
+        lsum = fmaf(wgt, sm_l[n][hh], lsum);
+      }
+    }
+    const int h = h0 + hh;
+    if (direct) {
+      store_out<T>(p.out, b * p.os[0] + (int64_t)h * p.os[1] + d, lsum > 0.f ? a / lsum : 0.f, p.out_f32);
+      if (p.lse && d == 0)
+        p.lse[((int64_t)b * p.num_q_heads + h) * p.seq_q] = lsum > 0.f ? M + logf(lsum) : -INFINITY;
+    } else {
+      const int64_t slot = ((int64_t)b * Hc + (h - p.head_begin)) * nchunks + cidx;
+      ws[slot * D + d] = a;
+      if (d == 0) {
+        float* ml = ws + (int64_t)p.batch * Hc * nchunks * D;
+        ml[slot * 2] = M;
+        ml[slot * 2 + 1] = lsum;
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
     sdpa_decode_combine_kernel(const SdpaParams p, const int chunk, const int nchunks, const float* __restrict__ ws) {
@@ -306,14 +615,44 @@ __global__ void __launch_bounds__(128)
 template <typename T, int D, int GT>
 cudaError_t launch_partial(const SdpaParams& p, int chunk, int nchunks, float* ws, int direct, cudaStream_t stream) {
   const int gchunks = (p.group + GT - 1) / GT;
-  dim3 grid((unsigned)nchunks, (unsigned)((p.head_count / p.group) * gchunks), (unsigned)p.batch);
-  if (p.block_table) sdpa_decode_partial_kernel<T, D, GT, true><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct);
-  else sdpa_decode_partial_kernel<T, D, GT, false><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct);
+  const unsigned heads_y = (unsigned)((p.head_count / p.group) * gchunks);
+  const bool head_fast = p.ks[1] < p.ks[2] && nchunks <= 65535;
+  if (head_fast) {
+    dim3 grid(heads_y, (unsigned)nchunks, (unsigned)p.batch);
+    if (p.block_table) sdpa_decode_partial_kernel<T, D, GT, true, true><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct);
+    else sdpa_decode_partial_kernel<T, D, GT, false, true><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct);
+  } else {
+    dim3 grid((unsigned)nchunks, heads_y, (unsigned)p.batch);
+    if (p.block_table) sdpa_decode_partial_kernel<T, D, GT, true, false><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct);
+    else sdpa_decode_partial_kernel<T, D, GT, false, false><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct);
+  }
+  return cudaGetLastError();
+}
+
+template <typename T, int D, bool NH16>
+cudaError_t launch_gqa(const SdpaParams& p, int chunk, int nchunks, float* ws, int direct, cudaStream_t stream) {
+  const unsigned kvheads = (unsigned)(p.head_count / p.group);
+  const bool head_fast = p.ks[1] < p.ks[2] && nchunks <= 65535;
+  const dim3 grid = head_fast ? dim3(kvheads, (unsigned)nchunks, (unsigned)p.batch)
+                              : dim3((unsigned)nchunks, kvheads, (unsigned)p.batch);
+  const bool paged = p.block_table != nullptr;
+#define AIDN_GQA_LAUNCH(PG, HF) \
+  sdpa_decode_gqa_kernel<T, D, NH16, PG, HF><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct)
+  if (paged && head_fast) AIDN_GQA_LAUNCH(true, true);
+  else if (paged) AIDN_GQA_LAUNCH(true, false);
+  else if (head_fast) AIDN_GQA_LAUNCH(false, true);
+  else AIDN_GQA_LAUNCH(false, false);
+#undef AIDN_GQA_LAUNCH
   return cudaGetLastError();
 }
 
 template <typename T, int D>
 cudaError_t launch_partial_g(const SdpaParams& p, int chunk, int nchunks, float* ws, int direct, cudaStream_t stream) {
+  if constexpr (sizeof(T) == 2 && (D == 64 || D == 128)) {
+    // several query heads per KV head: the tensor-core kernel (chunks are multiples of 8 keys; its steps are 16)
+    if (p.group >= 2 && p.group <= 8) return launch_gqa<T, D, false>(p, chunk, nchunks, ws, direct, stream);
+    if (p.group > 8 && p.group <= 16) return launch_gqa<T, D, true>(p, chunk, nchunks, ws, direct, stream);
+  }
   if (p.group == 1) return launch_partial<T, D, 1>(p, chunk, nchunks, ws, direct, stream);
   if (p.group == 2) return launch_partial<T, D, 2>(p, chunk, nchunks, ws, direct, stream);
   if (p.group <= 4) return launch_partial<T, D, 4>(p, chunk, nchunks, ws, direct, stream);
