@@ -127,17 +127,37 @@ __device__ __forceinline__ int64_t kv_limit_of(const SdpaParams& p, int b) {
   return lim;
 }
 
-// Pool row of key `key` of batch entry b (the key itself without a block table); -1 for an entry outside the pool.
-__device__ __forceinline__ int64_t kv_row_of(const SdpaParams& p, int b, int64_t key) {
-  if (!p.block_table) return key;
+// Paged K/V addressing in two halves, so that a kernel can issue the block-table read a step ahead and touch its
+// result only when the row is needed (anything computed from the entry right after the read would make the warp
+// wait for it there).
+//   kv_block_read: the raw entry of key's block (volatile: issued where the caller placed it).
+//   kv_row_from:   pool row of the key from that entry; -1, and `bad` set, for an entry outside the pool.  No
+//                  branch on the entry; the caller reports `bad` once, at its end, with report_bad_block().
+__device__ __forceinline__ int32_t kv_block_read(const SdpaParams& p, int b, int64_t key) {
   const uint32_t k32 = (uint32_t)key;
   const uint32_t blk = p.block_shift >= 0 ? (k32 >> p.block_shift) : (k32 / (uint32_t)p.block_size);
-  const int32_t phys = __ldg(p.block_table + (int64_t)b * p.bt_stride + blk);
-  if (phys < 0 || (p.num_blocks > 0 && phys >= p.num_blocks)) {
-    if (p.status) atomicOr(p.status, kStatusBadBlock);
-    return -1;
-  }
-  return (int64_t)phys * p.block_size + (k32 - blk * (uint32_t)p.block_size);
+  int32_t phys;
+  asm volatile("ld.global.nc.s32 %0, [%1];" : "=r"(phys) : "l"(p.block_table + (int64_t)b * p.bt_stride + blk));
+  return phys;
+}
+
+__device__ __forceinline__ int64_t kv_row_from(const SdpaParams& p, int64_t key, int32_t phys, bool& bad) {
+  const uint32_t k32 = (uint32_t)key;
+  const uint32_t blk = p.block_shift >= 0 ? (k32 >> p.block_shift) : (k32 / (uint32_t)p.block_size);
+  const bool out = phys < 0 || (p.num_blocks > 0 && phys >= p.num_blocks);
+  bad = bad || out;
+  const int64_t row = (int64_t)phys * p.block_size + (k32 - blk * (uint32_t)p.block_size);
+  return out ? -1 : row;
+}
+
+// Pool row of key `key` of batch entry b (the key itself without a block table): read and use in one place.
+__device__ __forceinline__ int64_t kv_row_of(const SdpaParams& p, int b, int64_t key, bool& bad) {
+  if (!p.block_table) return key;
+  return kv_row_from(p, key, kv_block_read(p, b, key), bad);
+}
+
+__device__ __forceinline__ void report_bad_block(const SdpaParams& p, bool bad) {
+  if (bad && p.status) atomicOr(p.status, kStatusBadBlock);
 }
 
 // Host-side launchers (one per kernel family); each returns the CUDA error of its launch.

@@ -14,6 +14,7 @@
 // one thread per head over the whole sequence.
 //
 // Scratch layout (fp32): acc[B][Hc][nchunks][D] followed by ml[B][Hc][nchunks][2], Hc = heads of the shard.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -140,7 +141,18 @@ __global__ void __launch_bounds__(kDecWarps * 32)
     for (int e = 0; e < EPL; ++e) acc[g][e] = 0.f;
   }
 
+  bool bad_block = false;
   constexpr int KPW = KPI * kUnroll;
+  // Paged: one block-table read per key, issued an iteration ahead of the row loads that need it; the entry stays
+  // raw in its register until then.
+  int32_t blk_next[kUnroll];
+  if constexpr (PAGED) {
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t key = start + warp * KPW + u * KPI + grp;
+      blk_next[u] = key < end ? kv_block_read(p, b, key) : 0;
+    }
+  }
   for (int64_t kb = start + warp * KPW; kb < end; kb += kDecWarps * KPW) {
     uint4 kv[kUnroll], vv[kUnroll];
     bool ok[kUnroll];
@@ -150,9 +162,11 @@ __global__ void __launch_bounds__(kDecWarps * 32)
       const int64_t key = kb + u * KPI + grp;
       ok[u] = key < end;
       row[u] = key;
-      if constexpr (PAGED) {  // one block-table read per key, then the same 16-byte row loads
-        row[u] = ok[u] ? kv_row_of(p, b, key) : -1;
+      if constexpr (PAGED) {
+        row[u] = ok[u] ? kv_row_from(p, key, blk_next[u], bad_block) : -1;
         ok[u] = row[u] >= 0;
+        const int64_t key_next = key + kDecWarps * KPW;
+        blk_next[u] = key_next < end ? kv_block_read(p, b, key_next) : 0;
       }
     }
 #pragma unroll
@@ -221,6 +235,7 @@ __global__ void __launch_bounds__(kDecWarps * 32)
     }
   }
 
+  report_bad_block(p, bad_block);
   // merge the NG lane groups of the CTA
   const int ng = warp * KPI + grp;
 #pragma unroll
@@ -284,8 +299,11 @@ __global__ void __launch_bounds__(kDecWarps * 32)
 // Fragment geometry (g = lane / 4, c = lane % 4), per 16-key step starting at key kb:
 //   K: thread loads rows kb + g and kb + 8 + g, 16-byte chunks i*4 + c (i < D/32); chunk register pair h supplies
 //      k-step 2i + h: slots (2c, 2c+1) <- d = (i*4+c)*8 + 4h + {0,1}, slots (2c+8, 2c+9) <- d = ... + 2 + {0,1}.
-//   V: thread loads rows kb + {2c, 2c+1, 2c+8, 2c+9}, chunks g + 8x (x < D/64); n-tile j = 8x + 2w + hh has its
-//      column n at d = (n + 8x)*8 + 2w + hh.
+//   V: P V runs transposed, O^T[d x heads] += V^T[d x keys] P^T[keys x heads], so that the 8 (or 16) live heads
+//      are the N dimension and no accumulator register is spent on padding.  The thread loads rows
+//      kb + {2c, 2c+1, 2c+8, 2c+9}; for D = 128 chunks g and g + 8, for D = 64 chunk g.  M-tile m has its row r at
+//      d = r*8 + m (D = 128) or d = (r % 8)*8 + 4*(r / 8) + m (D = 64); the S accumulators of Q K^T are, as they
+//      stand, the B fragments of P^T.
 template <typename T>
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1);
@@ -327,7 +345,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
   static_assert(sizeof(T) == 2 && (D == 64 || D == 128), "16-bit inputs, head_dim 64 or 128");
   constexpr int KI = D / 32;      // 16-byte K chunks per thread and row
   constexpr int VX = D / 64;      // 16-byte V chunks per thread and row
-  constexpr int NT = D / 8;       // n-tiles of the P V product
+  constexpr int MT = D / 16;      // m-tiles of the transposed P V product
+  constexpr int HN = NH16 ? 2 : 1;  // n-tiles of heads
   constexpr int ROWS = NH16 ? 16 : 8;
   constexpr int NG = kDecWarps;
 
@@ -374,16 +393,28 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
   const T* kbase = static_cast<const T*>(p.k) + (PAGED ? 0 : b * p.ks[0]) + (int64_t)kvh * p.ks[1];
   const T* vbase = static_cast<const T*>(p.v) + (PAGED ? 0 : b * p.vs[0]) + (int64_t)kvh * p.vs[1];
 
-  float acc[NT][4];
+  float acc[MT][HN][4];   // O^T: rows d_lo(m) (regs 0,1) and d_hi(m) (regs 2,3), columns heads 2c, 2c+1 (+8 per n-tile)
 #pragma unroll
-  for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+  for (int j = 0; j < MT; ++j)
+#pragma unroll
+    for (int hn = 0; hn < HN; ++hn) acc[j][hn][0] = acc[j][hn][1] = acc[j][hn][2] = acc[j][hn][3] = 0.f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8; l is this thread's share of the sum
 
-  // Pool row of key kb + idx (idx < 16), or -1 beyond the chunk.
+  bool bad_block = false;
+  // Paged: raw block-table entry of key kb + (lane % 16), read two steps ahead; rows_from turns it into the pool row
+  // (-1 beyond the chunk) when the step's loads are issued.
   auto rows_of = [&](int64_t kb) -> int32_t {
     if constexpr (PAGED) {
       const int64_t key = kb + (lane & 15);
-      return key < end ? (int32_t)kv_row_of(p, b, key) : -1;
+      return key < end ? kv_block_read(p, b, key) : 0;
+    } else {
+      return 0;
+    }
+  };
+  auto rows_from = [&](int32_t entries, int64_t kb) -> int32_t {
+    if constexpr (PAGED) {
+      const int64_t key = kb + (lane & 15);
+      return key < end ? (int32_t)kv_row_from(p, key, entries, bad_block) : -1;
     } else {
       return 0;
     }
@@ -417,7 +448,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
 
   constexpr int kStep = 16;
   int64_t kb = start + warp * kStep;
-  int32_t rows = rows_of(kb);
+  int32_t rows = rows_from(rows_of(kb), kb);
+  int32_t ent_next = rows_of(kb + NG * kStep);   // block-table reads run ahead of the loads that need them
   if (kb < end) {
     load_k(rows, kb);
     load_v(rows, kb);
@@ -438,7 +470,8 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
     }
     // the next step's keys are requested while this step's softmax and P V run
     const int64_t kb_next = kb + NG * kStep;
-    const int32_t rows_next = rows_of(kb_next);
+    const int32_t rows_next = rows_from(ent_next, kb_next);
+    ent_next = rows_of(kb_next + NG * kStep);
     if (kb_next < end) load_k(rows_next, kb_next);
 
     // ---- online softmax over the step's 16 keys ---------------------------------------------------------
@@ -486,39 +519,58 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
       l1 = l1 * c1 + s1;
       m0 = n0;
       m1 = n1;
-      if (c0 != 1.f || (NH16 && c1 != 1.f)) {
+      // the accumulator columns are heads 2c, 2c+1 (+8): fetch their correction factors from the lanes that own them
+      const float ca = __shfl_sync(0xffffffffu, c0, 8 * c), cb = __shfl_sync(0xffffffffu, c0, 8 * c + 4);
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-          acc[j][0] *= c0;
-          acc[j][1] *= c0;
-          if (NH16) {
-            acc[j][2] *= c1;
-            acc[j][3] *= c1;
-          }
+      for (int j = 0; j < MT; ++j) {
+        acc[j][0][0] *= ca;
+        acc[j][0][1] *= cb;
+        acc[j][0][2] *= ca;
+        acc[j][0][3] *= cb;
+      }
+      if (NH16) {
+        const float cc = __shfl_sync(0xffffffffu, c1, 8 * c), cd = __shfl_sync(0xffffffffu, c1, 8 * c + 4);
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          acc[j][HN - 1][0] *= cc;
+          acc[j][HN - 1][1] *= cd;
+          acc[j][HN - 1][2] *= cc;
+          acc[j][HN - 1][3] *= cd;
         }
       }
     }
-    const uint32_t pa0 = pack_pair<T>(pr[0][0], pr[0][1]), pa1 = pack_pair<T>(pr[0][2], pr[0][3]);
-    const uint32_t pa2 = pack_pair<T>(pr[1][0], pr[1][1]), pa3 = pack_pair<T>(pr[1][2], pr[1][3]);
+    // P^T as B fragments: (keys 2c, 2c+1) and (keys 2c+8, 2c+9) of head g, and of head g+8
+    const uint32_t pb0 = pack_pair<T>(pr[0][0], pr[0][1]), pb1 = pack_pair<T>(pr[1][0], pr[1][1]);
+    const uint32_t pc0 = pack_pair<T>(pr[0][2], pr[0][3]), pc1 = pack_pair<T>(pr[1][2], pr[1][3]);
 
-    // ---- O += P V ----------------------------------------------------------------------------------------
+    // ---- O^T += V^T P^T ------------------------------------------------------------------------------------
+    {
+      uint32_t vw[4][VX][4];
 #pragma unroll
-    for (int x = 0; x < VX; ++x) {
-      const uint32_t r0[4] = {vreg[0][x].x, vreg[0][x].y, vreg[0][x].z, vreg[0][x].w};
-      const uint32_t r1[4] = {vreg[1][x].x, vreg[1][x].y, vreg[1][x].z, vreg[1][x].w};
-      const uint32_t r2[4] = {vreg[2][x].x, vreg[2][x].y, vreg[2][x].z, vreg[2][x].w};
-      const uint32_t r3[4] = {vreg[3][x].x, vreg[3][x].y, vreg[3][x].z, vreg[3][x].w};
+      for (int e = 0; e < 4; ++e)
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        // low halves: d = 2w, high halves: d = 2w + 1 of the chunk; two keys of one d share a register
-        mma16816<T>(acc[x * 8 + 2 * w], pa0, pa1, pa2, pa3, __byte_perm(r0[w], r1[w], 0x5410), __byte_perm(r2[w], r3[w], 0x5410));
-        mma16816<T>(acc[x * 8 + 2 * w + 1], pa0, pa1, pa2, pa3, __byte_perm(r0[w], r1[w], 0x7632), __byte_perm(r2[w], r3[w], 0x7632));
+        for (int x = 0; x < VX; ++x) {
+          vw[e][x][0] = vreg[e][x].x; vw[e][x][1] = vreg[e][x].y; vw[e][x][2] = vreg[e][x].z; vw[e][x][3] = vreg[e][x].w;
+        }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        // element m of the row's chunk; two keys of one d are paired in one register by a byte permute
+        const uint32_t sel = (m & 1) ? 0x7632u : 0x5410u;
+        constexpr int xh = VX - 1;                              // chunk holding rows g+8
+        const int wl = m >> 1, wh = (D == 128) ? (m >> 1) : 2 + (m >> 1);
+        const uint32_t a0 = __byte_perm(vw[0][0][wl], vw[1][0][wl], sel);
+        const uint32_t a1 = __byte_perm(vw[0][xh][wh], vw[1][xh][wh], sel);
+        const uint32_t a2 = __byte_perm(vw[2][0][wl], vw[3][0][wl], sel);
+        const uint32_t a3 = __byte_perm(vw[2][xh][wh], vw[3][xh][wh], sel);
+        mma16816<T>(acc[m][0], a0, a1, a2, a3, pb0, pb1);
+        if (NH16) mma16816<T>(acc[m][HN - 1], a0, a1, a2, a3, pc0, pc1);
       }
     }
     if (kb_next < end) load_v(rows_next, kb_next);
     rows = rows_next;
   }
 
+  report_bad_block(p, bad_block);
   // ---- merge the warps of the CTA ---------------------------------------------------------------------------
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
   l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -533,14 +585,15 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
     }
   }
 #pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    const int x = j >> 3, w = (j >> 1) & 3, hh = j & 1;
+  for (int m = 0; m < MT; ++m) {
+    const int d_lo = g * 8 + m, d_hi = (D == 128) ? (g + 8) * 8 + m : g * 8 + 4 + m;
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int d = ((2 * c + e) + 8 * x) * 8 + 2 * w + hh;
-      sm_acc[warp][g][d] = acc[j][e];
-      if (NH16) sm_acc[warp][g + 8][d] = acc[j][2 + e];
-    }
+    for (int hn = 0; hn < HN; ++hn)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        sm_acc[warp][8 * hn + 2 * c + e][d_lo] = acc[m][hn][e];
+        sm_acc[warp][8 * hn + 2 * c + e][d_hi] = acc[m][hn][2 + e];
+      }
   }
   __syncthreads();
 
@@ -632,7 +685,7 @@ cudaError_t launch_partial(const SdpaParams& p, int chunk, int nchunks, float* w
 template <typename T, int D, bool NH16>
 cudaError_t launch_gqa(const SdpaParams& p, int chunk, int nchunks, float* ws, int direct, cudaStream_t stream) {
   const unsigned kvheads = (unsigned)(p.head_count / p.group);
-  const bool head_fast = p.ks[1] < p.ks[2] && nchunks <= 65535;
+  const bool head_fast = p.ks[1] < p.ks[2] && nchunks <= 65535 && !getenv("AIDN_EXP_NO_HEAD_FAST");
   const dim3 grid = head_fast ? dim3(kvheads, (unsigned)nchunks, (unsigned)p.batch)
                               : dim3((unsigned)nchunks, kvheads, (unsigned)p.batch);
   const bool paged = p.block_table != nullptr;

@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaPar
     if (c < kend) kend = c;
   }
 
+  bool bad_block = false;
   float m[kRowsPerWarp], l[kRowsPerWarp], acc[kRowsPerWarp][ND];
 #pragma unroll
   for (int r = 0; r < kRowsPerWarp; ++r) {
@@ -68,7 +69,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaPar
   for (int64_t j0 = 0; j0 < kend; j0 += kBN) {
     __syncthreads();  // previous tile fully consumed (also orders the Q stores before first use)
     if (paged) {
-      if (tid < kBN) kv_rows[tid] = (j0 + tid < kend) ? kv_row_of(p, b, j0 + tid) : -1;
+      if (tid < kBN) kv_rows[tid] = (j0 + tid < kend) ? kv_row_of(p, b, j0 + tid, bad_block) : -1;
       __syncthreads();
     }
     for (int idx = tid; idx < kBN * DMAX; idx += kWarps * 32) {
@@ -147,6 +148,7 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaPar
     __syncwarp();
   }
 
+  report_bad_block(p, bad_block);
 #pragma unroll
   for (int r = 0; r < kRowsPerWarp; ++r) {
     const int64_t row = row0 + warp * kRowsPerWarp + r;

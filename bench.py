@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqapaged|c5shard] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard] [--impl reference]
 
 One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
 default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
@@ -46,6 +46,8 @@ WORKLOADS = {
                     name="paged_decode_B64_H32_D128_block16_kvlen512-4096_bf16"),
     "c4gqa": dict(B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
                   name="gqa_decode_B64_Hq32_Hkv8_D128_kvlen512-4096_bf16"),
+    "c4gqatm": dict(B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode", token_major=True,
+                    name="gqa_decode_token_major_cache_B64_Hq32_Hkv8_D128_kvlen512-4096_bf16"),
     "c4gqapaged": dict(B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode", block_size=16,
                        name="paged_gqa_decode_B64_Hq32_Hkv8_D128_block16_kvlen512-4096_bf16"),
 }
@@ -163,7 +165,7 @@ def make_inputs(w, device, seed):
 class Runner:
     """One workload bound to one handle of the C ABI; `step()` enqueues one forward pass."""
 
-    def __init__(self, w, device_index, seed):
+    def __init__(self, w, device_index, seed, decode_chunk=0):
         from aidotnet.tensors_b200 import native as N
         self.N = N
         self.w = w
@@ -173,15 +175,24 @@ class Runner:
         self.out = torch.empty((w["B"], w["Hq"], w["Sq"], w["D"]), dtype=torch.float32, device=dev)
         self.h = N.Handle(device=device_index, qkv_dtype=N.BF16, out_dtype=N.F32, head_dim=w["D"], num_q_heads=w["Hq"],
                           num_kv_heads=w["Hkv"], causal=w["causal"], causal_bottom_right=True,
-                          max_batch=w["B"], max_seq_q=w["Sq"], max_seq_kv=w["Sk"])
+                          max_batch=w["B"], max_seq_q=w["Sq"], max_seq_kv=w["Sk"], decode_chunk=decode_chunk)
         self.stream = torch.cuda.current_stream(dev).cuda_stream
         self.launches = 0
         self.paged = {}
+        if w.get("token_major"):   # the cache stored [B, S, Hkv, D], as a KV-cache append writes it
+            self.k = self.k.permute(0, 2, 1, 3).contiguous()
+            self.v = self.v.permute(0, 2, 1, 3).contiguous()
+            st = (w["Sk"] * w["Hkv"] * w["D"], w["D"], w["Hkv"] * w["D"])
+            self.paged = dict(k_stride=st, v_stride=st)
         bs = w.get("block_size")
         if bs:
             # Scatter the logical blocks of every sequence over one shared pool [blocks, bs, Hkv, D].
             nb = w["B"] * w["Sk"] // bs
             perm = torch.randperm(nb, generator=torch.Generator().manual_seed(seed & 0x7fffffff))
+            if os.environ.get("AIDN_EXP_TABLE") == "identity":
+                perm = torch.arange(nb)
+            elif os.environ.get("AIDN_EXP_TABLE") == "coarse":   # shuffle runs of 64 blocks (2 MiB of a GQA pool)
+                perm = (torch.randperm(nb // 64, generator=torch.Generator().manual_seed(1))[:, None] * 64 + torch.arange(64)[None]).reshape(-1)
             for name in ("k", "v"):
                 logical = getattr(self, name).permute(0, 2, 1, 3).reshape(nb, bs, w["Hkv"], w["D"])
                 pool = torch.empty_like(logical)
@@ -310,6 +321,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--decode-chunk", type=int, default=0, help="keys per split of the decode kernel (0 = library's choice)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     w = WORKLOADS[args.workload]
@@ -333,7 +345,7 @@ def main():
     if sampler:
         sampler.start()
 
-    runner = Runner(w, local, 0xA1D00000 + 2 + rank)
+    runner = Runner(w, local, 0xA1D00000 + 2 + rank, args.decode_chunk)
     kvh = runner.kv_len_host
     fl, by = algorithmic_flops(w, kvh), algorithmic_bytes(w, kvh)
     secs, launches = runner.time_steps(args.steps, args.warmup, sampler, dist)
