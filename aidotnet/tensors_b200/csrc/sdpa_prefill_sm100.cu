@@ -52,6 +52,7 @@ constexpr int kStageBytesPerWarp = 4096;   // epilogue staging: 32 rows x 128 B 
 constexpr int kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8 between rescales
 constexpr int kSchedConsumers = kSoftmaxWarps + 1;
+constexpr int kItemWords = 12;   // mailbox entry: item, b, kvh, n_max, then (h, t, n, valid) of both tiles
 
 template <int HD>
 struct Cfg {
@@ -63,8 +64,9 @@ struct Cfg {
   static constexpr int kBarOff = kStageOff + kSoftmaxWarps * kStageBytesPerWarp;
   // q_full[2] q_empty[2] kv_full[S] kv_empty[S] s_full[2] p_full[2] o_full[2] sched_full[2] sched_empty[2]
   static constexpr int kNumBars = 14 + 2 * kStages;
-  static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // sched_item[2], tmem ptr, abort flag
-  static constexpr int kSmemBytes = kMiscOff + 16 + 1024 /*align slack*/;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem ptr, abort flag, then the 2-slot item mailbox
+  static constexpr int kMailOff = kMiscOff + 16;
+  static constexpr int kSmemBytes = kMailOff + 2 * kItemWords * 4 + 1024 /*align slack*/;
   static constexpr int kOCol = 256;
 };
 
@@ -94,6 +96,29 @@ struct Item {
   TileInfo tile[2];
   int b, kvh, n_max;
 };
+
+// The producer decodes a work item once (two integer divisions and the tile counts) and hands the result to the
+// nine consumer warps through shared memory, so that none of them repeats that work on its critical path.
+__device__ __forceinline__ void publish_item(volatile int* box, int item, const Item& it) {
+  box[1] = it.b; box[2] = it.kvh; box[3] = it.n_max;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    box[4 + 4 * i] = it.tile[i].h; box[5 + 4 * i] = it.tile[i].t;
+    box[6 + 4 * i] = it.tile[i].n; box[7 + 4 * i] = it.tile[i].valid ? 1 : 0;
+  }
+  box[0] = item;
+}
+
+__device__ __forceinline__ Item read_item(const volatile int* box) {
+  Item it;
+  it.b = box[1]; it.kvh = box[2]; it.n_max = box[3];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    it.tile[i].h = box[4 + 4 * i]; it.tile[i].t = box[5 + 4 * i];
+    it.tile[i].n = box[6 + 4 * i]; it.tile[i].valid = box[7 + 4 * i] != 0;
+  }
+  return it;
+}
 
 __device__ __forceinline__ Item decode_item(const PrefillParams& pp, int item) {
   const SdpaParams& p = pp.p;
@@ -164,7 +189,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t bar_o_full = bar_p_full + 16;                 // [2]
   const uint32_t bar_sched_full = bar_o_full + 16;             // [2]
   const uint32_t bar_sched_empty = bar_sched_full + 16;        // [2]
-  volatile int* sched_item = reinterpret_cast<volatile int*>(smem_gen + C::kMiscOff);  // [2]
+  volatile int* mailbox = reinterpret_cast<volatile int*>(smem_gen + C::kMailOff);  // [2][kItemWords]
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::kMiscOff + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kMiscOff + 12);
 
@@ -234,12 +259,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         bool ok = mbar_wait(bar_sched_full + 8 * slot, (uint32_t)((seq >> 1) & 1), abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
-        item = sched_item[slot];
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_sched_empty + 8 * slot);
+        item = mailbox[slot * kItemWords];
       }
-      if (item >= pp.total_items) break;
-      const Item it = decode_item(pp, item);
+      if (item >= pp.total_items) break;   // no further mailbox traffic after the end marker
+      const Item it = read_item(mailbox + (seq & 1) * kItemWords);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_sched_empty + 8 * (seq & 1));
       const TileInfo ti = it.tile[i];
       if (!ti.valid) continue;
       const int b = it.b;
@@ -517,12 +542,17 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int seq = 0; alive; ++seq) {
         const int slot = seq & 1;
         if (!mbar_wait(bar_sched_empty + 8 * slot, (uint32_t)(((seq >> 1) & 1) ^ 1), abort_flag, wait_ns)) break;
+        Item it;
+        if (item < pp.total_items) it = decode_item(pp, item);
         if (leader) {
-          sched_item[slot] = item;
+          if (item < pp.total_items) publish_item(mailbox + slot * kItemWords, item, it);
+          else mailbox[slot * kItemWords] = item;   // end marker
           mbar_arrive(bar_sched_full + 8 * slot);
         }
         if (item >= pp.total_items) break;
-        const Item it = decode_item(pp, item);
+        unsigned long long* ptrace = pp.debug_mode == 2
+            ? reinterpret_cast<unsigned long long*>(pp.debug) + (size_t)item * 16 : nullptr;
+        if (ptrace && leader) ptrace[6] = globaltimer_ns();
         auto load_tile = [&](const CUtensorMap* tm, uint32_t dst, uint32_t bar, int row, int head) {
           if (leader) {
             mbar_expect_tx(bar, (uint32_t)C::kTileBytes);
@@ -581,6 +611,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (it.n_max > 0) {
           load_q(0);
           if (alive) load_kv(&tm_k, 0, true);
+          if (ptrace && leader) ptrace[0] = globaltimer_ns();
           if (alive) load_q(1);
           for (int j = 0; j < it.n_max && alive; ++j) {
             load_kv(&tm_v, j, false);
@@ -612,12 +643,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         {
           const int slot = seq & 1;
           if (!mbar_wait(bar_sched_full + 8 * slot, (uint32_t)((seq >> 1) & 1), abort_flag, wait_ns)) break;
-          item = sched_item[slot];
-          __syncwarp();
-          if (leader) mbar_arrive(bar_sched_empty + 8 * slot);
+          item = mailbox[slot * kItemWords];
         }
         if (item >= pp.total_items) break;
-        const Item it = decode_item(pp, item);
+        const Item it = read_item(mailbox + (seq & 1) * kItemWords);
+        __syncwarp();
+        if (leader) mbar_arrive(bar_sched_empty + 8 * (seq & 1));
+        unsigned long long* mtrace = pp.debug_mode == 2
+            ? reinterpret_cast<unsigned long long*>(pp.debug) + (size_t)item * 16 : nullptr;
+        if (mtrace && leader) mtrace[7] = globaltimer_ns();
         if (it.n_max == 0) continue;
         auto kv_slot = [&](uint32_t t) { return (int)(t % C::kStages); };
         auto kv_wait = [&](uint32_t t) {
@@ -653,9 +687,11 @@ __global__ void __launch_bounds__(kThreads, 1)
         // S_i(0) = Q_i K_0^T
         const uint32_t t0 = t_cons;   // ring index of K_0 of this item; V_j is t0 + 2j + 1, K_{j+1} is t0 + 2j + 2
         const uint32_t kaddr = kv_wait(t0);
+        if (mtrace && leader) mtrace[14] = globaltimer_ns();
         for (int i = 0; i < 2 && alive; ++i) {
           if (it.tile[i].n == 0) continue;
           if (!mbar_wait(bar_q_full + 8 * i, q_uses[i] & 1u, abort_flag, wait_ns)) { alive = false; break; }
+          if (mtrace && leader && i == 0) mtrace[8] = globaltimer_ns();
           ++q_uses[i];
           tc_fence_after();
           issue_qk(i, kaddr, it.tile[i].n == 1);
