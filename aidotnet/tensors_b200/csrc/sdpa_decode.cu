@@ -18,6 +18,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "sm100_ptx.cuh"
 
 namespace aidn {
 namespace {
@@ -629,6 +630,345 @@ __global__ void __launch_bounds__(kDecWarps * 32, 2)
   }
 }
 
+// ---- the same kernel fed through shared memory -------------------------------------------------------------------
+// The register-fed kernel above keeps at most one step of K and one of V per warp in flight (its prefetch lives in
+// registers), which leaves the warps waiting on HBM latency.  Here each warp owns a ring of kRingStages
+// shared-memory stages (16 keys of K and 16 of V each) filled with 16-byte cp.async copies - a warp-wide copy moves
+// two whole rows, so requests are fully coalesced - and retired in order with cp.async.wait_group: up to
+// kRingStages steps per warp are in flight whatever the register budget, there is no flag to spin on, and rows
+// past the chunk's end or outside the pool are zero-filled by the copy itself (source size 0).  Rows are stored
+// un-padded with their 16-byte chunks XOR-swizzled (K: chunk ^ 4*(row & 1); V: chunk ^ 2*((row / 2) & 3)) so that
+// the fragment reads of both products are bank-conflict free.  Fragment geometry and arithmetic are those of the
+// kernel above.  After the loop a warp reuses its own ring for the partials it hands to the merge.
+constexpr int kRingStages = 3;
+
+template <int D>
+struct RingCfg {
+  static constexpr int kRowBytes = D * 2;
+  static constexpr int kKBytes = 16 * kRowBytes;
+  static constexpr int kStageBytes = 2 * kKBytes;
+  static constexpr int kWarpBytes = kRingStages * kStageBytes;
+  static constexpr int kSmemBytes = kDecWarps * kWarpBytes;
+  static_assert(kWarpBytes >= 16 * (D + 2) * 4, "a warp's partials must fit in its ring");
+};
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const uint32_t n = valid ? 16u : 0u;   // 0: nothing is read and the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T, int D, bool NH16, bool PAGED, bool HEAD_FAST>
+__global__ void __launch_bounds__(kDecWarps * 32, 2)
+    sdpa_decode_gqa_ring_kernel(const SdpaParams p, const int chunk, const int nchunks, float* __restrict__ ws,
+                                const int direct) {
+  static_assert(sizeof(T) == 2 && (D == 64 || D == 128), "16-bit inputs, head_dim 64 or 128");
+  using R = RingCfg<D>;
+  constexpr int KI = D / 32, VX = D / 64, MT = D / 16;
+  constexpr int HN = NH16 ? 2 : 1;
+  constexpr int ROWS = NH16 ? 16 : 8;
+  constexpr int NG = kDecWarps;
+  constexpr int kStep = 16;
+
+  extern __shared__ __align__(128) uint8_t ring_smem[];
+  const uint32_t smem0 = ptx::smem_u32(ring_smem);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int b = blockIdx.z;
+  const int kvh = p.head_begin / p.group + (HEAD_FAST ? (int)blockIdx.x : (int)blockIdx.y);
+  const int h0 = kvh * p.group;
+  const int nheads = p.group;
+  const int cidx = HEAD_FAST ? blockIdx.y : blockIdx.x;
+
+  const int64_t L = decode_len(p, b);
+  const int64_t start = (int64_t)cidx * chunk;
+  const int Hc = p.head_count;
+
+  if (start >= L) {
+    if (direct && cidx == 0) {
+      for (int idx = tid; idx < nheads * D; idx += kDecWarps * 32) {
+        const int hh = idx / D, d = idx - hh * D;
+        store_out<T>(p.out, b * p.os[0] + (int64_t)(h0 + hh) * p.os[1] + d, 0.f, p.out_f32);
+        if (p.lse && d == 0) p.lse[((int64_t)b * p.num_q_heads + h0 + hh) * p.seq_q] = -INFINITY;
+      }
+    }
+    return;
+  }
+  const int64_t end = (start + chunk < L) ? start + chunk : L;
+
+  const uint32_t my_ring = smem0 + warp * R::kWarpBytes;
+  const T* kbase = static_cast<const T*>(p.k) + (PAGED ? 0 : b * p.ks[0]) + (int64_t)kvh * p.ks[1];
+  const T* vbase = static_cast<const T*>(p.v) + (PAGED ? 0 : b * p.vs[0]) + (int64_t)kvh * p.vs[1];
+  bool bad_block = false;
+
+  constexpr int CH = D / 8;          // 16-byte chunks per row
+  constexpr int RPL = 16 * CH / 32;  // rows each lane copies per step (of K, and of V)
+  const int my_ch = lane % CH, my_r0 = lane / CH;
+  // Raw block-table entry of key kb + lane % 16 (paged), read a step before the copies that need it are issued.
+  auto entry_of = [&](int64_t kb) -> int32_t {
+    if constexpr (PAGED) {
+      const int64_t key = kb + (lane & 15);
+      return key < end ? kv_block_read(p, b, key) : 0;
+    } else {
+      return 0;
+    }
+  };
+  // Issues the copies of the step at kb into `stage` and commits them as one group.  Returns the step's row mask
+  // (bit i: key kb + i is inside the chunk and its row inside the pool); the other rows are zero-filled.
+  auto issue = [&](int stage, int64_t kb, int32_t entry) -> uint32_t {
+    const int64_t key = kb + (lane & 15);
+    int64_t row = -1;
+    if (key < end) {
+      if constexpr (PAGED) row = kv_row_from(p, key, entry, bad_block);
+      else row = key;
+    }
+    const uint32_t base = my_ring + stage * R::kStageBytes;
+#pragma unroll
+    for (int r = 0; r < RPL; ++r) {
+      const int ri = my_r0 + (32 / CH) * r;
+      const int64_t rr = __shfl_sync(0xffffffffu, row, ri);
+      const bool valid = rr >= 0;
+      const int64_t ro = valid ? rr : 0;
+      cp_async16(base + ri * R::kRowBytes + ((my_ch ^ ((ri & 1) << 2)) << 4), kbase + ro * p.ks[2] + my_ch * 8, valid);
+      cp_async16(base + R::kKBytes + ri * R::kRowBytes + ((my_ch ^ (((ri >> 1) & 3) << 1)) << 4),
+                 vbase + ro * p.vs[2] + my_ch * 8, valid);
+    }
+    cp_async_commit();
+    return __ballot_sync(0xffffffffu, row >= 0) & 0xffffu;
+  };
+
+  // Q in fragment order
+  uint32_t qa[KI][4], qb[KI][4];
+#pragma unroll
+  for (int i = 0; i < KI; ++i) {
+    uint4 u = make_uint4(0, 0, 0, 0), w = make_uint4(0, 0, 0, 0);
+    if (g < nheads)
+      u = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + b * p.qs[0] + (int64_t)(h0 + g) * p.qs[1] + (i * 4 + c) * 8);
+    if (NH16 && g + 8 < nheads)
+      w = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + b * p.qs[0] + (int64_t)(h0 + g + 8) * p.qs[1] + (i * 4 + c) * 8);
+    qa[i][0] = u.x; qa[i][1] = u.y; qa[i][2] = u.z; qa[i][3] = u.w;
+    qb[i][0] = w.x; qb[i][1] = w.y; qb[i][2] = w.z; qb[i][3] = w.w;
+  }
+
+  float acc[MT][HN][4];
+#pragma unroll
+  for (int j = 0; j < MT; ++j)
+#pragma unroll
+    for (int hn = 0; hn < HN; ++hn) acc[j][hn][0] = acc[j][hn][1] = acc[j][hn][2] = acc[j][hn][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+  // prologue: fill the ring (a group is committed per stage even when it is empty, so that wait_group counts steps)
+  const int64_t kb0 = start + warp * kStep;
+  constexpr int64_t kStride = NG * kStep;
+  uint32_t row_mask[kRingStages];
+#pragma unroll
+  for (int s = 0; s < kRingStages; ++s) {
+    const int64_t kbs = kb0 + s * kStride;
+    row_mask[s] = 0;
+    if (kbs < end) row_mask[s] = issue(s, kbs, entry_of(kbs));
+    else cp_async_commit();
+  }
+  int32_t ent_next = entry_of(kb0 + kRingStages * kStride);
+
+  int step = 0;
+  for (int64_t kb = kb0; kb < end; kb += kStride, ++step) {
+    const int stage = step % kRingStages;
+    cp_async_wait<kRingStages - 1>();   // this step's group has landed (later steps may still be in flight)
+    __syncwarp();                       // ... for every lane's copies
+    const uint32_t base = my_ring + stage * R::kStageBytes;
+    uint32_t rows_ok = 0;
+#pragma unroll
+    for (int s = 0; s < kRingStages; ++s)
+      if (s == stage) rows_ok = row_mask[s];
+
+    // ---- S = Q K^T ------------------------------------------------------------------------------------
+    float sacc[2][4];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      sacc[t][0] = sacc[t][1] = sacc[t][2] = sacc[t][3] = 0.f;
+#pragma unroll
+      for (int i = 0; i < KI; ++i) {
+        uint32_t kw[4];
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(kw[0]), "=r"(kw[1]), "=r"(kw[2]), "=r"(kw[3])
+                     : "r"(base + (t * 8 + g) * R::kRowBytes + (((i * 4 + c) ^ ((g & 1) << 2)) << 4)));
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+          mma16816<T>(sacc[t], qa[i][2 * h], qb[i][2 * h], qa[i][2 * h + 1], qb[i][2 * h + 1], kw[2 * h], kw[2 * h + 1]);
+      }
+    }
+    // ---- V fragments to registers, then the stage is free for the copies two steps ahead ---------------
+    uint32_t vw[4][VX][4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+#pragma unroll
+      for (int x = 0; x < VX; ++x) {
+        const int vr = 2 * c + (e & 1) + (e >> 1) * 8;   // (vr / 2) & 3 == c
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(vw[e][x][0]), "=r"(vw[e][x][1]), "=r"(vw[e][x][2]), "=r"(vw[e][x][3])
+                     : "r"(base + R::kKBytes + vr * R::kRowBytes + (((g + 8 * x) ^ (c << 1)) << 4)));
+      }
+    __syncwarp();   // every lane has read the stage: refill it with the step kRingStages ahead
+    {
+      const int64_t kb_new = kb + kRingStages * kStride;
+      const int32_t ent_new = ent_next;
+      ent_next = entry_of(kb_new + kStride);
+      uint32_t mask_new = 0;
+      if (kb_new < end) mask_new = issue(stage, kb_new, ent_new);
+      else cp_async_commit();
+#pragma unroll
+      for (int s = 0; s < kRingStages; ++s)
+        if (s == stage) row_mask[s] = mask_new;
+    }
+
+    // ---- online softmax over the step's 16 keys ---------------------------------------------------------
+    float pr[2][4];
+    {
+      float mt0 = -INFINITY, mt1 = -INFINITY;
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int idx = t * 8 + 2 * c + e;
+          const int64_t key = kb + idx;
+          const bool ok = (rows_ok >> idx) & 1u;
+          float v0 = -INFINITY, v1 = -INFINITY;
+          if (ok && g < nheads) v0 = finish_logit(p, sacc[t][e] * p.scale, b, h0 + g, 0, key, L);
+          if (NH16 && ok && g + 8 < nheads) v1 = finish_logit(p, sacc[t][2 + e] * p.scale, b, h0 + g + 8, 0, key, L);
+          sacc[t][e] = v0;
+          sacc[t][2 + e] = v1;
+          mt0 = fmaxf(mt0, v0);
+          mt1 = fmaxf(mt1, v1);
+        }
+      mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 1));
+      mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 2));
+      if (NH16) {
+        mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 1));
+        mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 2));
+      }
+      const float n0 = fmaxf(m0, mt0), n1 = fmaxf(m1, mt1);
+      const float c0 = (m0 == -INFINITY) ? 0.f : softmax_exp<T>(m0 - n0);
+      const float c1 = (m1 == -INFINITY) ? 0.f : softmax_exp<T>(m1 - n1);
+      float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          pr[t][e] = (sacc[t][e] == -INFINITY) ? 0.f : softmax_exp<T>(sacc[t][e] - n0);
+          pr[t][2 + e] = (!NH16 || sacc[t][2 + e] == -INFINITY) ? 0.f : softmax_exp<T>(sacc[t][2 + e] - n1);
+          s0 += pr[t][e];
+          s1 += pr[t][2 + e];
+        }
+      l0 = l0 * c0 + s0;
+      l1 = l1 * c1 + s1;
+      m0 = n0;
+      m1 = n1;
+      const float ca = __shfl_sync(0xffffffffu, c0, 8 * c), cb = __shfl_sync(0xffffffffu, c0, 8 * c + 4);
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        acc[j][0][0] *= ca;
+        acc[j][0][1] *= cb;
+        acc[j][0][2] *= ca;
+        acc[j][0][3] *= cb;
+      }
+      if (NH16) {
+        const float cc = __shfl_sync(0xffffffffu, c1, 8 * c), cd = __shfl_sync(0xffffffffu, c1, 8 * c + 4);
+#pragma unroll
+        for (int j = 0; j < MT; ++j) {
+          acc[j][HN - 1][0] *= cc;
+          acc[j][HN - 1][1] *= cd;
+          acc[j][HN - 1][2] *= cc;
+          acc[j][HN - 1][3] *= cd;
+        }
+      }
+    }
+    const uint32_t pb0 = pack_pair<T>(pr[0][0], pr[0][1]), pb1 = pack_pair<T>(pr[1][0], pr[1][1]);
+    const uint32_t pc0 = pack_pair<T>(pr[0][2], pr[0][3]), pc1 = pack_pair<T>(pr[1][2], pr[1][3]);
+
+    // ---- O^T += V^T P^T ------------------------------------------------------------------------------------
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const uint32_t sel = (m & 1) ? 0x7632u : 0x5410u;
+      constexpr int xh = VX - 1;
+      const int wl = m >> 1, wh = (D == 128) ? (m >> 1) : 2 + (m >> 1);
+      const uint32_t a0 = __byte_perm(vw[0][0][wl], vw[1][0][wl], sel);
+      const uint32_t a1 = __byte_perm(vw[0][xh][wh], vw[1][xh][wh], sel);
+      const uint32_t a2 = __byte_perm(vw[2][0][wl], vw[3][0][wl], sel);
+      const uint32_t a3 = __byte_perm(vw[2][xh][wh], vw[3][xh][wh], sel);
+      mma16816<T>(acc[m][0], a0, a1, a2, a3, pb0, pb1);
+      if (NH16) mma16816<T>(acc[m][HN - 1], a0, a1, a2, a3, pc0, pc1);
+    }
+  }
+
+  report_bad_block(p, bad_block);
+  cp_async_wait<0>();
+  __syncwarp();
+  // The warp's ring is free now: its partials go there.
+  float* sm_acc = reinterpret_cast<float*>(ring_smem + warp * R::kWarpBytes);   // [ROWS][D], then m[ROWS], l[ROWS]
+  float* sm_m = sm_acc + ROWS * D;
+  float* sm_l = sm_m + ROWS;
+  constexpr int kWarpFloats = R::kWarpBytes / 4;
+  // ---- merge the warps of the CTA ---------------------------------------------------------------------------
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (c == 0) {
+    sm_m[g] = m0;
+    sm_l[g] = l0;
+    if (NH16) {
+      sm_m[g + 8] = m1;
+      sm_l[g + 8] = l1;
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    const int d_lo = g * 8 + m, d_hi = (D == 128) ? (g + 8) * 8 + m : g * 8 + 4 + m;
+#pragma unroll
+    for (int hn = 0; hn < HN; ++hn)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        sm_acc[(8 * hn + 2 * c + e) * D + d_lo] = acc[m][hn][e];
+        sm_acc[(8 * hn + 2 * c + e) * D + d_hi] = acc[m][hn][2 + e];
+      }
+  }
+  __syncthreads();
+
+  const float* all = reinterpret_cast<const float*>(ring_smem);   // warp n's partials start at n * kWarpFloats
+  for (int idx = tid; idx < nheads * D; idx += kDecWarps * 32) {
+    const int hh = idx / D, d = idx - hh * D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < NG; ++n) M = fmaxf(M, all[n * kWarpFloats + ROWS * D + hh]);
+    float a = 0.f, lsum = 0.f;
+    if (M != -INFINITY) {
+#pragma unroll
+      for (int n = 0; n < NG; ++n) {
+        const float mn = all[n * kWarpFloats + ROWS * D + hh];
+        const float wgt = (mn == -INFINITY) ? 0.f : softmax_exp<T>(mn - M);
+        a = fmaf(wgt, all[n * kWarpFloats + hh * D + d], a);
+        lsum = fmaf(wgt, all[n * kWarpFloats + ROWS * D + ROWS + hh], lsum);
+      }
+    }
+    const int h = h0 + hh;
+    if (direct) {
+      store_out<T>(p.out, b * p.os[0] + (int64_t)h * p.os[1] + d, lsum > 0.f ? a / lsum : 0.f, p.out_f32);
+      if (p.lse && d == 0)
+        p.lse[((int64_t)b * p.num_q_heads + h) * p.seq_q] = lsum > 0.f ? M + logf(lsum) : -INFINITY;
+    } else {
+      const int64_t slot = ((int64_t)b * Hc + (h - p.head_begin)) * nchunks + cidx;
+      ws[slot * D + d] = a;
+      if (d == 0) {
+        float* ml = ws + (int64_t)p.batch * Hc * nchunks * D;
+        ml[slot * 2] = M;
+        ml[slot * 2 + 1] = lsum;
+      }
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
     sdpa_decode_combine_kernel(const SdpaParams p, const int chunk, const int nchunks, const float* __restrict__ ws) {
@@ -689,8 +1029,14 @@ cudaError_t launch_gqa(const SdpaParams& p, int chunk, int nchunks, float* ws, i
   const dim3 grid = head_fast ? dim3(kvheads, (unsigned)nchunks, (unsigned)p.batch)
                               : dim3((unsigned)nchunks, kvheads, (unsigned)p.batch);
   const bool paged = p.block_table != nullptr;
-#define AIDN_GQA_LAUNCH(PG, HF) \
-  sdpa_decode_gqa_kernel<T, D, NH16, PG, HF><<<grid, kDecWarps * 32, 0, stream>>>(p, chunk, nchunks, ws, direct)
+  constexpr int smem = RingCfg<D>::kSmemBytes;
+#define AIDN_GQA_LAUNCH(PG, HF)                                                                                 \
+  do {                                                                                                          \
+    auto kern = sdpa_decode_gqa_ring_kernel<T, D, NH16, PG, HF>;                                                \
+    cudaError_t ea = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);             \
+    if (ea != cudaSuccess) return ea;                                                                           \
+    kern<<<grid, kDecWarps * 32, smem, stream>>>(p, chunk, nchunks, ws, direct);                                \
+  } while (0)
   if (paged && head_fast) AIDN_GQA_LAUNCH(true, true);
   else if (paged) AIDN_GQA_LAUNCH(true, false);
   else if (head_fast) AIDN_GQA_LAUNCH(false, true);
