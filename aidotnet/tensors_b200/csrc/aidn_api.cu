@@ -86,17 +86,21 @@ namespace {
 // 512 keys per CTA so that ragged kv_len values balance, and never fewer than 64.
 int pick_chunk(const aidn_sdpa* h, int64_t batch, int64_t seq_kv) {
   if (h->d.decode_chunk > 0) return h->d.decode_chunk;
-  const int gt = h->group <= 2 ? h->group : (h->group <= 4 ? 4 : 8);  // as the decode launcher picks
+  const int gt = h->group <= 2 ? h->group : (h->group <= 4 ? 4 : 8);  // as the FFMA decode launcher picks
   int gchunks = (h->group + gt - 1) / gt;
-  // 16-bit inputs with 2..16 query heads per KV head run the tensor-core decode kernel: one CTA per KV head and split
-  if (h->d.qkv_dtype != AIDN_F32 && (h->d.head_dim == 64 || h->d.head_dim == 128) && h->group >= 2 && h->group <= 16)
+  int64_t cap = 512;
+  // 16-bit inputs with up to 16 query heads per KV head run the tensor-core decode kernel: one CTA per KV head and
+  // split, and chunks up to 1024 keys (its per-CTA prologue and merge are heavier, its steady state faster)
+  if (h->d.qkv_dtype != AIDN_F32 && (h->d.head_dim == 64 || h->d.head_dim == 128) && h->group <= 16) {
     gchunks = 1;
+    cap = 1024;
+  }
   const int64_t items = batch * (h->head_count / h->group) * gchunks;
   const int64_t target = 148 * 8;
   int64_t splits = (target + items - 1) / items;
   if (splits < 1) splits = 1;
   int64_t chunk = align_up((seq_kv + splits - 1) / splits, 64);
-  if (chunk > 512) chunk = 512;
+  if (chunk > cap) chunk = cap;
   if (chunk < 64) chunk = 64;
   return (int)chunk;
 }

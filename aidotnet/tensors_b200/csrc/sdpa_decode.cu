@@ -1,10 +1,14 @@
 // Split-KV decode (seq_q == 1): the HBM-bound half of the attention path.
 //
-// One CTA streams one chunk of one (batch, kv head)'s keys and values exactly once with 16-byte
-// coalesced loads (a key row of D elements is covered by D*sizeof(T)/16 adjacent lanes), serves all
-// query heads of that kv head from registers, and writes an un-normalised partial (max, sum, acc[D]);
-// a second kernel merges the partials of a (batch, head) by log-sum-exp.  Only keys below kv_len[b]
-// (and the causal limit) are touched, so padding costs no bandwidth.
+// One CTA streams one chunk of one (batch, kv head)'s keys and values exactly once, serves all query heads of that
+// kv head, and writes an un-normalised partial (max, sum, acc[D]); a second kernel merges the partials of a
+// (batch, head) by log-sum-exp.  Only keys below kv_len[b] (and the causal limit) are touched, so padding costs no
+// bandwidth.  Two partial kernels:
+//   * sdpa_decode_gqa_ring_kernel - fp16 / bf16, head_dim 64 or 128, up to 16 query heads per kv head (plain
+//     multi-head attention included): K/V go through a per-warp cp.async shared-memory ring and both products run
+//     on mma.sync with the heads as the M / N dimension.  This is the kernel the benchmark's decode step uses.
+//   * sdpa_decode_partial_kernel  - everything else (fp32 inputs, head_dim 256, more than 16 heads per kv head):
+//     16-byte streaming loads straight into registers and FFMA arithmetic.
 //
 // Supersedes flash_decode_partial / flash_decode_reduce of the reference
 // (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/CudaFlashDecodeKernels.cs:19-81), which run one
@@ -14,7 +18,6 @@
 // one thread per head over the whole sequence.
 //
 // Scratch layout (fp32): acc[B][Hc][nchunks][D] followed by ml[B][Hc][nchunks][2], Hc = heads of the shard.
-#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -338,308 +341,15 @@ __device__ __forceinline__ uint32_t pack_pair<__half>(float lo, float hi) {
   return r;
 }
 
+// Feeding: each warp owns a ring of kRingStages shared-memory stages (16 keys of K and 16 of V each) filled with
+// 16-byte cp.async copies - a warp-wide copy moves two whole rows, so requests are fully coalesced - and retired in
+// order with cp.async.wait_group: up to kRingStages steps per warp are in flight whatever the register budget (a
+// variant that prefetched into registers held one step in flight and reached 0.71 of the HBM peak where this one
+// reaches 0.85), there is no flag to spin on, and rows past the chunk's end or outside the pool are zero-filled by
+// the copy itself (source size 0).  Rows are stored un-padded with their 16-byte chunks XOR-swizzled
+// (K: chunk ^ 4*(row & 1); V: chunk ^ 2*((row / 2) & 3)) so that the fragment reads of both products are
+// bank-conflict free.  After the loop a warp reuses its own ring for the partials it hands to the merge.
 // NH16: more than 8 query heads per KV head (rows 8..15 of the tile are live).
-template <typename T, int D, bool NH16, bool PAGED, bool HEAD_FAST>
-__global__ void __launch_bounds__(kDecWarps * 32, 2)
-    sdpa_decode_gqa_kernel(const SdpaParams p, const int chunk, const int nchunks, float* __restrict__ ws,
-                           const int direct) {
-  static_assert(sizeof(T) == 2 && (D == 64 || D == 128), "16-bit inputs, head_dim 64 or 128");
-  constexpr int KI = D / 32;      // 16-byte K chunks per thread and row
-  constexpr int VX = D / 64;      // 16-byte V chunks per thread and row
-  constexpr int MT = D / 16;      // m-tiles of the transposed P V product
-  constexpr int HN = NH16 ? 2 : 1;  // n-tiles of heads
-  constexpr int ROWS = NH16 ? 16 : 8;
-  constexpr int NG = kDecWarps;
-
-  __shared__ float sm_m[NG][ROWS];
-  __shared__ float sm_l[NG][ROWS];
-  __shared__ __align__(16) float sm_acc[NG][ROWS][D];
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = lane >> 2, c = lane & 3;
-  const int b = blockIdx.z;
-  const int kvh = p.head_begin / p.group + (HEAD_FAST ? (int)blockIdx.x : (int)blockIdx.y);
-  const int h0 = kvh * p.group;
-  const int nheads = p.group;
-  const int cidx = HEAD_FAST ? blockIdx.y : blockIdx.x;
-
-  const int64_t L = decode_len(p, b);
-  const int64_t start = (int64_t)cidx * chunk;
-  const int Hc = p.head_count;
-
-  if (start >= L) {
-    if (direct && cidx == 0) {
-      for (int idx = tid; idx < nheads * D; idx += kDecWarps * 32) {
-        const int hh = idx / D, d = idx - hh * D;
-        store_out<T>(p.out, b * p.os[0] + (int64_t)(h0 + hh) * p.os[1] + d, 0.f, p.out_f32);
-        if (p.lse && d == 0) p.lse[((int64_t)b * p.num_q_heads + h0 + hh) * p.seq_q] = -INFINITY;
-      }
-    }
-    return;
-  }
-  const int64_t end = (start + chunk < L) ? start + chunk : L;
-
-  // Q in fragment order: qa[i][0..3] = chunk i*4+c of head g, qb = head g+8 (zero rows beyond the group).
-  uint32_t qa[KI][4], qb[KI][4];
-#pragma unroll
-  for (int i = 0; i < KI; ++i) {
-    uint4 u = make_uint4(0, 0, 0, 0), w = make_uint4(0, 0, 0, 0);
-    if (g < nheads)
-      u = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + b * p.qs[0] + (int64_t)(h0 + g) * p.qs[1] + (i * 4 + c) * 8);
-    if (NH16 && g + 8 < nheads)
-      w = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.q) + b * p.qs[0] + (int64_t)(h0 + g + 8) * p.qs[1] + (i * 4 + c) * 8);
-    qa[i][0] = u.x; qa[i][1] = u.y; qa[i][2] = u.z; qa[i][3] = u.w;
-    qb[i][0] = w.x; qb[i][1] = w.y; qb[i][2] = w.z; qb[i][3] = w.w;
-  }
-  const T* kbase = static_cast<const T*>(p.k) + (PAGED ? 0 : b * p.ks[0]) + (int64_t)kvh * p.ks[1];
-  const T* vbase = static_cast<const T*>(p.v) + (PAGED ? 0 : b * p.vs[0]) + (int64_t)kvh * p.vs[1];
-
-  float acc[MT][HN][4];   // O^T: rows d_lo(m) (regs 0,1) and d_hi(m) (regs 2,3), columns heads 2c, 2c+1 (+8 per n-tile)
-#pragma unroll
-  for (int j = 0; j < MT; ++j)
-#pragma unroll
-    for (int hn = 0; hn < HN; ++hn) acc[j][hn][0] = acc[j][hn][1] = acc[j][hn][2] = acc[j][hn][3] = 0.f;
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8; l is this thread's share of the sum
-
-  bool bad_block = false;
-  // Paged: raw block-table entry of key kb + (lane % 16), read two steps ahead; rows_from turns it into the pool row
-  // (-1 beyond the chunk) when the step's loads are issued.
-  auto rows_of = [&](int64_t kb) -> int32_t {
-    if constexpr (PAGED) {
-      const int64_t key = kb + (lane & 15);
-      return key < end ? kv_block_read(p, b, key) : 0;
-    } else {
-      return 0;
-    }
-  };
-  auto rows_from = [&](int32_t entries, int64_t kb) -> int32_t {
-    if constexpr (PAGED) {
-      const int64_t key = kb + (lane & 15);
-      return key < end ? (int32_t)kv_row_from(p, key, entries, bad_block) : -1;
-    } else {
-      return 0;
-    }
-  };
-  auto row_at = [&](int32_t rows, int64_t kb, int idx) -> int64_t {
-    if constexpr (PAGED) {
-      return __shfl_sync(0xffffffffu, rows, idx);
-    } else {
-      return kb + idx < end ? kb + idx : -1;
-    }
-  };
-  uint4 kreg[2][KI], vreg[4][VX];
-  auto load_k = [&](int32_t rows, int64_t kb) {
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int64_t r = row_at(rows, kb, t * 8 + g);
-#pragma unroll
-      for (int i = 0; i < KI; ++i)
-        kreg[t][i] = r >= 0 ? ld_stream16(kbase + r * p.ks[2] + (i * 4 + c) * 8) : make_uint4(0, 0, 0, 0);
-    }
-  };
-  auto load_v = [&](int32_t rows, int64_t kb) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const int64_t r = row_at(rows, kb, 2 * c + (e & 1) + (e >> 1) * 8);
-#pragma unroll
-      for (int x = 0; x < VX; ++x)
-        vreg[e][x] = r >= 0 ? ld_stream16(vbase + r * p.vs[2] + (g + 8 * x) * 8) : make_uint4(0, 0, 0, 0);
-    }
-  };
-
-  constexpr int kStep = 16;
-  int64_t kb = start + warp * kStep;
-  int32_t rows = rows_from(rows_of(kb), kb);
-  int32_t ent_next = rows_of(kb + NG * kStep);   // block-table reads run ahead of the loads that need them
-  if (kb < end) {
-    load_k(rows, kb);
-    load_v(rows, kb);
-  }
-  for (; kb < end; kb += NG * kStep) {
-    // ---- S = Q K^T ------------------------------------------------------------------------------------
-    float sacc[2][4];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      sacc[t][0] = sacc[t][1] = sacc[t][2] = sacc[t][3] = 0.f;
-#pragma unroll
-      for (int i = 0; i < KI; ++i) {
-        const uint32_t kw[4] = {kreg[t][i].x, kreg[t][i].y, kreg[t][i].z, kreg[t][i].w};
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-          mma16816<T>(sacc[t], qa[i][2 * h], qb[i][2 * h], qa[i][2 * h + 1], qb[i][2 * h + 1], kw[2 * h], kw[2 * h + 1]);
-      }
-    }
-    // the next step's keys are requested while this step's softmax and P V run
-    const int64_t kb_next = kb + NG * kStep;
-    const int32_t rows_next = rows_from(ent_next, kb_next);
-    ent_next = rows_of(kb_next + NG * kStep);
-    if (kb_next < end) load_k(rows_next, kb_next);
-
-    // ---- online softmax over the step's 16 keys ---------------------------------------------------------
-    float pr[2][4];   // probabilities in the S fragment layout
-    {
-      float mt0 = -INFINITY, mt1 = -INFINITY;
-#pragma unroll
-      for (int t = 0; t < 2; ++t)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int64_t key = kb + t * 8 + 2 * c + e;
-          bool ok = key < end;
-          if constexpr (PAGED) {   // every lane takes part in the shuffle, whatever its own key is
-            const int32_t key_row = __shfl_sync(0xffffffffu, rows, t * 8 + 2 * c + e);
-            ok = ok && key_row >= 0;
-          }
-          float v0 = -INFINITY, v1 = -INFINITY;
-          if (ok && g < nheads) v0 = finish_logit(p, sacc[t][e] * p.scale, b, h0 + g, 0, key, L);
-          if (NH16 && ok && g + 8 < nheads) v1 = finish_logit(p, sacc[t][2 + e] * p.scale, b, h0 + g + 8, 0, key, L);
-          sacc[t][e] = v0;
-          sacc[t][2 + e] = v1;
-          mt0 = fmaxf(mt0, v0);
-          mt1 = fmaxf(mt1, v1);
-        }
-      mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 1));
-      mt0 = fmaxf(mt0, __shfl_xor_sync(0xffffffffu, mt0, 2));
-      if (NH16) {
-        mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 1));
-        mt1 = fmaxf(mt1, __shfl_xor_sync(0xffffffffu, mt1, 2));
-      }
-      const float n0 = fmaxf(m0, mt0), n1 = fmaxf(m1, mt1);
-      const float c0 = (m0 == -INFINITY) ? 0.f : softmax_exp<T>(m0 - n0);   // n0 == -inf only if m0 is, too
-      const float c1 = (m1 == -INFINITY) ? 0.f : softmax_exp<T>(m1 - n1);
-      float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-      for (int t = 0; t < 2; ++t)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          pr[t][e] = (sacc[t][e] == -INFINITY) ? 0.f : softmax_exp<T>(sacc[t][e] - n0);
-          pr[t][2 + e] = (!NH16 || sacc[t][2 + e] == -INFINITY) ? 0.f : softmax_exp<T>(sacc[t][2 + e] - n1);
-          s0 += pr[t][e];
-          s1 += pr[t][2 + e];
-        }
-      l0 = l0 * c0 + s0;
-      l1 = l1 * c1 + s1;
-      m0 = n0;
-      m1 = n1;
-      // the accumulator columns are heads 2c, 2c+1 (+8): fetch their correction factors from the lanes that own them
-      const float ca = __shfl_sync(0xffffffffu, c0, 8 * c), cb = __shfl_sync(0xffffffffu, c0, 8 * c + 4);
-#pragma unroll
-      for (int j = 0; j < MT; ++j) {
-        acc[j][0][0] *= ca;
-        acc[j][0][1] *= cb;
-        acc[j][0][2] *= ca;
-        acc[j][0][3] *= cb;
-      }
-      if (NH16) {
-        const float cc = __shfl_sync(0xffffffffu, c1, 8 * c), cd = __shfl_sync(0xffffffffu, c1, 8 * c + 4);
-#pragma unroll
-        for (int j = 0; j < MT; ++j) {
-          acc[j][HN - 1][0] *= cc;
-          acc[j][HN - 1][1] *= cd;
-          acc[j][HN - 1][2] *= cc;
-          acc[j][HN - 1][3] *= cd;
-        }
-      }
-    }
-    // P^T as B fragments: (keys 2c, 2c+1) and (keys 2c+8, 2c+9) of head g, and of head g+8
-    const uint32_t pb0 = pack_pair<T>(pr[0][0], pr[0][1]), pb1 = pack_pair<T>(pr[1][0], pr[1][1]);
-    const uint32_t pc0 = pack_pair<T>(pr[0][2], pr[0][3]), pc1 = pack_pair<T>(pr[1][2], pr[1][3]);
-
-    // ---- O^T += V^T P^T ------------------------------------------------------------------------------------
-    {
-      uint32_t vw[4][VX][4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-#pragma unroll
-        for (int x = 0; x < VX; ++x) {
-          vw[e][x][0] = vreg[e][x].x; vw[e][x][1] = vreg[e][x].y; vw[e][x][2] = vreg[e][x].z; vw[e][x][3] = vreg[e][x].w;
-        }
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        // element m of the row's chunk; two keys of one d are paired in one register by a byte permute
-        const uint32_t sel = (m & 1) ? 0x7632u : 0x5410u;
-        constexpr int xh = VX - 1;                              // chunk holding rows g+8
-        const int wl = m >> 1, wh = (D == 128) ? (m >> 1) : 2 + (m >> 1);
-        const uint32_t a0 = __byte_perm(vw[0][0][wl], vw[1][0][wl], sel);
-        const uint32_t a1 = __byte_perm(vw[0][xh][wh], vw[1][xh][wh], sel);
-        const uint32_t a2 = __byte_perm(vw[2][0][wl], vw[3][0][wl], sel);
-        const uint32_t a3 = __byte_perm(vw[2][xh][wh], vw[3][xh][wh], sel);
-        mma16816<T>(acc[m][0], a0, a1, a2, a3, pb0, pb1);
-        if (NH16) mma16816<T>(acc[m][HN - 1], a0, a1, a2, a3, pc0, pc1);
-      }
-    }
-    if (kb_next < end) load_v(rows_next, kb_next);
-    rows = rows_next;
-  }
-
-  report_bad_block(p, bad_block);
-  // ---- merge the warps of the CTA ---------------------------------------------------------------------------
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  if (c == 0) {
-    sm_m[warp][g] = m0;
-    sm_l[warp][g] = l0;
-    if (NH16) {
-      sm_m[warp][g + 8] = m1;
-      sm_l[warp][g + 8] = l1;
-    }
-  }
-#pragma unroll
-  for (int m = 0; m < MT; ++m) {
-    const int d_lo = g * 8 + m, d_hi = (D == 128) ? (g + 8) * 8 + m : g * 8 + 4 + m;
-#pragma unroll
-    for (int hn = 0; hn < HN; ++hn)
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        sm_acc[warp][8 * hn + 2 * c + e][d_lo] = acc[m][hn][e];
-        sm_acc[warp][8 * hn + 2 * c + e][d_hi] = acc[m][hn][2 + e];
-      }
-  }
-  __syncthreads();
-
-  for (int idx = tid; idx < nheads * D; idx += kDecWarps * 32) {
-    const int hh = idx / D, d = idx - hh * D;
-    float M = -INFINITY;
-#pragma unroll
-    for (int n = 0; n < NG; ++n) M = fmaxf(M, sm_m[n][hh]);
-    float a = 0.f, lsum = 0.f;
-    if (M != -INFINITY) {
-#pragma unroll
-      for (int n = 0; n < NG; ++n) {
-        const float mn = sm_m[n][hh];
-        const float wgt = (mn == -INFINITY) ? 0.f : softmax_exp<T>(mn - M);
-        a = fmaf(wgt, sm_acc[n][hh][d], a);
-        lsum = fmaf(wgt, sm_l[n][hh], lsum);
-      }
-    }
-    const int h = h0 + hh;
-    if (direct) {
-      store_out<T>(p.out, b * p.os[0] + (int64_t)h * p.os[1] + d, lsum > 0.f ? a / lsum : 0.f, p.out_f32);
-      if (p.lse && d == 0)
-        p.lse[((int64_t)b * p.num_q_heads + h) * p.seq_q] = lsum > 0.f ? M + logf(lsum) : -INFINITY;
-    } else {
-      const int64_t slot = ((int64_t)b * Hc + (h - p.head_begin)) * nchunks + cidx;
-      ws[slot * D + d] = a;
-      if (d == 0) {
-        float* ml = ws + (int64_t)p.batch * Hc * nchunks * D;
-        ml[slot * 2] = M;
-        ml[slot * 2 + 1] = lsum;
-      }
-    }
-  }
-}
-
-// ---- the same kernel fed through shared memory -------------------------------------------------------------------
-// The register-fed kernel above keeps at most one step of K and one of V per warp in flight (its prefetch lives in
-// registers), which leaves the warps waiting on HBM latency.  Here each warp owns a ring of kRingStages
-// shared-memory stages (16 keys of K and 16 of V each) filled with 16-byte cp.async copies - a warp-wide copy moves
-// two whole rows, so requests are fully coalesced - and retired in order with cp.async.wait_group: up to
-// kRingStages steps per warp are in flight whatever the register budget, there is no flag to spin on, and rows
-// past the chunk's end or outside the pool are zero-filled by the copy itself (source size 0).  Rows are stored
-// un-padded with their 16-byte chunks XOR-swizzled (K: chunk ^ 4*(row & 1); V: chunk ^ 2*((row / 2) & 3)) so that
-// the fragment reads of both products are bank-conflict free.  Fragment geometry and arithmetic are those of the
-// kernel above.  After the loop a warp reuses its own ring for the partials it hands to the merge.
 constexpr int kRingStages = 3;
 
 template <int D>
@@ -1025,7 +735,7 @@ cudaError_t launch_partial(const SdpaParams& p, int chunk, int nchunks, float* w
 template <typename T, int D, bool NH16>
 cudaError_t launch_gqa(const SdpaParams& p, int chunk, int nchunks, float* ws, int direct, cudaStream_t stream) {
   const unsigned kvheads = (unsigned)(p.head_count / p.group);
-  const bool head_fast = p.ks[1] < p.ks[2] && nchunks <= 65535 && !getenv("AIDN_EXP_NO_HEAD_FAST");
+  const bool head_fast = p.ks[1] < p.ks[2] && nchunks <= 65535;
   const dim3 grid = head_fast ? dim3(kvheads, (unsigned)nchunks, (unsigned)p.batch)
                               : dim3((unsigned)nchunks, kvheads, (unsigned)p.batch);
   const bool paged = p.block_table != nullptr;
@@ -1048,8 +758,9 @@ cudaError_t launch_gqa(const SdpaParams& p, int chunk, int nchunks, float* ws, i
 template <typename T, int D>
 cudaError_t launch_partial_g(const SdpaParams& p, int chunk, int nchunks, float* ws, int direct, cudaStream_t stream) {
   if constexpr (sizeof(T) == 2 && (D == 64 || D == 128)) {
-    // several query heads per KV head: the tensor-core kernel (chunks are multiples of 8 keys; its steps are 16)
-    if (p.group >= 2 && p.group <= 8) return launch_gqa<T, D, false>(p, chunk, nchunks, ws, direct, stream);
+    // 16-bit inputs with up to 16 query heads per KV head (plain multi-head attention included: the padding rows
+    // of the MMA tile cost nothing on an HBM-bound kernel): the tensor-core kernel with the cp.async ring
+    if (p.group <= 8) return launch_gqa<T, D, false>(p, chunk, nchunks, ws, direct, stream);
     if (p.group > 8 && p.group <= 16) return launch_gqa<T, D, true>(p, chunk, nchunks, ws, direct, stream);
   }
   if (p.group == 1) return launch_partial<T, D, 1>(p, chunk, nchunks, ws, direct, stream);

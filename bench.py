@@ -189,10 +189,6 @@ class Runner:
             # Scatter the logical blocks of every sequence over one shared pool [blocks, bs, Hkv, D].
             nb = w["B"] * w["Sk"] // bs
             perm = torch.randperm(nb, generator=torch.Generator().manual_seed(seed & 0x7fffffff))
-            if os.environ.get("AIDN_EXP_TABLE") == "identity":
-                perm = torch.arange(nb)
-            elif os.environ.get("AIDN_EXP_TABLE") == "coarse":   # shuffle runs of 64 blocks (2 MiB of a GQA pool)
-                perm = (torch.randperm(nb // 64, generator=torch.Generator().manual_seed(1))[:, None] * 64 + torch.arange(64)[None]).reshape(-1)
             for name in ("k", "v"):
                 logical = getattr(self, name).permute(0, 2, 1, 3).reshape(nb, bs, w["Hkv"], w["D"])
                 pool = torch.empty_like(logical)
