@@ -53,7 +53,7 @@ WORKLOADS = {
 }
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each,
 # see profiles/): prefill C2 measured directly; decode C4 measured on the B=16 quarter and scaled by 4.
-NCU_TRAFFIC_BYTES = {"c2": 651.0e6, "c4": 4 * 527.4e6, "c4q": 527.4e6}
+NCU_TRAFFIC_BYTES = {"c2": 651.5e6, "c4": 4 * 525.5e6, "c4q": 525.5e6}
 METRIC = "attention TFLOP/s/GPU & % bf16 peak (prefill); decode HBM GB/s; 1/2/4/8 GPUs"
 
 
