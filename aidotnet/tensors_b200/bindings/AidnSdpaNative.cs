@@ -41,6 +41,17 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         public int gather_output;
     }
 
+    /// <summary>Paged K/V: the block pool of DevicePagedKVCache ([MaxBlocks, BlockSize, KvHeads, HeadDim]) and the
+    /// int32 block table uploaded with AllocateIntBuffer.</summary>
+    [StructLayout(LayoutKind.Sequential)]
+    internal struct AidnPagedKv
+    {
+        public IntPtr block_table;
+        public long block_table_stride;
+        public int block_size;
+        public int num_blocks;
+    }
+
     internal static class AidnSdpaNative
     {
         private const string Lib = "aidotnet_sdpa_sm100";
@@ -58,6 +69,7 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         [DllImport(Lib)] public static extern int aidn_sdpa_create(ref AidnSdpaDesc desc, out IntPtr handle);
         [DllImport(Lib)] public static extern long aidn_sdpa_workspace_bytes(IntPtr handle, long batch, long seqQ, long seqKv);
         [DllImport(Lib)] public static extern int aidn_sdpa_launch(IntPtr handle, ref AidnSdpaArgs args, IntPtr cuStream);
+        [DllImport(Lib)] public static extern int aidn_sdpa_launch_paged(IntPtr handle, ref AidnSdpaArgs args, ref AidnPagedKv paged, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_sdpa_poll(IntPtr handle, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_sdpa_last_path(IntPtr handle);
         [DllImport(Lib)] public static extern int aidn_sdpa_last_launch_count(IntPtr handle);
