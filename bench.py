@@ -52,8 +52,21 @@ WORKLOADS = {
                        name="paged_gqa_decode_B64_Hq32_Hkv8_D128_block16_kvlen512-4096_bf16"),
 }
 # DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each,
-# see profiles/): prefill C2 measured directly; decode C4 measured on the B=16 quarter and scaled by 4.
-NCU_TRAFFIC_BYTES = {"c2": 651.5e6, "c4": 4 * 525.5e6, "c4q": 525.5e6}
+# see profiles/).  Prefill C2 was captured directly.  Decode was captured on the B=16 quarter of C4 (525.5 MB of
+# traffic for 520.1 MB of algorithmic bytes); every (batch, head) streams its own keys once, so traffic grows in
+# proportion to the bytes streamed and a full-size launch is that ratio times its own algorithmic bytes.
+NCU_TRAFFIC_BYTES = {"c2": 651.5e6, "c4q": 525.5e6}
+NCU_DECODE_TRAFFIC_RATIO = 525.5 / 520.1
+
+
+def ncu_traffic(workload_key, w, algorithmic_bytes):
+    if workload_key in NCU_TRAFFIC_BYTES:
+        return NCU_TRAFFIC_BYTES[workload_key]
+    if w["kind"] == "decode" and workload_key in ("c4",):
+        return NCU_DECODE_TRAFFIC_RATIO * algorithmic_bytes
+    return None
+
+
 METRIC = "attention TFLOP/s/GPU & % bf16 peak (prefill); decode HBM GB/s; 1/2/4/8 GPUs"
 
 
@@ -379,8 +392,8 @@ def main():
         decode_obj = {"workload": wd["name"], "value": gbs * world, "unit": "GB/s", "ms_per_step": dsecs / dsteps * 1e3,
                       "tokens_per_s": wd["B"] * world / (dsecs / dsteps), "gpu_launches": dl,
                       "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s",
-                                   "frac": gbs / pk["hbm"], "traffic": NCU_TRAFFIC_BYTES["c4"],
-                                   "traffic_unit": "bytes per launch (ncu, B=16 capture x 4)", "algorithmic": dby,
+                                   "frac": gbs / pk["hbm"], "traffic": ncu_traffic("c4", wd, dby),
+                                   "traffic_unit": "bytes per launch (ncu, B=16 capture scaled by the bytes streamed)", "algorithmic": dby,
                                    "algorithmic_unit": "bytes per launch", "peak_source": pk["source"]}}
         del rd
 
@@ -405,7 +418,7 @@ def main():
             "tokens_per_s": w["B"] * w["Sq"] * world / per_step,
             "roofline": {"bound": "tensor" if prefill else "hbm", "achieved": per_gpu, "peak": peak,
                          "unit": "TFLOP/s" if prefill else "GB/s", "frac": per_gpu / peak,
-                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "traffic_unit": "bytes per launch (ncu)",
+                         "traffic": ncu_traffic(args.workload, w, by), "traffic_unit": "bytes per launch (ncu)",
                          "algorithmic": fl if prefill else by, "algorithmic_unit": "FLOP per launch" if prefill else "bytes per launch",
                          "peak_source": pk["source"] + (" (burst)" if prefill else "")},
             "cpu_baseline": cpu,
