@@ -543,7 +543,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int slot = seq & 1;
         if (!mbar_wait(bar_sched_empty + 8 * slot, (uint32_t)(((seq >> 1) & 1) ^ 1), abort_flag, wait_ns)) break;
         Item it;
-        if (item < pp.total_items) it = decode_item(pp, item);
+        if (item < pp.total_items) {
+          it = decode_item(pp, item);
+          // Row pairs: the second tile runs one KV tile longer.  Alternating which softmax warpgroup gets it keeps
+          // that lag from building up on one side from item to item.
+          if (!pp.pair_heads && (seq & 1)) {
+            const TileInfo t0 = it.tile[0];
+            it.tile[0] = it.tile[1];
+            it.tile[1] = t0;
+          }
+        }
         if (leader) {
           if (item < pp.total_items) publish_item(mailbox + slot * kItemWords, item, it);
           else mailbox[slot * kItemWords] = item;   // end marker
