@@ -6,6 +6,7 @@ Method names, argument order, argument meaning and error behaviour follow
     ScaledDotProductAttention  :8322-8379      FlashAttention      :8522-8538
     FlashAttentionV2           :8540-8578      GroupedQueryAttention :8721-8759
     FlashDecode                :2968-3021      PagedAttentionDecode/Prefill{,Gqa} :2845-2966
+    QkvProjectionRoPECacheD64  :8389-8439      RopeInterleaved     :8441-8470
 
 and the interface they implement (``Engines/DirectGpu/IDirectGpuBackend.cs:1421-1503``).  Buffers are
 ``GpuBuffer`` objects (the mirror of ``IGpuBuffer``, ``IDirectGpuBackend.cs:3776-3803``): a device
@@ -332,6 +333,53 @@ class CudaBackend:
             raise ValueError("PagedAttentionDecodeBatched: blockTables / seqLens are too small or not int32")
         return self._paged("PagedAttentionDecodeBatched", q, kcache, vcache, blockTables, heads, kvHeads, headDim,
                            blockSize, 1, maxSeqLen, 0, scale, batch=batch, seqLens=seqLens, tableStride=blocksPerSeq)
+
+    # -- the decode step in front of attention ----------------------------------------------------------------
+    def QkvProjectionRoPECacheD64(self, input: GpuBuffer, packedWeights: GpuBuffer, bias: GpuBuffer, cosine: GpuBuffer,
+                                  sine: GpuBuffer, query: GpuBuffer, keyCache: GpuBuffer, valueCache: GpuBuffer,
+                                  heads: int, cacheCapacity: int, position: int) -> None:
+        """One resident fp32 token through the packed Q/K/V weights (output-major, Q rows then K then V), + packed
+        bias, interleaved RoPE on Q and K, Q written to ``query`` and the K / V rows to row ``position`` of the dense
+        caches [cacheCapacity, heads, 64] (``CudaBackend.cs:8389-8439``).  One kernel, no scratch buffers; the weights
+        may be bf16 and the caches 16-bit (``GpuBuffer.dtype``), which is what the decode kernel then reads."""
+        for name, buf in (("input", input), ("packedWeights", packedWeights), ("bias", bias), ("cosine", cosine),
+                          ("sine", sine), ("query", query), ("keyCache", keyCache), ("valueCache", valueCache)):
+            if buf is None:
+                raise ValueError(f"{name} must not be null")          # ArgumentNullException
+        if heads <= 0:
+            raise ValueError("heads must be > 0")
+        if cacheCapacity <= 0:
+            raise ValueError("cacheCapacity must be > 0")
+        if position < 0 or position >= cacheCapacity:
+            raise ValueError("position must be in [0, cacheCapacity)")
+        dimension = 64
+        model = heads * dimension
+        projection = 3 * model
+        if (input.Size < model or packedWeights.Size < projection * model or bias.Size < projection or
+                cosine.Size < cacheCapacity * (dimension // 2) or sine.Size < cacheCapacity * (dimension // 2) or
+                query.Size < model or keyCache.Size < cacheCapacity * model or valueCache.Size < cacheCapacity * model):
+            raise ValueError("QKV/RoPE/cache buffers are smaller than the requested canonical extents.")
+        N.qkv_rope_cache(input=input.Handle, weights=packedWeights.Handle, bias=bias.Handle, cosine=cosine.Handle,
+                         sine=sine.Handle, query=query.Handle, key_cache=keyCache.Handle, value_cache=valueCache.Handle,
+                         tokens=1, heads=heads, kv_heads=heads, head_dim=dimension, position=position,
+                         weight_dtype=_DTYPE[packedWeights.dtype], query_dtype=_DTYPE[query.dtype],
+                         cache_dtype=_DTYPE[keyCache.dtype], cache_capacity=cacheCapacity, max_position=cacheCapacity,
+                         stream=self.stream.cuda_stream)
+        self.launch_count += 1
+
+    def RopeInterleaved(self, input: GpuBuffer, cos: GpuBuffer, sin: GpuBuffer, output: GpuBuffer, rows: int,
+                        headDim: int, seqLen: int, startPosition: int) -> None:
+        """Interleaved RoPE over ``rows`` rows of ``headDim`` fp32 values; row r sits at position
+        startPosition + r % seqLen (``CudaBackend.cs:8441-8470``, kernel ``CudaAttentionKernels.cs:1023-1050``)."""
+        if rows <= 0 or headDim <= 0 or seqLen <= 0:
+            raise ValueError("rows, headDim and seqLen must be positive")
+        if input.Size < rows * headDim or output.Size < rows * headDim:
+            raise ValueError("RoPE buffers are smaller than rows * headDim")
+        if cos.Size < (startPosition + seqLen) * (headDim // 2) or sin.Size < (startPosition + seqLen) * (headDim // 2):
+            raise ValueError("cos/sin caches do not reach startPosition + seqLen")
+        N.rope_interleaved(input.Handle, cos.Handle, sin.Handle, output.Handle, rows, headDim, seqLen, startPosition,
+                           self.stream.cuda_stream)
+        self.launch_count += 1
 
     def Dispose(self) -> None:
         for h in self._handles.values():

@@ -509,6 +509,65 @@ int aidn_sdpa_decode_noalloc(const aidn_sdpa_desc* desc, const aidn_sdpa_args* a
   return AIDN_OK;
 }
 
+int aidn_qkv_rope_cache(const aidn_qkv_rope_args* a, void* cu_stream) {
+  g_err[0] = 0;
+  if (!a) return fail(AIDN_EINVAL, "qkv_rope_cache: null argument");
+  if (!a->input || !a->weights || !a->cosine || !a->sine || !a->query || !a->key_cache || !a->value_cache)
+    return fail(AIDN_EINVAL, "qkv_rope_cache: null buffer");
+  if (a->heads <= 0) return fail(AIDN_EINVAL, "qkv_rope_cache: heads must be > 0");
+  if (a->kv_heads <= 0 || a->kv_heads > a->heads || a->heads % a->kv_heads != 0)
+    return fail(AIDN_EINVAL, "qkv_rope_cache: kv_heads must divide heads");
+  if (a->head_dim <= 0 || a->head_dim > 256 || a->head_dim % 2 != 0)
+    return fail(AIDN_EINVAL, "qkv_rope_cache: head_dim must be even and in [2, 256]");
+  if (a->tokens <= 0) return fail(AIDN_EINVAL, "qkv_rope_cache: tokens must be > 0");
+  if (a->cache_capacity <= 0 || a->max_position <= 0) return fail(AIDN_EINVAL, "qkv_rope_cache: cache_capacity and max_position must be > 0");
+  if (!a->positions && (a->position < 0 || (int64_t)a->position + a->tokens > a->max_position))
+    return fail(AIDN_EINVAL, "qkv_rope_cache: position outside the cos/sin tables");
+  if (!a->positions && !a->cache_rows && (int64_t)a->position + a->tokens > a->cache_capacity)
+    return fail(AIDN_EINVAL, "qkv_rope_cache: position outside the cache");   /* ArgumentOutOfRangeException(position) */
+  if (a->weight_dtype != AIDN_F32 && a->weight_dtype != AIDN_BF16) return fail(AIDN_EINVAL, "qkv_rope_cache: weights are fp32 or bf16");
+  if (a->query_dtype < AIDN_F32 || a->query_dtype > AIDN_BF16 || a->cache_dtype < AIDN_F32 || a->cache_dtype > AIDN_BF16)
+    return fail(AIDN_EINVAL, "qkv_rope_cache: unknown output dtype");
+  const int64_t model = (int64_t)a->heads * a->head_dim;
+  if (model % 8 != 0) return fail(AIDN_EUNSUPPORTED, "qkv_rope_cache: heads * head_dim must be a multiple of 8");
+  if (model > aidn::qkv_rope_max_model())
+    return fail(AIDN_EUNSUPPORTED, "qkv_rope_cache: heads * head_dim above %lld", (long long)aidn::qkv_rope_max_model());
+  if ((uintptr_t)a->weights % 16 != 0 || (uintptr_t)a->input % 16 != 0)
+    return fail(AIDN_EINVAL, "qkv_rope_cache: input and weights must be 16-byte aligned");
+  int dev = -1, sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return fail_cuda(e, "qkv_rope_cache: device query");
+  if (!aidn_sdpa_device_supported(dev))
+    return fail(AIDN_EUNSUPPORTED, "qkv_rope_cache: device %d is not compute capability 10.x", dev);
+  aidn::QkvRopeParams p;
+  std::memset(&p, 0, sizeof(p));
+  p.input = a->input; p.weights = a->weights; p.bias = a->bias; p.cosine = a->cosine; p.sine = a->sine;
+  p.query = a->query; p.key_cache = a->key_cache; p.value_cache = a->value_cache;
+  p.positions = a->positions; p.cache_rows = a->cache_rows;
+  p.tokens = a->tokens; p.heads = a->heads; p.kv_heads = a->kv_heads; p.head_dim = a->head_dim;
+  p.position = a->position; p.query_dtype = a->query_dtype; p.cache_dtype = a->cache_dtype;
+  p.cache_capacity = a->cache_capacity; p.max_position = a->max_position; p.model = (int32_t)model;
+  int launches = 0;
+  e = aidn::launch_qkv_rope_cache(p, a->weight_dtype, sms, (cudaStream_t)cu_stream, &launches);
+  if (e != cudaSuccess) return fail_cuda(e, "qkv_rope_cache");
+  return AIDN_OK;
+}
+
+int aidn_rope_interleaved(const float* input, const float* cosine, const float* sine, float* output, int64_t rows,
+                          int32_t head_dim, int32_t seq_len, int32_t start_position, void* cu_stream) {
+  g_err[0] = 0;
+  if (rows <= 0 || head_dim <= 0 || seq_len <= 0) return fail(AIDN_EINVAL, "rope_interleaved: rows, headDim and seqLen must be > 0");
+  if (head_dim % 2 != 0) return fail(AIDN_EINVAL, "rope_interleaved: headDim must be even");
+  if (start_position < 0) return fail(AIDN_EINVAL, "rope_interleaved: startPosition must be >= 0");
+  if (!input || !cosine || !sine || !output) return fail(AIDN_EINVAL, "rope_interleaved: null buffer");
+  if ((uintptr_t)input % 8 != 0 || (uintptr_t)output % 8 != 0) return fail(AIDN_EINVAL, "rope_interleaved: buffers must be 8-byte aligned");
+  cudaError_t e = aidn::launch_rope_interleaved(input, cosine, sine, output, rows, head_dim, seq_len, start_position,
+                                                (cudaStream_t)cu_stream);
+  if (e != cudaSuccess) return fail_cuda(e, "rope_interleaved");
+  return AIDN_OK;
+}
+
 static int cast_common(int kind, const void* src, void* dst, int64_t n, void* cu_stream) {
   g_err[0] = 0;
   if (n < 0 || (n > 0 && (!src || !dst))) return fail(AIDN_EINVAL, "cast: bad argument");

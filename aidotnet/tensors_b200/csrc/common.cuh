@@ -170,6 +170,31 @@ cudaError_t launch_decode_static(const SdpaParams& p, int dtype, int chunk, int 
                                  int* launches);
 cudaError_t launch_cast(int kind, const void* src, void* dst, int64_t n, cudaStream_t stream);
 
+// Packed Q/K/V projection + RoPE + KV-cache write (csrc/qkv_rope_cache.cu).
+struct QkvRopeParams {
+  const float* input;
+  const void* weights;
+  const float* bias;
+  const float* cosine;
+  const float* sine;
+  void* query;
+  void* key_cache;
+  void* value_cache;
+  const int32_t* positions;
+  const int32_t* cache_rows;
+  int32_t tokens, heads, kv_heads, head_dim;
+  int32_t position;
+  int32_t query_dtype, cache_dtype;
+  int64_t cache_capacity, max_position;
+  int32_t model;
+};
+
+int64_t qkv_rope_max_model();
+cudaError_t launch_qkv_rope_cache(const QkvRopeParams& p, int weight_dtype, int num_sms, cudaStream_t stream,
+                                  int* launches);
+cudaError_t launch_rope_interleaved(const float* in, const float* cosc, const float* sinc, float* out, int64_t rows,
+                                    int head_dim, int seq_len, int start_position, cudaStream_t stream);
+
 struct PrefillPlan;  // opaque to callers of the sm100 prefill launcher
 bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why);
 cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t stream, int32_t* sched, int num_sms,

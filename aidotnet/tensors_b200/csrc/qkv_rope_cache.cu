@@ -1,0 +1,232 @@
+// Decode-step front end: y = W x + b for the packed Q/K/V projection of up to 8 resident tokens, interleaved RoPE on
+// the Q and K heads, Q written out and the K / V rows written straight into the KV cache the decode kernel reads.
+//
+// Replaces CudaBackend.QkvProjectionRoPECacheD64 of the reference
+// (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/CudaBackend.cs:8389-8439: one fp32 token, head_dim 64, cache
+// [capacity, heads, 64]; its general path is cuBLAS GEMV + BiasAdd + rope_interleaved + three device copies through
+// three scratch allocations) and rope_interleaved (CUDA/Kernels/CudaAttentionKernels.cs:1023-1050).
+//
+// The step is a GEMV: every weight is used once per token, so it is bound by streaming W from HBM
+// ((heads + 2 kv_heads) * head_dim * model * sizeof(weight) bytes; nothing here is shaped for tensor cores).  A warp owns
+// one rotation pair of output rows (2r, 2r+1) - the two rows RoPE mixes - streams both with 16-byte no-allocate loads,
+// keeps the tokens' activations in shared memory, and finishes the pair in registers: bias, rotation by the token's
+// (cos, sin), store in the destination dtype.  Up to 8 tokens share one pass over W.
+#include "common.cuh"
+
+namespace aidn {
+
+namespace {
+
+constexpr int kQkvWarps = 4;
+
+__device__ __forceinline__ uint4 ld_stream16(const void* ptr) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(ptr));
+  return r;
+}
+
+template <typename WT>
+struct WVec;
+template <>
+struct WVec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+    f[0] = __uint_as_float(u.x); f[1] = __uint_as_float(u.y); f[2] = __uint_as_float(u.z); f[3] = __uint_as_float(u.w);
+  }
+};
+template <>
+struct WVec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void unpack(const uint4& u, float* f) {
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+
+__device__ __forceinline__ void store_as(void* base, int64_t idx, float x, int dtype) {
+  if (dtype == AIDN_F32) static_cast<float*>(base)[idx] = x;
+  else if (dtype == AIDN_F16) static_cast<__half*>(base)[idx] = __float2half_rn(x);
+  else static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(x);
+}
+
+// T tokens starting at token t_base share this pass over W.
+template <typename WT, int T>
+__global__ void __launch_bounds__(kQkvWarps * 32) qkv_rope_cache_kernel(const QkvRopeParams p, const int t_base) {
+  constexpr int N = WVec<WT>::N;
+  extern __shared__ __align__(16) float xs[];   // [T][model]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int model = p.model;
+  const int D = p.head_dim;
+  const int ntok = min(T, p.tokens - t_base);
+
+  for (int idx = tid * 4; idx < T * model; idx += kQkvWarps * 32 * 4) {
+    const int t = idx / model;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (t < ntok) v = *reinterpret_cast<const float4*>(p.input + (int64_t)(t_base + t) * model + (idx - t * model));
+    *reinterpret_cast<float4*>(xs + idx) = v;
+  }
+  __syncthreads();
+
+  const int q_rows = p.heads * D, kv_rows = p.kv_heads * D;
+  const int pairs = (q_rows + 2 * kv_rows) / 2;
+  const WT* W = static_cast<const WT*>(p.weights);
+
+  for (int pair = blockIdx.x * kQkvWarps + warp; pair < pairs; pair += gridDim.x * kQkvWarps) {
+    const int r0 = 2 * pair;
+    const WT* w0 = W + (int64_t)r0 * model;
+    const WT* w1 = w0 + model;
+    float a0[T], a1[T];
+#pragma unroll
+    for (int t = 0; t < T; ++t) a0[t] = a1[t] = 0.f;
+
+    constexpr int kUnroll = 4;
+    for (int k0 = lane * N; k0 < model; k0 += 32 * N * kUnroll) {
+      uint4 u0[kUnroll], u1[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int k = k0 + u * 32 * N;
+        const bool ok = k < model;
+        u0[u] = ok ? ld_stream16(w0 + k) : make_uint4(0, 0, 0, 0);
+        u1[u] = ok ? ld_stream16(w1 + k) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int k = k0 + u * 32 * N;
+        if (k >= model) continue;
+        float f0[N], f1[N];
+        WVec<WT>::unpack(u0[u], f0);
+        WVec<WT>::unpack(u1[u], f1);
+#pragma unroll
+        for (int t = 0; t < T; ++t) {
+          const float* x = xs + t * model + k;
+#pragma unroll
+          for (int e = 0; e < N; e += 4) {
+            const float4 xv = *reinterpret_cast<const float4*>(x + e);
+            a0[t] = fmaf(f0[e], xv.x, a0[t]); a0[t] = fmaf(f0[e + 1], xv.y, a0[t]);
+            a0[t] = fmaf(f0[e + 2], xv.z, a0[t]); a0[t] = fmaf(f0[e + 3], xv.w, a0[t]);
+            a1[t] = fmaf(f1[e], xv.x, a1[t]); a1[t] = fmaf(f1[e + 1], xv.y, a1[t]);
+            a1[t] = fmaf(f1[e + 2], xv.z, a1[t]); a1[t] = fmaf(f1[e + 3], xv.w, a1[t]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int t = 0; t < T; ++t)
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        a0[t] += __shfl_xor_sync(0xffffffffu, a0[t], o);
+        a1[t] += __shfl_xor_sync(0xffffffffu, a1[t], o);
+      }
+
+    // lane t finishes token t: bias, rotation, store
+    if (lane < ntok) {
+      float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+      for (int t = 0; t < T; ++t)
+        if (lane == t) { y0 = a0[t]; y1 = a1[t]; }
+      if (p.bias) { y0 += p.bias[r0]; y1 += p.bias[r0 + 1]; }
+      const int tok = t_base + lane;
+      const int64_t pos = p.positions ? p.positions[tok] : (int64_t)p.position + tok;
+      const int64_t crow = p.cache_rows ? p.cache_rows[tok] : pos;
+      const bool is_q = r0 < q_rows;
+      const bool is_k = !is_q && r0 < q_rows + kv_rows;
+      if (is_q || is_k) {   // interleaved RoPE: (x_even, x_odd) -> (x_even c - x_odd s, x_even s + x_odd c)
+        const int within = is_q ? r0 : r0 - q_rows;
+        const int i = (within % D) >> 1;
+        float c = 1.f, s = 0.f;
+        if (pos >= 0 && pos < p.max_position) {
+          c = p.cosine[pos * (D / 2) + i];
+          s = p.sine[pos * (D / 2) + i];
+        }
+        const float e = y0 * c - y1 * s, o = y0 * s + y1 * c;
+        y0 = e;
+        y1 = o;
+      }
+      if (is_q) {
+        const int64_t at = (int64_t)tok * q_rows + r0;
+        store_as(p.query, at, y0, p.query_dtype);
+        store_as(p.query, at + 1, y1, p.query_dtype);
+      } else if (crow >= 0 && crow < p.cache_capacity) {   // a row outside the cache is not written
+        const int within = is_k ? r0 - q_rows : r0 - q_rows - kv_rows;
+        const int64_t at = crow * kv_rows + within;
+        void* dst = is_k ? p.key_cache : p.value_cache;
+        store_as(dst, at, y0, p.cache_dtype);
+        store_as(dst, at + 1, y1, p.cache_dtype);
+      }
+    }
+  }
+}
+
+__global__ void rope_interleaved_kernel(const float* __restrict__ in, const float* __restrict__ cosc,
+                                        const float* __restrict__ sinc, float* __restrict__ out, int64_t rows,
+                                        int head_dim, int seq_len, int start_position) {
+  const int half = head_dim / 2;
+  const int64_t g = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (g >= rows * half) return;
+  const int i = (int)(g % half);
+  const int64_t row = g / half;
+  const int64_t pos = start_position + row % seq_len;
+  const float c = cosc[pos * half + i], s = sinc[pos * half + i];
+  const float2 x = *reinterpret_cast<const float2*>(in + row * head_dim + 2 * i);
+  *reinterpret_cast<float2*>(out + row * head_dim + 2 * i) = make_float2(x.x * c - x.y * s, x.x * s + x.y * c);
+}
+
+template <typename WT, int T>
+cudaError_t launch_qkv_t(const QkvRopeParams& p, int t_base, int num_sms, cudaStream_t stream) {
+  const size_t smem = (size_t)T * p.model * sizeof(float);
+  auto kern = qkv_rope_cache_kernel<WT, T>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  const int pairs = (p.heads + 2 * p.kv_heads) * p.head_dim / 2;
+  int grid = (pairs + kQkvWarps - 1) / kQkvWarps;
+  const int cap = num_sms * 8;   // grid-stride beyond eight CTAs per SM
+  if (grid > cap) grid = cap;
+  kern<<<grid, kQkvWarps * 32, smem, stream>>>(p, t_base);
+  return cudaGetLastError();
+}
+
+template <typename WT>
+cudaError_t launch_qkv_w(const QkvRopeParams& p, int num_sms, cudaStream_t stream, int* launches) {
+  *launches = 0;
+  for (int t_base = 0; t_base < p.tokens; t_base += 8) {
+    const int n = p.tokens - t_base;
+    cudaError_t e;
+    if (n == 1) e = launch_qkv_t<WT, 1>(p, t_base, num_sms, stream);
+    else if (n == 2) e = launch_qkv_t<WT, 2>(p, t_base, num_sms, stream);
+    else if (n <= 4) e = launch_qkv_t<WT, 4>(p, t_base, num_sms, stream);
+    else e = launch_qkv_t<WT, 8>(p, t_base, num_sms, stream);
+    if (e != cudaSuccess) return e;
+    ++*launches;
+  }
+  return cudaSuccess;
+}
+
+}  // namespace
+
+// Largest model dimension one launch can stage for 8 tokens (shared memory per CTA).
+int64_t qkv_rope_max_model() { return 200 * 1024 / (8 * (int64_t)sizeof(float)); }
+
+cudaError_t launch_qkv_rope_cache(const QkvRopeParams& p, int weight_dtype, int num_sms, cudaStream_t stream,
+                                  int* launches) {
+  if (weight_dtype == AIDN_F32) return launch_qkv_w<float>(p, num_sms, stream, launches);
+  return launch_qkv_w<__nv_bfloat16>(p, num_sms, stream, launches);
+}
+
+cudaError_t launch_rope_interleaved(const float* in, const float* cosc, const float* sinc, float* out, int64_t rows,
+                                    int head_dim, int seq_len, int start_position, cudaStream_t stream) {
+  const int64_t n = rows * (head_dim / 2);
+  if (n == 0) return cudaSuccess;
+  rope_interleaved_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(in, cosc, sinc, out, rows, head_dim, seq_len,
+                                                                          start_position);
+  return cudaGetLastError();
+}
+
+}  // namespace aidn

@@ -46,12 +46,17 @@ constexpr int kSoftmaxWarps = 8;   // 2 tiles x 4 warps
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr int kThreads = 384;          // 3 warpgroups: softmax 0, softmax 1, {producer, UMMA issuer, 2 idle}
-constexpr int kSoftmaxRegs = 216;      // per-thread registers after setmaxnreg (8*32*216 + 4*32*72 == 384*168)
+// Per-thread registers after setmaxnreg.  8*32*216 + 4*32*72 == 384*168: the two figures must add up to what the CTA
+// was launched with - setmaxnreg.inc waits, without any bound, for registers that another warpgroup of the same CTA has
+// given up, and a sum above the launch allocation never becomes available.
+constexpr int kSoftmaxRegs = 216;
 constexpr int kOtherRegs = 72;
 constexpr int kStageBytesPerWarp = 4096;   // epilogue staging: 32 rows x 128 B (128-byte swizzle), one per softmax warp
 constexpr int kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8 between rescales
 constexpr int kSchedConsumers = kSoftmaxWarps + 1;
+static_assert(kSoftmaxWarps * 32 * kSoftmaxRegs + 4 * 32 * kOtherRegs <= kThreads * 168,
+              "setmaxnreg budget exceeds the registers the CTA is launched with");
 constexpr int kItemWords = 12;   // mailbox entry: item, b, kvh, n_max, then (h, t, n, valid) of both tiles
 
 template <int HD>

@@ -26,7 +26,7 @@ EXPORTS = (
     "aidn_sdpa_create", "aidn_sdpa_workspace_bytes", "aidn_sdpa_launch", "aidn_sdpa_poll", "aidn_sdpa_last_path",
     "aidn_sdpa_last_launch_count", "aidn_sdpa_destroy", "aidn_sdpa_last_error", "aidn_sdpa_device_supported",
     "aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32",
-    "aidn_sdpa_decode_noalloc", "aidn_sdpa_launch_paged",
+    "aidn_sdpa_decode_noalloc", "aidn_sdpa_launch_paged", "aidn_qkv_rope_cache", "aidn_rope_interleaved",
 )
 
 
@@ -57,6 +57,18 @@ class PagedKv(ctypes.Structure):
     _fields_ = [
         ("block_table", ctypes.c_void_p), ("block_table_stride", ctypes.c_int64), ("block_size", ctypes.c_int32),
         ("num_blocks", ctypes.c_int32),
+    ]
+
+
+class QkvRopeArgs(ctypes.Structure):
+    _fields_ = [
+        ("input", ctypes.c_void_p), ("weights", ctypes.c_void_p), ("bias", ctypes.c_void_p),
+        ("cosine", ctypes.c_void_p), ("sine", ctypes.c_void_p), ("query", ctypes.c_void_p),
+        ("key_cache", ctypes.c_void_p), ("value_cache", ctypes.c_void_p), ("positions", ctypes.c_void_p),
+        ("cache_rows", ctypes.c_void_p), ("tokens", ctypes.c_int32), ("heads", ctypes.c_int32),
+        ("kv_heads", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("position", ctypes.c_int32),
+        ("weight_dtype", ctypes.c_int32), ("query_dtype", ctypes.c_int32), ("cache_dtype", ctypes.c_int32),
+        ("cache_capacity", ctypes.c_int64), ("max_position", ctypes.c_int64),
     ]
 
 
@@ -106,6 +118,11 @@ def load() -> ctypes.CDLL:
     lib.aidn_sdpa_launch_paged.argtypes = [ctypes.c_void_p, ctypes.POINTER(SdpaArgs), ctypes.POINTER(PagedKv),
                                            ctypes.c_void_p]
     lib.aidn_sdpa_launch_paged.restype = ctypes.c_int
+    lib.aidn_qkv_rope_cache.argtypes = [ctypes.POINTER(QkvRopeArgs), ctypes.c_void_p]
+    lib.aidn_qkv_rope_cache.restype = ctypes.c_int
+    lib.aidn_rope_interleaved.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                          ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
+    lib.aidn_rope_interleaved.restype = ctypes.c_int
     lib.aidn_sdpa_debug_set.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
     lib.aidn_sdpa_debug_set.restype = ctypes.c_int
     _lib = lib
@@ -217,3 +234,25 @@ def decode_noalloc(desc: SdpaDesc, args: SdpaArgs, stream: int) -> None:
     16 MiB array).  For hosts that may not allocate device memory where they decode; calls that overlap on the GPU
     race on the shared array, so keep them on one stream."""
     check(load().aidn_sdpa_decode_noalloc(ctypes.byref(desc), ctypes.byref(args), ctypes.c_void_p(stream)))
+
+
+def qkv_rope_cache(*, input: int, weights: int, bias: Optional[int], cosine: int, sine: int, query: int, key_cache: int,
+                   value_cache: int, tokens: int, heads: int, kv_heads: int, head_dim: int, position: int = 0,
+                   positions: Optional[int] = None, cache_rows: Optional[int] = None, weight_dtype: int = F32,
+                   query_dtype: int = F32, cache_dtype: int = F32, cache_capacity: int, max_position: int,
+                   stream: int) -> None:
+    """Packed Q/K/V projection + bias + interleaved RoPE + KV-cache write for ``tokens`` resident tokens."""
+    a = QkvRopeArgs()
+    a.input, a.weights, a.bias, a.cosine, a.sine = input, weights, bias, cosine, sine
+    a.query, a.key_cache, a.value_cache, a.positions, a.cache_rows = query, key_cache, value_cache, positions, cache_rows
+    a.tokens, a.heads, a.kv_heads, a.head_dim, a.position = tokens, heads, kv_heads, head_dim, position
+    a.weight_dtype, a.query_dtype, a.cache_dtype = weight_dtype, query_dtype, cache_dtype
+    a.cache_capacity, a.max_position = cache_capacity, max_position
+    check(load().aidn_qkv_rope_cache(ctypes.byref(a), ctypes.c_void_p(stream)))
+
+
+def rope_interleaved(input: int, cosine: int, sine: int, output: int, rows: int, head_dim: int, seq_len: int,
+                     start_position: int, stream: int) -> None:
+    check(load().aidn_rope_interleaved(ctypes.c_void_p(input), ctypes.c_void_p(cosine), ctypes.c_void_p(sine),
+                                       ctypes.c_void_p(output), rows, head_dim, seq_len, start_position,
+                                       ctypes.c_void_p(stream)))

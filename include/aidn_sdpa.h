@@ -179,6 +179,39 @@ AIDN_API int aidn_sdpa_device_supported(int32_t device);
  * (CudaBackend.cs:2994-2996). */
 AIDN_API int aidn_sdpa_decode_noalloc(const aidn_sdpa_desc* desc, const aidn_sdpa_args* args, void* cu_stream);
 
+/* The decode step in front of the attention call: packed Q/K/V projection of resident tokens, bias, interleaved RoPE
+ * on Q and K, Q written out and the K / V rows written into the KV cache, in one pass over the weights.  Replaces
+ * CudaBackend.QkvProjectionRoPECacheD64 (CudaBackend.cs:8389-8439: one fp32 token, head_dim 64, cache
+ * [capacity, heads, 64], `position` both the RoPE position and the cache row) and generalises it: any even head_dim,
+ * grouped-query projections (heads + 2*kv_heads output heads), several tokens per call (each with its own position
+ * and cache row - e.g. one token of every sequence of a decode batch, with cache rows taken from a paged pool), bf16
+ * weights, and a 16-bit cache that the decode kernel reads directly.  All pointers are device memory. */
+typedef struct {
+  const float* input;        /* [tokens, model] fp32, model = heads * head_dim                                  */
+  const void* weights;       /* [(heads + 2*kv_heads) * head_dim, model], output-major: Q rows, K rows, V rows  */
+  const float* bias;         /* [(heads + 2*kv_heads) * head_dim], or NULL                                      */
+  const float* cosine;       /* [max_position, head_dim / 2], indexed by absolute position                      */
+  const float* sine;
+  void* query;               /* [tokens, heads * head_dim], query_dtype                                         */
+  void* key_cache;           /* [cache_capacity, kv_heads, head_dim], cache_dtype                               */
+  void* value_cache;
+  const int32_t* positions;  /* [tokens] RoPE position of each token, or NULL: position + token index           */
+  const int32_t* cache_rows; /* [tokens] cache row each token's K / V goes to, or NULL: the token's position    */
+  int32_t tokens, heads, kv_heads, head_dim;
+  int32_t position;          /* first token's position when positions == NULL                                   */
+  int32_t weight_dtype;      /* AIDN_F32 or AIDN_BF16                                                           */
+  int32_t query_dtype;       /* aidn_dtype                                                                      */
+  int32_t cache_dtype;       /* aidn_dtype                                                                      */
+  int64_t cache_capacity;    /* rows of the caches; a token whose row lies outside writes no K / V              */
+  int64_t max_position;      /* rows of cosine / sine; a position outside them is left unrotated                */
+} aidn_qkv_rope_args;
+AIDN_API int aidn_qkv_rope_cache(const aidn_qkv_rope_args* args, void* cu_stream);
+/* rope_interleaved (CUDA/Kernels/CudaAttentionKernels.cs:1023-1050; CudaBackend.RopeInterleaved): rows of head_dim
+ * fp32 values, row r at position start_position + r % seq_len, pairs (2i, 2i+1) rotated by (cos, sin)[position][i]. */
+AIDN_API int aidn_rope_interleaved(const float* input, const float* cosine, const float* sine, float* output,
+                                   int64_t rows, int32_t head_dim, int32_t seq_len, int32_t start_position,
+                                   void* cu_stream);
+
 /* dtype staging (IDirectGpuBackend.cs:1890 ConvertToFp16, :1911 ConvertToFp32; bf16 rounding per
  * NumericOperations/BFloat16.cs:65-84: round-to-nearest-even, NaN keeps its top payload bits plus the quiet bit). */
 AIDN_API int aidn_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* cu_stream);

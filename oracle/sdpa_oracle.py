@@ -217,3 +217,48 @@ def paged_attention_rows(q: np.ndarray, kcache: np.ndarray, vcache: np.ndarray, 
             w = np.exp(logits - logits.max())
             out[qi, h] = (w / w.sum()) @ vc[rows, kvh, :]
     return out.astype(np.float32)
+
+
+# ---- packed Q/K/V projection + interleaved RoPE + KV-cache write ------------------------------------------------
+def rope_interleaved(x: np.ndarray, cosine: np.ndarray, sine: np.ndarray, seq_len: int, start_position: int) -> np.ndarray:
+    """rope_interleaved of the reference (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/
+    CudaAttentionKernels.cs:1023-1050): ``x`` is [rows, head_dim]; row r sits at position start_position + r % seq_len;
+    pair (2i, 2i+1) becomes (e c - o s, e s + o c) with (c, s) = (cosine, sine)[position, i].  float32 arithmetic."""
+    x = np.asarray(x, dtype=np.float32)
+    rows, head_dim = x.shape
+    pos = start_position + np.arange(rows) % seq_len
+    c = np.asarray(cosine, np.float32)[pos]          # [rows, head_dim / 2]
+    s = np.asarray(sine, np.float32)[pos]
+    e, o = x[:, 0::2], x[:, 1::2]
+    out = np.empty_like(x)
+    out[:, 0::2] = e * c - o * s
+    out[:, 1::2] = e * s + o * c
+    return out
+
+
+def qkv_rope_cache(x, weights, bias, cosine, sine, *, heads: int, kv_heads: int, head_dim: int, positions, cache_rows,
+                   key_cache: np.ndarray, value_cache: np.ndarray):
+    """The composition CudaBackend.QkvProjectionRoPECacheD64 falls back to (CudaBackend.cs:8428-8438): projected =
+    x W^T, + bias, RopeInterleaved over the Q and K heads at the token's position, Q returned, the K and V rows copied
+    into cache row ``cache_rows[t]``.  ``x`` [tokens, model]; ``weights`` [(heads + 2 kv_heads) head_dim, model] with the
+    Q rows first, then K, then V; caches [capacity, kv_heads * head_dim] are updated in place.  Accumulates in float64
+    (the check on the GPU's fp32 dot products)."""
+    x = np.asarray(x, np.float64)
+    w = np.asarray(weights, np.float64)
+    y = x @ w.T
+    if bias is not None:
+        y = y + np.asarray(bias, np.float64)
+    y = y.astype(np.float32)
+    tokens = x.shape[0]
+    q_rows, kv_rows = heads * head_dim, kv_heads * head_dim
+    q = np.empty((tokens, q_rows), np.float32)
+    for t in range(tokens):
+        pos = int(positions[t])
+        qk = y[t, :q_rows + kv_rows].reshape(-1, head_dim)
+        rot = rope_interleaved(qk, cosine, sine, 1, pos).reshape(-1)
+        q[t] = rot[:q_rows]
+        row = int(cache_rows[t])
+        if 0 <= row < key_cache.shape[0]:
+            key_cache[row] = rot[q_rows:]
+            value_cache[row] = y[t, q_rows + kv_rows:]
+    return q

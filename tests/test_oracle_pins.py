@@ -191,3 +191,58 @@ def test_materialize_respects_kv_len_and_unused_entries():
     assert np.array_equal(out[0, :, :4], kc[2].transpose(1, 0, 2)) and np.array_equal(out[0, :, 4:7], kc[5, :3].transpose(1, 0, 2))
     assert np.all(out[0, :, 7:] == 0)
     assert np.array_equal(out[1, :, 8:12], kc[3].transpose(1, 0, 2))
+
+
+# ---- RoPE and the packed Q/K/V projection ---------------------------------------------------------------------
+def _rope_cache(max_seq, head_dim, theta=10000.0):
+    """BuildRopeCache of the reference's tests (DirectGpu/RopeGqaOpenClTests.cs:51-67)."""
+    half = head_dim // 2
+    pos = np.arange(max_seq, dtype=np.float64)[:, None]
+    freq = 1.0 / np.power(theta, 2.0 * np.arange(half) / head_dim)[None, :]
+    return np.cos(pos * freq).astype(np.float32), np.sin(pos * freq).astype(np.float32)
+
+
+@pytest.mark.parametrize("start", [0, 5])
+def test_rope_interleaved_against_the_reference_loop(start):
+    """RopeInterleaved_MatchesCpuReference (DirectGpu/RopeGqaOpenClTests.cs:92-117): heads 3, seqLen 6, headDim 8,
+    maxSeq 32, expected values from the scalar RopeReference loop (:69-90), restated here element by element."""
+    heads, seq_len, head_dim, max_seq = 3, 6, 8, 32
+    rows = heads * seq_len
+    rng = np.random.default_rng(7)
+    x = rng.uniform(-1, 1, (rows, head_dim)).astype(np.float32)
+    cos, sin = _rope_cache(max_seq, head_dim)
+    want = np.zeros_like(x)
+    for row in range(rows):
+        pos = start + row % seq_len
+        for i in range(head_dim // 2):
+            c, s = cos[pos, i], sin[pos, i]
+            xe, xo = x[row, 2 * i], x[row, 2 * i + 1]
+            want[row, 2 * i] = np.float32(xe * c) - np.float32(xo * s)
+            want[row, 2 * i + 1] = np.float32(xe * s) + np.float32(xo * c)
+    got = O.rope_interleaved(x, cos, sin, seq_len, start)
+    assert np.abs(got - want).max() <= 1e-6
+    assert np.abs(np.linalg.norm(got, axis=1) - np.linalg.norm(x, axis=1)).max() <= 1e-5   # a rotation keeps norms
+
+
+@pytest.mark.parametrize("heads,capacity,position", [(4, 16, 0), (8, 64, 17), (16, 128, 127)])
+def test_qkv_rope_cache_composition(heads, capacity, position):
+    """The shapes of DriverOnlyQkvRopeCacheD64_MatchesOracle (DirectGpu/DirectPtxWmmaTests.cs:2110-2113): head_dim 64,
+    cache [capacity, heads, 64].  The oracle must equal the reference's fallback composition written out step by step
+    (MatMulTransposed, BiasAdd, RopeInterleaved over 2*heads rows, three copies; CudaBackend.cs:8428-8438)."""
+    D, model = 64, heads * 64
+    rng = np.random.default_rng(900 + heads)
+    x = rng.uniform(-1, 1, (1, model)).astype(np.float32)
+    w = (rng.uniform(-1, 1, (3 * model, model)) / np.sqrt(model)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, 3 * model).astype(np.float32)
+    cos, sin = _rope_cache(capacity, D)
+    projected = (x.astype(np.float64) @ w.astype(np.float64).T).astype(np.float32)[0]
+    biased = projected + b
+    rotated = O.rope_interleaved(biased[:2 * model].reshape(2 * heads, D), cos, sin, 1, position).reshape(-1)
+    kc = np.zeros((capacity, model), np.float32)
+    vc = np.zeros((capacity, model), np.float32)
+    q = O.qkv_rope_cache(x, w, b, cos, sin, heads=heads, kv_heads=heads, head_dim=D, positions=[position],
+                         cache_rows=[position], key_cache=kc, value_cache=vc)
+    assert np.abs(q[0] - rotated[:model]).max() <= 1e-6
+    assert np.abs(kc[position] - rotated[model:]).max() <= 1e-6
+    assert np.abs(vc[position] - biased[2 * model:]).max() <= 1e-6
+    assert not kc[np.arange(capacity) != position].any()
