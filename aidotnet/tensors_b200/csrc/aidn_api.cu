@@ -136,12 +136,12 @@ extern "C" {
 const char* aidn_sdpa_last_error(void) { return g_err; }
 
 int aidn_sdpa_device_supported(int32_t device) {
-  cudaDeviceProp prop;
-  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
-  return prop.major == 10 ? 1 : 0;
+  return major == 10 ? 1 : 0;
 }
 
 int aidn_sdpa_create(const aidn_sdpa_desc* desc, aidn_sdpa_t* out) {
@@ -534,12 +534,22 @@ int aidn_qkv_rope_cache(const aidn_qkv_rope_args* a, void* cu_stream) {
     return fail(AIDN_EUNSUPPORTED, "qkv_rope_cache: heads * head_dim above %lld", (long long)aidn::qkv_rope_max_model());
   if ((uintptr_t)a->weights % 16 != 0 || (uintptr_t)a->input % 16 != 0)
     return fail(AIDN_EINVAL, "qkv_rope_cache: input and weights must be 16-byte aligned");
-  int dev = -1, sms = 0;
+  // per-device facts, looked up once: this entry point has no handle to keep them in
+  static int g_sms[64] = {0};
+  static int g_ok[64] = {0};
+  int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (e != cudaSuccess) return fail_cuda(e, "qkv_rope_cache: device query");
-  if (!aidn_sdpa_device_supported(dev))
-    return fail(AIDN_EUNSUPPORTED, "qkv_rope_cache: device %d is not compute capability 10.x", dev);
+  if (dev < 0 || dev >= 64) return fail(AIDN_EUNSUPPORTED, "qkv_rope_cache: device ordinal %d", dev);
+  if (g_sms[dev] == 0) {
+    int sms_q = 0;
+    e = cudaDeviceGetAttribute(&sms_q, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return fail_cuda(e, "qkv_rope_cache: device query");
+    g_ok[dev] = aidn_sdpa_device_supported(dev);
+    g_sms[dev] = sms_q;
+  }
+  const int sms = g_sms[dev];
+  if (!g_ok[dev]) return fail(AIDN_EUNSUPPORTED, "qkv_rope_cache: device %d is not compute capability 10.x", dev);
   aidn::QkvRopeParams p;
   std::memset(&p, 0, sizeof(p));
   p.input = a->input; p.weights = a->weights; p.bias = a->bias; p.cosine = a->cosine; p.sine = a->sine;

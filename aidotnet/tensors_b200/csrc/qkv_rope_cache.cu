@@ -17,7 +17,6 @@ namespace aidn {
 
 namespace {
 
-constexpr int kQkvWarps = 4;
 
 __device__ __forceinline__ uint4 ld_stream16(const void* ptr) {
   uint4 r;
@@ -55,9 +54,11 @@ __device__ __forceinline__ void store_as(void* base, int64_t idx, float x, int d
   else static_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(x);
 }
 
-// T tokens starting at token t_base share this pass over W.
-template <typename WT, int T>
-__global__ void __launch_bounds__(kQkvWarps * 32) qkv_rope_cache_kernel(const QkvRopeParams p, const int t_base) {
+// T tokens starting at token t_base share this pass over W.  The activations of all T tokens sit in shared memory once
+// per CTA, so the CTA is made wide (WARPS) when they are large: occupancy is then bounded by warps, not by CTAs.
+template <typename WT, int T, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) qkv_rope_cache_kernel(const QkvRopeParams p, const int t_base) {
+  constexpr int kQkvWarps = WARPS;
   constexpr int N = WVec<WT>::N;
   extern __shared__ __align__(16) float xs[];   // [T][model]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -65,11 +66,24 @@ __global__ void __launch_bounds__(kQkvWarps * 32) qkv_rope_cache_kernel(const Qk
   const int D = p.head_dim;
   const int ntok = min(T, p.tokens - t_base);
 
-  for (int idx = tid * 4; idx < T * model; idx += kQkvWarps * 32 * 4) {
-    const int t = idx / model;
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (t < ntok) v = *reinterpret_cast<const float4*>(p.input + (int64_t)(t_base + t) * model + (idx - t * model));
-    *reinterpret_cast<float4*>(xs + idx) = v;
+  {
+    constexpr int kStageUnroll = 4;   // independent loads in flight per thread
+    for (int base = tid * 4; base < T * model; base += kQkvWarps * 32 * 4 * kStageUnroll) {
+      float4 v[kStageUnroll];
+#pragma unroll
+      for (int u = 0; u < kStageUnroll; ++u) {
+        const int idx = base + u * kQkvWarps * 32 * 4;
+        const int t = idx / model;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < T * model && t < ntok)
+          v[u] = *reinterpret_cast<const float4*>(p.input + (int64_t)(t_base + t) * model + (idx - t * model));
+      }
+#pragma unroll
+      for (int u = 0; u < kStageUnroll; ++u) {
+        const int idx = base + u * kQkvWarps * 32 * 4;
+        if (idx < T * model) *reinterpret_cast<float4*>(xs + idx) = v[u];
+      }
+    }
   }
   __syncthreads();
 
@@ -163,6 +177,198 @@ __global__ void __launch_bounds__(kQkvWarps * 32) qkv_rope_cache_kernel(const Qk
   }
 }
 
+// ---- several tokens, bf16 weights: the same pass over W on the warp-level tensor cores ------------------------------
+// With T tokens the FFMA form reads T activations from shared memory per weight and becomes bound by that.  Here a CTA
+// of 16 warps takes 16 output rows (8 rotation pairs) at a time as the M dimension of mma.sync.m16n8k16, the tokens
+// (padded to 8) as N, and splits K across its warps; the partial sums meet in shared memory and 64 threads finish the
+// tile (bias, rotation, stores).  As in the decode kernel, the k order is free: a thread's 16-byte weight chunk feeds
+// the k slots in the order it arrives and the activations are read in the matching order, so W goes from global
+// memory straight into the A fragments.  The fp32 activations are split once per CTA into bf16 hi + lo (x = hi + lo
+// to 2^-17) and multiplied in two MMAs, which keeps the result at fp32-GEMV accuracy.
+constexpr int kMmaWarps = 16;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                               uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(kMmaWarps * 32) qkv_rope_cache_mma_kernel(const QkvRopeParams p, const int t_base) {
+  extern __shared__ __align__(16) uint8_t qsm[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int model = p.model, D = p.head_dim;
+  const int ntok = min(8, p.tokens - t_base);
+  const int pitch = model * 2 + 64;                       // bytes per token row of hi (and of lo): bank-conflict free
+  uint8_t* x_hi = qsm;                                    // [8][pitch]
+  uint8_t* x_lo = qsm + 8 * pitch;                        // [8][pitch]
+  float* part = reinterpret_cast<float*>(qsm + 16 * pitch);   // [kMmaWarps][16 rows][8 tokens]
+  float* rope = part + kMmaWarps * 128;                       // [8 tokens][D/2] cos, then [8][D/2] sin
+  long long* tokrow = reinterpret_cast<long long*>(rope + 8 * D);   // [8] cache row of each token, -1 = none
+
+  // stage the activations: four independent 16-byte loads per thread in flight, then split and store
+  {
+    const int n4 = 8 * model / 4;
+    constexpr int kStageUnroll = 4;
+    for (int base = tid; base < n4; base += kMmaWarps * 32 * kStageUnroll) {
+      float4 v[kStageUnroll];
+#pragma unroll
+      for (int u = 0; u < kStageUnroll; ++u) {
+        const int idx = base + u * kMmaWarps * 32;
+        const int t = idx / (model / 4), k = (idx - t * (model / 4)) * 4;
+        v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (idx < n4 && t < ntok) v[u] = *reinterpret_cast<const float4*>(p.input + (int64_t)(t_base + t) * model + k);
+      }
+#pragma unroll
+      for (int u = 0; u < kStageUnroll; ++u) {
+        const int idx = base + u * kMmaWarps * 32;
+        if (idx >= n4) continue;
+        const int t = idx / (model / 4), k = (idx - t * (model / 4)) * 4;
+        const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+        __nv_bfloat16 h[4], l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          h[e] = __float2bfloat16_rn(f[e]);
+          l[e] = __float2bfloat16_rn(f[e] - __bfloat162float(h[e]));
+        }
+        *reinterpret_cast<__nv_bfloat162*>(x_hi + t * pitch + k * 2) = __halves2bfloat162(h[0], h[1]);
+        *reinterpret_cast<__nv_bfloat162*>(x_hi + t * pitch + k * 2 + 4) = __halves2bfloat162(h[2], h[3]);
+        *reinterpret_cast<__nv_bfloat162*>(x_lo + t * pitch + k * 2) = __halves2bfloat162(l[0], l[1]);
+        *reinterpret_cast<__nv_bfloat162*>(x_lo + t * pitch + k * 2 + 4) = __halves2bfloat162(l[2], l[3]);
+      }
+    }
+  }
+  // per-token rotation rows and cache rows, fetched once so that finishing a tile touches no dependent global loads
+  for (int idx = tid; idx < 8 * (D / 2); idx += kMmaWarps * 32) {
+    const int t = idx / (D / 2), i = idx - t * (D / 2);
+    float cs = 1.f, sn = 0.f;
+    if (t < ntok) {
+      const int tok = t_base + t;
+      const int64_t pos = p.positions ? p.positions[tok] : (int64_t)p.position + tok;
+      if (pos >= 0 && pos < p.max_position) {
+        cs = p.cosine[pos * (D / 2) + i];
+        sn = p.sine[pos * (D / 2) + i];
+      }
+      if (i == 0) {
+        const int64_t crow = p.cache_rows ? p.cache_rows[tok] : pos;
+        tokrow[t] = (crow >= 0 && crow < p.cache_capacity) ? crow : -1;
+      }
+    }
+    rope[t * (D / 2) + i] = cs;
+    rope[8 * (D / 2) + t * (D / 2) + i] = sn;
+  }
+  __syncthreads();
+
+  const int q_rows = p.heads * D, kv_rows = p.kv_heads * D;
+  const int tiles = (q_rows + 2 * kv_rows) / 16;
+  const __nv_bfloat16* W = static_cast<const __nv_bfloat16*>(p.weights);
+  const int chunks = model / 8;                     // 16-byte chunks per weight row
+  const uint32_t hi_s = (uint32_t)__cvta_generic_to_shared(x_hi), lo_s = (uint32_t)__cvta_generic_to_shared(x_lo);
+
+  // This warp's K slice is chunks warp*4 + c, + 64, + 128, ...; a batch is kBatch of them (all loads in flight at once).
+  // The first batch of the next tile is requested before the current tile is handed to the finishing threads, so the
+  // weight stream does not stop at the tile boundary.
+  constexpr int kBatch = 8;
+  constexpr int kChunkStep = 4 * kMmaWarps;
+  uint4 we[kBatch], wo[kBatch];
+  auto load_batch = [&](int tile, int ch0) {
+    // MMA row m < 8 is weight row 16*tile + 2m (the even row of pair m), row m + 8 the odd row of the same pair
+    const __nv_bfloat16* w_even = W + (int64_t)(16 * tile + 2 * g) * model;
+    const __nv_bfloat16* w_odd = w_even + model;
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int ch = ch0 + u * kChunkStep;
+      const bool ok = ch < chunks;
+      we[u] = ok ? ld_stream16(w_even + ch * 8) : make_uint4(0, 0, 0, 0);
+      wo[u] = ok ? ld_stream16(w_odd + ch * 8) : make_uint4(0, 0, 0, 0);
+    }
+  };
+  const int ch_first = warp * 4 + c;
+  if ((int)blockIdx.x < tiles) load_batch(blockIdx.x, ch_first);
+
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int ch0 = ch_first; ch0 < chunks; ch0 += kChunkStep * kBatch) {
+      if (ch0 != ch_first) load_batch(tile, ch0);
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int ch = ch0 + u * kChunkStep;
+        if (ch >= chunks) continue;
+        // activations of token g for the same chunk: registers 2h / 2h+1 feed k-step h like the weight registers do
+        uint32_t bh[4], bl[4];
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(bh[0]), "=r"(bh[1]), "=r"(bh[2]), "=r"(bh[3])
+                     : "r"(hi_s + g * pitch + ch * 16));
+        asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(bl[0]), "=r"(bl[1]), "=r"(bl[2]), "=r"(bl[3])
+                     : "r"(lo_s + g * pitch + ch * 16));
+        const uint32_t ae[4] = {we[u].x, we[u].y, we[u].z, we[u].w};
+        const uint32_t ao[4] = {wo[u].x, wo[u].y, wo[u].z, wo[u].w};
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          mma_bf16_16816(acc, ae[2 * h], ao[2 * h], ae[2 * h + 1], ao[2 * h + 1], bh[2 * h], bh[2 * h + 1]);
+          mma_bf16_16816(acc, ae[2 * h], ao[2 * h], ae[2 * h + 1], ao[2 * h + 1], bl[2 * h], bl[2 * h + 1]);
+        }
+      }
+    }
+    if (tile + (int)gridDim.x < tiles) load_batch(tile + gridDim.x, ch_first);
+    // acc: [0,1] = even row of pair g for tokens 2c, 2c+1; [2,3] = odd row
+    float* mine = part + warp * 128;
+    mine[g * 8 + 2 * c] = acc[0];
+    mine[g * 8 + 2 * c + 1] = acc[1];
+    mine[(g + 8) * 8 + 2 * c] = acc[2];
+    mine[(g + 8) * 8 + 2 * c + 1] = acc[3];
+    __syncthreads();
+    if (tid < 64) {
+      const int pr = tid >> 3, t = tid & 7;
+      float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) {
+        y0 += part[w * 128 + pr * 8 + t];
+        y1 += part[w * 128 + (pr + 8) * 8 + t];
+      }
+      if (t < ntok) {
+        const int r0 = 16 * tile + 2 * pr;
+        if (p.bias) { y0 += p.bias[r0]; y1 += p.bias[r0 + 1]; }
+        const int tok = t_base + t;
+        const int64_t crow = tokrow[t];
+        const bool is_q = r0 < q_rows;
+        const bool is_k = !is_q && r0 < q_rows + kv_rows;
+        if (is_q || is_k) {
+          const int within = is_q ? r0 : r0 - q_rows;
+          const int i = (within % D) >> 1;
+          const float cs = rope[t * (D / 2) + i], sn = rope[8 * (D / 2) + t * (D / 2) + i];
+          const float e = y0 * cs - y1 * sn, o = y0 * sn + y1 * cs;
+          y0 = e;
+          y1 = o;
+        }
+        if (is_q) {
+          const int64_t at = (int64_t)tok * q_rows + r0;
+          store_as(p.query, at, y0, p.query_dtype);
+          store_as(p.query, at + 1, y1, p.query_dtype);
+        } else if (crow >= 0) {
+          const int within = is_k ? r0 - q_rows : r0 - q_rows - kv_rows;
+          const int64_t at = crow * kv_rows + within;
+          void* dst = is_k ? p.key_cache : p.value_cache;
+          store_as(dst, at, y0, p.cache_dtype);
+          store_as(dst, at + 1, y1, p.cache_dtype);
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+cudaError_t launch_qkv_mma(const QkvRopeParams& p, int t_base, int num_sms, cudaStream_t stream) {
+  const size_t smem = 16 * ((size_t)p.model * 2 + 64) + kMmaWarps * 128 * sizeof(float) + 8 * p.head_dim * sizeof(float) + 64;
+  cudaError_t e = cudaFuncSetAttribute(qkv_rope_cache_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return e;
+  const int tiles = (p.heads + 2 * p.kv_heads) * p.head_dim / 16;
+  const int per_sm = smem <= 100 * 1024 ? 2 : 1;
+  int grid = tiles < num_sms * per_sm ? tiles : num_sms * per_sm;
+  qkv_rope_cache_mma_kernel<<<grid, kMmaWarps * 32, smem, stream>>>(p, t_base);
+  return cudaGetLastError();
+}
+
 __global__ void rope_interleaved_kernel(const float* __restrict__ in, const float* __restrict__ cosc,
                                         const float* __restrict__ sinc, float* __restrict__ out, int64_t rows,
                                         int head_dim, int seq_len, int start_position) {
@@ -179,8 +385,9 @@ __global__ void rope_interleaved_kernel(const float* __restrict__ in, const floa
 
 template <typename WT, int T>
 cudaError_t launch_qkv_t(const QkvRopeParams& p, int t_base, int num_sms, cudaStream_t stream) {
+  constexpr int kQkvWarps = T >= 4 ? 16 : (T == 2 ? 8 : 4);
   const size_t smem = (size_t)T * p.model * sizeof(float);
-  auto kern = qkv_rope_cache_kernel<WT, T>;
+  auto kern = qkv_rope_cache_kernel<WT, T, kQkvWarps>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
@@ -196,10 +403,12 @@ cudaError_t launch_qkv_t(const QkvRopeParams& p, int t_base, int num_sms, cudaSt
 template <typename WT>
 cudaError_t launch_qkv_w(const QkvRopeParams& p, int num_sms, cudaStream_t stream, int* launches) {
   *launches = 0;
+  const bool mma_ok = sizeof(WT) == 2 && ((p.heads + 2 * p.kv_heads) * p.head_dim) % 16 == 0;
   for (int t_base = 0; t_base < p.tokens; t_base += 8) {
     const int n = p.tokens - t_base;
     cudaError_t e;
-    if (n == 1) e = launch_qkv_t<WT, 1>(p, t_base, num_sms, stream);
+    if (n >= 2 && mma_ok) e = launch_qkv_mma(p, t_base, num_sms, stream);
+    else if (n == 1) e = launch_qkv_t<WT, 1>(p, t_base, num_sms, stream);
     else if (n == 2) e = launch_qkv_t<WT, 2>(p, t_base, num_sms, stream);
     else if (n <= 4) e = launch_qkv_t<WT, 4>(p, t_base, num_sms, stream);
     else e = launch_qkv_t<WT, 8>(p, t_base, num_sms, stream);

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|qkvrope|qkvrope1|qkvrope32] [--impl reference]
 
 One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
 default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
@@ -37,6 +37,13 @@ WORKLOADS = {
                     name="long_context_shard_B1_Hq8_Hkv1_S32768_D128_causal_bf16"),
     "c3paged": dict(B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill", block_size=16,
                     name="paged_gqa_prefill_B2_Hq32_Hkv8_S8192_D128_block16_causal_bf16"),
+    # the decode step in front of attention: packed Q/K/V projection of 8 resident tokens + RoPE + cache write
+    "qkvrope": dict(kind="gemv", tokens=8, heads=32, kv_heads=8, D=128, weight="bf16", cache_rows=1 << 16,
+                    name="qkv_rope_cache_T8_Hq32_Hkv8_D128_bf16_weights"),
+    "qkvrope1": dict(kind="gemv", tokens=1, heads=32, kv_heads=8, D=128, weight="bf16", cache_rows=1 << 16,
+                     name="qkv_rope_cache_T1_Hq32_Hkv8_D128_bf16_weights"),
+    "qkvrope32": dict(kind="gemv", tokens=1, heads=64, kv_heads=64, D=64, weight="f32", cache_rows=1 << 12,
+                      name="qkv_rope_cache_T1_H64_D64_fp32_weights_reference_contract"),
     "c4q": dict(B=16, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
                 name="batched_decode_quarter_B16_H32_D128_kvlen512-4096_bf16"),
     "c4": dict(B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
@@ -173,6 +180,73 @@ def make_inputs(w, device, seed):
     if w["kind"] == "decode":
         kv_len = np.random.Generator(np.random.Philox(seed)).integers(512, w["Sk"] + 1, w["B"]).astype(np.int32)
     return q, k, v, kv_len
+
+
+def run_gemv(args, w, pk):
+    """Times aidn_qkv_rope_cache.  The step is a GEMV: its algorithmic bytes are the packed weights (each read once)
+    plus activations and outputs.  Several weight copies are cycled so that no step finds its weights in the L2."""
+    from aidotnet.tensors_b200 import native as N
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    g = torch.Generator(device=dev).manual_seed(11)
+    T, H, Hkv, D = w["tokens"], w["heads"], w["kv_heads"], w["D"]
+    model, rows = H * D, (H + 2 * Hkv) * D
+    wdt = torch.bfloat16 if w["weight"] == "bf16" else torch.float32
+    copies = max(2, int(400e6 // (rows * model * (2 if w["weight"] == "bf16" else 4))) + 1)
+    weights = [(torch.randn(rows, model, generator=g, device=dev) / model ** 0.5).to(wdt) for _ in range(copies)]
+    x = torch.randn(T, model, generator=g, device=dev)
+    bias = torch.randn(rows, generator=g, device=dev) * 0.1
+    max_pos = 4096
+    ang = torch.rand(max_pos, D // 2, generator=g, device=dev) * 6.28
+    cos, sin = torch.cos(ang), torch.sin(ang)
+    cdt = wdt
+    q = torch.empty(T, model, dtype=cdt, device=dev)
+    kc = torch.zeros(w["cache_rows"], Hkv * D, dtype=cdt, device=dev)
+    vc = torch.zeros_like(kc)
+    pos = torch.randint(0, max_pos, (T,), generator=g, device=dev, dtype=torch.int32)
+    crow = torch.randperm(w["cache_rows"], generator=g, device=dev)[:T].to(torch.int32)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    dt = {torch.bfloat16: N.BF16, torch.float32: N.F32}
+    # One prebuilt argument block per weight copy: a step is then a single C call (the kernel is a few microseconds
+    # long, so per-call Python work would otherwise be what the events time).
+    lib = N.load()
+    blocks = []
+    for wt in weights:
+        a = N.QkvRopeArgs()
+        a.input, a.weights, a.bias, a.cosine, a.sine = x.data_ptr(), wt.data_ptr(), bias.data_ptr(), cos.data_ptr(), sin.data_ptr()
+        a.query, a.key_cache, a.value_cache = q.data_ptr(), kc.data_ptr(), vc.data_ptr()
+        a.positions, a.cache_rows = pos.data_ptr(), crow.data_ptr()
+        a.tokens, a.heads, a.kv_heads, a.head_dim, a.position = T, H, Hkv, D, 0
+        a.weight_dtype, a.query_dtype, a.cache_dtype = dt[wdt], dt[cdt], dt[cdt]
+        a.cache_capacity, a.max_position = w["cache_rows"], max_pos
+        blocks.append(a)
+    import ctypes
+    cstream = ctypes.c_void_p(stream)
+    def step(i):
+        rc = lib.aidn_qkv_rope_cache(ctypes.byref(blocks[i % copies]), cstream)
+        if rc != 0:
+            raise RuntimeError(N.last_error())
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    per_step = e0.elapsed_time(e1) / 1e3 / args.steps
+    esz = 2 if w["weight"] == "bf16" else 4
+    by = rows * model * esz + T * model * 4 + rows * 4 + T * rows * esz
+    gbs = by / 1e9 / per_step
+    print(json.dumps({
+        "metric": "decode-step Q/K/V projection + RoPE + cache write, HBM GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": w["weight"], "data": "synthetic",
+        "config": {"workload": w["name"], "l2": "%d weight copies (%.0f MB) cycled, larger than the 126 MB L2" % (copies, copies * rows * model * esz / 1e6)},
+        "tokens_per_s": T / per_step,
+        "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s", "frac": gbs / pk["hbm"],
+                     "traffic": None, "algorithmic": by, "algorithmic_unit": "bytes per launch", "peak_source": pk["source"]},
+        "gpu_launches": args.steps}))
 
 
 class Runner:
@@ -350,6 +424,10 @@ def main():
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
         dist = dist_mod
     pk = peaks()
+    if w["kind"] == "gemv":
+        if rank == 0:
+            run_gemv(args, w, pk)
+        return
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
