@@ -52,6 +52,15 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         public int num_blocks;
     }
 
+    /// <summary>Arguments of aidn_qkv_rope_cache (QkvProjectionRoPECacheD64 generalised, see include/aidn_sdpa.h).</summary>
+    [StructLayout(LayoutKind.Sequential)]
+    internal struct AidnQkvRopeArgs
+    {
+        public IntPtr input, weights, bias, cosine, sine, query, key_cache, value_cache, positions, cache_rows;
+        public int tokens, heads, kv_heads, head_dim, position, weight_dtype, query_dtype, cache_dtype;
+        public long cache_capacity, max_position;
+    }
+
     internal static class AidnSdpaNative
     {
         private const string Lib = "aidotnet_sdpa_sm100";
@@ -70,6 +79,8 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         [DllImport(Lib)] public static extern long aidn_sdpa_workspace_bytes(IntPtr handle, long batch, long seqQ, long seqKv);
         [DllImport(Lib)] public static extern int aidn_sdpa_launch(IntPtr handle, ref AidnSdpaArgs args, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_sdpa_launch_paged(IntPtr handle, ref AidnSdpaArgs args, ref AidnPagedKv paged, IntPtr cuStream);
+        [DllImport(Lib)] public static extern int aidn_qkv_rope_cache(ref AidnQkvRopeArgs args, IntPtr cuStream);
+        [DllImport(Lib)] public static extern int aidn_rope_interleaved(IntPtr input, IntPtr cosine, IntPtr sine, IntPtr output, long rows, int headDim, int seqLen, int startPosition, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_sdpa_poll(IntPtr handle, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_sdpa_last_path(IntPtr handle);
         [DllImport(Lib)] public static extern int aidn_sdpa_last_launch_count(IntPtr handle);

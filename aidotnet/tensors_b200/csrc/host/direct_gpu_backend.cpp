@@ -273,5 +273,51 @@ void CudaBackend::PagedAttentionPrefillGqa(const GpuBuffer& q, const GpuBuffer& 
         (int64_t)startPos + numQueries, startPos, scale);
 }
 
+// ---- the decode step in front of attention -----------------------------------------------------------------------
+void CudaBackend::QkvProjectionRoPECacheD64(const GpuBuffer& input, const GpuBuffer& packedWeights, const GpuBuffer& bias,
+                                            const GpuBuffer& cosine, const GpuBuffer& sine, const GpuBuffer& query,
+                                            const GpuBuffer& keyCache, const GpuBuffer& valueCache, int heads,
+                                            int cacheCapacity, int position) {
+  if (!input.Handle || !packedWeights.Handle || !bias.Handle || !cosine.Handle || !sine.Handle || !query.Handle ||
+      !keyCache.Handle || !valueCache.Handle)
+    throw std::invalid_argument("QkvProjectionRoPECacheD64: buffers must not be null");   // ArgumentNullException
+  if (heads <= 0) throw std::invalid_argument("heads must be > 0");
+  if (cacheCapacity <= 0) throw std::invalid_argument("cacheCapacity must be > 0");
+  if (position < 0 || position >= cacheCapacity) throw std::invalid_argument("position must be in [0, cacheCapacity)");
+  const int64_t dimension = 64, model = heads * dimension, projection = 3 * model;
+  const int64_t cacheElements = cacheCapacity * model, ropeElements = cacheCapacity * (dimension / 2);
+  if (input.Size < model || packedWeights.Size < projection * model || bias.Size < projection ||
+      cosine.Size < ropeElements || sine.Size < ropeElements || query.Size < model || keyCache.Size < cacheElements ||
+      valueCache.Size < cacheElements)
+    throw std::invalid_argument("QKV/RoPE/cache buffers are smaller than the requested canonical extents.");
+  aidn_qkv_rope_args a;
+  std::memset(&a, 0, sizeof(a));
+  a.input = static_cast<const float*>(input.Handle);
+  a.weights = packedWeights.Handle;
+  a.bias = static_cast<const float*>(bias.Handle);
+  a.cosine = static_cast<const float*>(cosine.Handle);
+  a.sine = static_cast<const float*>(sine.Handle);
+  a.query = query.Handle; a.key_cache = keyCache.Handle; a.value_cache = valueCache.Handle;
+  a.tokens = 1; a.heads = heads; a.kv_heads = heads; a.head_dim = (int32_t)dimension; a.position = position;
+  a.weight_dtype = packedWeights.Dtype; a.query_dtype = query.Dtype; a.cache_dtype = keyCache.Dtype;
+  a.cache_capacity = cacheCapacity; a.max_position = cacheCapacity;
+  Check(aidn_qkv_rope_cache(&a, stream_), "aidn_qkv_rope_cache");
+  ++launch_count_;
+}
+
+void CudaBackend::RopeInterleaved(const GpuBuffer& input, const GpuBuffer& cos, const GpuBuffer& sin,
+                                  const GpuBuffer& output, int rows, int headDim, int seqLen, int startPosition) {
+  if (rows <= 0 || headDim <= 0 || seqLen <= 0) throw std::invalid_argument("rows, headDim and seqLen must be positive");
+  if (input.Size < (int64_t)rows * headDim || output.Size < (int64_t)rows * headDim)
+    throw std::invalid_argument("RoPE buffers are smaller than rows * headDim");
+  const int64_t need = (int64_t)(startPosition + seqLen) * (headDim / 2);
+  if (cos.Size < need || sin.Size < need) throw std::invalid_argument("cos/sin caches do not reach startPosition + seqLen");
+  Check(aidn_rope_interleaved(static_cast<const float*>(input.Handle), static_cast<const float*>(cos.Handle),
+                              static_cast<const float*>(sin.Handle), static_cast<float*>(output.Handle), rows, headDim,
+                              seqLen, startPosition, stream_),
+        "aidn_rope_interleaved");
+  ++launch_count_;
+}
+
 }  // namespace host
 }  // namespace aidn

@@ -6,6 +6,7 @@
 //   ScaledDotProductAttention  CudaBackend.cs:8322-8379     FlashAttention        CudaBackend.cs:8522-8538
 //   FlashAttentionV2           CudaBackend.cs:8540-8578     GroupedQueryAttention CudaBackend.cs:8721-8759
 //   FlashDecode                CudaBackend.cs:2968-3021     PagedAttention{Decode,Prefill}{,Gqa} CudaBackend.cs:2845-2966
+//   QkvProjectionRoPECacheD64  CudaBackend.cs:8389-8439     RopeInterleaved       CudaBackend.cs:8441-8470
 //
 // ArgumentException / ArgumentOutOfRangeException map to std::invalid_argument, InvalidOperationException to
 // std::runtime_error.  There is no CPU fallback: a failing call throws.
@@ -69,6 +70,14 @@ class CudaBackend {
   void PagedAttentionPrefillGqa(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
                                 const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int kvHeads,
                                 int headDim, int blockSize, int numQueries, int startPos, float scale);
+
+  // The decode step in front of attention (CudaBackend.cs:8389-8439 and :8441-8470).
+  void QkvProjectionRoPECacheD64(const GpuBuffer& input, const GpuBuffer& packedWeights, const GpuBuffer& bias,
+                                 const GpuBuffer& cosine, const GpuBuffer& sine, const GpuBuffer& query,
+                                 const GpuBuffer& keyCache, const GpuBuffer& valueCache, int heads, int cacheCapacity,
+                                 int position);
+  void RopeInterleaved(const GpuBuffer& input, const GpuBuffer& cos, const GpuBuffer& sin, const GpuBuffer& output,
+                       int rows, int headDim, int seqLen, int startPosition);
 
   void Synchronize();
   int64_t LaunchCount() const { return launch_count_; }   // kernels enqueued (GpuLaunchProbe, CudaBackend.cs:5407)

@@ -275,6 +275,76 @@ int main() {
       cudaFree(bt.Handle);
     }
   }
+  {  // DirectGpu/DirectPtxWmmaTests.cs:2110-2113, 2307-2309: one fp32 token, head_dim 64, cache [capacity, heads, 64];
+     // DirectGpu/RopeGqaOpenClTests.cs:92-117: interleaved RoPE against the scalar loop
+    std::printf("qkv projection + RoPE + cache write, rope_interleaved\n");
+    struct Case { int heads, capacity, position; };
+    const Case cases[] = {{4, 16, 0}, {8, 64, 17}, {16, 128, 127}};
+    for (const Case& c : cases) {
+      const int D = 64, model = c.heads * D, half = D / 2;
+      auto x = uniform(model, 61 + c.heads), w = uniform(3 * model * model, 62 + c.heads), b = uniform(3 * model, 63);
+      for (auto& f : w) f /= std::sqrt((float)model);
+      std::vector<float> cosv((size_t)c.capacity * half), sinv((size_t)c.capacity * half);
+      for (int pos = 0; pos < c.capacity; ++pos)
+        for (int i = 0; i < half; ++i) {
+          const double angle = pos / std::pow(10000.0, (2.0 * i) / D);
+          cosv[(size_t)pos * half + i] = (float)std::cos(angle);
+          sinv[(size_t)pos * half + i] = (float)std::sin(angle);
+        }
+      std::vector<double> y(3 * model);
+      for (int r = 0; r < 3 * model; ++r) {
+        double acc = b[r];
+        for (int k = 0; k < model; ++k) acc += (double)w[(size_t)r * model + k] * x[k];
+        y[r] = acc;
+      }
+      std::vector<double> wantq(model), wantk((size_t)c.capacity * model, 0.0), wantv((size_t)c.capacity * model, 0.0);
+      for (int r = 0; r < 2 * model; r += 2) {
+        const int i = (r % D) / 2;
+        const double cs = cosv[(size_t)c.position * half + i], sn = sinv[(size_t)c.position * half + i];
+        const double e = y[r] * cs - y[r + 1] * sn, o = y[r] * sn + y[r + 1] * cs;
+        if (r < model) { wantq[r] = e; wantq[r + 1] = o; }
+        else { wantk[(size_t)c.position * model + r - model] = e; wantk[(size_t)c.position * model + r - model + 1] = o; }
+      }
+      for (int r = 0; r < model; ++r) wantv[(size_t)c.position * model + r] = y[2 * model + r];
+      DeviceArray dx(x), dw(w), db(b), dc(cosv), ds(sinv), dq((int64_t)model);
+      std::vector<float> zeros((size_t)c.capacity * model, 0.f);
+      DeviceArray dk(zeros), dvv(zeros);
+      backend.QkvProjectionRoPECacheD64(dx.buf, dw.buf, db.buf, dc.buf, ds.buf, dq.buf, dk.buf, dvv.buf, c.heads, c.capacity, c.position);
+      backend.Synchronize();
+      EXPECT(max_abs_diff(dq.download(), wantq) <= 2e-5 && max_abs_diff(dk.download(), wantk) <= 2e-5 &&
+             max_abs_diff(dvv.download(), wantv) <= 2e-5, "qkv/rope/cache heads=%d capacity=%d position=%d", c.heads, c.capacity, c.position);
+      bool threw = false;
+      try { backend.QkvProjectionRoPECacheD64(dx.buf, dw.buf, db.buf, dc.buf, ds.buf, dq.buf, dk.buf, dvv.buf, c.heads, c.capacity, c.capacity); }
+      catch (const std::invalid_argument&) { threw = true; }
+      EXPECT(threw, "position == cacheCapacity must throw");
+    }
+    {
+      const int heads = 3, seqLen = 6, headDim = 8, maxSeq = 32, rows = heads * seqLen, half = headDim / 2;
+      auto x = uniform(rows * headDim, 71);
+      std::vector<float> cosv(maxSeq * half), sinv(maxSeq * half);
+      for (int pos = 0; pos < maxSeq; ++pos)
+        for (int i = 0; i < half; ++i) {
+          const double angle = pos / std::pow(10000.0, (2.0 * i) / headDim);
+          cosv[pos * half + i] = (float)std::cos(angle);
+          sinv[pos * half + i] = (float)std::sin(angle);
+        }
+      for (int start : {0, 5}) {
+        std::vector<double> want(x.size());
+        for (int row = 0; row < rows; ++row)
+          for (int i = 0; i < half; ++i) {
+            const int pos = start + row % seqLen;
+            const double cs = cosv[pos * half + i], sn = sinv[pos * half + i];
+            const double xe = x[row * headDim + 2 * i], xo = x[row * headDim + 2 * i + 1];
+            want[row * headDim + 2 * i] = xe * cs - xo * sn;
+            want[row * headDim + 2 * i + 1] = xe * sn + xo * cs;
+          }
+        DeviceArray dx(x), dc(cosv), ds(sinv), dout((int64_t)x.size());
+        backend.RopeInterleaved(dx.buf, dc.buf, ds.buf, dout.buf, rows, headDim, seqLen, start);
+        backend.Synchronize();
+        EXPECT(max_abs_diff(dout.download(), want) <= 1e-6, "rope_interleaved start=%d", start);
+      }
+    }
+  }
   {  // argument errors throw, as ArgumentOutOfRangeException / ArgumentException do in the reference
     std::printf("argument errors\n");
     std::vector<float> z(64, 0.f);
