@@ -7,6 +7,7 @@ Method names, argument order, argument meaning and error behaviour follow
     FlashAttentionV2           :8540-8578      GroupedQueryAttention :8721-8759
     FlashDecode                :2968-3021      PagedAttentionDecode/Prefill{,Gqa} :2845-2966
     QkvProjectionRoPECacheD64  :8389-8439      RopeInterleaved     :8441-8470
+    FlashAttentionBackward     :8580-8604
 
 and the interface they implement (``Engines/DirectGpu/IDirectGpuBackend.cs:1421-1503``).  Buffers are
 ``GpuBuffer`` objects (the mirror of ``IGpuBuffer``, ``IDirectGpuBackend.cs:3776-3803``): a device
@@ -333,6 +334,37 @@ class CudaBackend:
             raise ValueError("PagedAttentionDecodeBatched: blockTables / seqLens are too small or not int32")
         return self._paged("PagedAttentionDecodeBatched", q, kcache, vcache, blockTables, heads, kvHeads, headDim,
                            blockSize, 1, maxSeqLen, 0, scale, batch=batch, seqLens=seqLens, tableStride=blocksPerSeq)
+
+    def FlashAttentionBackward(self, gradOutput: GpuBuffer, query: GpuBuffer, key: GpuBuffer, value: GpuBuffer,
+                               output: GpuBuffer, softmaxStats: GpuBuffer, gradQuery: GpuBuffer, gradKey: GpuBuffer,
+                               gradValue: GpuBuffer, batch: int, numHeads: int, seqQ: int, seqK: int, headDim: int,
+                               scale: float, isCausal: bool, attentionBias: Optional[GpuBuffer] = None,
+                               biasBatchStride: int = 0) -> None:
+        """dQ, dK, dV from dO, Q, K, V, O and the statistics FlashAttentionV2 wrote (``CudaBackend.cs:8580-8604``);
+        top-left causal, optional additive bias with the forward's batch stride; deterministic.  The gradient buffers
+        are fp32."""
+        self._check_dims(batch, numHeads, seqQ, seqK, headDim)
+        qsz, ksz = batch * numHeads * seqQ * headDim, batch * numHeads * seqK * headDim
+        if (gradOutput.Size < qsz or query.Size < qsz or output.Size < qsz or gradQuery.Size < qsz or key.Size < ksz or
+                value.Size < ksz or gradKey.Size < ksz or gradValue.Size < ksz or softmaxStats.Size < batch * numHeads * seqQ):
+            raise ValueError("Attention tensor buffers are smaller than the requested dimensions.")
+        if any(g.dtype != torch.float32 for g in (gradQuery, gradKey, gradValue, softmaxStats)):
+            raise ValueError("gradients and softmaxStats are fp32 buffers")
+        if gradOutput.dtype != output.dtype:
+            raise ValueError("gradOutput must have the dtype of output")
+        h = self._handle(qkv_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[output.dtype], head_dim=headDim,
+                         num_q_heads=numHeads, num_kv_heads=numHeads, causal=bool(isCausal), causal_bottom_right=False,
+                         causal_offset=0, emit_lse=True,
+                         mask_kind=N.MASK_ADD_F32 if attentionBias is not None else N.MASK_NONE)
+        nbytes = h.backward_workspace_bytes(batch, seqQ)
+        ws, ws_bytes = self._workspace(nbytes)
+        h.backward(q=query.Handle, k=key.Handle, v=value.Handle, out=output.Handle, lse=softmaxStats.Handle,
+                   dout=gradOutput.Handle, dq=gradQuery.Handle, dk=gradKey.Handle, dv=gradValue.Handle, batch=batch,
+                   seq_q=seqQ, seq_kv=seqK, stream=self.stream.cuda_stream, workspace=ws, workspace_bytes=ws_bytes,
+                   mask=attentionBias.Handle if attentionBias is not None else None,
+                   mask_stride=(biasBatchStride, seqQ * seqK, seqK, 1) if attentionBias is not None else (0, 0, 0, 0),
+                   scale=float(scale))
+        self.launch_count += h.last_launch_count
 
     # -- the decode step in front of attention ----------------------------------------------------------------
     def QkvProjectionRoPECacheD64(self, input: GpuBuffer, packedWeights: GpuBuffer, bias: GpuBuffer, cosine: GpuBuffer,

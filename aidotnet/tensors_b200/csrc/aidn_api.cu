@@ -266,12 +266,12 @@ int aidn_sdpa_poll(aidn_sdpa_t h, void* cu_stream) {
 
 namespace {
 
-// The launch shared by aidn_sdpa_launch (pg == nullptr) and aidn_sdpa_launch_paged.
-int launch_common(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* pg, void* cu_stream) {
+// Validates a launch request and flattens it into the kernels' parameter block (shared by the forward launches and
+// the backward).
+int build_params(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* pg, aidn::SdpaParams& p) {
   g_err[0] = 0;
   if (!h || !a) return fail(AIDN_EINVAL, "launch: null argument");
   const aidn_sdpa_desc& d = h->d;
-  cudaStream_t stream = (cudaStream_t)cu_stream;
   if (!a->q || !a->k || !a->v || !a->out) return fail(AIDN_EINVAL, "launch: null tensor pointer");
   if (a->batch <= 0 || a->seq_q <= 0 || a->seq_kv <= 0)
     return fail(AIDN_EINVAL, "launch: attention dimensions must be positive");
@@ -280,7 +280,6 @@ int launch_common(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* p
   if (d.mask_kind != AIDN_MASK_NONE && !a->mask) return fail(AIDN_EINVAL, "launch: mask_kind set but mask pointer is null");
   if (a->scale < 0.f || std::isnan(a->scale)) return fail(AIDN_EINVAL, "launch: scale must be >= 0");
 
-  aidn::SdpaParams p;
   std::memset(&p, 0, sizeof(p));
   p.q = a->q;
   p.k = a->k;
@@ -339,6 +338,17 @@ int launch_common(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* p
   for (int i = 0; i < 3; ++i)
     if (p.qs[i] < 0 || p.ks[i] < 0 || p.vs[i] < 0 || p.os[i] < 0) return fail(AIDN_EINVAL, "launch: negative stride");
   if (p.head_count > 65535) return fail(AIDN_EINVAL, "launch: more than 65535 heads in one shard");
+  return AIDN_OK;
+}
+
+// The launch shared by aidn_sdpa_launch (pg == nullptr) and aidn_sdpa_launch_paged.
+int launch_common(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* pg, void* cu_stream) {
+  aidn::SdpaParams p;
+  const int rc = build_params(h, a, pg, p);
+  if (rc != AIDN_OK) return rc;
+  const aidn_sdpa_desc& d = h->d;
+  cudaStream_t stream = (cudaStream_t)cu_stream;
+  const int64_t D = d.head_dim;
 
   const size_t esz = elem_size(d.qkv_dtype);
   const bool vec_ok = aligned16(p.q, p.qs, esz) && aligned16(p.k, p.ks, esz) && aligned16(p.v, p.vs, esz);
@@ -428,6 +438,43 @@ int aidn_sdpa_launch_paged(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_pa
     return fail(AIDN_EINVAL, "launch_paged: null aidn_paged_kv");
   }
   return launch_common(h, a, paged, cu_stream);
+}
+
+int64_t aidn_sdpa_backward_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq_q) {
+  if (!h || batch <= 0 || seq_q <= 0) {
+    fail(AIDN_EINVAL, "backward_workspace_bytes: bad argument");
+    return -1;
+  }
+  return align_up(batch * h->head_count * seq_q * (int64_t)sizeof(float), 256);
+}
+
+int aidn_sdpa_backward(aidn_sdpa_t h, const aidn_sdpa_bwd_args* a, void* cu_stream) {
+  g_err[0] = 0;
+  if (!h || !a) return fail(AIDN_EINVAL, "backward: null argument");
+  if (!a->dout || !a->dq || !a->dk || !a->dv) return fail(AIDN_EINVAL, "backward: null gradient pointer");
+  if (!a->fwd.lse) return fail(AIDN_EINVAL, "backward: the forward's log-sum-exp (fwd.lse) is required");
+  if (h->d.softcap > 0.f) return fail(AIDN_EUNSUPPORTED, "backward: logit softcap is not differentiated here");
+  aidn::BwdParams bp;
+  const int rc = build_params(h, &a->fwd, a->paged, bp.p);
+  if (rc != AIDN_OK) return rc;
+  bp.p.lse = a->fwd.lse;   // read here, whatever desc.emit_lse says
+  const int64_t need = aidn_sdpa_backward_workspace_bytes(h, a->fwd.batch, a->fwd.seq_q);
+  if (!a->fwd.workspace || a->fwd.workspace_bytes < need)
+    return fail(AIDN_EWORKSPACE, "backward: workspace of %lld bytes, need %lld", (long long)a->fwd.workspace_bytes, (long long)need);
+  if ((uintptr_t)a->fwd.workspace % 16 != 0) return fail(AIDN_EINVAL, "backward: workspace must be 16-byte aligned");
+  bp.dout = a->dout;
+  if (all_zero(a->do_stride)) std::memcpy(bp.dos, bp.p.os, sizeof(bp.dos));
+  else std::memcpy(bp.dos, a->do_stride, sizeof(bp.dos));
+  for (int i = 0; i < 3; ++i)
+    if (bp.dos[i] < 0) return fail(AIDN_EINVAL, "backward: negative stride");
+  bp.dq = a->dq; bp.dk = a->dk; bp.dv = a->dv;
+  bp.delta = static_cast<float*>(a->fwd.workspace);
+  int launches = 0;
+  cudaError_t e = aidn::launch_backward(bp, h->d.qkv_dtype, (cudaStream_t)cu_stream, &launches);
+  if (e != cudaSuccess) return fail_cuda(e, "backward");
+  h->last_path = AIDN_PATH_GENERIC;
+  h->last_launches = launches;
+  return AIDN_OK;
 }
 
 // Decode for callers that cannot allocate device memory (no handle, no workspace): see include/aidn_sdpa.h.

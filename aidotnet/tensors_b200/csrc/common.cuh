@@ -170,6 +170,19 @@ cudaError_t launch_decode_static(const SdpaParams& p, int dtype, int chunk, int 
                                  int* launches);
 cudaError_t launch_cast(int kind, const void* src, void* dst, int64_t n, cudaStream_t stream);
 
+// Attention backward (csrc/sdpa_backward.cu): the forward's parameter block (p.out = O, p.lse = log-sum-exp, both
+// inputs here) plus dO, the gradient outputs and the delta scratch.
+struct BwdParams {
+  SdpaParams p;
+  const void* dout;   // dtype of p.out
+  int64_t dos[3];
+  float* dq;          // [B, Hc, Sq, D] fp32, Hc = heads of the shard
+  float* dk;          // [B, Hc / group, Sk, D] fp32
+  float* dv;
+  float* delta;       // [B, Hc, Sq] scratch
+};
+cudaError_t launch_backward(const BwdParams& bp, int dtype, cudaStream_t stream, int* launches);
+
 // Packed Q/K/V projection + RoPE + KV-cache write (csrc/qkv_rope_cache.cu).
 struct QkvRopeParams {
   const float* input;

@@ -1,0 +1,363 @@
+// Attention backward with LSE recompute: dQ, dK, dV from dO, Q, K, V, O and the forward's log-sum-exp.
+//
+// Replaces flash_attention_backward_gradq_deterministic / _gradkv_deterministic of the reference
+// (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/CudaAttentionKernels.cs:251-390; host
+// CUDA/CudaBackend.cs:8580-8704; CPU Engines/CpuEngine.cs:29474): one thread per query row, and one thread per
+// (key, d) that recomputes the whole score row per query.  As there, every output cell is owned by one thread and
+// summed in a fixed order, so the result is deterministic (no atomics).
+//
+//   P  = exp(S - lse),  S = scale * Q K^T (+ bias, masks)          delta_i = sum_d dO_id O_id
+//   dV = P^T dO         dP = dO V^T        dS = P * (dP - delta)   dQ = scale * dS K     dK = scale * dS^T Q
+//
+// fp32 FFMA arithmetic with K/V (or Q/dO) tiles staged in shared memory, any head_dim <= 256, every mask kind of the
+// forward, grouped-query attention (dK / dV sum over the query heads of the group).  A correctness-first kernel: it
+// shares the generic forward kernel's tiling, not the tcgen05 kernel's.
+#include "common.cuh"
+
+namespace aidn {
+namespace {
+
+constexpr int kRows = 16;      // query rows per tile
+constexpr int kKeys = 32;      // keys per tile
+constexpr int kBwdWarps = 4;
+
+template <typename T>
+__device__ __forceinline__ float load_o(const void* base, int64_t idx, int f32) {
+  return f32 ? static_cast<const float*>(base)[idx] : to_float<T>(static_cast<const T*>(base)[idx]);
+}
+
+// delta[b, h, i] = sum_d dO * O; one warp per row.
+template <typename T>
+__global__ void __launch_bounds__(128) bwd_delta_kernel(const BwdParams bp) {
+  const SdpaParams& p = bp.p;
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int hl = blockIdx.y, b = blockIdx.z;
+  if (row >= p.seq_q) return;
+  const int h = p.head_begin + hl;
+  const int64_t ob = b * p.os[0] + (int64_t)h * p.os[1] + row * p.os[2];
+  const int64_t gb = b * bp.dos[0] + (int64_t)h * bp.dos[1] + row * bp.dos[2];
+  float acc = 0.f;
+  for (int d = lane; d < p.head_dim; d += 32) acc += load_o<T>(bp.dout, gb + d, p.out_f32) * load_o<T>(p.out, ob + d, p.out_f32);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) bp.delta[((int64_t)b * p.head_count + hl) * p.seq_q + row] = acc;
+}
+
+// Probability and score gradient of (row, key): p = exp(logit - lse), ds = p * (dp - delta).
+__device__ __forceinline__ void prob_and_ds(const SdpaParams& p, float s, float dp, float lse, float delta, int b, int h,
+                                            int64_t row, int64_t key, int64_t kv_limit, float& pj, float& ds) {
+  pj = 0.f;
+  if (row < p.seq_q && key < p.seq_kv && lse != -INFINITY) {
+    const float val = finish_logit(p, s * p.scale, b, h, row, key, kv_limit);
+    if (val != -INFINITY) pj = expf(val - lse);
+  }
+  ds = pj * (dp - delta);
+}
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(kBwdWarps * 32) bwd_dq_kernel(const BwdParams bp) {
+  const SdpaParams& p = bp.p;
+  constexpr int PITCH = DMAX + 4;
+  constexpr int ND = DMAX / 32;
+  extern __shared__ __align__(16) float smem[];
+  float* Qs = smem;                       // [kRows][PITCH]
+  float* Gs = Qs + kRows * PITCH;         // dO, [kRows][PITCH]
+  float* Ks = Gs + kRows * PITCH;         // [kKeys][PITCH]
+  float* Vs = Ks + kKeys * PITCH;         // [kKeys][PITCH]
+  float* Ds = Vs + kKeys * PITCH;         // dS, [kRows][kKeys]
+  __shared__ int64_t kv_rows[kKeys];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z, hl = blockIdx.y, h = p.head_begin + hl, kvh = h / p.group;
+  const int64_t row0 = (int64_t)blockIdx.x * kRows;
+  const int D = p.head_dim;
+  const bool paged = p.block_table != nullptr;
+  const T* qb = static_cast<const T*>(p.q) + b * p.qs[0] + (int64_t)h * p.qs[1];
+  const T* kb = static_cast<const T*>(p.k) + (paged ? 0 : b * p.ks[0]) + (int64_t)kvh * p.ks[1];
+  const T* vb = static_cast<const T*>(p.v) + (paged ? 0 : b * p.vs[0]) + (int64_t)kvh * p.vs[1];
+
+  for (int idx = tid; idx < kRows * DMAX; idx += kBwdWarps * 32) {
+    const int r = idx / DMAX, d = idx - r * DMAX;
+    const int64_t row = row0 + r;
+    const bool ok = row < p.seq_q && d < D;
+    Qs[r * PITCH + d] = ok ? to_float<T>(qb[row * p.qs[2] + d]) : 0.f;
+    Gs[r * PITCH + d] = ok ? load_o<T>(bp.dout, b * bp.dos[0] + (int64_t)h * bp.dos[1] + row * bp.dos[2] + d, p.out_f32) : 0.f;
+  }
+  float lse[4], delta[4];
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int64_t row = row0 + warp * 4 + r;
+    lse[r] = row < p.seq_q ? p.lse[((int64_t)b * p.num_q_heads + h) * p.seq_q + row] : -INFINITY;
+    delta[r] = row < p.seq_q ? bp.delta[((int64_t)b * p.head_count + hl) * p.seq_q + row] : 0.f;
+  }
+  const int64_t kv_limit = kv_limit_of(p, b);
+  int64_t kend = kv_limit;
+  if (p.causal) {
+    int64_t last_row = row0 + kRows - 1;
+    if (last_row > p.seq_q - 1) last_row = p.seq_q - 1;
+    const int64_t c = last_row + p.causal_offset + 1;
+    if (c < kend) kend = c;
+  }
+  bool bad_block = false;
+  float acc[4][ND];
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+#pragma unroll
+    for (int i = 0; i < ND; ++i) acc[r][i] = 0.f;
+
+  for (int64_t j0 = 0; j0 < kend; j0 += kKeys) {
+    __syncthreads();
+    if (paged) {
+      if (tid < kKeys) kv_rows[tid] = (j0 + tid < kend) ? kv_row_of(p, b, j0 + tid, bad_block) : -1;
+      __syncthreads();
+    }
+    for (int idx = tid; idx < kKeys * DMAX; idx += kBwdWarps * 32) {
+      const int j = idx / DMAX, d = idx - j * DMAX;
+      const int64_t key = j0 + j;
+      const int64_t row = paged ? kv_rows[j] : key;
+      const bool ok = key < p.seq_kv && d < D && row >= 0;
+      Ks[j * PITCH + d] = ok ? to_float<T>(kb[row * p.ks[2] + d]) : 0.f;
+      Vs[j * PITCH + d] = ok ? to_float<T>(vb[row * p.vs[2] + d]) : 0.f;
+    }
+    __syncthreads();
+
+    float s[4] = {0.f, 0.f, 0.f, 0.f}, dp[4] = {0.f, 0.f, 0.f, 0.f};
+    const float4* krow = reinterpret_cast<const float4*>(Ks + lane * PITCH);
+    const float4* vrow = reinterpret_cast<const float4*>(Vs + lane * PITCH);
+#pragma unroll 2
+    for (int d4 = 0; d4 < DMAX / 4; ++d4) {
+      const float4 kv = krow[d4], vv = vrow[d4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const float4 qv = reinterpret_cast<const float4*>(Qs + (warp * 4 + r) * PITCH)[d4];
+        const float4 gv = reinterpret_cast<const float4*>(Gs + (warp * 4 + r) * PITCH)[d4];
+        s[r] = fmaf(qv.x, kv.x, s[r]); s[r] = fmaf(qv.y, kv.y, s[r]); s[r] = fmaf(qv.z, kv.z, s[r]); s[r] = fmaf(qv.w, kv.w, s[r]);
+        dp[r] = fmaf(gv.x, vv.x, dp[r]); dp[r] = fmaf(gv.y, vv.y, dp[r]); dp[r] = fmaf(gv.z, vv.z, dp[r]); dp[r] = fmaf(gv.w, vv.w, dp[r]);
+      }
+    }
+    const int64_t key = j0 + lane;
+    const bool key_ok = !(paged && kv_rows[lane] < 0);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      float pj, ds;
+      prob_and_ds(p, s[r], dp[r], key_ok ? lse[r] : -INFINITY, delta[r], b, h, row0 + warp * 4 + r, key, kv_limit, pj, ds);
+      Ds[(warp * 4 + r) * kKeys + lane] = ds;
+    }
+    __syncwarp();
+#pragma unroll 2
+    for (int j4 = 0; j4 < kKeys / 4; ++j4) {
+      float4 dv4[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) dv4[r] = reinterpret_cast<const float4*>(Ds + (warp * 4 + r) * kKeys)[j4];
+#pragma unroll
+      for (int i = 0; i < ND; ++i) {
+        const float k0 = Ks[(j4 * 4 + 0) * PITCH + lane + 32 * i], k1 = Ks[(j4 * 4 + 1) * PITCH + lane + 32 * i];
+        const float k2 = Ks[(j4 * 4 + 2) * PITCH + lane + 32 * i], k3 = Ks[(j4 * 4 + 3) * PITCH + lane + 32 * i];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          acc[r][i] = fmaf(dv4[r].x, k0, acc[r][i]); acc[r][i] = fmaf(dv4[r].y, k1, acc[r][i]);
+          acc[r][i] = fmaf(dv4[r].z, k2, acc[r][i]); acc[r][i] = fmaf(dv4[r].w, k3, acc[r][i]);
+        }
+      }
+    }
+    __syncwarp();
+  }
+  report_bad_block(p, bad_block);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int64_t row = row0 + warp * 4 + r;
+    if (row >= p.seq_q) continue;
+    float* out = bp.dq + (((int64_t)b * p.head_count + hl) * p.seq_q + row) * D;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) out[d] = acc[r][i] * p.scale;
+    }
+  }
+}
+
+template <typename T, int DMAX>
+__global__ void __launch_bounds__(kBwdWarps * 32) bwd_dkv_kernel(const BwdParams bp) {
+  const SdpaParams& p = bp.p;
+  constexpr int PITCH = DMAX + 4;
+  constexpr int ND = DMAX / 32;
+  constexpr int KPW = kKeys / kBwdWarps;   // keys owned by a warp in the accumulation phase
+  extern __shared__ __align__(16) float smem[];
+  float* Ks = smem;                       // [kKeys][PITCH]
+  float* Vs = Ks + kKeys * PITCH;
+  float* Qs = Vs + kKeys * PITCH;         // [kRows][PITCH]
+  float* Gs = Qs + kRows * PITCH;
+  float* Ps = Gs + kRows * PITCH;         // [kRows][kKeys]
+  float* Ds = Ps + kRows * kKeys;         // [kRows][kKeys]
+  __shared__ int64_t kv_rows[kKeys];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.z;
+  const int kvl = blockIdx.y;                              // kv head within the shard
+  const int kvh = p.head_begin / p.group + kvl;
+  const int64_t j0 = (int64_t)blockIdx.x * kKeys;
+  const int D = p.head_dim;
+  const bool paged = p.block_table != nullptr;
+  const T* kb = static_cast<const T*>(p.k) + (paged ? 0 : b * p.ks[0]) + (int64_t)kvh * p.ks[1];
+  const T* vb = static_cast<const T*>(p.v) + (paged ? 0 : b * p.vs[0]) + (int64_t)kvh * p.vs[1];
+  const int64_t kv_limit = kv_limit_of(p, b);
+  bool bad_block = false;
+
+  if (paged) {
+    if (tid < kKeys) kv_rows[tid] = (j0 + tid < kv_limit) ? kv_row_of(p, b, j0 + tid, bad_block) : -1;
+    __syncthreads();
+  }
+  for (int idx = tid; idx < kKeys * DMAX; idx += kBwdWarps * 32) {
+    const int j = idx / DMAX, d = idx - j * DMAX;
+    const int64_t key = j0 + j;
+    const int64_t row = paged ? kv_rows[j] : key;
+    const bool ok = key < p.seq_kv && d < D && row >= 0;
+    Ks[j * PITCH + d] = ok ? to_float<T>(kb[row * p.ks[2] + d]) : 0.f;
+    Vs[j * PITCH + d] = ok ? to_float<T>(vb[row * p.vs[2] + d]) : 0.f;
+  }
+
+  float accK[KPW][ND], accV[KPW][ND];
+#pragma unroll
+  for (int jj = 0; jj < KPW; ++jj)
+#pragma unroll
+    for (int i = 0; i < ND; ++i) accK[jj][i] = accV[jj][i] = 0.f;
+
+  // first query row that can see key j0 (causal: key <= row + offset)
+  int64_t r_first = 0;
+  if (p.causal) {
+    r_first = j0 - p.causal_offset;
+    if (r_first < 0) r_first = 0;
+    r_first = r_first / kRows * kRows;
+  }
+  const bool tile_visible = j0 < kv_limit;
+
+  for (int g = 0; g < p.group && tile_visible; ++g) {
+    const int h = kvh * p.group + g, hl = h - p.head_begin;
+    const T* qb = static_cast<const T*>(p.q) + b * p.qs[0] + (int64_t)h * p.qs[1];
+    for (int64_t row0 = r_first; row0 < p.seq_q; row0 += kRows) {
+      __syncthreads();   // previous tile consumed (and K/V staged before the first use)
+      for (int idx = tid; idx < kRows * DMAX; idx += kBwdWarps * 32) {
+        const int r = idx / DMAX, d = idx - r * DMAX;
+        const int64_t row = row0 + r;
+        const bool ok = row < p.seq_q && d < D;
+        Qs[r * PITCH + d] = ok ? to_float<T>(qb[row * p.qs[2] + d]) : 0.f;
+        Gs[r * PITCH + d] = ok ? load_o<T>(bp.dout, b * bp.dos[0] + (int64_t)h * bp.dos[1] + row * bp.dos[2] + d, p.out_f32) : 0.f;
+      }
+      __syncthreads();
+      // phase A: warp w takes rows 4w..4w+3, lane j takes key j0 + j
+      {
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, dp[4] = {0.f, 0.f, 0.f, 0.f};
+        const float4* krow = reinterpret_cast<const float4*>(Ks + lane * PITCH);
+        const float4* vrow = reinterpret_cast<const float4*>(Vs + lane * PITCH);
+#pragma unroll 2
+        for (int d4 = 0; d4 < DMAX / 4; ++d4) {
+          const float4 kv = krow[d4], vv = vrow[d4];
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const float4 qv = reinterpret_cast<const float4*>(Qs + (warp * 4 + r) * PITCH)[d4];
+            const float4 gv = reinterpret_cast<const float4*>(Gs + (warp * 4 + r) * PITCH)[d4];
+            s[r] = fmaf(qv.x, kv.x, s[r]); s[r] = fmaf(qv.y, kv.y, s[r]); s[r] = fmaf(qv.z, kv.z, s[r]); s[r] = fmaf(qv.w, kv.w, s[r]);
+            dp[r] = fmaf(gv.x, vv.x, dp[r]); dp[r] = fmaf(gv.y, vv.y, dp[r]); dp[r] = fmaf(gv.z, vv.z, dp[r]); dp[r] = fmaf(gv.w, vv.w, dp[r]);
+          }
+        }
+        const int64_t key = j0 + lane;
+        const bool key_ok = !(paged && kv_rows[lane] < 0);
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int64_t row = row0 + warp * 4 + r;
+          float lse = -INFINITY, delta = 0.f;
+          if (row < p.seq_q && key_ok) {
+            lse = p.lse[((int64_t)b * p.num_q_heads + h) * p.seq_q + row];
+            delta = bp.delta[((int64_t)b * p.head_count + hl) * p.seq_q + row];
+          }
+          float pj, ds;
+          prob_and_ds(p, s[r], dp[r], lse, delta, b, h, row, key, kv_limit, pj, ds);
+          Ps[(warp * 4 + r) * kKeys + lane] = pj;
+          Ds[(warp * 4 + r) * kKeys + lane] = ds;
+        }
+      }
+      __syncthreads();
+      // phase B: warp w owns keys KPW*w .. KPW*w + KPW - 1, lane owns dims lane + 32 i; rows in ascending order
+#pragma unroll 2
+      for (int r = 0; r < kRows; ++r) {
+        float pw[KPW], dw[KPW];
+#pragma unroll
+        for (int jj = 0; jj < KPW; ++jj) {
+          pw[jj] = Ps[r * kKeys + warp * KPW + jj];
+          dw[jj] = Ds[r * kKeys + warp * KPW + jj];
+        }
+#pragma unroll
+        for (int i = 0; i < ND; ++i) {
+          const float gq = Gs[r * PITCH + lane + 32 * i], qq = Qs[r * PITCH + lane + 32 * i];
+#pragma unroll
+          for (int jj = 0; jj < KPW; ++jj) {
+            accV[jj][i] = fmaf(pw[jj], gq, accV[jj][i]);
+            accK[jj][i] = fmaf(dw[jj], qq, accK[jj][i]);
+          }
+        }
+      }
+    }
+  }
+  report_bad_block(p, bad_block);
+#pragma unroll
+  for (int jj = 0; jj < KPW; ++jj) {
+    const int64_t key = j0 + warp * KPW + jj;
+    if (key >= p.seq_kv) continue;
+    const int64_t base = (((int64_t)b * (p.head_count / p.group) + kvl) * p.seq_kv + key) * D;
+#pragma unroll
+    for (int i = 0; i < ND; ++i) {
+      const int d = lane + 32 * i;
+      if (d < D) {
+        bp.dk[base + d] = accK[jj][i] * p.scale;
+        bp.dv[base + d] = accV[jj][i];
+      }
+    }
+  }
+}
+
+template <typename T, int DMAX>
+cudaError_t launch_bwd_t(const BwdParams& bp, cudaStream_t stream, int* launches) {
+  const SdpaParams& p = bp.p;
+  constexpr int PITCH = DMAX + 4;
+  dim3 g0((unsigned)((p.seq_q + 3) / 4), (unsigned)p.head_count, (unsigned)p.batch);
+  bwd_delta_kernel<T><<<g0, 128, 0, stream>>>(bp);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const size_t smem_q = sizeof(float) * ((2 * kRows + 2 * kKeys) * PITCH + kRows * kKeys);
+  const size_t smem_kv = sizeof(float) * ((2 * kRows + 2 * kKeys) * PITCH + 2 * kRows * kKeys);
+  auto kq = bwd_dq_kernel<T, DMAX>;
+  auto kkv = bwd_dkv_kernel<T, DMAX>;
+  if (smem_kv > 48 * 1024) {
+    e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv);
+    if (e != cudaSuccess) return e;
+  }
+  dim3 g1((unsigned)((p.seq_q + kRows - 1) / kRows), (unsigned)p.head_count, (unsigned)p.batch);
+  kq<<<g1, kBwdWarps * 32, smem_q, stream>>>(bp);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  dim3 g2((unsigned)((p.seq_kv + kKeys - 1) / kKeys), (unsigned)(p.head_count / p.group), (unsigned)p.batch);
+  kkv<<<g2, kBwdWarps * 32, smem_kv, stream>>>(bp);
+  *launches = 3;
+  return cudaGetLastError();
+}
+
+template <typename T>
+cudaError_t launch_bwd_d(const BwdParams& bp, cudaStream_t stream, int* launches) {
+  if (bp.p.head_dim <= 64) return launch_bwd_t<T, 64>(bp, stream, launches);
+  if (bp.p.head_dim <= 128) return launch_bwd_t<T, 128>(bp, stream, launches);
+  return launch_bwd_t<T, 256>(bp, stream, launches);
+}
+
+}  // namespace
+
+cudaError_t launch_backward(const BwdParams& bp, int dtype, cudaStream_t stream, int* launches) {
+  switch (dtype) {
+    case AIDN_F32: return launch_bwd_d<float>(bp, stream, launches);
+    case AIDN_F16: return launch_bwd_d<__half>(bp, stream, launches);
+    default: return launch_bwd_d<__nv_bfloat16>(bp, stream, launches);
+  }
+}
+
+}  // namespace aidn

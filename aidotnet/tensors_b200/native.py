@@ -72,6 +72,13 @@ class QkvRopeArgs(ctypes.Structure):
     ]
 
 
+class SdpaBwdArgs(ctypes.Structure):
+    _fields_ = [
+        ("fwd", SdpaArgs), ("paged", ctypes.POINTER(PagedKv)), ("dout", ctypes.c_void_p),
+        ("do_stride", ctypes.c_int64 * 3), ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
+    ]
+
+
 class AidnError(RuntimeError):
     def __init__(self, status: int, message: str):
         super().__init__(f"aidn_sdpa status {status}: {message}")
@@ -118,6 +125,10 @@ def load() -> ctypes.CDLL:
     lib.aidn_sdpa_launch_paged.argtypes = [ctypes.c_void_p, ctypes.POINTER(SdpaArgs), ctypes.POINTER(PagedKv),
                                            ctypes.c_void_p]
     lib.aidn_sdpa_launch_paged.restype = ctypes.c_int
+    lib.aidn_sdpa_backward.argtypes = [ctypes.c_void_p, ctypes.POINTER(SdpaBwdArgs), ctypes.c_void_p]
+    lib.aidn_sdpa_backward.restype = ctypes.c_int
+    lib.aidn_sdpa_backward_workspace_bytes.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64]
+    lib.aidn_sdpa_backward_workspace_bytes.restype = ctypes.c_int64
     lib.aidn_qkv_rope_cache.argtypes = [ctypes.POINTER(QkvRopeArgs), ctypes.c_void_p]
     lib.aidn_qkv_rope_cache.restype = ctypes.c_int
     lib.aidn_rope_interleaved.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
@@ -192,6 +203,27 @@ class Handle:
             check(self._lib.aidn_sdpa_launch_paged(self._h, ctypes.byref(a), ctypes.byref(pg), ctypes.c_void_p(stream)))
             return
         check(self._lib.aidn_sdpa_launch(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
+
+    def backward_workspace_bytes(self, batch: int, seq_q: int) -> int:
+        n = self._lib.aidn_sdpa_backward_workspace_bytes(self._h, batch, seq_q)
+        if n < 0:
+            raise AidnError(EINVAL, last_error())
+        return int(n)
+
+    def backward(self, *, q: int, k: int, v: int, out: int, lse: int, dout: int, dq: int, dk: int, dv: int, batch: int,
+                 seq_q: int, seq_kv: int, stream: int, workspace: int, workspace_bytes: int, mask: Optional[int] = None,
+                 mask_stride: Sequence[int] = (0, 0, 0, 0), kv_len: Optional[int] = None, q_stride=None, k_stride=None,
+                 v_stride=None, o_stride=None, do_stride=None, scale: float = 0.0) -> None:
+        """dQ, dK, dV (dense fp32) from dO, Q, K, V, the forward output ``out`` and its log-sum-exp ``lse``."""
+        a = SdpaBwdArgs()
+        f = a.fwd
+        f.q, f.k, f.v, f.out, f.lse, f.mask, f.kv_len = q, k, v, out, lse, mask, kv_len
+        f.mask_stride = (ctypes.c_int64 * 4)(*mask_stride)
+        f.batch, f.seq_q, f.seq_kv = batch, seq_q, seq_kv
+        f.q_stride, f.k_stride, f.v_stride, f.o_stride = _arr3(q_stride), _arr3(k_stride), _arr3(v_stride), _arr3(o_stride)
+        f.scale, f.workspace, f.workspace_bytes = scale, workspace, workspace_bytes
+        a.dout, a.do_stride, a.dq, a.dk, a.dv = dout, _arr3(do_stride), dq, dk, dv
+        check(self._lib.aidn_sdpa_backward(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
 
     def poll(self, stream: int) -> None:
         check(self._lib.aidn_sdpa_poll(self._h, ctypes.c_void_p(stream)))

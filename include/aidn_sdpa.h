@@ -179,6 +179,25 @@ AIDN_API int aidn_sdpa_device_supported(int32_t device);
  * (CudaBackend.cs:2994-2996). */
 AIDN_API int aidn_sdpa_decode_noalloc(const aidn_sdpa_desc* desc, const aidn_sdpa_args* args, void* cu_stream);
 
+/* Backward of the same attention (FlashAttentionBackward, IDirectGpuBackend.cs:1479-1483, CudaBackend.cs:8580-8704;
+ * CPU CpuEngine.cs:29474): dQ, dK, dV from dO, Q, K, V, O and the forward's log-sum-exp, deterministic (every gradient
+ * cell is summed by one thread in a fixed order, as the reference's *_deterministic kernels do).  `fwd` is the forward
+ * launch's argument block with fwd.out = O and fwd.lse = the statistics, both read here; masks, bias, causal offset,
+ * kv_len, grouped-query heads and paged K/V mean what they mean forward (no gradient is produced for a bias).  dO has
+ * O's dtype; the gradients are dense fp32: dq [B, Hc, Sq, D], dk / dv [B, Hc / group, Sk, D], Hc = the heads of the
+ * handle's shard.  fwd.workspace must hold aidn_sdpa_backward_workspace_bytes().  Logit softcap is not supported. */
+typedef struct {
+  aidn_sdpa_args fwd;
+  const aidn_paged_kv* paged; /* NULL for contiguous K / V                                                     */
+  const void* dout;           /* dO, element (b,h,s,d) at do_stride (all zero = o_stride of fwd)               */
+  int64_t do_stride[3];
+  float* dq;
+  float* dk;
+  float* dv;
+} aidn_sdpa_bwd_args;
+AIDN_API int64_t aidn_sdpa_backward_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq_q);
+AIDN_API int aidn_sdpa_backward(aidn_sdpa_t h, const aidn_sdpa_bwd_args* args, void* cu_stream);
+
 /* The decode step in front of the attention call: packed Q/K/V projection of resident tokens, bias, interleaved RoPE
  * on Q and K, Q written out and the K / V rows written into the KV cache, in one pass over the weights.  Replaces
  * CudaBackend.QkvProjectionRoPECacheD64 (CudaBackend.cs:8389-8439: one fp32 token, head_dim 64, cache

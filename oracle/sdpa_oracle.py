@@ -262,3 +262,52 @@ def qkv_rope_cache(x, weights, bias, cosine, sine, *, heads: int, kv_heads: int,
             key_cache[row] = rot[q_rows:]
             value_cache[row] = y[t, q_rows + kv_rows:]
     return q
+
+
+# ---- attention backward -----------------------------------------------------------------------------------------
+def sdpa_backward(q, k, v, dout, *, scale: Optional[float] = None, causal: bool = False,
+                  causal_offset: Optional[int] = None, bias: Optional[np.ndarray] = None,
+                  keep: Optional[np.ndarray] = None, kv_len: Optional[np.ndarray] = None):
+    """dQ, dK, dV of ``sdpa`` in float64 (small cases), restating FlashAttentionBackward of the reference
+    (src/AiDotNet.Tensors/Engines/CpuEngine.cs:29474 and the deterministic CUDA kernels,
+    CUDA/Kernels/CudaAttentionKernels.cs:251-390): P = softmax(scale Q K^T + bias, masks), dV = P^T dO,
+    dP = dO V^T, dS = P (dP - rowsum(dO O)), dQ = scale dS K, dK = scale dS^T Q.  ``q`` [B,Hq,Sq,D],
+    ``k``/``v`` [B,Hkv,Sk,D] (grouped-query: the gradients of a KV head sum over its query heads); ``bias`` /
+    ``keep`` broadcastable to [B,Hq,Sq,Sk].  Also returns O and the log-sum-exp the GPU call consumes."""
+    q, k, v, dout = (np.asarray(a, np.float64) for a in (q, k, v, dout))
+    B, Hq, Sq, D = q.shape
+    Hkv, Sk = k.shape[1], k.shape[2]
+    g = Hq // Hkv
+    if scale is None:
+        scale = 1.0 / np.sqrt(D)
+    if causal_offset is None:
+        causal_offset = Sk - Sq
+    kk, vv = np.repeat(k, g, axis=1), np.repeat(v, g, axis=1)
+    s = np.einsum("bhid,bhjd->bhij", q, kk) * scale
+    if bias is not None:
+        s = s + np.asarray(bias, np.float64)
+    vis = np.ones((B, Hq, Sq, Sk), bool)
+    if keep is not None:
+        vis &= np.broadcast_to(np.asarray(keep) != 0, vis.shape)
+    if causal:
+        vis &= (np.arange(Sk)[None, :] <= np.arange(Sq)[:, None] + causal_offset)[None, None]
+    if kv_len is not None:
+        vis &= (np.arange(Sk)[None, :] < np.asarray(kv_len)[:, None])[:, None, None, :]
+    s = np.where(vis, s, -np.inf)
+    m = s.max(axis=-1, keepdims=True)
+    m = np.where(np.isfinite(m), m, 0.0)
+    e = np.where(vis, np.exp(s - m), 0.0)
+    l = e.sum(axis=-1, keepdims=True)
+    p = np.divide(e, l, out=np.zeros_like(e), where=l > 0)
+    o = np.einsum("bhij,bhjd->bhid", p, vv)
+    lse = np.where(l[..., 0] > 0, m[..., 0] + np.log(np.where(l[..., 0] > 0, l[..., 0], 1.0)), -np.inf)
+    dv_full = np.einsum("bhij,bhid->bhjd", p, dout)
+    dp = np.einsum("bhid,bhjd->bhij", dout, vv)
+    delta = (dout * o).sum(axis=-1, keepdims=True)
+    ds = p * (dp - delta)
+    dq = np.einsum("bhij,bhjd->bhid", ds, kk) * scale
+    dk_full = np.einsum("bhij,bhid->bhjd", ds, q) * scale
+    dk = dk_full.reshape(B, Hkv, g, Sk, D).sum(axis=2)
+    dv = dv_full.reshape(B, Hkv, g, Sk, D).sum(axis=2)
+    return (dq.astype(np.float32), dk.astype(np.float32), dv.astype(np.float32), o.astype(np.float32),
+            lse.astype(np.float32))

@@ -246,3 +246,36 @@ def test_qkv_rope_cache_composition(heads, capacity, position):
     assert np.abs(kc[position] - rotated[model:]).max() <= 1e-6
     assert np.abs(vc[position] - biased[2 * model:]).max() <= 1e-6
     assert not kc[np.arange(capacity) != position].any()
+
+
+# ---- backward ----------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("causal,gqa", [(False, False), (True, False), (True, True)])
+def test_backward_oracle_against_finite_differences_of_the_forward(causal, gqa):
+    """The backward restatement is pinned on the forward oracle itself: central differences of
+    L = sum(dO * sdpa(Q, K, V)) in float64 accumulation must reproduce dQ, dK, dV (top-left causal as
+    FlashAttentionBackward uses, with a bias, a padded batch entry and grouped-query heads)."""
+    rng = np.random.default_rng(21 + causal + 2 * gqa)
+    B, Hq, Hkv, Sq, Sk, D = 2, 4, (2 if gqa else 4), 5, 7, 8
+    q = rng.standard_normal((B, Hq, Sq, D)).astype(np.float32) * 0.5
+    k = rng.standard_normal((B, Hkv, Sk, D)).astype(np.float32) * 0.5
+    v = rng.standard_normal((B, Hkv, Sk, D)).astype(np.float32) * 0.5
+    dout = rng.standard_normal((B, Hq, Sq, D)).astype(np.float32)
+    bias = rng.standard_normal((1, Hq, Sq, Sk)).astype(np.float32) * 0.3
+    kv_len = np.array([Sk, 4], np.int32)
+    kw = dict(scale=0.3, causal=causal, causal_offset=0, kv_len=kv_len)
+    dq, dk, dv, o, lse = O.sdpa_backward(q, k, v, dout, bias=bias, **kw)
+    fwd = lambda q_, k_, v_: O.sdpa(q_, k_, v_, mask=bias, mask_kind=O.MASK_ADD_F32, f64=True, want_lse=True, **kw)
+    o_ref, lse_ref, _ = fwd(q, k, v)
+    assert np.abs(o - o_ref).max() <= 2e-6 and np.abs(lse - lse_ref)[np.isfinite(lse_ref)].max() <= 2e-6
+    loss = lambda q_, k_, v_: float((dout.astype(np.float64) * fwd(q_, k_, v_)[0].astype(np.float64)).sum())
+    eps = 1e-2
+    for name, x, grad in (("q", q, dq), ("k", k, dk), ("v", v, dv)):
+        for _ in range(6):
+            idx = tuple(rng.integers(0, n) for n in x.shape)
+            xp, xm = x.copy(), x.copy()
+            xp[idx] += eps
+            xm[idx] -= eps
+            args_p = {"q": (xp, k, v), "k": (q, xp, v), "v": (q, k, xp)}[name]
+            args_m = {"q": (xm, k, v), "k": (q, xm, v), "v": (q, k, xm)}[name]
+            fd = (loss(*args_p) - loss(*args_m)) / (2 * eps)
+            assert abs(fd - grad[idx]) <= 2e-3 + 2e-3 * abs(fd), (name, idx, fd, grad[idx])
