@@ -52,6 +52,17 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         public int num_blocks;
     }
 
+    /// <summary>Arguments of aidn_sdpa_backward: the forward block (out = O, lse = statistics) plus dO and the gradients.</summary>
+    [StructLayout(LayoutKind.Sequential)]
+    internal unsafe struct AidnSdpaBwdArgs
+    {
+        public AidnSdpaArgs fwd;
+        public IntPtr paged;      // AidnPagedKv*, or zero
+        public IntPtr dout;
+        public fixed long do_stride[3];
+        public IntPtr dq, dk, dv;
+    }
+
     /// <summary>Arguments of aidn_qkv_rope_cache (QkvProjectionRoPECacheD64 generalised, see include/aidn_sdpa.h).</summary>
     [StructLayout(LayoutKind.Sequential)]
     internal struct AidnQkvRopeArgs
@@ -79,6 +90,8 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         [DllImport(Lib)] public static extern long aidn_sdpa_workspace_bytes(IntPtr handle, long batch, long seqQ, long seqKv);
         [DllImport(Lib)] public static extern int aidn_sdpa_launch(IntPtr handle, ref AidnSdpaArgs args, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_sdpa_launch_paged(IntPtr handle, ref AidnSdpaArgs args, ref AidnPagedKv paged, IntPtr cuStream);
+        [DllImport(Lib)] public static extern long aidn_sdpa_backward_workspace_bytes(IntPtr handle, long batch, long seqQ);
+        [DllImport(Lib)] public static extern int aidn_sdpa_backward(IntPtr handle, ref AidnSdpaBwdArgs args, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_qkv_rope_cache(ref AidnQkvRopeArgs args, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_rope_interleaved(IntPtr input, IntPtr cosine, IntPtr sine, IntPtr output, long rows, int headDim, int seqLen, int startPosition, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_sdpa_poll(IntPtr handle, IntPtr cuStream);

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|qkvrope|qkvrope1|qkvrope32] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|qkvrope|qkvrope1|qkvrope32] [--impl reference]
 
 One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
 default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
@@ -37,6 +37,9 @@ WORKLOADS = {
                     name="long_context_shard_B1_Hq8_Hkv1_S32768_D128_causal_bf16"),
     "c3paged": dict(B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill", block_size=16,
                     name="paged_gqa_prefill_B2_Hq32_Hkv8_S8192_D128_block16_causal_bf16"),
+    # attention backward (deterministic FFMA kernels) on a quarter of the C2 shape
+    "c2bwd": dict(kind="bwd", B=1, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
+                  name="llama_backward_B1_H32_S2048_D128_causal_bf16"),
     # the decode step in front of attention: packed Q/K/V projection of 8 resident tokens + RoPE + cache write
     "qkvrope": dict(kind="gemv", tokens=8, heads=32, kv_heads=8, D=128, weight="bf16", cache_rows=1 << 16,
                     name="qkv_rope_cache_T8_Hq32_Hkv8_D128_bf16_weights"),
@@ -249,6 +252,52 @@ def run_gemv(args, w, pk):
         "gpu_launches": args.steps}))
 
 
+def run_bwd(args, w, pk):
+    """Times aidn_sdpa_backward (delta + dQ + dK/dV kernels).  FLOP convention: 10*D per visible (query, key) pair
+    (five matrix products: S, dP, dV, dQ, dK), causal pairs counted once."""
+    from aidotnet.tensors_b200 import native as N
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    q, k, v, _ = make_inputs(w, dev, 5)
+    B, Hq, Hkv, Sq, Sk, D = w["B"], w["Hq"], w["Hkv"], w["Sq"], w["Sk"], w["D"]
+    out = torch.empty((B, Hq, Sq, D), device=dev)
+    lse = torch.empty((B, Hq, Sq), device=dev)
+    dout = torch.randn((B, Hq, Sq, D), device=dev)
+    dq = torch.empty((B, Hq, Sq, D), device=dev)
+    dk = torch.empty((B, Hkv, Sk, D), device=dev)
+    dv = torch.empty_like(dk)
+    h = N.Handle(device=dev.index, qkv_dtype=N.BF16, head_dim=D, num_q_heads=Hq, num_kv_heads=Hkv, causal=w["causal"],
+                 causal_bottom_right=True, emit_lse=True)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    common = dict(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), lse=lse.data_ptr(), batch=B,
+                  seq_q=Sq, seq_kv=Sk, stream=stream)
+    h.launch(**common)
+    nb = h.backward_workspace_bytes(B, Sq)
+    ws = torch.empty(nb, dtype=torch.uint8, device=dev)
+    step = lambda: h.backward(dout=dout.data_ptr(), dq=dq.data_ptr(), dk=dk.data_ptr(), dv=dv.data_ptr(),
+                              workspace=ws.data_ptr(), workspace_bytes=nb, **common)
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    per_step = e0.elapsed_time(e1) / 1e3 / args.steps
+    fl = 10 * B * Hq * D * visible_pairs(Sq, Sk, w["causal"])
+    tf = fl / 1e12 / per_step
+    print(json.dumps({
+        "metric": "attention backward TFLOP/s/GPU", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32 arithmetic on bf16 inputs", "data": "synthetic",
+        "config": {"workload": w["name"], "flop_convention": "10*D*visible(q,k) pairs"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16"], "unit": "TFLOP/s", "frac": tf / pk["bf16"],
+                     "traffic": None, "algorithmic": fl, "algorithmic_unit": "FLOP per launch",
+                     "peak_source": pk["source"] + " (burst); the kernels are FFMA, not tensor-core, code"},
+        "gpu_launches": 3 * args.steps}))
+
+
 class Runner:
     """One workload bound to one handle of the C ABI; `step()` enqueues one forward pass."""
 
@@ -451,6 +500,10 @@ def main():
     if w["kind"] == "gemv":
         if rank == 0:
             run_gemv(args, w, pk)
+        return
+    if w["kind"] == "bwd":
+        if rank == 0:
+            run_bwd(args, w, pk)
         return
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
