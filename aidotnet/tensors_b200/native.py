@@ -27,6 +27,7 @@ EXPORTS = (
     "aidn_sdpa_last_launch_count", "aidn_sdpa_destroy", "aidn_sdpa_last_error", "aidn_sdpa_device_supported",
     "aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32",
     "aidn_sdpa_decode_noalloc", "aidn_sdpa_launch_paged", "aidn_qkv_rope_cache", "aidn_rope_interleaved",
+    "aidn_sdpa_backward", "aidn_sdpa_backward_workspace_bytes",
 )
 
 
