@@ -273,6 +273,52 @@ void CudaBackend::PagedAttentionPrefillGqa(const GpuBuffer& q, const GpuBuffer& 
         (int64_t)startPos + numQueries, startPos, scale);
 }
 
+void CudaBackend::FlashAttentionBackward(const GpuBuffer& gradOutput, const GpuBuffer& query, const GpuBuffer& key,
+                                         const GpuBuffer& value, const GpuBuffer& output, const GpuBuffer& softmaxStats,
+                                         const GpuBuffer& gradQuery, const GpuBuffer& gradKey, const GpuBuffer& gradValue,
+                                         int batch, int numHeads, int seqQ, int seqK, int headDim, float scale,
+                                         bool isCausal, const GpuBuffer* attentionBias, int biasBatchStride) {
+  if (batch <= 0 || numHeads <= 0 || seqQ <= 0 || seqK <= 0 || headDim <= 0)
+    throw std::invalid_argument("Attention dimensions must be positive.");
+  const int64_t qsz = (int64_t)batch * numHeads * seqQ * headDim, ksz = (int64_t)batch * numHeads * seqK * headDim;
+  if (gradOutput.Size < qsz || query.Size < qsz || output.Size < qsz || gradQuery.Size < qsz || key.Size < ksz ||
+      value.Size < ksz || gradKey.Size < ksz || gradValue.Size < ksz || softmaxStats.Size < (int64_t)batch * numHeads * seqQ)
+    throw std::invalid_argument("Attention tensor buffers are smaller than the requested dimensions.");
+  if (gradQuery.Dtype != AIDN_F32 || gradKey.Dtype != AIDN_F32 || gradValue.Dtype != AIDN_F32 || softmaxStats.Dtype != AIDN_F32)
+    throw std::invalid_argument("gradients and softmaxStats are fp32 buffers");
+  aidn_sdpa_desc d = base_desc(device_, query, output, headDim, numHeads, numHeads);
+  d.causal = isCausal ? 1 : 0;
+  d.causal_bottom_right = 0;
+  d.emit_lse = 1;
+  d.mask_kind = attentionBias ? AIDN_MASK_ADD_F32 : AIDN_MASK_NONE;
+  aidn_sdpa_t h = Handle(d);
+  const int64_t need = aidn_sdpa_backward_workspace_bytes(h, batch, seqQ);
+  if (need < 0) Check(AIDN_EINVAL, "aidn_sdpa_backward_workspace_bytes");
+  if (need > workspace_bytes_) {
+    if (workspace_) cudaFree(workspace_);
+    workspace_ = nullptr;
+    workspace_bytes_ = 0;
+    if (cudaMalloc(&workspace_, (size_t)need) != cudaSuccess) throw std::runtime_error("CudaBackend: out of device memory");
+    workspace_bytes_ = need;
+  }
+  aidn_sdpa_bwd_args a;
+  std::memset(&a, 0, sizeof(a));
+  a.fwd.q = query.Handle; a.fwd.k = key.Handle; a.fwd.v = value.Handle; a.fwd.out = output.Handle;
+  a.fwd.lse = static_cast<float*>(softmaxStats.Handle);
+  a.fwd.batch = batch; a.fwd.seq_q = seqQ; a.fwd.seq_kv = seqK; a.fwd.scale = scale;
+  a.fwd.workspace = workspace_; a.fwd.workspace_bytes = workspace_bytes_;
+  if (attentionBias) {
+    a.fwd.mask = attentionBias->Handle;
+    a.fwd.mask_stride[0] = biasBatchStride; a.fwd.mask_stride[1] = (int64_t)seqQ * seqK;
+    a.fwd.mask_stride[2] = seqK; a.fwd.mask_stride[3] = 1;
+  }
+  a.dout = gradOutput.Handle;
+  a.dq = static_cast<float*>(gradQuery.Handle); a.dk = static_cast<float*>(gradKey.Handle);
+  a.dv = static_cast<float*>(gradValue.Handle);
+  Check(aidn_sdpa_backward(h, &a, stream_), "aidn_sdpa_backward");
+  launch_count_ += aidn_sdpa_last_launch_count(h);
+}
+
 // ---- the decode step in front of attention -----------------------------------------------------------------------
 void CudaBackend::QkvProjectionRoPECacheD64(const GpuBuffer& input, const GpuBuffer& packedWeights, const GpuBuffer& bias,
                                             const GpuBuffer& cosine, const GpuBuffer& sine, const GpuBuffer& query,

@@ -7,6 +7,7 @@
 //   FlashAttentionV2           CudaBackend.cs:8540-8578     GroupedQueryAttention CudaBackend.cs:8721-8759
 //   FlashDecode                CudaBackend.cs:2968-3021     PagedAttention{Decode,Prefill}{,Gqa} CudaBackend.cs:2845-2966
 //   QkvProjectionRoPECacheD64  CudaBackend.cs:8389-8439     RopeInterleaved       CudaBackend.cs:8441-8470
+//   FlashAttentionBackward     CudaBackend.cs:8580-8604
 //
 // ArgumentException / ArgumentOutOfRangeException map to std::invalid_argument, InvalidOperationException to
 // std::runtime_error.  There is no CPU fallback: a failing call throws.
@@ -70,6 +71,13 @@ class CudaBackend {
   void PagedAttentionPrefillGqa(const GpuBuffer& q, const GpuBuffer& kcache, const GpuBuffer& vcache,
                                 const GpuBuffer& blockTable, const GpuBuffer& output, int heads, int kvHeads,
                                 int headDim, int blockSize, int numQueries, int startPos, float scale);
+
+  // Backward of FlashAttentionV2 (CudaBackend.cs:8580-8604): fp32 gradient buffers, statistics from the forward.
+  void FlashAttentionBackward(const GpuBuffer& gradOutput, const GpuBuffer& query, const GpuBuffer& key,
+                              const GpuBuffer& value, const GpuBuffer& output, const GpuBuffer& softmaxStats,
+                              const GpuBuffer& gradQuery, const GpuBuffer& gradKey, const GpuBuffer& gradValue, int batch,
+                              int numHeads, int seqQ, int seqK, int headDim, float scale, bool isCausal,
+                              const GpuBuffer* attentionBias = nullptr, int biasBatchStride = 0);
 
   // The decode step in front of attention (CudaBackend.cs:8389-8439 and :8441-8470).
   void QkvProjectionRoPECacheD64(const GpuBuffer& input, const GpuBuffer& packedWeights, const GpuBuffer& bias,

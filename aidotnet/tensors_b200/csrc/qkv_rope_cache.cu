@@ -9,7 +9,7 @@
 // The step is a GEMV: every weight is used once per token, so it is bound by streaming W from HBM
 // ((heads + 2 kv_heads) * head_dim * model * sizeof(weight) bytes; nothing here is shaped for tensor cores).  A warp owns
 // one rotation pair of output rows (2r, 2r+1) - the two rows RoPE mixes - streams both with 16-byte no-allocate loads,
-// keeps the tokens' activations in shared memory, and finishes the pair in registers: bias, rotation by the token's
+// reads the tokens' activations from shared memory or through L1, and finishes the pair in registers: bias, rotation by the token's
 // (cos, sin), store in the destination dtype.  Up to 8 tokens share one pass over W.
 #include "common.cuh"
 
@@ -56,18 +56,21 @@ __device__ __forceinline__ void store_as(void* base, int64_t idx, float x, int d
 
 // T tokens starting at token t_base share this pass over W.  The activations of all T tokens sit in shared memory once
 // per CTA, so the CTA is made wide (WARPS) when they are large: occupancy is then bounded by warps, not by CTAs.
-template <typename WT, int T, int WARPS>
+// XS: the activations are staged in shared memory (measured faster with fp32 weights); otherwise they are read
+// through L1 (measured faster with bf16 weights, and free of any size limit).
+template <typename WT, int T, int WARPS, bool XS>
 __global__ void __launch_bounds__(WARPS * 32) qkv_rope_cache_kernel(const QkvRopeParams p, const int t_base) {
   constexpr int kQkvWarps = WARPS;
   constexpr int N = WVec<WT>::N;
-  extern __shared__ __align__(16) float xs[];   // [T][model]
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int model = p.model;
   const int D = p.head_dim;
   const int ntok = min(T, p.tokens - t_base);
 
-  {
+  extern __shared__ __align__(16) float xs[];   // [T][model] when XS
+  if constexpr (XS) {
     constexpr int kStageUnroll = 4;   // independent loads in flight per thread
+    const int tid = threadIdx.x;
     for (int base = tid * 4; base < T * model; base += kQkvWarps * 32 * 4 * kStageUnroll) {
       float4 v[kStageUnroll];
 #pragma unroll
@@ -84,9 +87,8 @@ __global__ void __launch_bounds__(WARPS * 32) qkv_rope_cache_kernel(const QkvRop
         if (idx < T * model) *reinterpret_cast<float4*>(xs + idx) = v[u];
       }
     }
+    __syncthreads();
   }
-  __syncthreads();
-
   const int q_rows = p.heads * D, kv_rows = p.kv_heads * D;
   const int pairs = (q_rows + 2 * kv_rows) / 2;
   const WT* W = static_cast<const WT*>(p.weights);
@@ -118,10 +120,11 @@ __global__ void __launch_bounds__(WARPS * 32) qkv_rope_cache_kernel(const QkvRop
         WVec<WT>::unpack(u1[u], f1);
 #pragma unroll
         for (int t = 0; t < T; ++t) {
-          const float* x = xs + t * model + k;
+          if (!XS && t >= ntok) continue;
+          const float* x = XS ? xs + t * model + k : p.input + (int64_t)(t_base + t) * model + k;
 #pragma unroll
           for (int e = 0; e < N; e += 4) {
-            const float4 xv = *reinterpret_cast<const float4*>(x + e);
+            const float4 xv = XS ? *reinterpret_cast<const float4*>(x + e) : __ldg(reinterpret_cast<const float4*>(x + e));
             a0[t] = fmaf(f0[e], xv.x, a0[t]); a0[t] = fmaf(f0[e + 1], xv.y, a0[t]);
             a0[t] = fmaf(f0[e + 2], xv.z, a0[t]); a0[t] = fmaf(f0[e + 3], xv.w, a0[t]);
             a1[t] = fmaf(f1[e], xv.x, a1[t]); a1[t] = fmaf(f1[e + 1], xv.y, a1[t]);
@@ -194,7 +197,16 @@ __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], uint32_t a0, uint3
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__global__ void __launch_bounds__(kMmaWarps * 32) qkv_rope_cache_mma_kernel(const QkvRopeParams p, const int t_base) {
+constexpr int kMmaThreads = (kMmaWarps + 2) * 32;   // 16 streaming warps + 2 finishing warps
+
+__device__ __forceinline__ void named_bar_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int count) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+__global__ void __launch_bounds__(kMmaThreads) qkv_rope_cache_mma_kernel(const QkvRopeParams p, const int t_base) {
   extern __shared__ __align__(16) uint8_t qsm[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -203,26 +215,26 @@ __global__ void __launch_bounds__(kMmaWarps * 32) qkv_rope_cache_mma_kernel(cons
   const int pitch = model * 2 + 64;                       // bytes per token row of hi (and of lo): bank-conflict free
   uint8_t* x_hi = qsm;                                    // [8][pitch]
   uint8_t* x_lo = qsm + 8 * pitch;                        // [8][pitch]
-  float* part = reinterpret_cast<float*>(qsm + 16 * pitch);   // [kMmaWarps][16 rows][8 tokens]
-  float* rope = part + kMmaWarps * 128;                       // [8 tokens][D/2] cos, then [8][D/2] sin
+  float* part = reinterpret_cast<float*>(qsm + 16 * pitch);   // [2 buffers][kMmaWarps][16 rows][8 tokens]
+  float* rope = part + 2 * kMmaWarps * 128;                       // [8 tokens][D/2] cos, then [8][D/2] sin
   long long* tokrow = reinterpret_cast<long long*>(rope + 8 * D);   // [8] cache row of each token, -1 = none
 
   // stage the activations: four independent 16-byte loads per thread in flight, then split and store
   {
     const int n4 = 8 * model / 4;
     constexpr int kStageUnroll = 4;
-    for (int base = tid; base < n4; base += kMmaWarps * 32 * kStageUnroll) {
+    for (int base = tid; base < n4; base += kMmaThreads * kStageUnroll) {
       float4 v[kStageUnroll];
 #pragma unroll
       for (int u = 0; u < kStageUnroll; ++u) {
-        const int idx = base + u * kMmaWarps * 32;
+        const int idx = base + u * kMmaThreads;
         const int t = idx / (model / 4), k = (idx - t * (model / 4)) * 4;
         v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (idx < n4 && t < ntok) v[u] = *reinterpret_cast<const float4*>(p.input + (int64_t)(t_base + t) * model + k);
       }
 #pragma unroll
       for (int u = 0; u < kStageUnroll; ++u) {
-        const int idx = base + u * kMmaWarps * 32;
+        const int idx = base + u * kMmaThreads;
         if (idx >= n4) continue;
         const int t = idx / (model / 4), k = (idx - t * (model / 4)) * 4;
         const float f[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
@@ -240,7 +252,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32) qkv_rope_cache_mma_kernel(cons
     }
   }
   // per-token rotation rows and cache rows, fetched once so that finishing a tile touches no dependent global loads
-  for (int idx = tid; idx < 8 * (D / 2); idx += kMmaWarps * 32) {
+  for (int idx = tid; idx < 8 * (D / 2); idx += kMmaThreads) {
     const int t = idx / (D / 2), i = idx - t * (D / 2);
     float cs = 1.f, sn = 0.f;
     if (t < ntok) {
@@ -284,10 +296,15 @@ __global__ void __launch_bounds__(kMmaWarps * 32) qkv_rope_cache_mma_kernel(cons
       wo[u] = ok ? ld_stream16(w_odd + ch * 8) : make_uint4(0, 0, 0, 0);
     }
   };
+  // Warps 0..15 stream the weights; warps 16..17 finish the tiles.  The partial sums change hands through two buffers
+  // and two pairs of named barriers (full: the tile's partials are written; free: they have been read), so the weight
+  // stream never waits for a tile to be finished.
+  if (warp < kMmaWarps) {
   const int ch_first = warp * 4 + c;
   if ((int)blockIdx.x < tiles) load_batch(blockIdx.x, ch_first);
 
-  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+  int it = 0;
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     for (int ch0 = ch_first; ch0 < chunks; ch0 += kChunkStep * kBatch) {
       if (ch0 != ch_first) load_batch(tile, ch0);
@@ -312,19 +329,30 @@ __global__ void __launch_bounds__(kMmaWarps * 32) qkv_rope_cache_mma_kernel(cons
     }
     if (tile + (int)gridDim.x < tiles) load_batch(tile + gridDim.x, ch_first);
     // acc: [0,1] = even row of pair g for tokens 2c, 2c+1; [2,3] = odd row
-    float* mine = part + warp * 128;
+    const int buf = it & 1;
+    if (it >= 2) named_bar_sync(3 + buf, kMmaThreads);   // the finishing warps have read this buffer's previous tile
+    float* mine = part + (buf * kMmaWarps + warp) * 128;
     mine[g * 8 + 2 * c] = acc[0];
     mine[g * 8 + 2 * c + 1] = acc[1];
     mine[(g + 8) * 8 + 2 * c] = acc[2];
     mine[(g + 8) * 8 + 2 * c + 1] = acc[3];
-    __syncthreads();
-    if (tid < 64) {
-      const int pr = tid >> 3, t = tid & 7;
+    __threadfence_block();
+    named_bar_arrive(1 + buf, kMmaThreads);
+  }
+  } else {
+  const int ftid = tid - kMmaWarps * 32;   // 0..63: (pair, token)
+  int it = 0;
+  for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+    const int buf = it & 1;
+    named_bar_sync(1 + buf, kMmaThreads);
+    const float* pb = part + buf * kMmaWarps * 128;
+    {
+      const int pr = ftid >> 3, t = ftid & 7;
       float y0 = 0.f, y1 = 0.f;
 #pragma unroll
       for (int w = 0; w < kMmaWarps; ++w) {
-        y0 += part[w * 128 + pr * 8 + t];
-        y1 += part[w * 128 + (pr + 8) * 8 + t];
+        y0 += pb[w * 128 + pr * 8 + t];
+        y1 += pb[w * 128 + (pr + 8) * 8 + t];
       }
       if (t < ntok) {
         const int r0 = 16 * tile + 2 * pr;
@@ -354,18 +382,19 @@ __global__ void __launch_bounds__(kMmaWarps * 32) qkv_rope_cache_mma_kernel(cons
         }
       }
     }
-    __syncthreads();
+    named_bar_arrive(3 + buf, kMmaThreads);   // the buffer may be overwritten (tile it + 2)
+  }
   }
 }
 
 cudaError_t launch_qkv_mma(const QkvRopeParams& p, int t_base, int num_sms, cudaStream_t stream) {
-  const size_t smem = 16 * ((size_t)p.model * 2 + 64) + kMmaWarps * 128 * sizeof(float) + 8 * p.head_dim * sizeof(float) + 64;
+  const size_t smem = 16 * ((size_t)p.model * 2 + 64) + 2 * kMmaWarps * 128 * sizeof(float) + 8 * p.head_dim * sizeof(float) + 64;
   cudaError_t e = cudaFuncSetAttribute(qkv_rope_cache_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return e;
   const int tiles = (p.heads + 2 * p.kv_heads) * p.head_dim / 16;
   const int per_sm = smem <= 100 * 1024 ? 2 : 1;
   int grid = tiles < num_sms * per_sm ? tiles : num_sms * per_sm;
-  qkv_rope_cache_mma_kernel<<<grid, kMmaWarps * 32, smem, stream>>>(p, t_base);
+  qkv_rope_cache_mma_kernel<<<grid, kMmaThreads, smem, stream>>>(p, t_base);
   return cudaGetLastError();
 }
 
@@ -385,43 +414,63 @@ __global__ void rope_interleaved_kernel(const float* __restrict__ in, const floa
 
 template <typename WT, int T>
 cudaError_t launch_qkv_t(const QkvRopeParams& p, int t_base, int num_sms, cudaStream_t stream) {
-  constexpr int kQkvWarps = T >= 4 ? 16 : (T == 2 ? 8 : 4);
-  const size_t smem = (size_t)T * p.model * sizeof(float);
-  auto kern = qkv_rope_cache_kernel<WT, T, kQkvWarps>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return e;
-  }
   const int pairs = (p.heads + 2 * p.kv_heads) * p.head_dim / 2;
-  int grid = (pairs + kQkvWarps - 1) / kQkvWarps;
-  const int cap = num_sms * 8;   // grid-stride beyond eight CTAs per SM
-  if (grid > cap) grid = cap;
-  kern<<<grid, kQkvWarps * 32, smem, stream>>>(p, t_base);
+  const size_t xbytes = (size_t)T * p.model * sizeof(float);
+  if (sizeof(WT) == 4 && xbytes <= 200 * 1024) {
+    constexpr int kQkvWarps = T >= 4 ? 16 : (T == 2 ? 8 : 4);   // wide CTAs when the staged activations are large
+    auto kern = qkv_rope_cache_kernel<WT, T, kQkvWarps, true>;
+    if (xbytes > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)xbytes);
+      if (e != cudaSuccess) return e;
+    }
+    int grid = (pairs + kQkvWarps - 1) / kQkvWarps;
+    if (grid > num_sms * 8) grid = num_sms * 8;   // grid-stride beyond eight CTAs per SM
+    kern<<<grid, kQkvWarps * 32, xbytes, stream>>>(p, t_base);
+  } else {
+    constexpr int kQkvWarps = 4;
+    int grid = (pairs + kQkvWarps - 1) / kQkvWarps;
+    if (grid > num_sms * 8) grid = num_sms * 8;
+    qkv_rope_cache_kernel<WT, T, kQkvWarps, false><<<grid, kQkvWarps * 32, 0, stream>>>(p, t_base);
+  }
   return cudaGetLastError();
 }
 
 template <typename WT>
 cudaError_t launch_qkv_w(const QkvRopeParams& p, int num_sms, cudaStream_t stream, int* launches) {
   *launches = 0;
-  const bool mma_ok = sizeof(WT) == 2 && ((p.heads + 2 * p.kv_heads) * p.head_dim) % 16 == 0;
-  for (int t_base = 0; t_base < p.tokens; t_base += 8) {
-    const int n = p.tokens - t_base;
+  const size_t mma_smem = 16 * ((size_t)p.model * 2 + 64) + 2 * kMmaWarps * 128 * sizeof(float) + 8 * p.head_dim * sizeof(float) + 64;
+  const bool mma_ok = sizeof(WT) == 2 && ((p.heads + 2 * p.kv_heads) * p.head_dim) % 16 == 0 && mma_smem <= 220 * 1024;
+  const int fit = 8;   // tokens per pass over W on the FFMA path (its activations come through L1, any model size)
+  for (int t_base = 0; t_base < p.tokens;) {
+    const int left = p.tokens - t_base;
     cudaError_t e;
-    if (n >= 2 && mma_ok) e = launch_qkv_mma(p, t_base, num_sms, stream);
-    else if (n == 1) e = launch_qkv_t<WT, 1>(p, t_base, num_sms, stream);
-    else if (n == 2) e = launch_qkv_t<WT, 2>(p, t_base, num_sms, stream);
-    else if (n <= 4) e = launch_qkv_t<WT, 4>(p, t_base, num_sms, stream);
-    else e = launch_qkv_t<WT, 8>(p, t_base, num_sms, stream);
+    int took;
+    if (left >= 2 && mma_ok) {
+      e = launch_qkv_mma(p, t_base, num_sms, stream);
+      took = left < 8 ? left : 8;
+    } else {
+      // the kernel instantiated for T tokens stages T rows of activations whatever it is given: T must fit
+      int tmpl = 1;
+      if (fit >= 8 && left >= 5) tmpl = 8;
+      else if (fit >= 4 && left >= 3) tmpl = 4;
+      else if (fit >= 2 && left >= 2) tmpl = 2;
+      took = left < tmpl ? left : tmpl;
+      if (tmpl == 8) e = launch_qkv_t<WT, 8>(p, t_base, num_sms, stream);
+      else if (tmpl == 4) e = launch_qkv_t<WT, 4>(p, t_base, num_sms, stream);
+      else if (tmpl == 2) e = launch_qkv_t<WT, 2>(p, t_base, num_sms, stream);
+      else e = launch_qkv_t<WT, 1>(p, t_base, num_sms, stream);
+    }
     if (e != cudaSuccess) return e;
     ++*launches;
+    t_base += took;
   }
   return cudaSuccess;
 }
 
 }  // namespace
 
-// Largest model dimension one launch can stage for 8 tokens (shared memory per CTA).
-int64_t qkv_rope_max_model() { return 200 * 1024 / (8 * (int64_t)sizeof(float)); }
+// Largest model dimension served (index arithmetic is 32-bit within a weight row).
+int64_t qkv_rope_max_model() { return 1 << 20; }
 
 cudaError_t launch_qkv_rope_cache(const QkvRopeParams& p, int weight_dtype, int num_sms, cudaStream_t stream,
                                   int* launches) {

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|qkvrope|qkvrope1|qkvrope32] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|qkvrope|qkvrope1|qkvrope70b|qkvrope32] [--impl reference]
 
 One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
 default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
@@ -43,6 +43,8 @@ WORKLOADS = {
     # the decode step in front of attention: packed Q/K/V projection of 8 resident tokens + RoPE + cache write
     "qkvrope": dict(kind="gemv", tokens=8, heads=32, kv_heads=8, D=128, weight="bf16", cache_rows=1 << 16,
                     name="qkv_rope_cache_T8_Hq32_Hkv8_D128_bf16_weights"),
+    "qkvrope70b": dict(kind="gemv", tokens=1, heads=64, kv_heads=8, D=128, weight="bf16", cache_rows=1 << 16,
+                       name="qkv_rope_cache_T1_Hq64_Hkv8_D128_bf16_weights"),
     "qkvrope1": dict(kind="gemv", tokens=1, heads=32, kv_heads=8, D=128, weight="bf16", cache_rows=1 << 16,
                      name="qkv_rope_cache_T1_Hq32_Hkv8_D128_bf16_weights"),
     "qkvrope32": dict(kind="gemv", tokens=1, heads=64, kv_heads=64, D=64, weight="f32", cache_rows=1 << 12,

@@ -345,6 +345,46 @@ int main() {
       }
     }
   }
+  {  // FlashAttentionBackward after FlashAttentionV2: dQ, dK, dV against a scalar reference in double (the formulas of
+     // CUDA/Kernels/CudaAttentionKernels.cs:251-390), top-left causal
+    std::printf("flash attention backward\n");
+    const int B = 2, H = 2, S = 11, D = 16;
+    const double scale = 0.25;
+    auto q = uniform(B * H * S * D, 81), k = uniform(B * H * S * D, 82), v = uniform(B * H * S * D, 83), go = uniform(B * H * S * D, 84);
+    DeviceArray dq_(q), dk_(k), dv_(v), dgo(go), dout((int64_t)B * H * S * D), dstats((int64_t)B * H * S);
+    DeviceArray gq((int64_t)B * H * S * D), gk((int64_t)B * H * S * D), gv((int64_t)B * H * S * D);
+    backend.FlashAttentionV2(dq_.buf, dk_.buf, dv_.buf, dout.buf, dstats.buf, B, H, S, S, D, (float)scale, true);
+    backend.FlashAttentionBackward(dgo.buf, dq_.buf, dk_.buf, dv_.buf, dout.buf, dstats.buf, gq.buf, gk.buf, gv.buf, B, H, S, S, D, (float)scale, true);
+    backend.Synchronize();
+    std::vector<double> wq((size_t)B * H * S * D, 0.0), wk(wq.size(), 0.0), wv(wq.size(), 0.0);
+    for (int bh = 0; bh < B * H; ++bh) {
+      const size_t base = (size_t)bh * S * D;
+      for (int i = 0; i < S; ++i) {
+        std::vector<double> p(S, 0.0), dp(S, 0.0);
+        double mx = -1e300, sum = 0, delta = 0;
+        for (int j = 0; j <= i; ++j) {
+          double dot = 0;
+          for (int d = 0; d < D; ++d) dot += (double)q[base + i * D + d] * k[base + j * D + d];
+          p[j] = dot * scale; mx = std::max(mx, p[j]);
+        }
+        for (int j = 0; j <= i; ++j) { p[j] = std::exp(p[j] - mx); sum += p[j]; }
+        std::vector<double> o(D, 0.0);
+        for (int j = 0; j <= i; ++j) { p[j] /= sum; for (int d = 0; d < D; ++d) o[d] += p[j] * v[base + j * D + d]; }
+        for (int d = 0; d < D; ++d) delta += (double)go[base + i * D + d] * o[d];
+        for (int j = 0; j <= i; ++j) {
+          for (int d = 0; d < D; ++d) dp[j] += (double)go[base + i * D + d] * v[base + j * D + d];
+          const double ds = p[j] * (dp[j] - delta);
+          for (int d = 0; d < D; ++d) {
+            wq[base + i * D + d] += ds * scale * k[base + j * D + d];
+            wk[base + j * D + d] += ds * scale * q[base + i * D + d];
+            wv[base + j * D + d] += p[j] * go[base + i * D + d];
+          }
+        }
+      }
+    }
+    EXPECT(max_abs_diff(gq.download(), wq) <= 2e-5 && max_abs_diff(gk.download(), wk) <= 2e-5 && max_abs_diff(gv.download(), wv) <= 2e-5,
+           "backward mismatch dq %g dk %g dv %g", max_abs_diff(gq.download(), wq), max_abs_diff(gk.download(), wk), max_abs_diff(gv.download(), wv));
+  }
   {  // argument errors throw, as ArgumentOutOfRangeException / ArgumentException do in the reference
     std::printf("argument errors\n");
     std::vector<float> z(64, 0.f);
