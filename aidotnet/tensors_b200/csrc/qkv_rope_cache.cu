@@ -412,6 +412,16 @@ __global__ void rope_interleaved_kernel(const float* __restrict__ in, const floa
   *reinterpret_cast<float2*>(out + row * head_dim + 2 * i) = make_float2(x.x * c - x.y * s, x.x * s + x.y * c);
 }
 
+// CTAs for `pairs` row pairs, one pair per warp and round: at most eight CTAs per SM are resident, and when the pairs
+// need more than one round every warp gets the same number of rounds (a grid-stride split that leaves a few warps with
+// one pair more than the rest ends the launch with those warps alone).
+inline int balanced_grid(int pairs, int warps_per_cta, int num_sms) {
+  const int warp_cap = num_sms * 8 * warps_per_cta;
+  const int rounds = (pairs + warp_cap - 1) / warp_cap;
+  const int warps = (pairs + rounds - 1) / rounds;
+  return (warps + warps_per_cta - 1) / warps_per_cta;
+}
+
 template <typename WT, int T>
 cudaError_t launch_qkv_t(const QkvRopeParams& p, int t_base, int num_sms, cudaStream_t stream) {
   const int pairs = (p.heads + 2 * p.kv_heads) * p.head_dim / 2;
@@ -423,13 +433,11 @@ cudaError_t launch_qkv_t(const QkvRopeParams& p, int t_base, int num_sms, cudaSt
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)xbytes);
       if (e != cudaSuccess) return e;
     }
-    int grid = (pairs + kQkvWarps - 1) / kQkvWarps;
-    if (grid > num_sms * 8) grid = num_sms * 8;   // grid-stride beyond eight CTAs per SM
+    const int grid = balanced_grid(pairs, kQkvWarps, num_sms);
     kern<<<grid, kQkvWarps * 32, xbytes, stream>>>(p, t_base);
   } else {
     constexpr int kQkvWarps = 4;
-    int grid = (pairs + kQkvWarps - 1) / kQkvWarps;
-    if (grid > num_sms * 8) grid = num_sms * 8;
+    const int grid = balanced_grid(pairs, kQkvWarps, num_sms);
     qkv_rope_cache_kernel<WT, T, kQkvWarps, false><<<grid, kQkvWarps * 32, 0, stream>>>(p, t_base);
   }
   return cudaGetLastError();
