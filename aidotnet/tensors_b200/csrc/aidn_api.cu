@@ -625,6 +625,26 @@ int aidn_rope_interleaved(const float* input, const float* cosine, const float* 
   return AIDN_OK;
 }
 
+int aidn_paged_kv_append(const void* new_keys, const void* new_values, void* key_pool, void* value_pool,
+                         const int32_t* block_table, int64_t start_position, int64_t tokens, int32_t block_size,
+                         int32_t num_blocks, int64_t row_bytes, void* cu_stream) {
+  g_err[0] = 0;
+  if (tokens < 0 || start_position < 0) return fail(AIDN_EINVAL, "paged_kv_append: newLen and the start position must be >= 0");
+  if (tokens == 0) return AIDN_OK;
+  if (!new_keys || !new_values || !key_pool || !value_pool || !block_table) return fail(AIDN_EINVAL, "paged_kv_append: null buffer");
+  if (block_size <= 0 || num_blocks <= 0) return fail(AIDN_EINVAL, "paged_kv_append: block_size and num_blocks must be > 0");
+  if (row_bytes <= 0 || row_bytes % 16 != 0) return fail(AIDN_EINVAL, "paged_kv_append: row_bytes must be a positive multiple of 16");
+  if (start_position + tokens > (int64_t)num_blocks * block_size)
+    return fail(AIDN_EINVAL, "paged_kv_append: the sequence would reach %lld tokens, above the pool capacity %lld",
+                (long long)(start_position + tokens), (long long)num_blocks * block_size);   /* InvalidOperationException there */
+  if ((uintptr_t)new_keys % 16 || (uintptr_t)new_values % 16 || (uintptr_t)key_pool % 16 || (uintptr_t)value_pool % 16)
+    return fail(AIDN_EINVAL, "paged_kv_append: buffers must be 16-byte aligned");
+  cudaError_t e = aidn::launch_paged_append(new_keys, new_values, key_pool, value_pool, block_table, start_position, tokens,
+                                            block_size, num_blocks, row_bytes, (cudaStream_t)cu_stream);
+  if (e != cudaSuccess) return fail_cuda(e, "paged_kv_append");
+  return AIDN_OK;
+}
+
 static int cast_common(int kind, const void* src, void* dst, int64_t n, void* cu_stream) {
   g_err[0] = 0;
   if (n < 0 || (n > 0 && (!src || !dst))) return fail(AIDN_EINVAL, "cast: bad argument");

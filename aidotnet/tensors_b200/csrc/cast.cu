@@ -110,4 +110,43 @@ cudaError_t launch_cast(int kind, const void* src, void* dst, int64_t n, cudaStr
   }
 }
 
+// ---- paged KV append ----------------------------------------------------------------------------------------------
+// The device half of DevicePagedKVCache.Append (src/AiDotNet.Tensors/Engines/DirectGpu/DevicePagedKVCache.cs:113-202):
+// new K / V rows [tokens, row_bytes] go to pool rows block_table[(start + t) / block_size] * block_size +
+// (start + t) % block_size.  The reference issues one device-to-device copy per run that stays inside a block (two
+// per block crossed); here one kernel scatters all rows of K and V with 16-byte copies.  Block bookkeeping (free list,
+// reference counts, copy-on-write) stays with the caller.
+namespace {
+__global__ void __launch_bounds__(256) paged_append_kernel(const uint4* __restrict__ src_k, const uint4* __restrict__ src_v,
+                                                           uint4* __restrict__ pool_k, uint4* __restrict__ pool_v,
+                                                           const int32_t* __restrict__ block_table, int64_t start,
+                                                           int64_t tokens, int block_size, int num_blocks, int row_vecs) {
+  const int64_t total = tokens * row_vecs;
+  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / row_vecs;
+    const int vec = (int)(idx - t * row_vecs);
+    const int64_t pos = start + t;
+    const int32_t blk = block_table[pos / block_size];
+    if (blk < 0 || blk >= num_blocks) continue;   // an entry outside the pool is skipped, not written through
+    const int64_t row = (int64_t)blk * block_size + pos % block_size;
+    pool_k[row * row_vecs + vec] = src_k[idx];
+    pool_v[row * row_vecs + vec] = src_v[idx];
+  }
+}
+}  // namespace
+
+cudaError_t launch_paged_append(const void* src_k, const void* src_v, void* pool_k, void* pool_v,
+                                const int32_t* block_table, int64_t start, int64_t tokens, int block_size, int num_blocks,
+                                int64_t row_bytes, cudaStream_t stream) {
+  if (tokens <= 0) return cudaSuccess;
+  const int row_vecs = (int)(row_bytes / 16);
+  const int64_t total = tokens * row_vecs;
+  const int64_t blocks = (total + 255) / 256;
+  const unsigned grid = (unsigned)(blocks < 148 * 16 ? blocks : 148 * 16);
+  paged_append_kernel<<<grid, 256, 0, stream>>>(static_cast<const uint4*>(src_k), static_cast<const uint4*>(src_v),
+                                                static_cast<uint4*>(pool_k), static_cast<uint4*>(pool_v), block_table,
+                                                start, tokens, block_size, num_blocks, row_vecs);
+  return cudaGetLastError();
+}
+
 }  // namespace aidn

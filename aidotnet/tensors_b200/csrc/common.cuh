@@ -169,6 +169,9 @@ int64_t decode_static_scratch_bytes();
 cudaError_t launch_decode_static(const SdpaParams& p, int dtype, int chunk, int nchunks, cudaStream_t stream,
                                  int* launches);
 cudaError_t launch_cast(int kind, const void* src, void* dst, int64_t n, cudaStream_t stream);
+cudaError_t launch_paged_append(const void* src_k, const void* src_v, void* pool_k, void* pool_v,
+                                const int32_t* block_table, int64_t start, int64_t tokens, int block_size, int num_blocks,
+                                int64_t row_bytes, cudaStream_t stream);
 
 // Attention backward (csrc/sdpa_backward.cu): the forward's parameter block (p.out = O, p.lse = log-sum-exp, both
 // inputs here) plus dO, the gradient outputs and the delta scratch.

@@ -27,7 +27,7 @@ EXPORTS = (
     "aidn_sdpa_last_launch_count", "aidn_sdpa_destroy", "aidn_sdpa_last_error", "aidn_sdpa_device_supported",
     "aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32",
     "aidn_sdpa_decode_noalloc", "aidn_sdpa_launch_paged", "aidn_qkv_rope_cache", "aidn_rope_interleaved",
-    "aidn_sdpa_backward", "aidn_sdpa_backward_workspace_bytes",
+    "aidn_sdpa_backward", "aidn_sdpa_backward_workspace_bytes", "aidn_paged_kv_append",
 )
 
 
@@ -130,6 +130,10 @@ def load() -> ctypes.CDLL:
     lib.aidn_sdpa_backward.restype = ctypes.c_int
     lib.aidn_sdpa_backward_workspace_bytes.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64]
     lib.aidn_sdpa_backward_workspace_bytes.restype = ctypes.c_int64
+    lib.aidn_paged_kv_append.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                         ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64,
+                                         ctypes.c_void_p]
+    lib.aidn_paged_kv_append.restype = ctypes.c_int
     lib.aidn_qkv_rope_cache.argtypes = [ctypes.POINTER(QkvRopeArgs), ctypes.c_void_p]
     lib.aidn_qkv_rope_cache.restype = ctypes.c_int
     lib.aidn_rope_interleaved.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
@@ -289,3 +293,11 @@ def rope_interleaved(input: int, cosine: int, sine: int, output: int, rows: int,
     check(load().aidn_rope_interleaved(ctypes.c_void_p(input), ctypes.c_void_p(cosine), ctypes.c_void_p(sine),
                                        ctypes.c_void_p(output), rows, head_dim, seq_len, start_position,
                                        ctypes.c_void_p(stream)))
+
+
+def paged_kv_append(new_keys: int, new_values: int, key_pool: int, value_pool: int, block_table: int, start_position: int,
+                    tokens: int, block_size: int, num_blocks: int, row_bytes: int, stream: int) -> None:
+    """Scatters ``tokens`` new K / V rows into the paged pools at positions start_position.. of one sequence."""
+    check(load().aidn_paged_kv_append(ctypes.c_void_p(new_keys), ctypes.c_void_p(new_values), ctypes.c_void_p(key_pool),
+                                      ctypes.c_void_p(value_pool), ctypes.c_void_p(block_table), start_position, tokens,
+                                      block_size, num_blocks, row_bytes, ctypes.c_void_p(stream)))

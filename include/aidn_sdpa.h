@@ -179,6 +179,15 @@ AIDN_API int aidn_sdpa_device_supported(int32_t device);
  * (CudaBackend.cs:2994-2996). */
 AIDN_API int aidn_sdpa_decode_noalloc(const aidn_sdpa_desc* desc, const aidn_sdpa_args* args, void* cu_stream);
 
+/* The device half of DevicePagedKVCache.Append (Engines/DirectGpu/DevicePagedKVCache.cs:113-202): `tokens` new K / V
+ * rows of `row_bytes` bytes each (kv_heads * head_dim * element size, a multiple of 16) are written to the pool rows of
+ * sequence positions start_position .. start_position + tokens - 1, looked up in the sequence's block table.  One
+ * kernel instead of one device copy per run inside a block; the free list, reference counts and copy-on-write stay in
+ * the caller's cache object.  Entries outside [0, num_blocks) are skipped. */
+AIDN_API int aidn_paged_kv_append(const void* new_keys, const void* new_values, void* key_pool, void* value_pool,
+                                  const int32_t* block_table, int64_t start_position, int64_t tokens,
+                                  int32_t block_size, int32_t num_blocks, int64_t row_bytes, void* cu_stream);
+
 /* Backward of the same attention (FlashAttentionBackward, IDirectGpuBackend.cs:1479-1483, CudaBackend.cs:8580-8704;
  * CPU CpuEngine.cs:29474): dQ, dK, dV from dO, Q, K, V, O and the forward's log-sum-exp, deterministic (every gradient
  * cell is summed by one thread in a fixed order, as the reference's *_deterministic kernels do).  `fwd` is the forward

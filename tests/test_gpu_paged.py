@@ -306,3 +306,41 @@ def test_paged_argument_errors():
         _launch_paged(torch.cat([q, q]), k, v, np.zeros((2, 2), np.int32), dtype="bf16", block_size=16, seq_q=1,
                       seq_kv=64, heads=2, kv_heads=2, head_dim=64)
     assert e.value.status == N.EINVAL
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_paged_kv_append_then_prefill(dtype):
+    """DevicePagedKVCache.Append's device half: a prompt is appended in three ragged pieces (crossing block
+    boundaries, starting mid-block), the pool rows must hold exactly those tokens, untouched rows stay untouched, and
+    a paged prefill over the pool equals the contiguous oracle."""
+    rng = np.random.default_rng(55)
+    heads, kv_heads, D, bs, nblocks = 4, 2, 64, 16, 9
+    total = 100
+    k, kf = gen((total, kv_heads, D), dtype, 1001)
+    v, vf = gen((total, kv_heads, D), dtype, 1002)
+    bt = rng.permutation(nblocks)[: (total + bs - 1) // bs].astype(np.int32)
+    btd = torch.from_numpy(bt).cuda()
+    kp = torch.full((nblocks, bs, kv_heads, D), 9.0, dtype=TORCH_DT[dtype], device="cuda")
+    vp = torch.full((nblocks, bs, kv_heads, D), -9.0, dtype=TORCH_DT[dtype], device="cuda")
+    row_bytes = kv_heads * D * k.element_size()
+    stream = torch.cuda.current_stream().cuda_stream
+    at = 0
+    for n in (21, 50, 29):
+        N.paged_kv_append(k[at:].data_ptr(), v[at:].data_ptr(), kp.data_ptr(), vp.data_ptr(), btd.data_ptr(), at, n, bs,
+                          nblocks, row_bytes, stream)
+        at += n
+    torch.cuda.synchronize()
+    flat_k, flat_v = kp.reshape(nblocks * bs, kv_heads, D), vp.reshape(nblocks * bs, kv_heads, D)
+    rows = np.array([bt[t // bs] * bs + t % bs for t in range(total)])
+    assert torch.equal(flat_k[rows], k) and torch.equal(flat_v[rows], v)
+    untouched = np.setdiff1d(np.arange(nblocks * bs), rows)
+    assert torch.all(flat_k[untouched] == 9.0) and torch.all(flat_v[untouched] == -9.0)
+    q, qf = gen((1, total, heads, D), dtype, 1003)
+    out, _ = _launch_paged(q, kp, vp, bt[None], dtype=dtype, block_size=bs, seq_q=total, seq_kv=total, heads=heads,
+                           kv_heads=kv_heads, head_dim=D, causal=True, causal_offset=0)
+    ref = O.sdpa(qf.transpose(0, 2, 1, 3), kf.transpose(1, 0, 2)[None], vf.transpose(1, 0, 2)[None], causal=True, causal_offset=0)
+    compare(out, ref.transpose(0, 2, 1, 3), dtype, "prefill over an appended pool")
+    with pytest.raises(N.AidnError) as e:
+        N.paged_kv_append(k.data_ptr(), v.data_ptr(), kp.data_ptr(), vp.data_ptr(), btd.data_ptr(), 140, 10, bs, nblocks,
+                          row_bytes, stream)
+    assert e.value.status == N.EINVAL
