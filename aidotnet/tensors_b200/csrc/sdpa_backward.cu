@@ -13,6 +13,8 @@
 // forward, grouped-query attention (dK / dV sum over the query heads of the group).  A correctness-first kernel: it
 // shares the generic forward kernel's tiling, not the tcgen05 kernel's.
 #include "common.cuh"
+#include "mma_sync.cuh"
+#include "sm100_ptx.cuh"
 
 namespace aidn {
 namespace {
@@ -316,6 +318,209 @@ __global__ void __launch_bounds__(kBwdWarps * 32) bwd_dkv_kernel(const BwdParams
   }
 }
 
+// ---- dQ on the warp-level tensor cores (fp16 / bf16 inputs, head_dim 64 or 128, contiguous K / V) ------------------
+// A CTA of 4 warps takes 64 query rows (16 per warp, held as resident A fragments of Q and dO) and streams K and V in
+// 32-key tiles through a 3-stage cp.async ring shared by the warps.  Per 16 keys a warp computes S = Q K^T and
+// dP = dO V^T (mma.sync, the 16-byte chunks of a K / V row feeding the k slots in arrival order as in the decode
+// kernel), turns them into dS = P (dP - delta) in registers, and accumulates dQ^T += K^T dS^T with the rows as the N
+// dimension: the dS accumulators are, as they stand, the B fragments, and the A fragments pair two keys of one d by a
+// byte permute of two K rows.  K is read in both patterns from one shared-memory copy; the chunk swizzle
+// 2*((row/2)&3) ^ 4*(row&1) keeps both reads bank-conflict free.  Deterministic: one thread owns each dQ cell.
+constexpr int kMmaRows = 64;
+constexpr int kMmaKeys = 32;
+constexpr int kMmaStages = 3;
+
+__device__ __forceinline__ int tile_swz(int row) { return (((row >> 1) & 3) << 1) ^ ((row & 1) << 2); }
+
+__device__ __forceinline__ void lds128(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+
+// 8 consecutive elements of a row as four registers of T pairs; `f32` rows are converted.
+template <typename T>
+__device__ __forceinline__ void load_frag8(const void* base, int64_t idx, int f32, bool ok, uint32_t (&r)[4]) {
+  r[0] = r[1] = r[2] = r[3] = 0u;
+  if (!ok) return;
+  if (f32) {
+    const float4 a = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx);
+    const float4 b = *reinterpret_cast<const float4*>(static_cast<const float*>(base) + idx + 4);
+    r[0] = pack_pair<T>(a.x, a.y); r[1] = pack_pair<T>(a.z, a.w); r[2] = pack_pair<T>(b.x, b.y); r[3] = pack_pair<T>(b.z, b.w);
+  } else {
+    const uint4 u = *reinterpret_cast<const uint4*>(static_cast<const T*>(base) + idx);
+    r[0] = u.x; r[1] = u.y; r[2] = u.z; r[3] = u.w;
+  }
+}
+
+template <typename T, int D>
+__global__ void __launch_bounds__(128, 2) bwd_dq_mma_kernel(const BwdParams bp) {
+  const SdpaParams& p = bp.p;
+  constexpr int KI = D / 32, VX = D / 64, MT = D / 16, CH = D / 8, ROWB = D * 2;
+  constexpr int TILEB = kMmaKeys * ROWB, STAGEB = 2 * TILEB;
+  extern __shared__ __align__(128) uint8_t bsm[];
+  const uint32_t s0 = ptx::smem_u32(bsm);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int b = blockIdx.z, hl = blockIdx.y, h = p.head_begin + hl, kvh = h / p.group;
+  const int64_t cta_row0 = (int64_t)blockIdx.x * kMmaRows;
+  const int64_t row0 = cta_row0 + warp * 16;
+  const int64_t rA = row0 + g, rB = row0 + g + 8;
+
+  uint32_t qa[KI][4], qb[KI][4], ga[KI][4], gb[KI][4];
+  {
+    const int64_t qbase = b * p.qs[0] + (int64_t)h * p.qs[1], gbase = b * bp.dos[0] + (int64_t)h * bp.dos[1];
+#pragma unroll
+    for (int i = 0; i < KI; ++i) {
+      const int col = (i * 4 + c) * 8;
+      load_frag8<T>(p.q, qbase + rA * p.qs[2] + col, 0, rA < p.seq_q, qa[i]);
+      load_frag8<T>(p.q, qbase + rB * p.qs[2] + col, 0, rB < p.seq_q, qb[i]);
+      load_frag8<T>(bp.dout, gbase + rA * bp.dos[2] + col, p.out_f32, rA < p.seq_q, ga[i]);
+      load_frag8<T>(bp.dout, gbase + rB * bp.dos[2] + col, p.out_f32, rB < p.seq_q, gb[i]);
+    }
+  }
+  float lseA = -INFINITY, lseB = -INFINITY, dlA = 0.f, dlB = 0.f;
+  if (rA < p.seq_q) {
+    lseA = p.lse[((int64_t)b * p.num_q_heads + h) * p.seq_q + rA];
+    dlA = bp.delta[((int64_t)b * p.head_count + hl) * p.seq_q + rA];
+  }
+  if (rB < p.seq_q) {
+    lseB = p.lse[((int64_t)b * p.num_q_heads + h) * p.seq_q + rB];
+    dlB = bp.delta[((int64_t)b * p.head_count + hl) * p.seq_q + rB];
+  }
+  const int64_t kv_limit = kv_limit_of(p, b);
+  int64_t kend = kv_limit;
+  if (p.causal) {
+    int64_t last_row = cta_row0 + kMmaRows - 1;
+    if (last_row > p.seq_q - 1) last_row = p.seq_q - 1;
+    const int64_t cl = last_row + p.causal_offset + 1;
+    if (cl < kend) kend = cl;
+  }
+  if (kend < 0) kend = 0;
+  const int nsteps = (int)((kend + kMmaKeys - 1) / kMmaKeys);
+
+  const T* kbase = static_cast<const T*>(p.k) + b * p.ks[0] + (int64_t)kvh * p.ks[1];
+  const T* vbase = static_cast<const T*>(p.v) + b * p.vs[0] + (int64_t)kvh * p.vs[1];
+  // the CTA's 128 threads copy a 32-key tile of K and of V: CH chunks per row
+  auto issue = [&](int step) {
+    const uint32_t base = s0 + (step % kMmaStages) * STAGEB;
+    const int64_t j0 = (int64_t)step * kMmaKeys;
+#pragma unroll
+    for (int r = 0; r < kMmaKeys * CH / 128; ++r) {
+      const int idx = tid + r * 128;
+      const int row = idx / CH, ch = idx - row * CH;
+      const int64_t key = j0 + row;
+      const bool valid = key < kend;
+      const int64_t ko = valid ? key : 0;
+      const uint32_t off = (uint32_t)(row * ROWB + ((ch ^ tile_swz(row)) << 4));
+      cp_async16(base + off, kbase + ko * p.ks[2] + ch * 8, valid);
+      cp_async16(base + TILEB + off, vbase + ko * p.vs[2] + ch * 8, valid);
+    }
+    cp_async_commit();
+  };
+
+  float acc[MT][2][4];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int hn = 0; hn < 2; ++hn) acc[m][hn][0] = acc[m][hn][1] = acc[m][hn][2] = acc[m][hn][3] = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < kMmaStages; ++s) {
+    if (s < nsteps) issue(s);
+    else cp_async_commit();
+  }
+  for (int step = 0; step < nsteps; ++step) {
+    cp_async_wait<kMmaStages - 1>();
+    __syncthreads();
+    const uint32_t kb_s = s0 + (step % kMmaStages) * STAGEB, vb_s = kb_s + TILEB;
+    const int64_t j0 = (int64_t)step * kMmaKeys;
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      float sacc[2][4], pacc[2][4];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        sacc[t][0] = sacc[t][1] = sacc[t][2] = sacc[t][3] = 0.f;
+        pacc[t][0] = pacc[t][1] = pacc[t][2] = pacc[t][3] = 0.f;
+        const int kr = hh * 16 + t * 8 + g;
+        const int sw = tile_swz(kr);
+#pragma unroll
+        for (int i = 0; i < KI; ++i) {
+          uint32_t kw[4], vw[4];
+          const uint32_t off = (uint32_t)(kr * ROWB + (((i * 4 + c) ^ sw) << 4));
+          lds128(kb_s + off, kw);
+          lds128(vb_s + off, vw);
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            mma16816<T>(sacc[t], qa[i][2 * h2], qb[i][2 * h2], qa[i][2 * h2 + 1], qb[i][2 * h2 + 1], kw[2 * h2], kw[2 * h2 + 1]);
+            mma16816<T>(pacc[t], ga[i][2 * h2], gb[i][2 * h2], ga[i][2 * h2 + 1], gb[i][2 * h2 + 1], vw[2 * h2], vw[2 * h2 + 1]);
+          }
+        }
+      }
+      float ds[2][4];
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int64_t key = j0 + hh * 16 + t * 8 + 2 * c + e;
+          float pj;
+          prob_and_ds(p, sacc[t][e], pacc[t][e], lseA, dlA, b, h, rA, key, kv_limit, pj, ds[t][e]);
+          prob_and_ds(p, sacc[t][2 + e], pacc[t][2 + e], lseB, dlB, b, h, rB, key, kv_limit, pj, ds[t][2 + e]);
+        }
+      const uint32_t bA0 = pack_pair<T>(ds[0][0], ds[0][1]), bA1 = pack_pair<T>(ds[1][0], ds[1][1]);
+      const uint32_t bB0 = pack_pair<T>(ds[0][2], ds[0][3]), bB1 = pack_pair<T>(ds[1][2], ds[1][3]);
+      uint32_t kt[4][VX][4];
+#pragma unroll
+      for (int e4 = 0; e4 < 4; ++e4) {
+        const int kr = hh * 16 + 2 * c + (e4 & 1) + (e4 >> 1) * 8;
+        const int sw = tile_swz(kr);
+#pragma unroll
+        for (int x = 0; x < VX; ++x) lds128(kb_s + (uint32_t)(kr * ROWB + (((g + 8 * x) ^ sw) << 4)), kt[e4][x]);
+      }
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const uint32_t sel = (m & 1) ? 0x7632u : 0x5410u;
+        constexpr int xh = VX - 1;
+        const int wl = m >> 1, wh = (D == 128) ? (m >> 1) : 2 + (m >> 1);
+        const uint32_t a0 = __byte_perm(kt[0][0][wl], kt[1][0][wl], sel);
+        const uint32_t a1 = __byte_perm(kt[0][xh][wh], kt[1][xh][wh], sel);
+        const uint32_t a2 = __byte_perm(kt[2][0][wl], kt[3][0][wl], sel);
+        const uint32_t a3 = __byte_perm(kt[2][xh][wh], kt[3][xh][wh], sel);
+        mma16816<T>(acc[m][0], a0, a1, a2, a3, bA0, bA1);
+        mma16816<T>(acc[m][1], a0, a1, a2, a3, bB0, bB1);
+      }
+    }
+    __syncthreads();   // every warp is done with the stage before it is refilled
+    if (step + kMmaStages < nsteps) issue(step + kMmaStages);
+    else cp_async_commit();
+  }
+
+  // acc[m][hn][e]: row row0 + 8 hn + 2c + (e & 1), d = d_lo(m) for e < 2, d_hi(m) for e >= 2
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    const int d_lo = g * 8 + m, d_hi = (D == 128) ? (g + 8) * 8 + m : g * 8 + 4 + m;
+#pragma unroll
+    for (int hn = 0; hn < 2; ++hn)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int64_t row = row0 + 8 * hn + 2 * c + e;
+        if (row >= p.seq_q) continue;
+        float* out = bp.dq + (((int64_t)b * p.head_count + hl) * p.seq_q + row) * D;
+        out[d_lo] = acc[m][hn][e] * p.scale;
+        out[d_hi] = acc[m][hn][2 + e] * p.scale;
+      }
+  }
+}
+
+// 16-byte vector loads of Q, K, V, dO rows: bases and strides must allow them.
+inline bool mma_aligned(const BwdParams& bp) {
+  const SdpaParams& p = bp.p;
+  auto ok = [](const void* ptr, const int64_t* st, size_t esz) {
+    if ((uintptr_t)ptr % 16) return false;
+    for (int i = 0; i < 3; ++i)
+      if ((st[i] * (int64_t)esz) % 16) return false;
+    return true;
+  };
+  return ok(p.q, p.qs, 2) && ok(p.k, p.ks, 2) && ok(p.v, p.vs, 2) && ok(bp.dout, bp.dos, p.out_f32 ? 4 : 2);
+}
+
 template <typename T, int DMAX>
 cudaError_t launch_bwd_t(const BwdParams& bp, cudaStream_t stream, int* launches) {
   const SdpaParams& p = bp.p;
@@ -333,8 +538,22 @@ cudaError_t launch_bwd_t(const BwdParams& bp, cudaStream_t stream, int* launches
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv);
     if (e != cudaSuccess) return e;
   }
-  dim3 g1((unsigned)((p.seq_q + kRows - 1) / kRows), (unsigned)p.head_count, (unsigned)p.batch);
-  kq<<<g1, kBwdWarps * 32, smem_q, stream>>>(bp);
+  bool dq_done = false;
+  if constexpr (sizeof(T) == 2 && (DMAX == 64 || DMAX == 128)) {
+    if (p.head_dim == DMAX && !p.block_table && mma_aligned(bp)) {
+      auto kq_mma = bwd_dq_mma_kernel<T, DMAX>;
+      const size_t smem_mma = (size_t)kMmaStages * 2 * kMmaKeys * DMAX * 2;
+      e = cudaFuncSetAttribute(kq_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma);
+      if (e != cudaSuccess) return e;
+      dim3 gm((unsigned)((p.seq_q + kMmaRows - 1) / kMmaRows), (unsigned)p.head_count, (unsigned)p.batch);
+      kq_mma<<<gm, 128, smem_mma, stream>>>(bp);
+      dq_done = true;
+    }
+  }
+  if (!dq_done) {
+    dim3 g1((unsigned)((p.seq_q + kRows - 1) / kRows), (unsigned)p.head_count, (unsigned)p.batch);
+    kq<<<g1, kBwdWarps * 32, smem_q, stream>>>(bp);
+  }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   dim3 g2((unsigned)((p.seq_kv + kKeys - 1) / kKeys), (unsigned)(p.head_count / p.group), (unsigned)p.batch);
