@@ -445,7 +445,10 @@ int64_t aidn_sdpa_backward_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t
     fail(AIDN_EINVAL, "backward_workspace_bytes: bad argument");
     return -1;
   }
-  return align_up(batch * h->head_count * seq_q * (int64_t)sizeof(float), 256);
+  int64_t bytes = align_up(batch * h->head_count * seq_q * (int64_t)sizeof(float), 256);   // delta
+  if (h->d.qkv_dtype != AIDN_F32 && h->d.out_dtype == AIDN_F32)                              // dO in the input dtype
+    bytes += align_up(batch * h->head_count * seq_q * (int64_t)h->d.head_dim * 2, 256);
+  return bytes;
 }
 
 int aidn_sdpa_backward(aidn_sdpa_t h, const aidn_sdpa_bwd_args* a, void* cu_stream) {
@@ -469,6 +472,10 @@ int aidn_sdpa_backward(aidn_sdpa_t h, const aidn_sdpa_bwd_args* a, void* cu_stre
     if (bp.dos[i] < 0) return fail(AIDN_EINVAL, "backward: negative stride");
   bp.dq = a->dq; bp.dk = a->dk; bp.dv = a->dv;
   bp.delta = static_cast<float*>(a->fwd.workspace);
+  bp.dout_t = nullptr;
+  if (h->d.qkv_dtype != AIDN_F32 && h->d.out_dtype == AIDN_F32)
+    bp.dout_t = static_cast<char*>(a->fwd.workspace) +
+                align_up(a->fwd.batch * h->head_count * a->fwd.seq_q * (int64_t)sizeof(float), 256);
   int launches = 0;
   cudaError_t e = aidn::launch_backward(bp, h->d.qkv_dtype, (cudaStream_t)cu_stream, &launches);
   if (e != cudaSuccess) return fail_cuda(e, "backward");

@@ -183,6 +183,7 @@ struct BwdParams {
   float* dk;          // [B, Hc / group, Sk, D] fp32
   float* dv;
   float* delta;       // [B, Hc, Sq] scratch
+  void* dout_t;       // scratch: dO in the input dtype, dense [B, Hc, Sq, D] (16-bit inputs with an fp32 dO), or null
 };
 cudaError_t launch_backward(const BwdParams& bp, int dtype, cudaStream_t stream, int* launches);
 

@@ -40,7 +40,12 @@ __global__ void __launch_bounds__(128) bwd_delta_kernel(const BwdParams bp) {
   const int64_t ob = b * p.os[0] + (int64_t)h * p.os[1] + row * p.os[2];
   const int64_t gb = b * bp.dos[0] + (int64_t)h * bp.dos[1] + row * bp.dos[2];
   float acc = 0.f;
-  for (int d = lane; d < p.head_dim; d += 32) acc += load_o<T>(bp.dout, gb + d, p.out_f32) * load_o<T>(p.out, ob + d, p.out_f32);
+  T* gt = bp.dout_t ? static_cast<T*>(bp.dout_t) + (((int64_t)b * p.head_count + hl) * p.seq_q + row) * p.head_dim : nullptr;
+  for (int d = lane; d < p.head_dim; d += 32) {
+    const float go = load_o<T>(bp.dout, gb + d, p.out_f32);
+    acc += go * load_o<T>(p.out, ob + d, p.out_f32);
+    if (gt) gt[d] = from_float<T>(go);   // the tensor-core dK / dV kernel streams dO with cp.async in the input dtype
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (lane == 0) bp.delta[((int64_t)b * p.head_count + hl) * p.seq_q + row] = acc;
@@ -509,6 +514,210 @@ __global__ void __launch_bounds__(128, 2) bwd_dq_mma_kernel(const BwdParams bp) 
   }
 }
 
+// ---- dK, dV on the warp-level tensor cores ---------------------------------------------------------------------------
+// A CTA of 4 warps owns 64 keys of one KV head (16 per warp; their K and V rows sit in shared memory for the whole
+// kernel) and streams Q and dO in 32-row tiles through a 3-stage cp.async ring, over the query heads of the group and
+// the row tiles that can see the keys.  Per 16 rows a warp computes S^T = K Q^T and dP^T = V dO^T (keys as M), turns
+// them into P^T and dS^T in registers, and accumulates dV^T += dO^T P and dK^T += Q^T dS with its keys as the N
+// dimension: P^T / dS^T accumulators are the B fragments as they stand, the A fragments pair two rows of one d by a
+// byte permute.  Rows are visited in ascending order by one warp per key: deterministic.
+template <typename T, int D>
+__global__ void __launch_bounds__(128, 2) bwd_dkv_mma_kernel(const BwdParams bp) {
+  const SdpaParams& p = bp.p;
+  constexpr int KI = D / 32, VX = D / 64, MT = D / 16, CH = D / 8, ROWB = D * 2;
+  constexpr int kOwn = 64;                                  // keys per CTA
+  constexpr int OWNB = kOwn * ROWB;                         // K (and V) of the CTA's keys
+  constexpr int TILEB = kMmaKeys * ROWB;                    // 32 rows of Q (and of dO)
+  constexpr int STAGEB = 2 * TILEB + 2 * kMmaKeys * 4;      // + lse[32] + delta[32]
+  extern __shared__ __align__(128) uint8_t bsm[];
+  const uint32_t s0 = ptx::smem_u32(bsm);
+  const uint32_t k_s = s0, v_s = s0 + OWNB, ring = s0 + 2 * OWNB;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, c = lane & 3;
+  const int b = blockIdx.z, kvl = blockIdx.y, kvh = p.head_begin / p.group + kvl;
+  const int64_t key0 = (int64_t)blockIdx.x * kOwn;
+  const int64_t kv_limit = kv_limit_of(p, b);
+  const T* kbase = static_cast<const T*>(p.k) + b * p.ks[0] + (int64_t)kvh * p.ks[1];
+  const T* vbase = static_cast<const T*>(p.v) + b * p.vs[0] + (int64_t)kvh * p.vs[1];
+
+  // own keys (zero rows past the end)
+#pragma unroll
+  for (int r = 0; r < kOwn * CH / 128; ++r) {
+    const int idx = tid + r * 128;
+    const int row = idx / CH, ch = idx - row * CH;
+    const int64_t key = key0 + row;
+    const bool valid = key < p.seq_kv;
+    const int64_t ko = valid ? key : 0;
+    const uint32_t off = (uint32_t)(row * ROWB + ((ch ^ tile_swz(row)) << 4));
+    cp_async16(k_s + off, kbase + ko * p.ks[2] + ch * 8, valid);
+    cp_async16(v_s + off, vbase + ko * p.vs[2] + ch * 8, valid);
+  }
+  cp_async_commit();
+
+  // row tiles that can see key0 or later keys of the CTA (causal: key <= row + offset)
+  int64_t r_first = 0;
+  if (p.causal) {
+    r_first = key0 - p.causal_offset;
+    if (r_first < 0) r_first = 0;
+    r_first = r_first / kMmaKeys * kMmaKeys;
+  }
+  const int tiles_per_head = key0 < kv_limit && r_first < p.seq_q ? (int)((p.seq_q - r_first + kMmaKeys - 1) / kMmaKeys) : 0;
+  const int nsteps = tiles_per_head * p.group;
+  const int dstr = p.head_dim;   // dO scratch rows are dense
+  const T* gsrc = bp.dout_t ? static_cast<const T*>(bp.dout_t) : static_cast<const T*>(bp.dout);
+
+  auto issue = [&](int step) {
+    const int gi = step / tiles_per_head, ti = step - gi * tiles_per_head;
+    const int h = kvh * p.group + gi, hl = h - p.head_begin;
+    const int64_t rbase = r_first + (int64_t)ti * kMmaKeys;
+    const uint32_t base = ring + (step % kMmaStages) * STAGEB;
+    const T* qsrc = static_cast<const T*>(p.q) + b * p.qs[0] + (int64_t)h * p.qs[1];
+    const int64_t g_off = bp.dout_t ? (((int64_t)b * p.head_count + hl) * p.seq_q) * dstr : b * bp.dos[0] + (int64_t)h * bp.dos[1];
+    const int64_t g_rs = bp.dout_t ? dstr : bp.dos[2];
+#pragma unroll
+    for (int r = 0; r < kMmaKeys * CH / 128; ++r) {
+      const int idx = tid + r * 128;
+      const int row = idx / CH, ch = idx - row * CH;
+      const int64_t qr = rbase + row;
+      const bool valid = qr < p.seq_q;
+      const int64_t ro = valid ? qr : 0;
+      const uint32_t off = (uint32_t)(row * ROWB + ((ch ^ tile_swz(row)) << 4));
+      cp_async16(base + off, qsrc + ro * p.qs[2] + ch * 8, valid);
+      cp_async16(base + TILEB + off, gsrc + g_off + ro * g_rs + ch * 8, valid);
+    }
+    if (tid < 2 * kMmaKeys) {   // lse and delta of the tile's rows: 4-byte copies, rows past the end zero-filled
+      const int row = tid & (kMmaKeys - 1);
+      const int64_t qr = rbase + row;
+      const bool valid = qr < p.seq_q;
+      const int64_t ro = valid ? qr : 0;
+      const float* src = tid < kMmaKeys ? p.lse + ((int64_t)b * p.num_q_heads + h) * p.seq_q + ro
+                                        : bp.delta + ((int64_t)b * p.head_count + hl) * p.seq_q + ro;
+      const uint32_t n = valid ? 4u : 0u;
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(base + 2 * TILEB + tid * 4), "l"(src), "r"(n) : "memory");
+    }
+    cp_async_commit();
+  };
+
+  float accV[MT][2][4], accK[MT][2][4];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int hn = 0; hn < 2; ++hn)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) accV[m][hn][e] = accK[m][hn][e] = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < kMmaStages; ++s) {
+    if (s < nsteps) issue(s);
+    else cp_async_commit();
+  }
+  const int okA = warp * 16 + g, okB = okA + 8;               // this thread's key rows in the CTA's K / V tiles
+  const int64_t keyA = key0 + okA, keyB = key0 + okB;
+  for (int step = 0; step < nsteps; ++step) {
+    cp_async_wait<kMmaStages - 1>();   // also covers the own-keys group, committed first
+    __syncthreads();
+    const int gi = step / tiles_per_head, ti = step - gi * tiles_per_head;
+    const int h = kvh * p.group + gi;
+    const int64_t rbase = r_first + (int64_t)ti * kMmaKeys;
+    const uint32_t q_s = ring + (step % kMmaStages) * STAGEB, g_s = q_s + TILEB;
+    const float* stat = reinterpret_cast<const float*>(bsm + (2 * OWNB + (step % kMmaStages) * STAGEB + 2 * TILEB));
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      float sacc[2][4], pacc[2][4];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        sacc[t][0] = sacc[t][1] = sacc[t][2] = sacc[t][3] = 0.f;
+        pacc[t][0] = pacc[t][1] = pacc[t][2] = pacc[t][3] = 0.f;
+        const int rr = hh * 16 + t * 8 + g;     // B-fragment column g = row rr of the tile
+        const int swr = tile_swz(rr), swa = tile_swz(okA), swb = tile_swz(okB);
+#pragma unroll
+        for (int i = 0; i < KI; ++i) {
+          uint32_t ka[4], kb[4], va[4], vb[4], qw[4], gw[4];
+          const int ch = i * 4 + c;
+          lds128(k_s + (uint32_t)(okA * ROWB + ((ch ^ swa) << 4)), ka);
+          lds128(k_s + (uint32_t)(okB * ROWB + ((ch ^ swb) << 4)), kb);
+          lds128(v_s + (uint32_t)(okA * ROWB + ((ch ^ swa) << 4)), va);
+          lds128(v_s + (uint32_t)(okB * ROWB + ((ch ^ swb) << 4)), vb);
+          lds128(q_s + (uint32_t)(rr * ROWB + ((ch ^ swr) << 4)), qw);
+          lds128(g_s + (uint32_t)(rr * ROWB + ((ch ^ swr) << 4)), gw);
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            mma16816<T>(sacc[t], ka[2 * h2], kb[2 * h2], ka[2 * h2 + 1], kb[2 * h2 + 1], qw[2 * h2], qw[2 * h2 + 1]);
+            mma16816<T>(pacc[t], va[2 * h2], vb[2 * h2], va[2 * h2 + 1], vb[2 * h2 + 1], gw[2 * h2], gw[2 * h2 + 1]);
+          }
+        }
+      }
+      // accumulators: [t][e] = (key A, row hh*16 + t*8 + 2c + e), [t][2 + e] = (key B, same row)
+      float pr[2][4], ds[2][4];
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int rt = hh * 16 + t * 8 + 2 * c + e;
+          const int64_t row = rbase + rt;
+          const float lse = row < p.seq_q ? stat[rt] : -INFINITY, dl = stat[kMmaKeys + rt];
+          prob_and_ds(p, sacc[t][e], pacc[t][e], lse, dl, b, h, row, keyA, kv_limit, pr[t][e], ds[t][e]);
+          prob_and_ds(p, sacc[t][2 + e], pacc[t][2 + e], lse, dl, b, h, row, keyB, kv_limit, pr[t][2 + e], ds[t][2 + e]);
+        }
+      // B fragments: n-tile 0 = keys A (g), n-tile 1 = keys B (g + 8); k = rows 2c, 2c+1 | 2c+8, 2c+9 of the half
+      const uint32_t pA0 = pack_pair<T>(pr[0][0], pr[0][1]), pA1 = pack_pair<T>(pr[1][0], pr[1][1]);
+      const uint32_t pB0 = pack_pair<T>(pr[0][2], pr[0][3]), pB1 = pack_pair<T>(pr[1][2], pr[1][3]);
+      const uint32_t sA0 = pack_pair<T>(ds[0][0], ds[0][1]), sA1 = pack_pair<T>(ds[1][0], ds[1][1]);
+      const uint32_t sB0 = pack_pair<T>(ds[0][2], ds[0][3]), sB1 = pack_pair<T>(ds[1][2], ds[1][3]);
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {   // 0: dV^T += dO^T P, 1: dK^T += Q^T dS
+        const uint32_t src_s = which == 0 ? g_s : q_s;
+        uint32_t rt4[4][VX][4];
+#pragma unroll
+        for (int e4 = 0; e4 < 4; ++e4) {
+          const int rr = hh * 16 + 2 * c + (e4 & 1) + (e4 >> 1) * 8;
+          const int sw = tile_swz(rr);
+#pragma unroll
+          for (int x = 0; x < VX; ++x) lds128(src_s + (uint32_t)(rr * ROWB + (((g + 8 * x) ^ sw) << 4)), rt4[e4][x]);
+        }
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const uint32_t sel = (m & 1) ? 0x7632u : 0x5410u;
+          constexpr int xh = VX - 1;
+          const int wl = m >> 1, wh = (D == 128) ? (m >> 1) : 2 + (m >> 1);
+          const uint32_t a0 = __byte_perm(rt4[0][0][wl], rt4[1][0][wl], sel);
+          const uint32_t a1 = __byte_perm(rt4[0][xh][wh], rt4[1][xh][wh], sel);
+          const uint32_t a2 = __byte_perm(rt4[2][0][wl], rt4[3][0][wl], sel);
+          const uint32_t a3 = __byte_perm(rt4[2][xh][wh], rt4[3][xh][wh], sel);
+          if (which == 0) {
+            mma16816<T>(accV[m][0], a0, a1, a2, a3, pA0, pA1);
+            mma16816<T>(accV[m][1], a0, a1, a2, a3, pB0, pB1);
+          } else {
+            mma16816<T>(accK[m][0], a0, a1, a2, a3, sA0, sA1);
+            mma16816<T>(accK[m][1], a0, a1, a2, a3, sB0, sB1);
+          }
+        }
+      }
+    }
+    __syncthreads();
+    if (step + kMmaStages < nsteps) issue(step + kMmaStages);
+    else cp_async_commit();
+  }
+  cp_async_wait<0>();
+
+  // acc[m][hn][e]: key key0 + warp*16 + 8 hn + 2c + (e & 1), d = d_lo(m) for e < 2, d_hi(m) for e >= 2
+#pragma unroll
+  for (int m = 0; m < MT; ++m) {
+    const int d_lo = g * 8 + m, d_hi = (D == 128) ? (g + 8) * 8 + m : g * 8 + 4 + m;
+#pragma unroll
+    for (int hn = 0; hn < 2; ++hn)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int64_t key = key0 + warp * 16 + 8 * hn + 2 * c + e;
+        if (key >= p.seq_kv) continue;
+        const int64_t base = (((int64_t)b * (p.head_count / p.group) + kvl) * p.seq_kv + key) * D;
+        bp.dv[base + d_lo] = accV[m][hn][e];
+        bp.dv[base + d_hi] = accV[m][hn][2 + e];
+        bp.dk[base + d_lo] = accK[m][hn][e] * p.scale;
+        bp.dk[base + d_hi] = accK[m][hn][2 + e] * p.scale;
+      }
+  }
+}
+
 // 16-byte vector loads of Q, K, V, dO rows: bases and strides must allow them.
 inline bool mma_aligned(const BwdParams& bp) {
   const SdpaParams& p = bp.p;
@@ -556,8 +765,22 @@ cudaError_t launch_bwd_t(const BwdParams& bp, cudaStream_t stream, int* launches
   }
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  dim3 g2((unsigned)((p.seq_kv + kKeys - 1) / kKeys), (unsigned)(p.head_count / p.group), (unsigned)p.batch);
-  kkv<<<g2, kBwdWarps * 32, smem_kv, stream>>>(bp);
+  bool dkv_done = false;
+  if constexpr (sizeof(T) == 2 && (DMAX == 64 || DMAX == 128)) {
+    if (dq_done && (bp.dout_t || !p.out_f32)) {
+      auto kkv_mma = bwd_dkv_mma_kernel<T, DMAX>;
+      const size_t smem_mma = 2 * 64 * (size_t)DMAX * 2 + (size_t)kMmaStages * (2 * kMmaKeys * DMAX * 2 + 2 * kMmaKeys * 4);
+      e = cudaFuncSetAttribute(kkv_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_mma);
+      if (e != cudaSuccess) return e;
+      dim3 gm((unsigned)((p.seq_kv + 63) / 64), (unsigned)(p.head_count / p.group), (unsigned)p.batch);
+      kkv_mma<<<gm, 128, smem_mma, stream>>>(bp);
+      dkv_done = true;
+    }
+  }
+  if (!dkv_done) {
+    dim3 g2((unsigned)((p.seq_kv + kKeys - 1) / kKeys), (unsigned)(p.head_count / p.group), (unsigned)p.batch);
+    kkv<<<g2, kBwdWarps * 32, smem_kv, stream>>>(bp);
+  }
   *launches = 3;
   return cudaGetLastError();
 }
