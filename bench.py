@@ -37,7 +37,7 @@ WORKLOADS = {
                     name="long_context_shard_B1_Hq8_Hkv1_S32768_D128_causal_bf16"),
     "c3paged": dict(B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill", block_size=16,
                     name="paged_gqa_prefill_B2_Hq32_Hkv8_S8192_D128_block16_causal_bf16"),
-    # attention backward (deterministic FFMA kernels) on a quarter of the C2 shape
+    # attention backward (deterministic; mma.sync kernels for 16-bit inputs) on a quarter of the C2 shape
     "c2bwd": dict(kind="bwd", B=1, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
                   name="llama_backward_B1_H32_S2048_D128_causal_bf16"),
     # the decode step in front of attention: packed Q/K/V projection of 8 resident tokens + RoPE + cache write
@@ -296,7 +296,7 @@ def run_bwd(args, w, pk):
         "config": {"workload": w["name"], "flop_convention": "10*D*visible(q,k) pairs"},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16"], "unit": "TFLOP/s", "frac": tf / pk["bf16"],
                      "traffic": None, "algorithmic": fl, "algorithmic_unit": "FLOP per launch",
-                     "peak_source": pk["source"] + " (burst); the kernels are FFMA, not tensor-core, code"},
+                     "peak_source": pk["source"] + " (burst); warp-level mma.sync kernels, not tcgen05"},
         "gpu_launches": 3 * args.steps}))
 
 
