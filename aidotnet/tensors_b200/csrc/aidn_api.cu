@@ -652,6 +652,138 @@ int aidn_paged_kv_append(const void* new_keys, const void* new_values, void* key
   return AIDN_OK;
 }
 
+// ---- fused multi-head attention forward ---------------------------------------------------------------------------
+namespace {
+struct MhaPlan {
+  int64_t off_x, off_w, off_q, off_k, off_v, off_o, total;
+};
+MhaPlan mha_plan(const aidn_sdpa* h, int64_t batch, int64_t seq, int input_dtype, int weight_dtype) {
+  const int64_t dm = (int64_t)h->d.num_q_heads * h->d.head_dim;
+  const int64_t act = align_up(batch * seq * dm * 2, 1024), wgt = align_up(dm * dm * 2, 1024);
+  MhaPlan pl;
+  int64_t off = 0;
+  pl.off_x = off; off += input_dtype == AIDN_F32 ? act : 0;
+  pl.off_w = off; off += weight_dtype == AIDN_F32 ? 4 * wgt : 0;
+  pl.off_q = off; off += act;
+  pl.off_k = off; off += act;
+  pl.off_v = off; off += act;
+  pl.off_o = off; off += act;
+  pl.total = off;
+  return pl;
+}
+int mha_check_handle(const aidn_sdpa* h) {
+  const aidn_sdpa_desc& d = h->d;
+  if (d.qkv_dtype == AIDN_F32 || d.out_dtype != d.qkv_dtype)
+    return fail(AIDN_EUNSUPPORTED, "mha: the handle must have a 16-bit qkv_dtype and out_dtype == qkv_dtype");
+  if (d.num_kv_heads != d.num_q_heads || h->head_count != d.num_q_heads)
+    return fail(AIDN_EUNSUPPORTED, "mha: the handle must cover all heads with num_kv_heads == num_q_heads");
+  if (d.head_dim != 64 && d.head_dim != 128) return fail(AIDN_EUNSUPPORTED, "mha: head_dim must be 64 or 128");
+  if (((int64_t)d.num_q_heads * d.head_dim) % 128 != 0)
+    return fail(AIDN_EUNSUPPORTED, "mha: heads * head_dim must be a multiple of 128");
+  if (d.emit_lse || d.softcap > 0.f || d.nccl_comm)
+    return fail(AIDN_EUNSUPPORTED, "mha: the handle must not ask for log-sum-exp, softcap or a gather");
+  if (d.mask_kind == AIDN_MASK_ADD_F32) return fail(AIDN_EUNSUPPORTED, "mha: the mask is a keep-mask (Tensor<bool>) or absent");
+  return AIDN_OK;
+}
+}  // namespace
+
+int64_t aidn_mha_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq, int32_t input_dtype, int32_t weight_dtype) {
+  g_err[0] = 0;
+  if (!h || batch <= 0 || seq <= 0) {
+    fail(AIDN_EINVAL, "mha_workspace_bytes: bad argument");
+    return -1;
+  }
+  if (mha_check_handle(h) != AIDN_OK) return -1;
+  return mha_plan(h, batch, seq, input_dtype, weight_dtype).total;
+}
+
+int aidn_mha_forward(aidn_sdpa_t h, const aidn_mha_args* a, void* cu_stream) {
+  g_err[0] = 0;
+  if (!h || !a) return fail(AIDN_EINVAL, "mha: null argument");
+  if (!a->input || !a->q_weight || !a->k_weight || !a->v_weight || !a->out_weight || !a->out)
+    return fail(AIDN_EINVAL, "mha: null tensor pointer");
+  if (a->batch <= 0 || a->seq <= 0) return fail(AIDN_EINVAL, "mha: batch and seq must be positive");
+  int rc = mha_check_handle(h);
+  if (rc != AIDN_OK) return rc;
+  const aidn_sdpa_desc& d = h->d;
+  auto dtype_ok = [&](int t) { return t == AIDN_F32 || t == d.qkv_dtype; };
+  if (!dtype_ok(a->input_dtype) || !dtype_ok(a->weight_dtype) || !dtype_ok(a->out_dtype))
+    return fail(AIDN_EINVAL, "mha: input, weight and output dtypes must be fp32 or the handle's qkv_dtype");
+  if (d.mask_kind != AIDN_MASK_NONE && !a->mask) return fail(AIDN_EINVAL, "mha: mask_kind set but mask pointer is null");
+  const MhaPlan pl = mha_plan(h, a->batch, a->seq, a->input_dtype, a->weight_dtype);
+  if (!a->workspace || a->workspace_bytes < pl.total)
+    return fail(AIDN_EWORKSPACE, "mha: workspace of %lld bytes, need %lld", (long long)(a->workspace ? a->workspace_bytes : 0),
+                (long long)pl.total);
+  if ((uintptr_t)a->workspace % 1024 != 0) return fail(AIDN_EINVAL, "mha: workspace must be 1024-byte aligned");
+  cudaStream_t stream = (cudaStream_t)cu_stream;
+  char* ws = static_cast<char*>(a->workspace);
+  const int64_t H = d.num_q_heads, D = d.head_dim, dm = H * D, S = a->seq, B = a->batch;
+  const int cast_kind = d.qkv_dtype == AIDN_BF16 ? 0 : 1;
+  int launches = 0;
+  cudaError_t e = cudaSuccess;
+
+  const void* x = a->input;
+  if (a->input_dtype == AIDN_F32) {
+    e = aidn::launch_cast(cast_kind, a->input, ws + pl.off_x, B * S * dm, stream);
+    if (e != cudaSuccess) return fail_cuda(e, "mha: input cast");
+    x = ws + pl.off_x;
+    ++launches;
+  }
+  const void* w[4] = {a->q_weight, a->k_weight, a->v_weight, a->out_weight};
+  if (a->weight_dtype == AIDN_F32) {
+    const int64_t wgt = align_up(dm * dm * 2, 1024);
+    for (int i = 0; i < 4; ++i) {
+      void* dst = ws + pl.off_w + i * wgt;
+      e = aidn::launch_cast(cast_kind, w[i], dst, dm * dm, stream);
+      if (e != cudaSuccess) return fail_cuda(e, "mha: weight cast");
+      w[i] = dst;
+      ++launches;
+    }
+  }
+
+  const char* why = "";
+  aidn::ProjGemm g;
+  std::memset(&g, 0, sizeof(g));
+  g.a = x;
+  g.batch = B; g.seq = S; g.k = dm; g.n = dm;
+  g.head_dim = (int)D;
+  g.bf16 = d.qkv_dtype == AIDN_BF16;
+  g.num_mats = 3;
+  g.out_f32 = false;
+  for (int i = 0; i < 3; ++i) g.w[i] = w[i];
+  g.c[0] = ws + pl.off_q; g.c[1] = ws + pl.off_k; g.c[2] = ws + pl.off_v;
+  g.c_stride[0] = H * S * D; g.c_stride[1] = S * D; g.c_stride[2] = D;    // [B, H, S, d]
+  if (!aidn::proj_gemm_sm100_supported(g, &why)) return fail(AIDN_EUNSUPPORTED, "mha: %s", why);
+  e = aidn::launch_proj_gemm_sm100(g, stream, h->num_sms, h->status_dev, &why);
+  if (e != cudaSuccess) return why[0] ? fail(AIDN_ECUDA, "mha: %s (%s)", why, cudaGetErrorName(e)) : fail_cuda(e, "mha: QKV projection");
+  ++launches;
+
+  aidn_sdpa_args sa;
+  std::memset(&sa, 0, sizeof(sa));
+  sa.q = g.c[0]; sa.k = g.c[1]; sa.v = g.c[2];
+  sa.out = ws + pl.off_o;
+  sa.mask = a->mask;
+  for (int i = 0; i < 4; ++i) sa.mask_stride[i] = a->mask_stride[i];
+  sa.batch = B; sa.seq_q = S; sa.seq_kv = S;
+  sa.o_stride[0] = S * dm; sa.o_stride[1] = D; sa.o_stride[2] = dm;      // heads side by side: [B, S, H*d]
+  rc = launch_common(h, &sa, nullptr, cu_stream);
+  if (rc != AIDN_OK) return rc;
+  launches += h->last_launches;
+
+  g.a = ws + pl.off_o;
+  g.num_mats = 1;
+  g.w[0] = w[3];
+  g.c[0] = a->out;
+  g.out_f32 = a->out_dtype == AIDN_F32;
+  g.c_stride[0] = S * dm; g.c_stride[1] = D; g.c_stride[2] = dm;
+  if (!aidn::proj_gemm_sm100_supported(g, &why)) return fail(AIDN_EUNSUPPORTED, "mha: %s", why);
+  e = aidn::launch_proj_gemm_sm100(g, stream, h->num_sms, h->status_dev, &why);
+  if (e != cudaSuccess) return why[0] ? fail(AIDN_ECUDA, "mha: %s (%s)", why, cudaGetErrorName(e)) : fail_cuda(e, "mha: output projection");
+  ++launches;
+  h->last_launches = launches;
+  return AIDN_OK;
+}
+
 static int cast_common(int kind, const void* src, void* dst, int64_t n, void* cu_stream) {
   g_err[0] = 0;
   if (n < 0 || (n > 0 && (!src || !dst))) return fail(AIDN_EINVAL, "cast: bad argument");

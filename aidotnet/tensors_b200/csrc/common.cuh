@@ -218,4 +218,22 @@ cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t st
                                  float* debug, int debug_mode, const char** why);
 cudaError_t prefill_sm100_prepare();  // one-time per-process function attribute setup
 
+// Projection GEMM of the fused multi-head-attention forward (csrc/proj_gemm_sm100.cu):
+// c[i][b, s, n] = sum_k a[b, s, k] * w[i][k, n] for up to three weight matrices that share a; column n lands at
+// c[i] + b*c_stride[0] + (n / head_dim)*c_stride[1] + s*c_stride[2] + n % head_dim.
+struct ProjGemm {
+  const void* a;        // [batch, seq, k] dense, 16-bit
+  const void* w[3];     // [k, n] row-major, 16-bit
+  void* c[3];
+  int64_t c_stride[3];  // elements for (batch, head, sequence position)
+  int64_t batch, seq, k, n;
+  int32_t num_mats;
+  int32_t head_dim;
+  bool out_f32;         // fp32 output, else the input dtype
+  bool bf16;            // bf16 inputs, else fp16
+};
+bool proj_gemm_sm100_supported(const ProjGemm& g, const char** why);
+cudaError_t launch_proj_gemm_sm100(const ProjGemm& g, cudaStream_t stream, int num_sms, int32_t* status,
+                                   const char** why);
+
 }  // namespace aidn

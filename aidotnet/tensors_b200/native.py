@@ -27,7 +27,8 @@ EXPORTS = (
     "aidn_sdpa_last_launch_count", "aidn_sdpa_destroy", "aidn_sdpa_last_error", "aidn_sdpa_device_supported",
     "aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32",
     "aidn_sdpa_decode_noalloc", "aidn_sdpa_launch_paged", "aidn_qkv_rope_cache", "aidn_rope_interleaved",
-    "aidn_sdpa_backward", "aidn_sdpa_backward_workspace_bytes", "aidn_paged_kv_append",
+    "aidn_sdpa_backward", "aidn_sdpa_backward_workspace_bytes", "aidn_paged_kv_append", "aidn_mha_forward",
+    "aidn_mha_workspace_bytes",
 )
 
 
@@ -77,6 +78,17 @@ class SdpaBwdArgs(ctypes.Structure):
     _fields_ = [
         ("fwd", SdpaArgs), ("paged", ctypes.POINTER(PagedKv)), ("dout", ctypes.c_void_p),
         ("do_stride", ctypes.c_int64 * 3), ("dq", ctypes.c_void_p), ("dk", ctypes.c_void_p), ("dv", ctypes.c_void_p),
+    ]
+
+
+class MhaArgs(ctypes.Structure):
+    _fields_ = [
+        ("input", ctypes.c_void_p), ("q_weight", ctypes.c_void_p), ("k_weight", ctypes.c_void_p),
+        ("v_weight", ctypes.c_void_p), ("out_weight", ctypes.c_void_p), ("out", ctypes.c_void_p),
+        ("mask", ctypes.c_void_p), ("mask_stride", ctypes.c_int64 * 4), ("batch", ctypes.c_int64),
+        ("seq", ctypes.c_int64), ("input_dtype", ctypes.c_int32), ("weight_dtype", ctypes.c_int32),
+        ("out_dtype", ctypes.c_int32), ("reserved", ctypes.c_int32), ("workspace", ctypes.c_void_p),
+        ("workspace_bytes", ctypes.c_int64),
     ]
 
 
@@ -134,6 +146,10 @@ def load() -> ctypes.CDLL:
                                          ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int64,
                                          ctypes.c_void_p]
     lib.aidn_paged_kv_append.restype = ctypes.c_int
+    lib.aidn_mha_workspace_bytes.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
+    lib.aidn_mha_workspace_bytes.restype = ctypes.c_int64
+    lib.aidn_mha_forward.argtypes = [ctypes.c_void_p, ctypes.POINTER(MhaArgs), ctypes.c_void_p]
+    lib.aidn_mha_forward.restype = ctypes.c_int
     lib.aidn_qkv_rope_cache.argtypes = [ctypes.POINTER(QkvRopeArgs), ctypes.c_void_p]
     lib.aidn_qkv_rope_cache.restype = ctypes.c_int
     lib.aidn_rope_interleaved.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
@@ -229,6 +245,26 @@ class Handle:
         f.scale, f.workspace, f.workspace_bytes = scale, workspace, workspace_bytes
         a.dout, a.do_stride, a.dq, a.dk, a.dv = dout, _arr3(do_stride), dq, dk, dv
         check(self._lib.aidn_sdpa_backward(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
+
+    def mha_workspace_bytes(self, batch: int, seq: int, input_dtype: int, weight_dtype: int) -> int:
+        n = self._lib.aidn_mha_workspace_bytes(self._h, batch, seq, input_dtype, weight_dtype)
+        if n < 0:
+            raise AidnError(EUNSUPPORTED, last_error())
+        return int(n)
+
+    def mha_forward(self, *, input: int, q_weight: int, k_weight: int, v_weight: int, out_weight: int, out: int,
+                    batch: int, seq: int, input_dtype: int, weight_dtype: int, out_dtype: int, workspace: int,
+                    workspace_bytes: int, stream: int, mask: Optional[int] = None,
+                    mask_stride: Sequence[int] = (0, 0, 0, 0)) -> None:
+        """Fused projections + attention + output projection ([batch, seq, heads*head_dim] in and out)."""
+        a = MhaArgs()
+        a.input, a.q_weight, a.k_weight, a.v_weight, a.out_weight, a.out = input, q_weight, k_weight, v_weight, out_weight, out
+        a.mask = mask
+        a.mask_stride = (ctypes.c_int64 * 4)(*mask_stride)
+        a.batch, a.seq = batch, seq
+        a.input_dtype, a.weight_dtype, a.out_dtype = input_dtype, weight_dtype, out_dtype
+        a.workspace, a.workspace_bytes = workspace, workspace_bytes
+        check(self._lib.aidn_mha_forward(self._h, ctypes.byref(a), ctypes.c_void_p(stream)))
 
     def poll(self, stream: int) -> None:
         check(self._lib.aidn_sdpa_poll(self._h, ctypes.c_void_p(stream)))

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|qkvrope|qkvrope1|qkvrope70b|qkvrope32] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|mha|mhaq|qkvrope|qkvrope1|qkvrope70b|qkvrope32] [--impl reference]
 
 One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
 default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
@@ -40,6 +40,9 @@ WORKLOADS = {
     # attention backward (deterministic; mma.sync kernels for 16-bit inputs) on a quarter of the C2 shape
     "c2bwd": dict(kind="bwd", B=1, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
                   name="llama_backward_B1_H32_S2048_D128_causal_bf16"),
+    # the in-library caller of the attention path: Q/K/V projections + attention + output projection in one call
+    "mha": dict(kind="mha", B=4, S=2048, heads=32, D=128, name="mha_forward_B4_S2048_dmodel4096_H32_bf16"),
+    "mhaq": dict(kind="mha", B=1, S=2048, heads=16, D=128, name="mha_forward_B1_S2048_dmodel2048_H16_bf16"),
     # the decode step in front of attention: packed Q/K/V projection of 8 resident tokens + RoPE + cache write
     "qkvrope": dict(kind="gemv", tokens=8, heads=32, kv_heads=8, D=128, weight="bf16", cache_rows=1 << 16,
                     name="qkv_rope_cache_T8_Hq32_Hkv8_D128_bf16_weights"),
@@ -300,6 +303,52 @@ def run_bwd(args, w, pk):
         "gpu_launches": 3 * args.steps}))
 
 
+def run_mha(args, w, pk):
+    """Times aidn_mha_forward with 16-bit input and weights resident in HBM (two projection GEMM launches around one
+    attention launch).  FLOP: 4 projections of 2*B*S*dm^2 plus the full (unmasked) attention 4*B*H*S^2*d."""
+    from aidotnet.tensors_b200 import native as N
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    B, S, H, D = w["B"], w["S"], w["heads"], w["D"]
+    dm = H * D
+    g = torch.Generator(device=dev).manual_seed(7)
+    x = (torch.randn((B, S, dm), device=dev, generator=g) * 0.5).to(torch.bfloat16)
+    ws = [(torch.randn((dm, dm), device=dev, generator=g) / dm ** 0.5).to(torch.bfloat16) for _ in range(4)]
+    out = torch.empty((B, S, dm), device=dev)
+    h = N.Handle(device=dev.index, qkv_dtype=N.BF16, out_dtype=N.BF16, head_dim=D, num_q_heads=H, num_kv_heads=H)
+    nb = h.mha_workspace_bytes(B, S, N.BF16, N.BF16)
+    wsb = torch.empty(nb + 1024, dtype=torch.uint8, device=dev)
+    base = (wsb.data_ptr() + 1023) // 1024 * 1024
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    step = lambda: h.mha_forward(input=x.data_ptr(), q_weight=ws[0].data_ptr(), k_weight=ws[1].data_ptr(),
+                                 v_weight=ws[2].data_ptr(), out_weight=ws[3].data_ptr(), out=out.data_ptr(), batch=B,
+                                 seq=S, input_dtype=N.BF16, weight_dtype=N.BF16, out_dtype=N.F32, workspace=base,
+                                 workspace_bytes=nb, stream=stream)
+    for _ in range(args.warmup):
+        step()
+    h.poll(stream)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    h.poll(stream)
+    per_step = e0.elapsed_time(e1) / 1e3 / args.steps
+    fl_proj = 4 * 2 * B * S * dm * dm
+    fl = fl_proj + 4 * B * H * S * S * D
+    tf = fl / 1e12 / per_step
+    print(json.dumps({
+        "metric": "multi-head attention forward TFLOP/s/GPU", "value": tf, "unit": "TFLOP/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": w["name"], "l2": "weights + activations of a step (%.0f MB) exceed the 126 MB L2"
+                   % ((4 * dm * dm * 2 + 5 * B * S * dm * 2 + B * S * dm * 4) / 1e6)},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16"], "unit": "TFLOP/s", "frac": tf / pk["bf16"],
+                     "traffic": None, "algorithmic": fl, "algorithmic_unit": "FLOP per step (3 launches)",
+                     "projection_share_of_flop": fl_proj / fl, "peak_source": pk["source"]},
+        "gpu_launches": 3 * args.steps}))
+
+
 class Runner:
     """One workload bound to one handle of the C ABI; `step()` enqueues one forward pass."""
 
@@ -506,6 +555,10 @@ def main():
     if w["kind"] == "bwd":
         if rank == 0:
             run_bwd(args, w, pk)
+        return
+    if w["kind"] == "mha":
+        if rank == 0:
+            run_mha(args, w, pk)
         return
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:

@@ -240,6 +240,39 @@ AIDN_API int aidn_rope_interleaved(const float* input, const float* cosine, cons
                                    int64_t rows, int32_t head_dim, int32_t seq_len, int32_t start_position,
                                    void* cu_stream);
 
+/* ---- fused multi-head attention forward ---------------------------------------------------------------------
+ * IEngine.MultiHeadAttentionForward (src/AiDotNet.Tensors/Engines/IEngine.cs:4201-4208; CPU
+ * CpuEngine.MultiHeadAttention.cs:68-338, GPU composition DirectGpuTensorEngine.MissingKernels.cs:5793-5870):
+ *   out = softmax((X Wq)(X Wk)^T / sqrt(d) [keep-mask]) (X Wv) Wout,   X [batch, seq, heads*d], each W [heads*d, heads*d]
+ * row-major and applied as x * W.  Three launches on the stream: one tcgen05 GEMM for the Q, K and V projections that
+ * writes [B, H, S, d] in 16 bits directly, the attention kernel of the handle, one tcgen05 GEMM for the output
+ * projection reading the attention output as [B, S, H*d].  fp32 inputs or weights are first rounded to the handle's
+ * 16-bit type inside the workspace (pass 16-bit weights, converted once with aidn_cast_*, to skip that per call).
+ * The handle gives heads, head_dim (64 or 128; heads*head_dim a multiple of 128) and the mask kind (none or a keep-mask
+ * broadcastable to [B, H, S, S]); it must have 16-bit qkv_dtype, out_dtype == qkv_dtype, num_kv_heads == num_q_heads,
+ * all heads, no log-sum-exp.  Other shapes: AIDN_EUNSUPPORTED (the caller keeps its decomposed route, as the
+ * reference's GPU engine does for its own unsupported cases, :5803-5815). */
+typedef struct {
+  const void* input;        /* [batch, seq, heads*head_dim], input_dtype                                         */
+  const void* q_weight;     /* [heads*head_dim, heads*head_dim], weight_dtype                                    */
+  const void* k_weight;
+  const void* v_weight;
+  const void* out_weight;
+  void* out;                /* [batch, seq, heads*head_dim], out_dtype                                           */
+  const void* mask;         /* per desc.mask_kind, or NULL                                                       */
+  int64_t mask_stride[4];   /* elements for (B, H, Sq, Sk); 0 = broadcast                                        */
+  int64_t batch, seq;
+  int32_t input_dtype;      /* AIDN_F32 or desc.qkv_dtype                                                        */
+  int32_t weight_dtype;     /* AIDN_F32 or desc.qkv_dtype                                                        */
+  int32_t out_dtype;        /* AIDN_F32 or desc.qkv_dtype                                                        */
+  int32_t reserved;
+  void* workspace;          /* device scratch of at least aidn_mha_workspace_bytes(), 1024-byte aligned          */
+  int64_t workspace_bytes;
+} aidn_mha_args;
+AIDN_API int64_t aidn_mha_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq, int32_t input_dtype,
+                                          int32_t weight_dtype);
+AIDN_API int aidn_mha_forward(aidn_sdpa_t h, const aidn_mha_args* args, void* cu_stream);
+
 /* dtype staging (IDirectGpuBackend.cs:1890 ConvertToFp16, :1911 ConvertToFp32; bf16 rounding per
  * NumericOperations/BFloat16.cs:65-84: round-to-nearest-even, NaN keeps its top payload bits plus the quiet bit). */
 AIDN_API int aidn_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* cu_stream);

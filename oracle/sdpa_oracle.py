@@ -311,3 +311,37 @@ def sdpa_backward(q, k, v, dout, *, scale: Optional[float] = None, causal: bool 
     dv = dv_full.reshape(B, Hkv, g, Sk, D).sum(axis=2)
     return (dq.astype(np.float32), dk.astype(np.float32), dv.astype(np.float32), o.astype(np.float32),
             lse.astype(np.float32))
+
+
+# ---- fused multi-head attention forward -----------------------------------------------------------------------------
+def mha_forward(x, wq, wk, wv, wo, num_heads: int, *, mask: Optional[np.ndarray] = None) -> np.ndarray:
+    """MultiHeadAttentionForward of the reference in float64
+    (src/AiDotNet.Tensors/Engines/CpuEngine.MultiHeadAttention.cs:155-338 float path, :350-510 the per-head
+    attention; contract src/AiDotNet.Tensors/Engines/IEngine.cs:4201-4208): ``x`` [B, S, Dm], each weight
+    [Dm, Dm] applied as ``x @ W``; Q/K/V split into ``num_heads`` heads of ``Dm / num_heads`` along the last
+    axis; scores scaled by ``1/sqrt(dHead)``; ``mask`` a boolean keep-mask broadcastable to [B, H, S, S] (false
+    = -inf before the softmax; a row with no visible key gives zeros, :481-485); heads concatenated as
+    [B, S, H*dHead] and multiplied by ``wo``."""
+    x, wq, wk, wv, wo = (np.asarray(a, np.float64) for a in (x, wq, wk, wv, wo))
+    B, S, Dm = x.shape
+    assert Dm % num_heads == 0
+    d = Dm // num_heads
+
+    def heads(t):   # [B, S, Dm] -> [B, H, S, d]
+        return t.reshape(B, S, num_heads, d).transpose(0, 2, 1, 3)
+
+    q, k, v = heads(x @ wq), heads(x @ wk), heads(x @ wv)
+    s = np.einsum("bhid,bhjd->bhij", q, k) / np.sqrt(d)
+    vis = np.ones((B, num_heads, S, S), bool)
+    if mask is not None:
+        m = np.asarray(mask)
+        assert m.ndim == 4
+        vis &= np.broadcast_to(m != 0, vis.shape)
+    s = np.where(vis, s, -np.inf)
+    mx = s.max(axis=-1, keepdims=True)
+    mx = np.where(np.isfinite(mx), mx, 0.0)
+    e = np.where(vis, np.exp(s - mx), 0.0)
+    l = e.sum(axis=-1, keepdims=True)
+    p = np.divide(e, l, out=np.zeros_like(e), where=l > 0)
+    o = np.einsum("bhij,bhjd->bhid", p, v).transpose(0, 2, 1, 3).reshape(B, S, Dm)
+    return (o @ wo).astype(np.float32)

@@ -30,18 +30,19 @@ def test_struct_layout_matches_header():
     import subprocess
     import tempfile
     from aidotnet.tensors_b200 import native
-    src = '#include "aidn_sdpa.h"\n#include <stdio.h>\nint main(){printf("%zu %zu %zu %zu %zu\\n", sizeof(aidn_sdpa_desc), sizeof(aidn_sdpa_args), sizeof(aidn_paged_kv), sizeof(aidn_qkv_rope_args), sizeof(aidn_sdpa_bwd_args));return 0;}\n'
+    src = '#include "aidn_sdpa.h"\n#include <stdio.h>\nint main(){printf("%zu %zu %zu %zu %zu %zu\\n", sizeof(aidn_sdpa_desc), sizeof(aidn_sdpa_args), sizeof(aidn_paged_kv), sizeof(aidn_qkv_rope_args), sizeof(aidn_sdpa_bwd_args), sizeof(aidn_mha_args));return 0;}\n'
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "t.c")
         open(c, "w").write(src)
         exe = os.path.join(d, "t")
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
-        a, b, c, d4, e5 = map(int, subprocess.check_output([exe]).split())
+        a, b, c, d4, e5, f6 = map(int, subprocess.check_output([exe]).split())
     assert ctypes.sizeof(native.SdpaDesc) == a
     assert ctypes.sizeof(native.SdpaArgs) == b
     assert ctypes.sizeof(native.PagedKv) == c
     assert ctypes.sizeof(native.QkvRopeArgs) == d4
     assert ctypes.sizeof(native.SdpaBwdArgs) == e5
+    assert ctypes.sizeof(native.MhaArgs) == f6
 
 
 def test_validation_without_gpu():

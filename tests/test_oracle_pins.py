@@ -279,3 +279,42 @@ def test_backward_oracle_against_finite_differences_of_the_forward(causal, gqa):
             args_m = {"q": (xm, k, v), "k": (q, xm, v), "v": (q, k, xm)}[name]
             fd = (loss(*args_p) - loss(*args_m)) / (2 * eps)
             assert abs(fd - grad[idx]) <= 2e-3 + 2e-3 * abs(fd), (name, idx, fd, grad[idx])
+
+
+@pytest.mark.parametrize("batch,seq,d_model,heads", [(3, 5, 12, 3), (2, 7, 24, 4), (1, 100, 32, 4), (4, 13, 48, 6),
+                                                      (5, 3, 8, 2), (2, 6, 6, 3), (3, 9, 30, 5), (1, 1, 16, 4)])
+@pytest.mark.parametrize("masked", ["none", "causal", "broadcast"])
+def test_mha_forward_matches_the_decomposed_chain(batch, seq, d_model, heads, masked):
+    """Engines/MultiHeadAttentionForwardTests.cs:101-124, 126-162, 164-203, 288-313 — the fused call equals the chain
+    Q/K/V MatMul -> split heads -> ScaledDotProductAttention -> merge heads -> output MatMul (1e-4 there), with no
+    mask, a causal keep-mask and a [1,1,S,S] mask broadcast over batch and heads; same shapes as the reference's
+    theory.  The chain is rebuilt here on the pinned attention oracle."""
+    rng = np.random.default_rng(batch * 1000 + seq * 10 + heads)
+    x = rng.standard_normal((batch, seq, d_model)).astype(np.float32)
+    ws = [(rng.standard_normal((d_model, d_model)) / np.sqrt(d_model)).astype(np.float32) for _ in range(4)]
+    mask = None
+    if masked == "causal":
+        mask = np.broadcast_to(np.tril(np.ones((seq, seq), bool)), (batch, heads, seq, seq)).copy()
+    elif masked == "broadcast":
+        mask = np.tril(np.ones((seq, seq), bool))[None, None]
+    fused = O.mha_forward(x, *ws, heads, mask=mask)
+    d = d_model // heads
+    split = lambda t: np.ascontiguousarray(t.reshape(batch, seq, heads, d).transpose(0, 2, 1, 3))
+    q, k, v = (split(x @ w) for w in ws[:3])
+    attn = O.sdpa(q, k, v, mask=mask, f64=True)
+    chain = attn.transpose(0, 2, 1, 3).reshape(batch, seq, d_model) @ ws[3]
+    assert fused.shape == (batch, seq, d_model)
+    assert np.abs(fused - chain).max() <= 1e-4
+    if masked == "causal" and seq > 1:
+        assert np.abs(fused - O.mha_forward(x, *ws, heads)).max() > 1e-4   # the mask changes the result (:154-161)
+
+
+def test_mha_forward_fully_masked_row_gives_zero_attention():
+    """CpuEngine.MultiHeadAttention.cs:481-485 — a query row with no visible key contributes zeros."""
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((1, 4, 8)).astype(np.float32)
+    ws = [rng.standard_normal((8, 8)).astype(np.float32) for _ in range(4)]
+    mask = np.ones((1, 1, 4, 4), bool)
+    mask[0, 0, 2, :] = False
+    out = O.mha_forward(x, *ws, 2, mask=mask)
+    assert np.all(out[0, 2] == 0) and np.abs(out[0, 1]).max() > 0
