@@ -366,6 +366,63 @@ class CudaBackend:
                    scale=float(scale))
         self.launch_count += h.last_launch_count
 
+    # -- the in-library caller of the attention path -------------------------------------------------------------
+    def MultiHeadAttentionForward(self, input: GpuBuffer, qWeight: GpuBuffer, kWeight: GpuBuffer, vWeight: GpuBuffer,
+                                  outWeight: GpuBuffer, output: GpuBuffer, batch: int, seq: int, dModel: int,
+                                  numHeads: int, mask: Optional[GpuBuffer] = None,
+                                  maskShape: Optional[Tuple[int, int, int, int]] = None) -> None:
+        """``IEngine.MultiHeadAttentionForward`` (``Engines/IEngine.cs:4201-4208``; checks as in
+        ``CpuEngine.MultiHeadAttention.cs:76-103``) on resident buffers: ``input`` [batch, seq, dModel], four
+        [dModel, dModel] weights applied as ``x @ W``, optional boolean keep-mask of shape ``maskShape`` broadcastable
+        to [batch, numHeads, seq, seq]; ``output`` [batch, seq, dModel].  fp32 buffers are rounded to bf16 on the way
+        in (16-bit buffers are used as they are) and the arithmetic runs on the tensor cores with fp32 accumulation.
+        Shapes the tensor-core route does not take raise ``AidnError`` with ``EUNSUPPORTED``: the caller then keeps the
+        decomposed chain, as the reference's GPU engine does (``DirectGpuTensorEngine.MissingKernels.cs:5803-5815``)."""
+        for name, buf in (("input", input), ("qWeight", qWeight), ("kWeight", kWeight), ("vWeight", vWeight),
+                          ("outWeight", outWeight), ("output", output)):
+            if buf is None:
+                raise ValueError(f"{name} must not be null")          # ArgumentNullException
+        if numHeads <= 0:
+            raise ValueError("numHeads must be positive.")            # ArgumentOutOfRangeException
+        if batch <= 0 or seq <= 0 or dModel <= 0:
+            raise ValueError("MultiHeadAttentionForward expects a non-empty [B, seq, dModel] input.")
+        if dModel % numHeads != 0:
+            raise ValueError(f"dModel ({dModel}) must be divisible by numHeads ({numHeads}).")
+        for name, w in (("qWeight", qWeight), ("kWeight", kWeight), ("vWeight", vWeight), ("outWeight", outWeight)):
+            if w.Size != dModel * dModel:
+                raise ValueError(f"{name} must be [{dModel}, {dModel}].")
+        if input.Size < batch * seq * dModel or output.Size < batch * seq * dModel:
+            raise ValueError("input / output buffers are smaller than [batch, seq, dModel].")
+        wdt = {w.dtype for w in (qWeight, kWeight, vWeight, outWeight)}
+        if len(wdt) != 1:
+            raise ValueError("the four weights must share one dtype")
+        sixteen = [b.dtype for b in (input, qWeight, output) if b.dtype != torch.float32]
+        if len(set(sixteen)) > 1:
+            raise ValueError("16-bit buffers must share one dtype")
+        compute = sixteen[0] if sixteen else torch.bfloat16
+        ms = (0, 0, 0, 0)
+        if mask is not None:
+            if maskShape is None or len(maskShape) != 4:
+                raise ValueError("maskShape must give the 4 mask dimensions")
+            full = (batch, numHeads, seq, seq)
+            dense = (maskShape[1] * maskShape[2] * maskShape[3], maskShape[2] * maskShape[3], maskShape[3], 1)
+            for ax in range(4):
+                if maskShape[ax] not in (1, full[ax]):
+                    raise ValueError("mask is not broadcastable to [batch, numHeads, seq, seq]")
+            ms = tuple(0 if (maskShape[ax] == 1 and full[ax] != 1) else dense[ax] for ax in range(4))
+        h = self._handle(qkv_dtype=_DTYPE[compute], out_dtype=_DTYPE[compute], head_dim=dModel // numHeads,
+                         num_q_heads=numHeads, num_kv_heads=numHeads,
+                         mask_kind=N.MASK_KEEP_U8 if mask is not None else N.MASK_NONE)
+        nbytes = h.mha_workspace_bytes(batch, seq, _DTYPE[input.dtype], _DTYPE[qWeight.dtype])
+        ws, ws_bytes = self._workspace(nbytes + 1024)
+        base = (ws + 1023) // 1024 * 1024
+        h.mha_forward(input=input.Handle, q_weight=qWeight.Handle, k_weight=kWeight.Handle, v_weight=vWeight.Handle,
+                      out_weight=outWeight.Handle, out=output.Handle, batch=batch, seq=seq,
+                      input_dtype=_DTYPE[input.dtype], weight_dtype=_DTYPE[qWeight.dtype],
+                      out_dtype=_DTYPE[output.dtype], workspace=base, workspace_bytes=ws_bytes - (base - ws),
+                      stream=self.stream.cuda_stream, mask=mask.Handle if mask is not None else None, mask_stride=ms)
+        self.launch_count += h.last_launch_count
+
     # -- the decode step in front of attention ----------------------------------------------------------------
     def QkvProjectionRoPECacheD64(self, input: GpuBuffer, packedWeights: GpuBuffer, bias: GpuBuffer, cosine: GpuBuffer,
                                   sine: GpuBuffer, query: GpuBuffer, keyCache: GpuBuffer, valueCache: GpuBuffer,

@@ -63,6 +63,21 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         public IntPtr dq, dk, dv;
     }
 
+    /// <summary>Arguments of aidn_mha_forward (IEngine.MultiHeadAttentionForward on resident buffers).</summary>
+    [StructLayout(LayoutKind.Sequential)]
+    internal unsafe struct AidnMhaArgs
+    {
+        public IntPtr input;                 // [batch, seq, heads*head_dim]
+        public IntPtr q_weight, k_weight, v_weight, out_weight;   // [dModel, dModel], y = x * W
+        public IntPtr @out;
+        public IntPtr mask;                  // Tensor<bool> bytes, or zero
+        public fixed long mask_stride[4];
+        public long batch, seq;
+        public int input_dtype, weight_dtype, out_dtype, reserved;
+        public IntPtr workspace;
+        public long workspace_bytes;
+    }
+
     /// <summary>Arguments of aidn_qkv_rope_cache (QkvProjectionRoPECacheD64 generalised, see include/aidn_sdpa.h).</summary>
     [StructLayout(LayoutKind.Sequential)]
     internal struct AidnQkvRopeArgs
@@ -93,6 +108,8 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         [DllImport(Lib)] public static extern int aidn_paged_kv_append(IntPtr newKeys, IntPtr newValues, IntPtr keyPool, IntPtr valuePool, IntPtr blockTable, long startPosition, long tokens, int blockSize, int numBlocks, long rowBytes, IntPtr cuStream);
         [DllImport(Lib)] public static extern long aidn_sdpa_backward_workspace_bytes(IntPtr handle, long batch, long seqQ);
         [DllImport(Lib)] public static extern int aidn_sdpa_backward(IntPtr handle, ref AidnSdpaBwdArgs args, IntPtr cuStream);
+        [DllImport(Lib)] public static extern long aidn_mha_workspace_bytes(IntPtr handle, long batch, long seq, int inputDtype, int weightDtype);
+        [DllImport(Lib)] public static extern int aidn_mha_forward(IntPtr handle, ref AidnMhaArgs args, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_qkv_rope_cache(ref AidnQkvRopeArgs args, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_rope_interleaved(IntPtr input, IntPtr cosine, IntPtr sine, IntPtr output, long rows, int headDim, int seqLen, int startPosition, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_sdpa_poll(IntPtr handle, IntPtr cuStream);

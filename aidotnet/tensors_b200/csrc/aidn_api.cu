@@ -714,7 +714,7 @@ int aidn_mha_forward(aidn_sdpa_t h, const aidn_mha_args* a, void* cu_stream) {
   if (!a->workspace || a->workspace_bytes < pl.total)
     return fail(AIDN_EWORKSPACE, "mha: workspace of %lld bytes, need %lld", (long long)(a->workspace ? a->workspace_bytes : 0),
                 (long long)pl.total);
-  if ((uintptr_t)a->workspace % 1024 != 0) return fail(AIDN_EINVAL, "mha: workspace must be 1024-byte aligned");
+  if ((uintptr_t)a->workspace % 256 != 0) return fail(AIDN_EINVAL, "mha: workspace must be 256-byte aligned");
   cudaStream_t stream = (cudaStream_t)cu_stream;
   char* ws = static_cast<char*>(a->workspace);
   const int64_t H = d.num_q_heads, D = d.head_dim, dm = H * D, S = a->seq, B = a->batch;

@@ -319,6 +319,73 @@ void CudaBackend::FlashAttentionBackward(const GpuBuffer& gradOutput, const GpuB
   launch_count_ += aidn_sdpa_last_launch_count(h);
 }
 
+// ---- the in-library caller of attention ----------------------------------------------------------------------------
+void CudaBackend::MultiHeadAttentionForward(const GpuBuffer& input, const GpuBuffer& qWeight, const GpuBuffer& kWeight,
+                                            const GpuBuffer& vWeight, const GpuBuffer& outWeight, const GpuBuffer& output,
+                                            int batch, int seq, int dModel, int numHeads, const GpuBuffer* mask,
+                                            const int* maskShape) {
+  if (!input.Handle || !qWeight.Handle || !kWeight.Handle || !vWeight.Handle || !outWeight.Handle || !output.Handle)
+    throw std::invalid_argument("MultiHeadAttentionForward: null buffer");
+  if (numHeads <= 0) throw std::invalid_argument("numHeads must be positive.");
+  if (batch <= 0 || seq <= 0 || dModel <= 0)
+    throw std::invalid_argument("MultiHeadAttentionForward expects a non-empty [B, seq, dModel] input.");
+  if (dModel % numHeads != 0) throw std::invalid_argument("dModel must be divisible by numHeads.");
+  const int64_t wsz = (int64_t)dModel * dModel, asz = (int64_t)batch * seq * dModel;
+  if (qWeight.Size != wsz || kWeight.Size != wsz || vWeight.Size != wsz || outWeight.Size != wsz)
+    throw std::invalid_argument("the projection weights must be [dModel, dModel].");
+  if (input.Size < asz || output.Size < asz)
+    throw std::invalid_argument("input / output buffers are smaller than [batch, seq, dModel].");
+  if (kWeight.Dtype != qWeight.Dtype || vWeight.Dtype != qWeight.Dtype || outWeight.Dtype != qWeight.Dtype)
+    throw std::invalid_argument("the four weights must share one dtype");
+  aidn_dtype compute = AIDN_BF16;
+  for (const GpuBuffer* b : {&input, &qWeight, &output})
+    if (b->Dtype != AIDN_F32) compute = b->Dtype;
+  for (const GpuBuffer* b : {&input, &qWeight, &output})
+    if (b->Dtype != AIDN_F32 && b->Dtype != compute) throw std::invalid_argument("16-bit buffers must share one dtype");
+  aidn_sdpa_desc d;
+  std::memset(&d, 0, sizeof(d));
+  d.device = device_;
+  d.qkv_dtype = compute;
+  d.out_dtype = compute;
+  d.head_dim = dModel / numHeads;
+  d.num_q_heads = numHeads;
+  d.num_kv_heads = numHeads;
+  d.mask_kind = mask ? AIDN_MASK_KEEP_U8 : AIDN_MASK_NONE;
+  aidn_mha_args a;
+  std::memset(&a, 0, sizeof(a));
+  if (mask) {
+    if (!maskShape) throw std::invalid_argument("maskShape must give the 4 mask dimensions");
+    const int full[4] = {batch, numHeads, seq, seq};
+    const int64_t dense[4] = {(int64_t)maskShape[1] * maskShape[2] * maskShape[3], (int64_t)maskShape[2] * maskShape[3],
+                              maskShape[3], 1};
+    for (int ax = 0; ax < 4; ++ax) {
+      if (maskShape[ax] != 1 && maskShape[ax] != full[ax])
+        throw std::invalid_argument("mask is not broadcastable to [batch, numHeads, seq, seq]");
+      a.mask_stride[ax] = (maskShape[ax] == 1 && full[ax] != 1) ? 0 : dense[ax];
+    }
+    a.mask = mask->Handle;
+  }
+  aidn_sdpa_t h = Handle(d);
+  const int64_t need = aidn_mha_workspace_bytes(h, batch, seq, input.Dtype, qWeight.Dtype);
+  if (need < 0) Check(AIDN_EUNSUPPORTED, "aidn_mha_workspace_bytes");
+  if (need > workspace_bytes_) {
+    if (workspace_) cudaFree(workspace_);
+    workspace_ = nullptr;
+    workspace_bytes_ = 0;
+    if (cudaMalloc(&workspace_, (size_t)need) != cudaSuccess) throw std::runtime_error("CudaBackend: out of device memory");
+    workspace_bytes_ = need;
+  }
+  a.input = input.Handle;
+  a.q_weight = qWeight.Handle; a.k_weight = kWeight.Handle; a.v_weight = vWeight.Handle; a.out_weight = outWeight.Handle;
+  a.out = output.Handle;
+  a.batch = batch; a.seq = seq;
+  a.input_dtype = input.Dtype; a.weight_dtype = qWeight.Dtype; a.out_dtype = output.Dtype;
+  a.workspace = workspace_;            // cudaMalloc memory is at least 256-byte aligned, which is what the call asks for
+  a.workspace_bytes = workspace_bytes_;
+  Check(aidn_mha_forward(h, &a, stream_), "aidn_mha_forward");
+  launch_count_ += aidn_sdpa_last_launch_count(h);
+}
+
 // ---- the decode step in front of attention -----------------------------------------------------------------------
 void CudaBackend::QkvProjectionRoPECacheD64(const GpuBuffer& input, const GpuBuffer& packedWeights, const GpuBuffer& bias,
                                             const GpuBuffer& cosine, const GpuBuffer& sine, const GpuBuffer& query,

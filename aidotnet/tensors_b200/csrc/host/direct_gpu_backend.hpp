@@ -7,7 +7,7 @@
 //   FlashAttentionV2           CudaBackend.cs:8540-8578     GroupedQueryAttention CudaBackend.cs:8721-8759
 //   FlashDecode                CudaBackend.cs:2968-3021     PagedAttention{Decode,Prefill}{,Gqa} CudaBackend.cs:2845-2966
 //   QkvProjectionRoPECacheD64  CudaBackend.cs:8389-8439     RopeInterleaved       CudaBackend.cs:8441-8470
-//   FlashAttentionBackward     CudaBackend.cs:8580-8604
+//   FlashAttentionBackward     CudaBackend.cs:8580-8604     MultiHeadAttentionForward  Engines/IEngine.cs:4201-4208
 //
 // ArgumentException / ArgumentOutOfRangeException map to std::invalid_argument, InvalidOperationException to
 // std::runtime_error.  There is no CPU fallback: a failing call throws.
@@ -86,6 +86,15 @@ class CudaBackend {
                                  int position);
   void RopeInterleaved(const GpuBuffer& input, const GpuBuffer& cos, const GpuBuffer& sin, const GpuBuffer& output,
                        int rows, int headDim, int seqLen, int startPosition);
+
+  // The in-library caller of attention (IEngine.cs:4201-4208; checks of CpuEngine.MultiHeadAttention.cs:76-103):
+  // input / output [batch, seq, dModel], four [dModel, dModel] weights applied as x * W, optional boolean keep-mask
+  // whose four dimensions `maskShape` broadcast to [batch, numHeads, seq, seq].  fp32 buffers are rounded to bf16 on
+  // the way in.  Shapes outside the tensor-core route throw std::runtime_error carrying AIDN_EUNSUPPORTED's message.
+  void MultiHeadAttentionForward(const GpuBuffer& input, const GpuBuffer& qWeight, const GpuBuffer& kWeight,
+                                 const GpuBuffer& vWeight, const GpuBuffer& outWeight, const GpuBuffer& output, int batch,
+                                 int seq, int dModel, int numHeads, const GpuBuffer* mask = nullptr,
+                                 const int* maskShape = nullptr);
 
   void Synchronize();
   int64_t LaunchCount() const { return launch_count_; }   // kernels enqueued (GpuLaunchProbe, CudaBackend.cs:5407)

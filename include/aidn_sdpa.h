@@ -266,7 +266,7 @@ typedef struct {
   int32_t weight_dtype;     /* AIDN_F32 or desc.qkv_dtype                                                        */
   int32_t out_dtype;        /* AIDN_F32 or desc.qkv_dtype                                                        */
   int32_t reserved;
-  void* workspace;          /* device scratch of at least aidn_mha_workspace_bytes(), 1024-byte aligned          */
+  void* workspace;          /* device scratch of at least aidn_mha_workspace_bytes(), 256-byte aligned           */
   int64_t workspace_bytes;
 } aidn_mha_args;
 AIDN_API int64_t aidn_mha_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq, int32_t input_dtype,

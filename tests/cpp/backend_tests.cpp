@@ -385,6 +385,68 @@ int main() {
     EXPECT(max_abs_diff(gq.download(), wq) <= 2e-5 && max_abs_diff(gk.download(), wk) <= 2e-5 && max_abs_diff(gv.download(), wv) <= 2e-5,
            "backward mismatch dq %g dk %g dv %g", max_abs_diff(gq.download(), wq), max_abs_diff(gk.download(), wk), max_abs_diff(gv.download(), wv));
   }
+  {  // MultiHeadAttentionForward: fp32 tensors in and out (the engine's contract), a causal [1,1,S,S] keep-mask; the
+     // scalar reference in double runs on the bf16-rounded operands (the call rounds fp32 operands to bf16)
+    std::printf("multi-head attention forward\n");
+    const int B = 2, S = 40, H = 2, Dh = 64, Dm = H * Dh;
+    auto rounded = [](std::vector<float> v) { for (auto& f : v) f = __bfloat162float(__float2bfloat16_rn(f)); return v; };
+    auto x = rounded(uniform(B * S * Dm, 91));
+    std::vector<float> w[4];
+    for (int i = 0; i < 4; ++i) { w[i] = uniform(Dm * Dm, 92 + i); for (auto& f : w[i]) f *= 0.1f; w[i] = rounded(w[i]); }
+    std::vector<unsigned char> keep((size_t)S * S);
+    for (int i = 0; i < S; ++i) for (int j = 0; j < S; ++j) keep[(size_t)i * S + j] = j <= i ? 1 : 0;
+    GpuBuffer mask;
+    mask.Size = (int64_t)keep.size();
+    cudaMalloc(&mask.Handle, keep.size());
+    cudaMemcpy(mask.Handle, keep.data(), keep.size(), cudaMemcpyHostToDevice);
+    DeviceArray dx(x), dwq(w[0]), dwk(w[1]), dwv(w[2]), dwo(w[3]), dout((int64_t)B * S * Dm);
+    const int mshape[4] = {1, 1, S, S};
+    const int64_t before = backend.LaunchCount();
+    backend.MultiHeadAttentionForward(dx.buf, dwq.buf, dwk.buf, dwv.buf, dwo.buf, dout.buf, B, S, Dm, H, &mask, mshape);
+    backend.Synchronize();
+    EXPECT(backend.LaunchCount() - before == 8, "expected 5 casts + 3 kernels, got %lld launches", (long long)(backend.LaunchCount() - before));
+    auto proj = [&](const std::vector<double>& a, const std::vector<float>& wm) {
+      std::vector<double> y((size_t)B * S * Dm, 0.0);
+      for (int r = 0; r < B * S; ++r)
+        for (int kk = 0; kk < Dm; ++kk) {
+          const double av = a[(size_t)r * Dm + kk];
+          for (int n = 0; n < Dm; ++n) y[(size_t)r * Dm + n] += av * wm[(size_t)kk * Dm + n];
+        }
+      return y;
+    };
+    std::vector<double> xd(x.begin(), x.end());
+    auto qd = proj(xd, w[0]), kd = proj(xd, w[1]), vd = proj(xd, w[2]);
+    std::vector<double> att((size_t)B * S * Dm, 0.0);
+    for (int b = 0; b < B; ++b)
+      for (int h = 0; h < H; ++h)
+        for (int i = 0; i < S; ++i) {
+          std::vector<double> p(S, 0.0);
+          double mx = -1e300, sum = 0;
+          for (int j = 0; j <= i; ++j) {
+            double dot = 0;
+            for (int d = 0; d < Dh; ++d) dot += qd[((size_t)b * S + i) * Dm + h * Dh + d] * kd[((size_t)b * S + j) * Dm + h * Dh + d];
+            p[j] = dot / std::sqrt((double)Dh); mx = std::max(mx, p[j]);
+          }
+          for (int j = 0; j <= i; ++j) { p[j] = std::exp(p[j] - mx); sum += p[j]; }
+          for (int j = 0; j <= i; ++j)
+            for (int d = 0; d < Dh; ++d) att[((size_t)b * S + i) * Dm + h * Dh + d] += p[j] / sum * vd[((size_t)b * S + j) * Dm + h * Dh + d];
+        }
+    auto want = proj(att, w[3]);
+    double mag = 0;
+    for (double t : want) mag = std::max(mag, std::fabs(t));
+    const double err = max_abs_diff(dout.download(), want);
+    EXPECT(err <= 2e-2 * mag, "mha forward: max error %g against magnitude %g", err, mag);
+    bool threw = false;
+    try { backend.MultiHeadAttentionForward(dx.buf, dwq.buf, dwk.buf, dwv.buf, dwo.buf, dout.buf, B, S, Dm, 3); } catch (const std::invalid_argument&) { threw = true; }
+    EXPECT(threw, "dModel %% numHeads != 0 must throw");
+    threw = false;
+    try { backend.MultiHeadAttentionForward(dx.buf, dwq.buf, dwk.buf, dwv.buf, dwo.buf, dout.buf, B, S, Dm, 0); } catch (const std::invalid_argument&) { threw = true; }
+    EXPECT(threw, "numHeads = 0 must throw");
+    threw = false;
+    try { backend.MultiHeadAttentionForward(dx.buf, dwq.buf, dwk.buf, dwv.buf, dwo.buf, dout.buf, B, S, Dm, 8); } catch (const std::runtime_error&) { threw = true; }
+    EXPECT(threw, "head_dim 16 is not a tensor-core shape: the call must refuse, not fall back");
+    cudaFree(mask.Handle);
+  }
   {  // argument errors throw, as ArgumentOutOfRangeException / ArgumentException do in the reference
     std::printf("argument errors\n");
     std::vector<float> z(64, 0.f);

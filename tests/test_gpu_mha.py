@@ -199,3 +199,43 @@ def test_mha_forward_rejections():
             assert ei.value.status == status, kw
         call(h)   # the same arguments without the fault go through
         h.poll(stream)
+
+
+def test_backend_mirror_fp32_tensors_and_mask():
+    """The engine-level call as the reference makes it: fp32 tensors, a [1,1,S,S] boolean mask
+    (MultiHeadAttentionForwardTests.cs:164-203), through the host mirror of the interface."""
+    from aidotnet.tensors_b200.backend import CudaBackend, GpuBuffer
+    B, S, heads, d = 2, 96, 2, 64
+    Dm = heads * d
+    x, xf, ws, wfs = _inputs(B, S, heads, d, "f32", 4700)
+    m = np.tril(np.ones((S, S), bool))[None, None].copy()
+    be = CudaBackend(0)
+    out = be.AllocateBuffer(B * S * Dm)
+    be.MultiHeadAttentionForward(GpuBuffer(x.view(-1)), *[GpuBuffer(w.view(-1)) for w in ws], out, B, S, Dm, heads,
+                                 mask=GpuBuffer(torch.from_numpy(m.astype(np.uint8)).cuda().view(-1)), maskShape=m.shape)
+    be.Synchronize()
+    want = O.mha_forward(_round(xf, "bf16"), *[_round(w, "bf16") for w in wfs], heads, mask=m)
+    _check(out.tensor.view(B, S, Dm), want, "backend mirror")
+    assert be.launch_count == 8   # input cast, 4 weight casts, projections, attention, output projection
+    be.Dispose()
+
+
+def test_backend_mirror_rejects_bad_shapes():
+    """MultiHeadAttentionForwardTests.cs:205-235 — wrong weight shape, dModel not divisible by numHeads, numHeads <= 0."""
+    from aidotnet.tensors_b200.backend import CudaBackend
+    be = CudaBackend(0)
+    B, S, Dm = 1, 8, 128
+    x, out, w = be.AllocateBuffer(B * S * Dm), be.AllocateBuffer(B * S * Dm), be.AllocateBuffer(Dm * Dm)
+    bad = be.AllocateBuffer(Dm * (Dm + 1))
+    with pytest.raises(ValueError):
+        be.MultiHeadAttentionForward(x, bad, w, w, w, out, B, S, Dm, 2)
+    with pytest.raises(ValueError):
+        be.MultiHeadAttentionForward(x, w, w, w, w, out, B, S, Dm, 3)
+    with pytest.raises(ValueError):
+        be.MultiHeadAttentionForward(x, w, w, w, w, out, B, S, Dm, 0)
+    with pytest.raises(ValueError):
+        be.MultiHeadAttentionForward(x, w, w, w, None, out, B, S, Dm, 2)
+    with pytest.raises(N.AidnError) as ei:   # head_dim 16: not a tensor-core shape, the caller keeps its chain
+        be.MultiHeadAttentionForward(x, w, w, w, w, out, B, S, Dm, 8)
+    assert ei.value.status == N.EUNSUPPORTED
+    be.Dispose()
