@@ -659,11 +659,12 @@ struct MhaPlan {
 };
 MhaPlan mha_plan(const aidn_sdpa* h, int64_t batch, int64_t seq, int input_dtype, int weight_dtype) {
   const int64_t dm = (int64_t)h->d.num_q_heads * h->d.head_dim;
-  const int64_t act = align_up(batch * seq * dm * 2, 1024), wgt = align_up(dm * dm * 2, 1024);
+  const int64_t esz = (int64_t)elem_size(h->d.qkv_dtype);
+  const int64_t act = align_up(batch * seq * dm * esz, 1024), wgt = align_up(dm * dm * esz, 1024);
   MhaPlan pl;
   int64_t off = 0;
-  pl.off_x = off; off += input_dtype == AIDN_F32 ? act : 0;
-  pl.off_w = off; off += weight_dtype == AIDN_F32 ? 4 * wgt : 0;
+  pl.off_x = off; off += input_dtype != h->d.qkv_dtype ? act : 0;
+  pl.off_w = off; off += weight_dtype != h->d.qkv_dtype ? 4 * wgt : 0;
   pl.off_q = off; off += act;
   pl.off_k = off; off += act;
   pl.off_v = off; off += act;
@@ -673,13 +674,10 @@ MhaPlan mha_plan(const aidn_sdpa* h, int64_t batch, int64_t seq, int input_dtype
 }
 int mha_check_handle(const aidn_sdpa* h) {
   const aidn_sdpa_desc& d = h->d;
-  if (d.qkv_dtype == AIDN_F32 || d.out_dtype != d.qkv_dtype)
-    return fail(AIDN_EUNSUPPORTED, "mha: the handle must have a 16-bit qkv_dtype and out_dtype == qkv_dtype");
+  if (d.out_dtype != d.qkv_dtype)
+    return fail(AIDN_EUNSUPPORTED, "mha: the handle must have out_dtype == qkv_dtype (the attention output feeds a projection)");
   if (d.num_kv_heads != d.num_q_heads || h->head_count != d.num_q_heads)
     return fail(AIDN_EUNSUPPORTED, "mha: the handle must cover all heads with num_kv_heads == num_q_heads");
-  if (d.head_dim != 64 && d.head_dim != 128) return fail(AIDN_EUNSUPPORTED, "mha: head_dim must be 64 or 128");
-  if (((int64_t)d.num_q_heads * d.head_dim) % 128 != 0)
-    return fail(AIDN_EUNSUPPORTED, "mha: heads * head_dim must be a multiple of 128");
   if (d.emit_lse || d.softcap > 0.f || d.nccl_comm)
     return fail(AIDN_EUNSUPPORTED, "mha: the handle must not ask for log-sum-exp, softcap or a gather");
   if (d.mask_kind == AIDN_MASK_ADD_F32) return fail(AIDN_EUNSUPPORTED, "mha: the mask is a keep-mask (Tensor<bool>) or absent");
@@ -719,19 +717,22 @@ int aidn_mha_forward(aidn_sdpa_t h, const aidn_mha_args* a, void* cu_stream) {
   char* ws = static_cast<char*>(a->workspace);
   const int64_t H = d.num_q_heads, D = d.head_dim, dm = H * D, S = a->seq, B = a->batch;
   const int cast_kind = d.qkv_dtype == AIDN_BF16 ? 0 : 1;
+  const int64_t esz = (int64_t)elem_size(d.qkv_dtype);
+  // tcgen05 GEMMs for 16-bit arithmetic on head sizes 64 / 128; the fp32 FFMA GEMM for everything else
+  const bool tensor_route = d.qkv_dtype != AIDN_F32 && (D == 64 || D == 128) && dm % 128 == 0 && d.path != AIDN_PATH_GENERIC;
   int launches = 0;
   cudaError_t e = cudaSuccess;
 
   const void* x = a->input;
-  if (a->input_dtype == AIDN_F32) {
+  if (a->input_dtype != d.qkv_dtype) {
     e = aidn::launch_cast(cast_kind, a->input, ws + pl.off_x, B * S * dm, stream);
     if (e != cudaSuccess) return fail_cuda(e, "mha: input cast");
     x = ws + pl.off_x;
     ++launches;
   }
   const void* w[4] = {a->q_weight, a->k_weight, a->v_weight, a->out_weight};
-  if (a->weight_dtype == AIDN_F32) {
-    const int64_t wgt = align_up(dm * dm * 2, 1024);
+  if (a->weight_dtype != d.qkv_dtype) {
+    const int64_t wgt = align_up(dm * dm * esz, 1024);
     for (int i = 0; i < 4; ++i) {
       void* dst = ws + pl.off_w + i * wgt;
       e = aidn::launch_cast(cast_kind, w[i], dst, dm * dm, stream);
@@ -753,10 +754,20 @@ int aidn_mha_forward(aidn_sdpa_t h, const aidn_mha_args* a, void* cu_stream) {
   for (int i = 0; i < 3; ++i) g.w[i] = w[i];
   g.c[0] = ws + pl.off_q; g.c[1] = ws + pl.off_k; g.c[2] = ws + pl.off_v;
   g.c_stride[0] = H * S * D; g.c_stride[1] = S * D; g.c_stride[2] = D;    // [B, H, S, d]
-  if (!aidn::proj_gemm_sm100_supported(g, &why)) return fail(AIDN_EUNSUPPORTED, "mha: %s", why);
-  e = aidn::launch_proj_gemm_sm100(g, stream, h->num_sms, h->status_dev, &why);
-  if (e != cudaSuccess) return why[0] ? fail(AIDN_ECUDA, "mha: %s (%s)", why, cudaGetErrorName(e)) : fail_cuda(e, "mha: QKV projection");
-  ++launches;
+  auto gemm = [&](const char* what) -> int {
+    if (tensor_route) {
+      if (!aidn::proj_gemm_sm100_supported(g, &why)) return fail(AIDN_EUNSUPPORTED, "mha: %s", why);
+      e = aidn::launch_proj_gemm_sm100(g, stream, h->num_sms, h->status_dev, &why);
+    } else {
+      if (!aidn::proj_gemm_generic_supported(g, &why)) return fail(AIDN_EUNSUPPORTED, "mha: %s", why);
+      e = aidn::launch_proj_gemm_generic(g, d.qkv_dtype, stream);
+    }
+    if (e != cudaSuccess) return why[0] ? fail(AIDN_ECUDA, "mha: %s (%s)", why, cudaGetErrorName(e)) : fail_cuda(e, what);
+    ++launches;
+    return AIDN_OK;
+  };
+  rc = gemm("mha: QKV projection");
+  if (rc != AIDN_OK) return rc;
 
   aidn_sdpa_args sa;
   std::memset(&sa, 0, sizeof(sa));
@@ -776,10 +787,8 @@ int aidn_mha_forward(aidn_sdpa_t h, const aidn_mha_args* a, void* cu_stream) {
   g.c[0] = a->out;
   g.out_f32 = a->out_dtype == AIDN_F32;
   g.c_stride[0] = S * dm; g.c_stride[1] = D; g.c_stride[2] = dm;
-  if (!aidn::proj_gemm_sm100_supported(g, &why)) return fail(AIDN_EUNSUPPORTED, "mha: %s", why);
-  e = aidn::launch_proj_gemm_sm100(g, stream, h->num_sms, h->status_dev, &why);
-  if (e != cudaSuccess) return why[0] ? fail(AIDN_ECUDA, "mha: %s (%s)", why, cudaGetErrorName(e)) : fail_cuda(e, "mha: output projection");
-  ++launches;
+  rc = gemm("mha: output projection");
+  if (rc != AIDN_OK) return rc;
   h->last_launches = launches;
   return AIDN_OK;
 }

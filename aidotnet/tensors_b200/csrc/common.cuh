@@ -222,8 +222,8 @@ cudaError_t prefill_sm100_prepare();  // one-time per-process function attribute
 // c[i][b, s, n] = sum_k a[b, s, k] * w[i][k, n] for up to three weight matrices that share a; column n lands at
 // c[i] + b*c_stride[0] + (n / head_dim)*c_stride[1] + s*c_stride[2] + n % head_dim.
 struct ProjGemm {
-  const void* a;        // [batch, seq, k] dense, 16-bit
-  const void* w[3];     // [k, n] row-major, 16-bit
+  const void* a;        // [batch, seq, k] dense; 16-bit for the tcgen05 kernel
+  const void* w[3];     // [k, n] row-major, same type as a
   void* c[3];
   int64_t c_stride[3];  // elements for (batch, head, sequence position)
   int64_t batch, seq, k, n;
@@ -235,5 +235,8 @@ struct ProjGemm {
 bool proj_gemm_sm100_supported(const ProjGemm& g, const char** why);
 cudaError_t launch_proj_gemm_sm100(const ProjGemm& g, cudaStream_t stream, int num_sms, int32_t* status,
                                    const char** why);
+// The same contract in fp32 FFMA arithmetic for any sizes and for a / w of `dtype` (csrc/proj_gemm_generic.cu).
+bool proj_gemm_generic_supported(const ProjGemm& g, const char** why);
+cudaError_t launch_proj_gemm_generic(const ProjGemm& g, int dtype, cudaStream_t stream);
 
 }  // namespace aidn

@@ -323,7 +323,7 @@ void CudaBackend::FlashAttentionBackward(const GpuBuffer& gradOutput, const GpuB
 void CudaBackend::MultiHeadAttentionForward(const GpuBuffer& input, const GpuBuffer& qWeight, const GpuBuffer& kWeight,
                                             const GpuBuffer& vWeight, const GpuBuffer& outWeight, const GpuBuffer& output,
                                             int batch, int seq, int dModel, int numHeads, const GpuBuffer* mask,
-                                            const int* maskShape) {
+                                            const int* maskShape, bool exact) {
   if (!input.Handle || !qWeight.Handle || !kWeight.Handle || !vWeight.Handle || !outWeight.Handle || !output.Handle)
     throw std::invalid_argument("MultiHeadAttentionForward: null buffer");
   if (numHeads <= 0) throw std::invalid_argument("numHeads must be positive.");
@@ -337,7 +337,9 @@ void CudaBackend::MultiHeadAttentionForward(const GpuBuffer& input, const GpuBuf
     throw std::invalid_argument("input / output buffers are smaller than [batch, seq, dModel].");
   if (kWeight.Dtype != qWeight.Dtype || vWeight.Dtype != qWeight.Dtype || outWeight.Dtype != qWeight.Dtype)
     throw std::invalid_argument("the four weights must share one dtype");
-  aidn_dtype compute = AIDN_BF16;
+  const int head = dModel / numHeads;
+  const bool tensor_shape = (head == 64 || head == 128) && dModel % 128 == 0;
+  aidn_dtype compute = (tensor_shape && !exact) ? AIDN_BF16 : AIDN_F32;
   for (const GpuBuffer* b : {&input, &qWeight, &output})
     if (b->Dtype != AIDN_F32) compute = b->Dtype;
   for (const GpuBuffer* b : {&input, &qWeight, &output})

@@ -89,12 +89,13 @@ class CudaBackend {
 
   // The in-library caller of attention (IEngine.cs:4201-4208; checks of CpuEngine.MultiHeadAttention.cs:76-103):
   // input / output [batch, seq, dModel], four [dModel, dModel] weights applied as x * W, optional boolean keep-mask
-  // whose four dimensions `maskShape` broadcast to [batch, numHeads, seq, seq].  fp32 buffers are rounded to bf16 on
-  // the way in.  Shapes outside the tensor-core route throw std::runtime_error carrying AIDN_EUNSUPPORTED's message.
+  // whose four dimensions `maskShape` broadcast to [batch, numHeads, seq, seq].  With head sizes 64 / 128 (dModel a
+  // multiple of 128) fp32 buffers are rounded to bf16 on the way in and the tensor cores do the arithmetic; any other
+  // shape, or exact == true with all-fp32 buffers, runs the fp32 route (the 1e-4 bound of the reference's tests).
   void MultiHeadAttentionForward(const GpuBuffer& input, const GpuBuffer& qWeight, const GpuBuffer& kWeight,
                                  const GpuBuffer& vWeight, const GpuBuffer& outWeight, const GpuBuffer& output, int batch,
                                  int seq, int dModel, int numHeads, const GpuBuffer* mask = nullptr,
-                                 const int* maskShape = nullptr);
+                                 const int* maskShape = nullptr, bool exact = false);
 
   void Synchronize();
   int64_t LaunchCount() const { return launch_count_; }   // kernels enqueued (GpuLaunchProbe, CudaBackend.cs:5407)

@@ -244,14 +244,18 @@ AIDN_API int aidn_rope_interleaved(const float* input, const float* cosine, cons
  * IEngine.MultiHeadAttentionForward (src/AiDotNet.Tensors/Engines/IEngine.cs:4201-4208; CPU
  * CpuEngine.MultiHeadAttention.cs:68-338, GPU composition DirectGpuTensorEngine.MissingKernels.cs:5793-5870):
  *   out = softmax((X Wq)(X Wk)^T / sqrt(d) [keep-mask]) (X Wv) Wout,   X [batch, seq, heads*d], each W [heads*d, heads*d]
- * row-major and applied as x * W.  Three launches on the stream: one tcgen05 GEMM for the Q, K and V projections that
- * writes [B, H, S, d] in 16 bits directly, the attention kernel of the handle, one tcgen05 GEMM for the output
- * projection reading the attention output as [B, S, H*d].  fp32 inputs or weights are first rounded to the handle's
- * 16-bit type inside the workspace (pass 16-bit weights, converted once with aidn_cast_*, to skip that per call).
- * The handle gives heads, head_dim (64 or 128; heads*head_dim a multiple of 128) and the mask kind (none or a keep-mask
- * broadcastable to [B, H, S, S]); it must have 16-bit qkv_dtype, out_dtype == qkv_dtype, num_kv_heads == num_q_heads,
- * all heads, no log-sum-exp.  Other shapes: AIDN_EUNSUPPORTED (the caller keeps its decomposed route, as the
- * reference's GPU engine does for its own unsupported cases, :5803-5815). */
+ * row-major and applied as x * W.  Three launches on the stream: one GEMM for the Q, K and V projections that writes
+ * [B, H, S, d] directly, the attention kernel of the handle, one GEMM for the output projection reading the attention
+ * output as [B, S, H*d].  Two routes, chosen from the handle:
+ *   - 16-bit qkv_dtype, head_dim 64 or 128, heads*head_dim a multiple of 128: tcgen05 GEMMs and the tcgen05 attention
+ *     kernel, fp32 accumulation.  fp32 inputs or weights are first rounded to the 16-bit type inside the workspace
+ *     (pass 16-bit weights, converted once with aidn_cast_*, to skip that per call).
+ *   - anything else (fp32 qkv_dtype, other head sizes or widths, desc.path == AIDN_PATH_GENERIC): FFMA GEMMs and the
+ *     generic attention kernel in fp32 arithmetic; with an fp32 handle this meets the 1e-4 bound of the reference's own
+ *     tests of the fused call (tests/AiDotNet.Tensors.Tests/Engines/MultiHeadAttentionForwardTests.cs:123).
+ * The handle gives heads, head_dim and the mask kind (none or a keep-mask broadcastable to [B, H, S, S]; a fully masked
+ * row gives zeros, CpuEngine.MultiHeadAttention.cs:481-485); it must have out_dtype == qkv_dtype,
+ * num_kv_heads == num_q_heads, all heads, no log-sum-exp, softcap or additive bias (else AIDN_EUNSUPPORTED). */
 typedef struct {
   const void* input;        /* [batch, seq, heads*head_dim], input_dtype                                         */
   const void* q_weight;     /* [heads*head_dim, heads*head_dim], weight_dtype                                    */

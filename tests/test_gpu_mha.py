@@ -162,9 +162,9 @@ def test_mha_forward_is_bit_reproducible():
 
 
 def test_mha_forward_rejections():
-    """Shapes outside the tensor-core route answer AIDN_EUNSUPPORTED (the caller keeps its decomposed chain, as the
-    reference's GPU engine does, DirectGpuTensorEngine.MissingKernels.cs:5803-5815); a short workspace, a null tensor
-    or a foreign dtype are argument errors (MultiHeadAttentionForwardTests.cs:205-235 for the reference's own)."""
+    """Handles that do not describe this op (grouped-query heads, an output type other than the attention type, a
+    log-sum-exp, softcap or additive-bias request) answer AIDN_EUNSUPPORTED; a short workspace, a null tensor or a
+    foreign dtype are argument errors (MultiHeadAttentionForwardTests.cs:205-235 for the reference's own)."""
     stream = torch.cuda.current_stream().cuda_stream
     buf = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
     p = (buf.data_ptr() + 1023) // 1024 * 1024
@@ -176,20 +176,16 @@ def test_mha_forward_rejections():
         args.update(kw)
         h.mha_forward(**args)
 
-    for kw, status in ((dict(head_dim=32, num_q_heads=4, num_kv_heads=4), N.EUNSUPPORTED),       # head_dim
-                       (dict(head_dim=64, num_q_heads=3, num_kv_heads=3), N.EUNSUPPORTED),       # d_model % 128
-                       (dict(head_dim=64, num_q_heads=4, num_kv_heads=2), N.EUNSUPPORTED),       # grouped-query
+    for kw, status in ((dict(head_dim=64, num_q_heads=4, num_kv_heads=2), N.EUNSUPPORTED),       # grouped-query
                        (dict(head_dim=64, num_q_heads=4, num_kv_heads=4, out_dtype=N.F32), N.EUNSUPPORTED),
-                       (dict(head_dim=64, num_q_heads=4, num_kv_heads=4, emit_lse=True), N.EUNSUPPORTED)):
+                       (dict(head_dim=64, num_q_heads=4, num_kv_heads=4, emit_lse=True), N.EUNSUPPORTED),
+                       (dict(head_dim=64, num_q_heads=4, num_kv_heads=4, softcap=2.0), N.EUNSUPPORTED),
+                       (dict(head_dim=64, num_q_heads=4, num_kv_heads=4, mask_kind=N.MASK_ADD_F32), N.EUNSUPPORTED)):
         kw.setdefault("out_dtype", N.BF16)
         with N.Handle(device=0, qkv_dtype=N.BF16, **kw) as h:
             with pytest.raises(N.AidnError) as ei:
                 call(h)
             assert ei.value.status == status, kw
-    with N.Handle(device=0, qkv_dtype=N.F32, out_dtype=N.F32, head_dim=64, num_q_heads=4, num_kv_heads=4) as h:
-        with pytest.raises(N.AidnError) as ei:
-            call(h)
-        assert ei.value.status == N.EUNSUPPORTED
     with N.Handle(device=0, qkv_dtype=N.BF16, out_dtype=N.BF16, head_dim=64, num_q_heads=2, num_kv_heads=2) as h:
         for kw, status in ((dict(workspace_bytes=1024), N.EWORKSPACE), (dict(workspace=None), N.EWORKSPACE),
                            (dict(workspace=p + (1 << 19) + 16), N.EINVAL), (dict(input=None), N.EINVAL), (dict(batch=0), N.EINVAL),
@@ -235,7 +231,55 @@ def test_backend_mirror_rejects_bad_shapes():
         be.MultiHeadAttentionForward(x, w, w, w, w, out, B, S, Dm, 0)
     with pytest.raises(ValueError):
         be.MultiHeadAttentionForward(x, w, w, w, None, out, B, S, Dm, 2)
-    with pytest.raises(N.AidnError) as ei:   # head_dim 16: not a tensor-core shape, the caller keeps its chain
-        be.MultiHeadAttentionForward(x, w, w, w, w, out, B, S, Dm, 8)
-    assert ei.value.status == N.EUNSUPPORTED
+    be.Dispose()
+
+
+REFERENCE_SHAPES = [(3, 5, 12, 3), (2, 7, 24, 4), (1, 100, 32, 4), (4, 13, 48, 6), (5, 3, 8, 2), (2, 6, 6, 3), (3, 9, 30, 5)]
+
+
+@pytest.mark.parametrize("batch,seq,d_model,heads", REFERENCE_SHAPES + [(1, s, 32, 4) for s in (1, 2, 3, 5, 31, 128)]
+                         + [(2, 70, 256, 2), (1, 200, 192, 3)])
+@pytest.mark.parametrize("masked", [False, True])
+def test_mha_forward_exact_route_meets_the_reference_bound(batch, seq, d_model, heads, masked):
+    """fp32 tensors through an fp32 handle: the shapes of MultiHeadAttentionForwardTests.cs:288-313 (head sizes 2 to 8),
+    its any-length theory (:237-266) and its causal-mask theory (:315-344), at the reference's own bound of 1e-4
+    absolute; also head sizes 128 and 64 with a width that is not a multiple of 128."""
+    rng = np.random.default_rng(seq * 100 + d_model)
+    xf = rng.standard_normal((batch, seq, d_model)).astype(np.float32)
+    wfs = [(rng.standard_normal((d_model, d_model)) / np.sqrt(d_model)).astype(np.float32) for _ in range(4)]
+    x, ws = torch.from_numpy(xf).cuda(), [torch.from_numpy(w).cuda() for w in wfs]
+    m = np.tril(np.ones((seq, seq), bool))[None, None].copy() if masked else None
+    mask = torch.from_numpy(m.astype(np.uint8)).cuda() if masked else None
+    out, launches = _run(x, ws, heads, dtype="f32", mask=mask)
+    assert launches == 3
+    want = O.mha_forward(xf, *wfs, heads, mask=m)
+    err = np.abs(out.cpu().numpy() - want).max()
+    assert err <= 1e-4, f"max error {err:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+def test_mha_forward_16bit_odd_head_size(dtype):
+    """16-bit tensors with a head size the tensor-core GEMM does not take (32): FFMA GEMM + generic attention."""
+    B, S, heads, d = 2, 50, 4, 32
+    x, xf, ws, wfs = _inputs(B, S, heads, d, dtype, 4800)
+    out, _ = _run(x, ws, heads, dtype=dtype)
+    _check(out, O.mha_forward(xf, *wfs, heads), f"output head_dim 32 {dtype}")
+
+
+def test_backend_mirror_exact_switch_and_small_heads():
+    """fp32 buffers: head size 64 goes to the tensor cores unless exact=True; head size 16 always runs in fp32."""
+    from aidotnet.tensors_b200.backend import CudaBackend, GpuBuffer
+    B, S = 2, 33
+    be = CudaBackend(0)
+    for heads, d, exact, tol in ((2, 64, True, 1e-4), (8, 16, False, 1e-4), (2, 64, False, None)):
+        Dm = heads * d
+        x, xf, ws, wfs = _inputs(B, S, heads, d, "f32", 4900 + d)
+        out = be.AllocateBuffer(B * S * Dm)
+        be.MultiHeadAttentionForward(GpuBuffer(x.view(-1)), *[GpuBuffer(w.view(-1)) for w in ws], out, B, S, Dm, heads, exact=exact)
+        be.Synchronize()
+        got = out.tensor.view(B, S, Dm)
+        if tol is not None:
+            assert np.abs(got.cpu().numpy() - O.mha_forward(xf, *wfs, heads)).max() <= tol
+        else:
+            _check(got, O.mha_forward(_round(xf, "bf16"), *[_round(w, "bf16") for w in wfs], heads), "tensor route")
     be.Dispose()
