@@ -11,8 +11,8 @@
 //   warps 2-5   epilogue: TMEM -> registers -> swizzled 128-byte staging rows -> TMA stores clipped at the sequence end
 //
 // The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue of one tile runs under the main loop of
-// the next.  CTAs are persistent and walk the tiles in a fixed order, row tiles fastest: the CTAs of one wave share
-// two or three weight panels and sweep A, which stays in L2.  Every wait is bounded; a CTA that gives up sets the
+// the next.  CTAs are persistent and walk the tiles in a fixed order, grouped so that the tiles in flight share a
+// block of A rows and a block of weight columns that fit in L2 together.  Every wait is bounded; a CTA that gives up sets the
 // time-out bit of the status word and leaves through the common teardown.
 //
 // Replaces, for the engine's MultiHeadAttentionForward (src/AiDotNet.Tensors/Engines/CpuEngine.MultiHeadAttention.cs:155-338:
@@ -59,6 +59,7 @@ struct GemmParams {
   int32_t row_tiles_per_batch;   // ceil(seq / 128)
   int32_t row_tiles;             // batch * row_tiles_per_batch
   int32_t col_tiles_per_mat;     // n / BN
+  int32_t col_tiles;             // col_tiles_per_mat * number of weight matrices
   int32_t total_tiles;
   int32_t k_blocks;              // ceil(k / 64)
   int32_t seq;
@@ -72,9 +73,19 @@ struct Tile {
   int b, s0, mat, n0;
 };
 
+// Tile order: groups of kGroupRows row tiles; inside a group the row tile runs fastest, then the column tile.  The
+// 148 tiles in flight then cover 16 row tiles x 9 column tiles (16 MB of A + 18 MB of W) instead of every row tile
+// against two weight panels, and the A rows of a group stay in L2 while the group walks across the weights.
+constexpr int kGroupRows = 16;
+
 __device__ __forceinline__ Tile decode_tile(const GemmParams& gp, int tile, int bn) {
   Tile t;
-  const int rt = tile % gp.row_tiles, ct = tile / gp.row_tiles;
+  const int per_group = kGroupRows * gp.col_tiles;
+  const int grp = tile / per_group, within = tile - grp * per_group;
+  const int rows_left = gp.row_tiles - grp * kGroupRows;
+  const int rows_here = rows_left < kGroupRows ? rows_left : kGroupRows;
+  const int ct = within / rows_here;
+  const int rt = grp * kGroupRows + (within - ct * rows_here);
   t.b = rt / gp.row_tiles_per_batch;
   t.s0 = (rt - t.b * gp.row_tiles_per_batch) * kBM;
   t.mat = ct / gp.col_tiles_per_mat;
@@ -289,6 +300,7 @@ cudaError_t launch_t(const ProjGemm& g, cudaStream_t stream, int num_sms, int32_
   gp.row_tiles_per_batch = (int)((g.seq + kBM - 1) / kBM);
   gp.row_tiles = (int)(g.batch * gp.row_tiles_per_batch);
   gp.col_tiles_per_mat = (int)(g.n / BN);
+  gp.col_tiles = gp.col_tiles_per_mat * g.num_mats;
   const int64_t total = (int64_t)gp.row_tiles * gp.col_tiles_per_mat * g.num_mats;
   if (total <= 0 || total > 0x3fffffff) { *why = "tile count out of range"; return cudaErrorInvalidValue; }
   gp.total_tiles = (int)total;
