@@ -18,7 +18,7 @@ CSRC = os.path.join(HERE, "csrc")
 BUILD = os.path.join(HERE, "build")
 LIBDIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIBDIR, "libaidotnet_sdpa_sm100.so")
-SOURCES = ["aidn_api.cu", "sdpa_generic.cu", "sdpa_decode.cu", "sdpa_prefill_sm100.cu", "cast.cu", "qkv_rope_cache.cu", "sdpa_backward.cu", "proj_gemm_sm100.cu", "proj_gemm_generic.cu"]
+SOURCES = ["aidn_api.cu", "sdpa_generic.cu", "sdpa_decode.cu", "sdpa_prefill_sm100.cu", "cast.cu", "qkv_rope_cache.cu", "sdpa_backward.cu", "proj_gemm_sm100.cu", "proj_gemm_generic.cu", "sdpa_backward_sm100.cu"]
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 

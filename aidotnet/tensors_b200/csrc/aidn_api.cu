@@ -476,10 +476,11 @@ int aidn_sdpa_backward(aidn_sdpa_t h, const aidn_sdpa_bwd_args* a, void* cu_stre
   if (h->d.qkv_dtype != AIDN_F32 && h->d.out_dtype == AIDN_F32)
     bp.dout_t = static_cast<char*>(a->fwd.workspace) +
                 align_up(a->fwd.batch * h->head_count * a->fwd.seq_q * (int64_t)sizeof(float), 256);
-  int launches = 0;
-  cudaError_t e = aidn::launch_backward(bp, h->d.qkv_dtype, (cudaStream_t)cu_stream, &launches);
+  bp.no_tcgen05 = h->d.path == AIDN_PATH_GENERIC ? 1 : 0;
+  int launches = 0, used_tcgen05 = 0;
+  cudaError_t e = aidn::launch_backward(bp, h->d.qkv_dtype, (cudaStream_t)cu_stream, &launches, &used_tcgen05);
   if (e != cudaSuccess) return fail_cuda(e, "backward");
-  h->last_path = AIDN_PATH_GENERIC;
+  h->last_path = used_tcgen05 ? AIDN_PATH_PREFILL_SM100 : AIDN_PATH_GENERIC;
   h->last_launches = launches;
   return AIDN_OK;
 }

@@ -184,8 +184,13 @@ struct BwdParams {
   float* dv;
   float* delta;       // [B, Hc, Sq] scratch
   void* dout_t;       // scratch: dO in the input dtype, dense [B, Hc, Sq, D] (16-bit inputs with an fp32 dO), or null
+  int32_t no_tcgen05; // 1: stay on the mma.sync / FFMA kernels (desc.path == AIDN_PATH_GENERIC)
 };
-cudaError_t launch_backward(const BwdParams& bp, int dtype, cudaStream_t stream, int* launches);
+// *used_tcgen05 tells which family ran the dQ and dK / dV launches.
+cudaError_t launch_backward(const BwdParams& bp, int dtype, cudaStream_t stream, int* launches, int* used_tcgen05);
+// tcgen05 dQ and dK / dV launches (csrc/sdpa_backward_sm100.cu); delta (and dout_t) must already be on the stream.
+bool backward_sm100_supported(const BwdParams& bp, int dtype);
+cudaError_t launch_backward_sm100(const BwdParams& bp, int dtype, cudaStream_t stream, int* launches, const char** why);
 
 // Packed Q/K/V projection + RoPE + KV-cache write (csrc/qkv_rope_cache.cu).
 struct QkvRopeParams {

@@ -12,6 +12,8 @@
 // fp32 FFMA arithmetic with K/V (or Q/dO) tiles staged in shared memory, any head_dim <= 256, every mask kind of the
 // forward, grouped-query attention (dK / dV sum over the query heads of the group).  A correctness-first kernel: it
 // shares the generic forward kernel's tiling, not the tcgen05 kernel's.
+#include <type_traits>
+
 #include "common.cuh"
 #include "mma_sync.cuh"
 #include "sm100_ptx.cuh"
@@ -731,13 +733,23 @@ inline bool mma_aligned(const BwdParams& bp) {
 }
 
 template <typename T, int DMAX>
-cudaError_t launch_bwd_t(const BwdParams& bp, cudaStream_t stream, int* launches) {
+cudaError_t launch_bwd_t(const BwdParams& bp, cudaStream_t stream, int* launches, int* used_tcgen05) {
   const SdpaParams& p = bp.p;
   constexpr int PITCH = DMAX + 4;
   dim3 g0((unsigned)((p.seq_q + 3) / 4), (unsigned)p.head_count, (unsigned)p.batch);
   bwd_delta_kernel<T><<<g0, 128, 0, stream>>>(bp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
+  *used_tcgen05 = 0;
+  if constexpr (sizeof(T) == 2 && (DMAX == 64 || DMAX == 128)) {
+    const int dtype = std::is_same_v<T, __half> ? AIDN_F16 : AIDN_BF16;
+    if (!bp.no_tcgen05 && p.head_dim == DMAX && backward_sm100_supported(bp, dtype)) {
+      const char* why = "";
+      *launches = 1;
+      *used_tcgen05 = 1;
+      return launch_backward_sm100(bp, dtype, stream, launches, &why);
+    }
+  }
   const size_t smem_q = sizeof(float) * ((2 * kRows + 2 * kKeys) * PITCH + kRows * kKeys);
   const size_t smem_kv = sizeof(float) * ((2 * kRows + 2 * kKeys) * PITCH + 2 * kRows * kKeys);
   auto kq = bwd_dq_kernel<T, DMAX>;
@@ -786,19 +798,19 @@ cudaError_t launch_bwd_t(const BwdParams& bp, cudaStream_t stream, int* launches
 }
 
 template <typename T>
-cudaError_t launch_bwd_d(const BwdParams& bp, cudaStream_t stream, int* launches) {
-  if (bp.p.head_dim <= 64) return launch_bwd_t<T, 64>(bp, stream, launches);
-  if (bp.p.head_dim <= 128) return launch_bwd_t<T, 128>(bp, stream, launches);
-  return launch_bwd_t<T, 256>(bp, stream, launches);
+cudaError_t launch_bwd_d(const BwdParams& bp, cudaStream_t stream, int* launches, int* used_tcgen05) {
+  if (bp.p.head_dim <= 64) return launch_bwd_t<T, 64>(bp, stream, launches, used_tcgen05);
+  if (bp.p.head_dim <= 128) return launch_bwd_t<T, 128>(bp, stream, launches, used_tcgen05);
+  return launch_bwd_t<T, 256>(bp, stream, launches, used_tcgen05);
 }
 
 }  // namespace
 
-cudaError_t launch_backward(const BwdParams& bp, int dtype, cudaStream_t stream, int* launches) {
+cudaError_t launch_backward(const BwdParams& bp, int dtype, cudaStream_t stream, int* launches, int* used_tcgen05) {
   switch (dtype) {
-    case AIDN_F32: return launch_bwd_d<float>(bp, stream, launches);
-    case AIDN_F16: return launch_bwd_d<__half>(bp, stream, launches);
-    default: return launch_bwd_d<__nv_bfloat16>(bp, stream, launches);
+    case AIDN_F32: return launch_bwd_d<float>(bp, stream, launches, used_tcgen05);
+    case AIDN_F16: return launch_bwd_d<__half>(bp, stream, launches, used_tcgen05);
+    default: return launch_bwd_d<__nv_bfloat16>(bp, stream, launches, used_tcgen05);
   }
 }
 

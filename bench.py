@@ -37,7 +37,7 @@ WORKLOADS = {
                     name="long_context_shard_B1_Hq8_Hkv1_S32768_D128_causal_bf16"),
     "c3paged": dict(B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill", block_size=16,
                     name="paged_gqa_prefill_B2_Hq32_Hkv8_S8192_D128_block16_causal_bf16"),
-    # attention backward (deterministic; mma.sync kernels for 16-bit inputs) on a quarter of the C2 shape
+    # attention backward (deterministic; tcgen05 dQ and dK/dV kernels for 16-bit inputs) on a quarter of the C2 shape
     "c2bwd": dict(kind="bwd", B=1, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
                   name="llama_backward_B1_H32_S2048_D128_causal_bf16"),
     # the in-library caller of the attention path: Q/K/V projections + attention + output projection in one call
@@ -295,11 +295,11 @@ def run_bwd(args, w, pk):
     print(json.dumps({
         "metric": "attention backward TFLOP/s/GPU", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32 arithmetic on bf16 inputs", "data": "synthetic",
+        "vs_baseline": None, "dtype": "bf16 (fp32 accumulation)", "data": "synthetic",
         "config": {"workload": w["name"], "flop_convention": "10*D*visible(q,k) pairs"},
         "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16"], "unit": "TFLOP/s", "frac": tf / pk["bf16"],
                      "traffic": None, "algorithmic": fl, "algorithmic_unit": "FLOP per launch",
-                     "peak_source": pk["source"] + " (burst); warp-level mma.sync kernels, not tcgen05"},
+                     "peak_source": pk["source"] + " (burst)"},
         "gpu_launches": 3 * args.steps}))
 
 

@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 
 
 def _fwd_bwd(q, k, v, dout, *, dtype, causal=False, causal_offset=0, bottom_right=False, mask=None, mask_kind=N.MASK_NONE,
-             kv_len=None, scale=0.0, head_begin=0, head_count=0):
+             kv_len=None, scale=0.0, head_begin=0, head_count=0, path=N.PATH_AUTO, info=None):
     B, Hq, Sq, D = q.shape
     Hkv, Sk = k.shape[1], k.shape[2]
     hc = head_count or Hq
@@ -22,7 +22,7 @@ def _fwd_bwd(q, k, v, dout, *, dtype, causal=False, causal_offset=0, bottom_righ
     lse = torch.full((B, Hq, Sq), float("nan"), device="cuda")
     h = N.Handle(device=0, qkv_dtype=AIDN_DT[dtype], head_dim=D, num_q_heads=Hq, num_kv_heads=Hkv, causal=causal,
                  causal_bottom_right=bottom_right, causal_offset=causal_offset, mask_kind=mask_kind, emit_lse=True,
-                 head_begin=head_begin, head_count=head_count)
+                 head_begin=head_begin, head_count=head_count, path=path)
     stream = torch.cuda.current_stream().cuda_stream
     ms = (0, 0, 0, 0)
     if mask is not None:
@@ -45,6 +45,8 @@ def _fwd_bwd(q, k, v, dout, *, dtype, causal=False, causal_offset=0, bottom_righ
     h.backward(dout=dout.data_ptr(), dq=dq.data_ptr(), dk=dk.data_ptr(), dv=dv.data_ptr(), workspace=wsb.data_ptr(),
                workspace_bytes=nbw, **common)
     h.poll(stream)
+    if info is not None:
+        info["path"] = h.last_path
     h.close()
     return dq, dk, dv
 
@@ -159,3 +161,30 @@ def test_backend_flash_attention_backward():
     with pytest.raises(ValueError):
         be.FlashAttentionBackward(gb, qb, kb, vb, out, stats, gq, gk, zeros(4), B, H, S, S, D, 0.25, True)
     be.Dispose()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("shape", [(1, 4, 4, 256, 256, 128), (2, 4, 2, 200, 333, 64), (1, 8, 1, 130, 517, 128), (2, 2, 2, 384, 128, 64),
+                                   (1, 2, 2, 1, 300, 128)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_backward_tensor_core_families(dtype, shape, causal):
+    """16-bit inputs with head_dim 64 / 128 run the tcgen05 kernels (several 128-row tiles per sequence, ragged ends,
+    grouped-query heads, bottom-right causal offsets, a padded batch entry); with desc.path = generic the same call stays
+    on the mma.sync kernels.  Both meet the oracle and each is bit-reproducible."""
+    B, Hq, Hkv, Sq, Sk, D = shape
+    q, qf = gen((B, Hq, Sq, D), dtype, 951)
+    k, kf = gen((B, Hkv, Sk, D), dtype, 952)
+    v, vf = gen((B, Hkv, Sk, D), dtype, 953)
+    dout, dof = gen((B, Hq, Sq, D), "f32", 954, scale=1.0)
+    kv_len = np.array([Sk, max(1, Sk - 77)][:B], np.int32)
+    off = Sk - Sq
+    rq, rk, rv, _, _ = O.sdpa_backward(qf, kf, vf, dof, causal=causal, causal_offset=off, kv_len=kv_len)
+    for path, want_path in ((N.PATH_AUTO, N.PATH_PREFILL_SM100), (N.PATH_GENERIC, N.PATH_GENERIC)):
+        info = {}
+        dq, dk, dv = _fwd_bwd(q, k, v, dout, dtype=dtype, causal=causal, bottom_right=True, kv_len=kv_len, path=path, info=info)
+        assert info["path"] == want_path
+        _check(dq, rq, dtype, f"dQ {shape} path {path}")
+        _check(dk, rk, dtype, f"dK {shape} path {path}")
+        _check(dv, rv, dtype, f"dV {shape} path {path}")
+        dq2, dk2, dv2 = _fwd_bwd(q, k, v, dout, dtype=dtype, causal=causal, bottom_right=True, kv_len=kv_len, path=path)
+        assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
