@@ -43,10 +43,27 @@ __global__ void __launch_bounds__(128) bwd_delta_kernel(const BwdParams bp) {
   const int64_t gb = b * bp.dos[0] + (int64_t)h * bp.dos[1] + row * bp.dos[2];
   float acc = 0.f;
   T* gt = bp.dout_t ? static_cast<T*>(bp.dout_t) + (((int64_t)b * p.head_count + hl) * p.seq_q + row) * p.head_dim : nullptr;
-  for (int d = lane; d < p.head_dim; d += 32) {
-    const float go = load_o<T>(bp.dout, gb + d, p.out_f32);
-    acc += go * load_o<T>(p.out, ob + d, p.out_f32);
-    if (gt) gt[d] = from_float<T>(go);   // the tensor-core dK / dV kernel streams dO with cp.async in the input dtype
+  // fp32 O and dO with 16-byte aligned rows: four elements per lane and load
+  const bool vec = p.out_f32 && p.head_dim % 4 == 0 && ((ob | gb) & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(bp.dout)) & 15) == 0 &&
+                   (!gt || sizeof(T) == 2) && ((reinterpret_cast<uintptr_t>(bp.dout_t) & 7) == 0);
+  if (vec) {
+    const float4* o4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.out) + ob);
+    const float4* g4 = reinterpret_cast<const float4*>(static_cast<const float*>(bp.dout) + gb);
+    for (int d4 = lane; d4 < p.head_dim / 4; d4 += 32) {
+      const float4 o = o4[d4], g = g4[d4];
+      acc += g.x * o.x + g.y * o.y + g.z * o.z + g.w * o.w;
+      if (gt) {
+        T t4[4] = {from_float<T>(g.x), from_float<T>(g.y), from_float<T>(g.z), from_float<T>(g.w)};
+        *reinterpret_cast<uint2*>(gt + 4 * d4) = *reinterpret_cast<const uint2*>(t4);
+      }
+    }
+  } else {
+    for (int d = lane; d < p.head_dim; d += 32) {
+      const float go = load_o<T>(bp.dout, gb + d, p.out_f32);
+      acc += go * load_o<T>(p.out, ob + d, p.out_f32);
+      if (gt) gt[d] = from_float<T>(go);   // the tensor-core dK / dV kernels stream dO in the input dtype
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);

@@ -14,10 +14,14 @@
 // the MN-major B operand - one shared-memory image, two descriptors.
 //
 //   warp 0      TMA producer          warp 1      UMMA issuer (one elected lane); owns TMEM
-//   warps 2-5   one row per thread: TMEM -> registers, P and dS, -> TMEM; at the end scale and store the accumulators
+//   warps 2-5   half 0, warps 6-9 half 1: one row per thread: TMEM -> registers, P and dS, -> TMEM; at the end the
+//               two groups scale and store one accumulator (or one half of dQ) each
 //
-// TMEM columns: S [0,128)  dP [128,256)  dK or dQ [256,256+D)  dV [256+D,256+2D).  UMMAs execute in issue order, so the
-// score products of step j+1, which overwrite P / dS of step j, cannot pass the gradient products that read them.
+// A streamed tile is processed as two halves of 64 rows, each with its own S / dP columns in TMEM and its own group of
+// four row warps, so that the tensor core computes the scores of one half (and the gradient products of the previous
+// one) while the other half is turned into P and dS, and every scheduler has two row warps to switch between.  TMEM columns: half h: S [128h, 128h+64)  dP [128h+64, 128h+128);  dK or dQ [256,256+D);
+// dV [256+D,256+2D).  Issue order  S(0) S(1) G(0) S(2) G(1) S(3) ...: UMMAs execute in issue order, so the scores of
+// half i+2, which overwrite P / dS of half i, cannot pass the gradient products G(i) that read them.
 //
 // Serves 16-bit inputs, head_dim 64 / 128, contiguous K / V, causal and length masks; everything else stays on the
 // kernels of sdpa_backward.cu.  Supersedes flash_attention_backward_deterministic_{dq,dkv} of the reference
@@ -36,7 +40,7 @@ namespace {
 using namespace ptx;
 
 constexpr int kT = 128;          // rows of every tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;     // producer, issuer, 2 x 4 row warps
 constexpr int kTmemCols = 512;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -47,10 +51,10 @@ struct BCfg {
   static constexpr int kHalves = HD / 64;
   static constexpr int kRing = HD == 128 ? 2 : 4;      // streamed (U, W) pairs in flight
   static constexpr int kRingOff = 2 * kTileBytes;
-  static constexpr int kVecOff = kRingOff + kRing * 2 * kTileBytes;   // per-warp lse / delta rows: 4 warps x 2 x 2 x 128 floats
-  static constexpr int kVecBytes = 4 * 2 * 2 * kT * 4;
+  static constexpr int kVecOff = kRingOff + kRing * 2 * kTileBytes;   // per-warp lse / delta rows: 8 warps x 2 x 2 x 64 floats
+  static constexpr int kVecBytes = 8 * 2 * 2 * 64 * 4;
   static constexpr int kBarOff = kVecOff + kVecBytes;
-  static constexpr int kNumBars = 4 + 2 * kRing;       // xy_full s_full p_full acc_full ring_full[R] ring_empty[R]
+  static constexpr int kNumBars = 6 + 2 * kRing;       // xy_full acc_full s_full[2] p_full[2] ring_full[R] ring_empty[R]
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kSmemBytes = kMiscOff + 16 + 1024;
   static constexpr int kAcc0 = 256;
@@ -135,8 +139,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t ring_smem = smem_base + C::kRingOff;
   float* vec_smem = reinterpret_cast<float*>(smem_gen + C::kVecOff);
   const uint32_t bars = smem_base + C::kBarOff;
-  const uint32_t bar_xy_full = bars, bar_s_full = bars + 8, bar_p_full = bars + 16, bar_acc_full = bars + 24;
-  const uint32_t bar_ring_full = bars + 32, bar_ring_empty = bar_ring_full + 8 * C::kRing;
+  const uint32_t bar_xy_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16, bar_p_full = bars + 32;   // [2] each
+  const uint32_t bar_ring_full = bars + 48, bar_ring_empty = bar_ring_full + 8 * C::kRing;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::kMiscOff + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kMiscOff + 12);
 
@@ -146,9 +150,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     mbar_init(bar_xy_full, 1);
-    mbar_init(bar_s_full, 1);
-    mbar_init(bar_p_full, 128);
     mbar_init(bar_acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_p_full + 8 * i, 128);
+    }
     for (int s = 0; s < C::kRing; ++s) {
       mbar_init(bar_ring_full + 8 * s, 1);
       mbar_init(bar_ring_empty + 8 * s, 1);
@@ -214,59 +220,82 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp == 1) {
     // ============================================ UMMA issuer =============================================
     const bool leader = elect_one();
-    constexpr uint32_t idesc_s = make_idesc(kT, kT, kBf16, false);
+    constexpr uint32_t idesc_s = make_idesc(kT, 64, kBf16, false);
     constexpr uint32_t idesc_g = make_idesc(kT, HD, kBf16, true);
     bool alive = w.steps > 0;
     if (alive && !mbar_wait(bar_xy_full, 0, abort_flag, wait_ns)) alive = false;
-    for (int j = 0; j < w.steps && alive; ++j) {
-      const int s = j % C::kRing;
-      if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)((j / C::kRing) & 1), abort_flag, wait_ns)) break;
-      tc_fence_after();
+    const int halves = 2 * w.steps;
+    // gradient products of half `hs`: acc0 += dS U (dK or dQ); KEYS: acc1 += P^T W (dV).  A from TMEM (16-bit, 8
+    // columns per 16 of K), B = the 64 streamed rows of the half, MN-major
+    auto issue_g = [&](int hs) {
+      const int j = hs >> 1, h = hs & 1, s = j % C::kRing;
       const uint32_t u_addr = ring_smem + s * 2 * C::kTileBytes, w_addr = u_addr + C::kTileBytes;
-      // S (or S^T) = X U^T and dP = Y W^T: both operands K-major
+      const uint32_t t_half = tmem_base + (uint32_t)(h * 128);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {
+        const uint64_t bd = make_smem_desc(u_addr + (uint32_t)((h * 4 + kk) * 2048), C::kHalfBytes, 1024);
+        if (leader) mma_ts(tmem_base + (uint32_t)C::kAcc0, t_half + 64u + (uint32_t)(kk * 8), bd, idesc_g, (hs > 0 || kk > 0) ? 1u : 0u);
+      }
+      if constexpr (KEYS) {
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          const uint64_t bd = make_smem_desc(w_addr + (uint32_t)((h * 4 + kk) * 2048), C::kHalfBytes, 1024);
+          if (leader) mma_ts(tmem_base + (uint32_t)C::kAcc1, t_half + (uint32_t)(kk * 8), bd, idesc_g, (hs > 0 || kk > 0) ? 1u : 0u);
+        }
+      }
+      if (leader) {
+        if (h == 1) tc_commit(bar_ring_empty + 8 * s);   // both halves of the streamed pair are consumed
+        if (hs == halves - 1) tc_commit(bar_acc_full);
+      }
+    };
+    for (int hs = 0; hs < halves && alive; ++hs) {
+      const int j = hs >> 1, h = hs & 1, s = j % C::kRing;
+      if (h == 0) {
+        if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)((j / C::kRing) & 1), abort_flag, wait_ns)) { alive = false; break; }
+        tc_fence_after();
+      }
+      const uint32_t u_addr = ring_smem + s * 2 * C::kTileBytes + (uint32_t)(h * 8192);   // rows 64h.. of each 64-column block
+      const uint32_t w_addr = u_addr + C::kTileBytes;
+      const uint32_t t_half = tmem_base + (uint32_t)(h * 128);
+      // S (or S^T) = X U^T and dP = Y W^T over the half's 64 streamed rows: both operands K-major
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk) {
         const uint32_t off = (uint32_t)((kk >> 2) * C::kHalfBytes + (kk & 3) * 32);
         const uint64_t ad = make_smem_desc(x_smem + off, 16, 1024), bd = make_smem_desc(u_addr + off, 16, 1024);
-        if (leader) mma_ss(tmem_base, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+        if (leader) mma_ss(t_half, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
       }
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk) {
         const uint32_t off = (uint32_t)((kk >> 2) * C::kHalfBytes + (kk & 3) * 32);
         const uint64_t ad = make_smem_desc(y_smem + off, 16, 1024), bd = make_smem_desc(w_addr + off, 16, 1024);
-        if (leader) mma_ss(tmem_base + 128u, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+        if (leader) mma_ss(t_half + 64u, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
       }
-      if (leader) tc_commit(bar_s_full);
-      if (!mbar_wait(bar_p_full, (uint32_t)(j & 1), abort_flag, wait_ns)) break;
-      tc_fence_after();
-      // acc0 += dS U (dK or dQ); KEYS: acc1 += P^T W (dV).  A from TMEM (16-bit, 8 columns per 16 of K), B MN-major
-#pragma unroll
-      for (int kk = 0; kk < kT / 16; ++kk) {
-        const uint64_t bd = make_smem_desc(u_addr + (uint32_t)(kk * 2048), C::kHalfBytes, 1024);
-        if (leader) mma_ts(tmem_base + (uint32_t)C::kAcc0, tmem_base + 128u + (uint32_t)(kk * 8), bd, idesc_g, (j > 0 || kk > 0) ? 1u : 0u);
+      if (leader) tc_commit(bar_s_full + 8 * h);
+      if (hs >= 1) {
+        const int prev = hs - 1;
+        if (!mbar_wait(bar_p_full + 8 * (prev & 1), (uint32_t)((prev >> 1) & 1), abort_flag, wait_ns)) { alive = false; break; }
+        tc_fence_after();
+        issue_g(prev);
       }
-      if constexpr (KEYS) {
-#pragma unroll
-        for (int kk = 0; kk < kT / 16; ++kk) {
-          const uint64_t bd = make_smem_desc(w_addr + (uint32_t)(kk * 2048), C::kHalfBytes, 1024);
-          if (leader) mma_ts(tmem_base + (uint32_t)C::kAcc1, tmem_base + (uint32_t)(kk * 8), bd, idesc_g, (j > 0 || kk > 0) ? 1u : 0u);
-        }
-      }
-      if (leader) {
-        tc_commit(bar_ring_empty + 8 * s);
-        if (j == w.steps - 1) tc_commit(bar_acc_full);
+    }
+    if (alive && halves > 0) {
+      const int prev = halves - 1;
+      if (mbar_wait(bar_p_full + 8 * (prev & 1), (uint32_t)((prev >> 1) & 1), abort_flag, wait_ns)) {
+        tc_fence_after();
+        issue_g(prev);
       }
     }
   } else {
     // ===================================== probabilities, dS, epilogue =====================================
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;   // which 64 streamed rows (= score columns) this warp's group handles
     const int row = quarter * 32 + lane;
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_bits, t_dp = t_s + 128u;
+    const uint32_t t_s = tmem_base + lane_bits + (uint32_t)(half * 128), t_dp = t_s + 64u;
     const float sl2 = p.scale * kLog2e;
     const int64_t kv_limit = kv_limit_of(p, w.b);
     const int64_t my_row = (int64_t)w.tile * kT + row;   // key (KEYS) or query index of this thread
-    float* my_vec = vec_smem + (warp - 2) * (2 * 2 * kT);   // [buffer][lse, delta][128]
+    float* my_vec = vec_smem + (warp - 2) * (2 * 2 * 64);   // [buffer][-lse*log2e, delta][64]
     // rows are queries: the thread's own -lse*log2(e) and delta
     float my_nl = -INFINITY, my_dl = 0.f;
     if (!KEYS && my_row < p.seq_q) {
@@ -276,15 +305,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     bool alive = true;
     for (int j = 0; j < w.steps; ++j) {
-      const int64_t col0 = (int64_t)step_tile(j) * kT;   // first query (KEYS) or key of the streamed tile
-      const float* nls = my_vec + (j & 1) * (2 * kT);
-      const float* dls = nls + kT;
+      const int64_t col0 = (int64_t)step_tile(j) * kT + half * 64;   // first query (KEYS) or key of this half
+      const float* nls = my_vec + (j & 1) * (2 * 64);
+      const float* dls = nls + 64;
       if constexpr (KEYS) {
         // the streamed queries' -lse*log2(e) and delta, one private copy per warp (no cross-warp barrier)
         const int h = step_head(j);
-        float* wl = my_vec + (j & 1) * (2 * kT);
+        float* wl = my_vec + (j & 1) * (2 * 64);
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
+        for (int t = 0; t < 2; ++t) {
           const int c = t * 32 + lane;
           const int64_t q = col0 + c;
           float nl = -INFINITY, dl = 0.f;
@@ -294,12 +323,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             dl = bp.delta[((int64_t)w.b * p.head_count + (h - p.head_begin)) * p.seq_q + q];
           }
           wl[c] = nl;
-          wl[kT + c] = dl;
+          wl[64 + c] = dl;
         }
         __syncwarp();
       }
-      // visible columns of this thread's row: [lo, hi]
-      int64_t lo = 0, hi = kT - 1;
+      // visible columns of this thread's row within the half: [lo, hi]
+      int64_t lo = 0, hi = 63;
       if constexpr (KEYS) {
         if (my_row >= kv_limit) hi = -1;
         if (p.causal) lo = my_row - p.causal_offset - col0;   // query >= key - offset
@@ -310,14 +339,14 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (c < hi) hi = c;
         }
       }
-      const bool edge = __any_sync(0xffffffffu, lo > 0 || hi < kT - 1);
+      const bool edge = __any_sync(0xffffffffu, lo > 0 || hi < 63);
 
-      bool ok = mbar_wait(bar_s_full, (uint32_t)(j & 1), abort_flag, wait_ns);
+      bool ok = mbar_wait(bar_s_full + 8 * half, (uint32_t)(j & 1), abort_flag, wait_ns);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { alive = false; break; }
       tc_fence_after();
 #pragma unroll
-      for (int c0 = 0; c0 < kT; c0 += 32) {
+      for (int c0 = 0; c0 < 64; c0 += 32) {
         uint32_t sr[32], dr[32];
         tmem_ld32(t_s + (uint32_t)c0, sr);
         tmem_ld32(t_dp + (uint32_t)c0, dr);
@@ -345,7 +374,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(bar_p_full);
+      mbar_arrive(bar_p_full + 8 * half);
     }
 
     // ---- epilogue: accumulators -> global, one row per thread ------------------------------------------------
@@ -369,13 +398,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         } else {
           out0 = bp.dq + (((int64_t)w.b * p.head_count + (w.h - p.head_begin)) * p.seq_q + my_row) * HD;
         }
-#pragma unroll
-        for (int a = 0; a < (KEYS ? 2 : 1); ++a) {
+        {
+          // the two groups of row warps split the stores: dK | dV, or the two halves of dQ's columns
+          const int a = KEYS ? half : 0;
           float* out = a == 0 ? out0 : out1;
           const float f = a == 0 ? p.scale : 1.f;
           const uint32_t t_acc = tmem_base + lane_bits + (uint32_t)(a == 0 ? C::kAcc0 : C::kAcc1);
+          const int c_begin = KEYS ? 0 : half * (HD / 2), c_end = KEYS ? HD : c_begin + HD / 2;
 #pragma unroll
-          for (int c0 = 0; c0 < HD; c0 += 32) {
+          for (int c0 = c_begin; c0 < c_end; c0 += 32) {
             uint32_t r[32];
             if (have) {
               tmem_ld32(t_acc + (uint32_t)c0, r);

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|mha|mhaq|qkvrope|qkvrope1|qkvrope70b|qkvrope32] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|c2bwdfull|c3bwd|mha|mhaq|qkvrope|qkvrope1|qkvrope70b|qkvrope32] [--impl reference]
 
 One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
 default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
@@ -40,6 +40,10 @@ WORKLOADS = {
     # attention backward (deterministic; tcgen05 dQ and dK/dV kernels for 16-bit inputs) on a quarter of the C2 shape
     "c2bwd": dict(kind="bwd", B=1, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
                   name="llama_backward_B1_H32_S2048_D128_causal_bf16"),
+    "c2bwdfull": dict(kind="bwd", B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
+                      name="llama_backward_B4_H32_S2048_D128_causal_bf16"),
+    "c3bwd": dict(kind="bwd", B=1, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True,
+                  name="gqa_backward_B1_Hq32_Hkv8_S8192_D128_causal_bf16"),
     # the in-library caller of the attention path: Q/K/V projections + attention + output projection in one call
     "mha": dict(kind="mha", B=4, S=2048, heads=32, D=128, name="mha_forward_B4_S2048_dmodel4096_H32_bf16"),
     "mhaq": dict(kind="mha", B=1, S=2048, heads=16, D=128, name="mha_forward_B1_S2048_dmodel2048_H16_bf16"),
