@@ -2,8 +2,9 @@
 // (TMA + mbarrier ring, tcgen05 UMMA with TMEM accumulators), recomputing the probabilities from the forward's
 // log-sum-exp.  Deterministic: every gradient tile is accumulated by one CTA in a fixed order, no atomics.
 //
-// A CTA owns one 128-row tile that stays in shared memory ("stationary") and streams the 128-row tiles of the other
-// sequence past it:
+// A work item is one 128-row tile that stays in shared memory ("stationary") while the 128-row tiles of the other
+// sequence stream past it; persistent CTAs walk the items, heaviest first, and the loads and first score products of
+// the next item run under the epilogue of the current one:
 //   KEYS = true  (dK, dV): rows are keys.  X = K tile, Y = V tile; per step U = Q tile, W = dO tile of one query head
 //                of the KV group.   S^T = X U^T,  dP^T = Y W^T,  dV += P^T W,  dK += dS^T U
 //   KEYS = false (dQ):     rows are queries.  X = Q tile, Y = dO tile; per step U = K tile, W = V tile.
@@ -54,7 +55,7 @@ struct BCfg {
   static constexpr int kVecOff = kRingOff + kRing * 2 * kTileBytes;   // per-warp lse / delta rows: 8 warps x 2 x 2 x 64 floats
   static constexpr int kVecBytes = 8 * 2 * 2 * 64 * 4;
   static constexpr int kBarOff = kVecOff + kVecBytes;
-  static constexpr int kNumBars = 6 + 2 * kRing;       // xy_full acc_full s_full[2] p_full[2] ring_full[R] ring_empty[R]
+  static constexpr int kNumBars = 8 + 2 * kRing;       // xy_full acc_full s_full[2] p_full[2] xy_empty acc_empty ring_full[R] ring_empty[R]
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;
   static constexpr int kSmemBytes = kMiscOff + 16 + 1024;
   static constexpr int kAcc0 = 256;
@@ -69,6 +70,7 @@ struct BwdSm100Params {
   float* dv;
   int32_t q_tiles, k_tiles;
   int32_t do_head_off;  // head coordinate of the dO tensor map = h - do_head_off
+  int32_t total_items;
   uint64_t wait_budget_ns;
 };
 
@@ -123,6 +125,12 @@ __device__ __forceinline__ Work decode_work(const BwdSm100Params& bp, int idx) {
   return w;
 }
 
+// step j streams tile (first + j % count) of query head h + j / count (KEYS) or key tile j of the KV head
+template <bool KEYS>
+__device__ __forceinline__ int step_head(const Work& w, int j) { return KEYS ? w.h + j / w.count : w.kvh; }
+template <bool KEYS>
+__device__ __forceinline__ int step_tile(const Work& w, int j) { return KEYS ? w.first + j % w.count : j; }
+
 template <typename T, int HD, bool KEYS>
 __global__ void __launch_bounds__(kThreads, 1)
     sdpa_backward_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -140,7 +148,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   float* vec_smem = reinterpret_cast<float*>(smem_gen + C::kVecOff);
   const uint32_t bars = smem_base + C::kBarOff;
   const uint32_t bar_xy_full = bars, bar_acc_full = bars + 8, bar_s_full = bars + 16, bar_p_full = bars + 32;   // [2] each
-  const uint32_t bar_ring_full = bars + 48, bar_ring_empty = bar_ring_full + 8 * C::kRing;
+  const uint32_t bar_xy_empty = bars + 48, bar_acc_empty = bars + 56;
+  const uint32_t bar_ring_full = bars + 64, bar_ring_empty = bar_ring_full + 8 * C::kRing;
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::kMiscOff + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kMiscOff + 12);
 
@@ -151,6 +160,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     *abort_flag = 0;
     mbar_init(bar_xy_full, 1);
     mbar_init(bar_acc_full, 1);
+    mbar_init(bar_xy_empty, 1);
+    mbar_init(bar_acc_empty, 8);   // one arrival per row warp
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_s_full + 8 * i, 1);
       mbar_init(bar_p_full + 8 * i, 128);
@@ -176,36 +187,38 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  const Work w = decode_work<KEYS>(bp, blockIdx.x);
-  // step j streams tile (first + j % count) of query head h + j / count (KEYS) or key tile j of the KV head
-  auto step_head = [&](int j) { return KEYS ? w.h + j / w.count : w.kvh; };
-  auto step_tile = [&](int j) { return KEYS ? w.first + j % w.count : j; };
+  // Persistent CTAs: CTA k takes items k, 2G-1-k, 2G+k, ... (G = grid size; the item list is ordered heaviest first, and
+  // the snake keeps the sum per CTA even).  Counters that persist across items give every barrier its phase:
+  // `live` = items with at least one step so far, `g` = steps so far.
+  const int G = (int)gridDim.x;
+  auto item_of = [&](int wave) {
+    const int k = (wave & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    return wave * G + k;
+  };
+  const int waves = (bp.total_items + G - 1) / G;
 
   if (warp == 0) {
     // ============================================ TMA producer ============================================
     const bool leader = elect_one();
-    auto load_tile = [&](const CUtensorMap* tm, uint32_t dst, uint32_t bar, int row, int head) {
+    uint32_t g = 0, live = 0;
+    bool alive = true;
+    for (int wave = 0; wave < waves && alive; ++wave) {
+      const int item = item_of(wave);
+      if (item >= bp.total_items) continue;
+      const Work w = decode_work<KEYS>(bp, item);
+      if (w.steps == 0) continue;
+      auto load_tile = [&](const CUtensorMap* tm, uint32_t dst, uint32_t bar, int row, int head) {
 #pragma unroll
-      for (int hf = 0; hf < C::kHalves; ++hf) tma_load_4d(dst + hf * C::kHalfBytes, tm, bar, hf * 64, row, head, w.b);
-    };
-    if (w.steps > 0) {
-      if (leader) {
-        mbar_expect_tx(bar_xy_full, 2u * C::kTileBytes);
-        if (KEYS) {
-          load_tile(&tm_k, x_smem, bar_xy_full, w.tile * kT, w.kvh);
-          load_tile(&tm_v, y_smem, bar_xy_full, w.tile * kT, w.kvh);
-        } else {
-          load_tile(&tm_q, x_smem, bar_xy_full, w.tile * kT, w.h);
-          load_tile(&tm_do, y_smem, bar_xy_full, w.tile * kT, w.h - bp.do_head_off);
-        }
-      }
-      for (int j = 0; j < w.steps; ++j) {
-        const int s = j % C::kRing;
-        if (!mbar_wait(bar_ring_empty + 8 * s, (uint32_t)(((j / C::kRing) & 1) ^ 1), abort_flag, wait_ns)) break;
+        for (int hf = 0; hf < C::kHalves; ++hf) tma_load_4d(dst + hf * C::kHalfBytes, tm, bar, hf * 64, row, head, w.b);
+      };
+      auto load_step = [&](int j) {
+        const uint32_t gs = g + (uint32_t)j;
+        const int s = (int)(gs % C::kRing);
+        if (!mbar_wait(bar_ring_empty + 8 * s, ((gs / C::kRing) & 1u) ^ 1u, abort_flag, wait_ns)) { alive = false; return; }
         if (leader) {
           const uint32_t bar = bar_ring_full + 8 * s;
           const uint32_t u_dst = ring_smem + s * 2 * C::kTileBytes, w_dst = u_dst + C::kTileBytes;
-          const int head = step_head(j), row = step_tile(j) * kT;
+          const int head = step_head<KEYS>(w, j), row = step_tile<KEYS>(w, j) * kT;
           mbar_expect_tx(bar, 2u * C::kTileBytes);
           if (KEYS) {
             load_tile(&tm_q, u_dst, bar, row, head);
@@ -215,75 +228,112 @@ __global__ void __launch_bounds__(kThreads, 1)
             load_tile(&tm_v, w_dst, bar, row, head);
           }
         }
+      };
+      // the first streamed tiles can land while the previous item still holds the stationary pair
+      int j = 0;
+      for (; j < C::kRing && j < w.steps && alive; ++j) load_step(j);
+      if (alive && !mbar_wait(bar_xy_empty, (live & 1u) ^ 1u, abort_flag, wait_ns)) alive = false;
+      if (alive && leader) {
+        mbar_expect_tx(bar_xy_full, 2u * C::kTileBytes);
+        if (KEYS) {
+          load_tile(&tm_k, x_smem, bar_xy_full, w.tile * kT, w.kvh);
+          load_tile(&tm_v, y_smem, bar_xy_full, w.tile * kT, w.kvh);
+        } else {
+          load_tile(&tm_q, x_smem, bar_xy_full, w.tile * kT, w.h);
+          load_tile(&tm_do, y_smem, bar_xy_full, w.tile * kT, w.h - bp.do_head_off);
+        }
       }
+      for (; j < w.steps && alive; ++j) load_step(j);
+      g += (uint32_t)w.steps;
+      ++live;
     }
   } else if (warp == 1) {
     // ============================================ UMMA issuer =============================================
     const bool leader = elect_one();
     constexpr uint32_t idesc_s = make_idesc(kT, 64, kBf16, false);
     constexpr uint32_t idesc_g = make_idesc(kT, HD, kBf16, true);
-    bool alive = w.steps > 0;
-    if (alive && !mbar_wait(bar_xy_full, 0, abort_flag, wait_ns)) alive = false;
-    const int halves = 2 * w.steps;
-    // gradient products of half `hs`: acc0 += dS U (dK or dQ); KEYS: acc1 += P^T W (dV).  A from TMEM (16-bit, 8
-    // columns per 16 of K), B = the 64 streamed rows of the half, MN-major
-    auto issue_g = [&](int hs) {
-      const int j = hs >> 1, h = hs & 1, s = j % C::kRing;
-      const uint32_t u_addr = ring_smem + s * 2 * C::kTileBytes, w_addr = u_addr + C::kTileBytes;
-      const uint32_t t_half = tmem_base + (uint32_t)(h * 128);
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const uint64_t bd = make_smem_desc(u_addr + (uint32_t)((h * 4 + kk) * 2048), C::kHalfBytes, 1024);
-        if (leader) mma_ts(tmem_base + (uint32_t)C::kAcc0, t_half + 64u + (uint32_t)(kk * 8), bd, idesc_g, (hs > 0 || kk > 0) ? 1u : 0u);
-      }
-      if constexpr (KEYS) {
+    uint32_t g = 0, live = 0;
+    bool alive = true;
+    for (int wave = 0; wave < waves && alive; ++wave) {
+      const int item = item_of(wave);
+      if (item >= bp.total_items) continue;
+      const Work w = decode_work<KEYS>(bp, item);
+      if (w.steps == 0) continue;
+      if (!mbar_wait(bar_xy_full, live & 1u, abort_flag, wait_ns)) break;
+      const int halves = 2 * w.steps;
+      // gradient products of half `hs`: acc0 += dS U (dK or dQ); KEYS: acc1 += P^T W (dV).  A from TMEM (16-bit, 8
+      // columns per 16 of K), B = the 64 streamed rows of the half, MN-major
+      auto issue_g = [&](int hs) {
+        const int h = hs & 1, s = (int)((g + (uint32_t)(hs >> 1)) % C::kRing);
+        if (hs == 0) {   // the row warps must have read the previous item's accumulators
+          if (!mbar_wait(bar_acc_empty, (live & 1u) ^ 1u, abort_flag, wait_ns)) { alive = false; return; }
+          tc_fence_after();
+        }
+        const uint32_t u_addr = ring_smem + s * 2 * C::kTileBytes, w_addr = u_addr + C::kTileBytes;
+        const uint32_t t_half = tmem_base + (uint32_t)(h * 128);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
-          const uint64_t bd = make_smem_desc(w_addr + (uint32_t)((h * 4 + kk) * 2048), C::kHalfBytes, 1024);
-          if (leader) mma_ts(tmem_base + (uint32_t)C::kAcc1, t_half + (uint32_t)(kk * 8), bd, idesc_g, (hs > 0 || kk > 0) ? 1u : 0u);
+          const uint64_t bd = make_smem_desc(u_addr + (uint32_t)((h * 4 + kk) * 2048), C::kHalfBytes, 1024);
+          if (leader) mma_ts(tmem_base + (uint32_t)C::kAcc0, t_half + 64u + (uint32_t)(kk * 8), bd, idesc_g, (hs > 0 || kk > 0) ? 1u : 0u);
+        }
+        if constexpr (KEYS) {
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t bd = make_smem_desc(w_addr + (uint32_t)((h * 4 + kk) * 2048), C::kHalfBytes, 1024);
+            if (leader) mma_ts(tmem_base + (uint32_t)C::kAcc1, t_half + (uint32_t)(kk * 8), bd, idesc_g, (hs > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        if (leader) {
+          if (h == 1) tc_commit(bar_ring_empty + 8 * s);   // both halves of the streamed pair are consumed
+          if (hs == halves - 1) {
+            tc_commit(bar_acc_full);
+            tc_commit(bar_xy_empty);                       // the stationary pair may be replaced
+          }
+        }
+      };
+      for (int hs = 0; hs < halves && alive; ++hs) {
+        const int h = hs & 1;
+        const uint32_t gs = g + (uint32_t)(hs >> 1);
+        const int s = (int)(gs % C::kRing);
+        if (h == 0) {
+          if (!mbar_wait(bar_ring_full + 8 * s, (gs / C::kRing) & 1u, abort_flag, wait_ns)) { alive = false; break; }
+        }
+        tc_fence_after();
+        const uint32_t u_addr = ring_smem + s * 2 * C::kTileBytes + (uint32_t)(h * 8192);   // rows 64h.. of each 64-column block
+        const uint32_t w_addr = u_addr + C::kTileBytes;
+        const uint32_t t_half = tmem_base + (uint32_t)(h * 128);
+        // S (or S^T) = X U^T and dP = Y W^T over the half's 64 streamed rows: both operands K-major
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * C::kHalfBytes + (kk & 3) * 32);
+          const uint64_t ad = make_smem_desc(x_smem + off, 16, 1024), bd = make_smem_desc(u_addr + off, 16, 1024);
+          if (leader) mma_ss(t_half, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+          const uint32_t off = (uint32_t)((kk >> 2) * C::kHalfBytes + (kk & 3) * 32);
+          const uint64_t ad = make_smem_desc(y_smem + off, 16, 1024), bd = make_smem_desc(w_addr + off, 16, 1024);
+          if (leader) mma_ss(t_half + 64u, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+        }
+        if (leader) tc_commit(bar_s_full + 8 * h);
+        if (hs >= 1) {
+          const int prev = hs - 1;
+          if (!mbar_wait(bar_p_full + 8 * (prev & 1), (g + (uint32_t)(prev >> 1)) & 1u, abort_flag, wait_ns)) { alive = false; break; }
+          tc_fence_after();
+          issue_g(prev);
         }
       }
-      if (leader) {
-        if (h == 1) tc_commit(bar_ring_empty + 8 * s);   // both halves of the streamed pair are consumed
-        if (hs == halves - 1) tc_commit(bar_acc_full);
+      if (alive) {
+        const int prev = halves - 1;
+        if (mbar_wait(bar_p_full + 8 * (prev & 1), (g + (uint32_t)(prev >> 1)) & 1u, abort_flag, wait_ns)) {
+          tc_fence_after();
+          issue_g(prev);
+        } else {
+          alive = false;
+        }
       }
-    };
-    for (int hs = 0; hs < halves && alive; ++hs) {
-      const int j = hs >> 1, h = hs & 1, s = j % C::kRing;
-      if (h == 0) {
-        if (!mbar_wait(bar_ring_full + 8 * s, (uint32_t)((j / C::kRing) & 1), abort_flag, wait_ns)) { alive = false; break; }
-        tc_fence_after();
-      }
-      const uint32_t u_addr = ring_smem + s * 2 * C::kTileBytes + (uint32_t)(h * 8192);   // rows 64h.. of each 64-column block
-      const uint32_t w_addr = u_addr + C::kTileBytes;
-      const uint32_t t_half = tmem_base + (uint32_t)(h * 128);
-      // S (or S^T) = X U^T and dP = Y W^T over the half's 64 streamed rows: both operands K-major
-#pragma unroll
-      for (int kk = 0; kk < HD / 16; ++kk) {
-        const uint32_t off = (uint32_t)((kk >> 2) * C::kHalfBytes + (kk & 3) * 32);
-        const uint64_t ad = make_smem_desc(x_smem + off, 16, 1024), bd = make_smem_desc(u_addr + off, 16, 1024);
-        if (leader) mma_ss(t_half, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
-      }
-#pragma unroll
-      for (int kk = 0; kk < HD / 16; ++kk) {
-        const uint32_t off = (uint32_t)((kk >> 2) * C::kHalfBytes + (kk & 3) * 32);
-        const uint64_t ad = make_smem_desc(y_smem + off, 16, 1024), bd = make_smem_desc(w_addr + off, 16, 1024);
-        if (leader) mma_ss(t_half + 64u, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
-      }
-      if (leader) tc_commit(bar_s_full + 8 * h);
-      if (hs >= 1) {
-        const int prev = hs - 1;
-        if (!mbar_wait(bar_p_full + 8 * (prev & 1), (uint32_t)((prev >> 1) & 1), abort_flag, wait_ns)) { alive = false; break; }
-        tc_fence_after();
-        issue_g(prev);
-      }
-    }
-    if (alive && halves > 0) {
-      const int prev = halves - 1;
-      if (mbar_wait(bar_p_full + 8 * (prev & 1), (uint32_t)((prev >> 1) & 1), abort_flag, wait_ns)) {
-        tc_fence_after();
-        issue_g(prev);
-      }
+      g += (uint32_t)w.steps;
+      ++live;
     }
   } else {
     // ===================================== probabilities, dS, epilogue =====================================
@@ -293,138 +343,149 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
     const uint32_t t_s = tmem_base + lane_bits + (uint32_t)(half * 128), t_dp = t_s + 64u;
     const float sl2 = p.scale * kLog2e;
-    const int64_t kv_limit = kv_limit_of(p, w.b);
-    const int64_t my_row = (int64_t)w.tile * kT + row;   // key (KEYS) or query index of this thread
     float* my_vec = vec_smem + (warp - 2) * (2 * 2 * 64);   // [buffer][-lse*log2e, delta][64]
-    // rows are queries: the thread's own -lse*log2(e) and delta
-    float my_nl = -INFINITY, my_dl = 0.f;
-    if (!KEYS && my_row < p.seq_q) {
-      const float lse = p.lse[((int64_t)w.b * p.num_q_heads + w.h) * p.seq_q + my_row];
-      my_nl = (lse == -INFINITY || lse == INFINITY) ? -INFINITY : -lse * kLog2e;
-      my_dl = bp.delta[((int64_t)w.b * p.head_count + (w.h - p.head_begin)) * p.seq_q + my_row];
-    }
+    uint32_t g = 0, live = 0;
     bool alive = true;
-    for (int j = 0; j < w.steps; ++j) {
-      const int64_t col0 = (int64_t)step_tile(j) * kT + half * 64;   // first query (KEYS) or key of this half
-      const float* nls = my_vec + (j & 1) * (2 * 64);
-      const float* dls = nls + 64;
-      if constexpr (KEYS) {
-        // the streamed queries' -lse*log2(e) and delta, one private copy per warp (no cross-warp barrier)
-        const int h = step_head(j);
-        float* wl = my_vec + (j & 1) * (2 * 64);
+    for (int wave = 0; wave < waves && alive; ++wave) {
+      const int item = item_of(wave);
+      if (item >= bp.total_items) continue;
+      const Work w = decode_work<KEYS>(bp, item);
+      const int64_t kv_limit = kv_limit_of(p, w.b);
+      const int64_t my_row = (int64_t)w.tile * kT + row;   // key (KEYS) or query index of this thread
+      // rows are queries: the thread's own -lse*log2(e) and delta
+      float my_nl = -INFINITY, my_dl = 0.f;
+      if (!KEYS && my_row < p.seq_q) {
+        const float lse = p.lse[((int64_t)w.b * p.num_q_heads + w.h) * p.seq_q + my_row];
+        my_nl = (lse == -INFINITY || lse == INFINITY) ? -INFINITY : -lse * kLog2e;
+        my_dl = bp.delta[((int64_t)w.b * p.head_count + (w.h - p.head_begin)) * p.seq_q + my_row];
+      }
+      for (int j = 0; j < w.steps; ++j) {
+        const int64_t col0 = (int64_t)step_tile<KEYS>(w, j) * kT + half * 64;   // first query (KEYS) or key of this half
+        const float* nls = my_vec + (j & 1) * (2 * 64);
+        const float* dls = nls + 64;
+        if constexpr (KEYS) {
+          // the streamed queries' -lse*log2(e) and delta, one private copy per warp (no cross-warp barrier)
+          const int h = step_head<KEYS>(w, j);
+          float* wl = my_vec + (j & 1) * (2 * 64);
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          const int c = t * 32 + lane;
-          const int64_t q = col0 + c;
-          float nl = -INFINITY, dl = 0.f;
-          if (q < p.seq_q) {
-            const float lse = p.lse[((int64_t)w.b * p.num_q_heads + h) * p.seq_q + q];
-            nl = (lse == -INFINITY || lse == INFINITY) ? -INFINITY : -lse * kLog2e;
-            dl = bp.delta[((int64_t)w.b * p.head_count + (h - p.head_begin)) * p.seq_q + q];
+          for (int t = 0; t < 2; ++t) {
+            const int c = t * 32 + lane;
+            const int64_t q = col0 + c;
+            float nl = -INFINITY, dl = 0.f;
+            if (q < p.seq_q) {
+              const float lse = p.lse[((int64_t)w.b * p.num_q_heads + h) * p.seq_q + q];
+              nl = (lse == -INFINITY || lse == INFINITY) ? -INFINITY : -lse * kLog2e;
+              dl = bp.delta[((int64_t)w.b * p.head_count + (h - p.head_begin)) * p.seq_q + q];
+            }
+            wl[c] = nl;
+            wl[64 + c] = dl;
           }
-          wl[c] = nl;
-          wl[64 + c] = dl;
+          __syncwarp();
         }
-        __syncwarp();
-      }
-      // visible columns of this thread's row within the half: [lo, hi]
-      int64_t lo = 0, hi = 63;
-      if constexpr (KEYS) {
-        if (my_row >= kv_limit) hi = -1;
-        if (p.causal) lo = my_row - p.causal_offset - col0;   // query >= key - offset
-      } else {
-        hi = kv_limit - 1 - col0;
-        if (p.causal) {
-          const int64_t c = my_row + p.causal_offset - col0;
-          if (c < hi) hi = c;
-        }
-      }
-      const bool edge = __any_sync(0xffffffffu, lo > 0 || hi < 63);
-
-      bool ok = mbar_wait(bar_s_full + 8 * half, (uint32_t)(j & 1), abort_flag, wait_ns);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { alive = false; break; }
-      tc_fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        uint32_t sr[32], dr[32];
-        tmem_ld32(t_s + (uint32_t)c0, sr);
-        tmem_ld32(t_dp + (uint32_t)c0, dr);
-        tc_wait_ld();
-        uint32_t pk[16], dk[16];
-#pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          float pv[2], dv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int cc = c0 + c + e;
-            const float nl = KEYS ? nls[cc] : my_nl;
-            const float dl = KEYS ? dls[cc] : my_dl;
-            float pe = ex2_approx(fmaf(__uint_as_float(sr[c + e]), sl2, nl));
-            if (edge && (cc < lo || cc > hi)) pe = 0.f;
-            pv[e] = pe;
-            dv[e] = pe * (__uint_as_float(dr[c + e]) - dl);
+        // visible columns of this thread's row within the half: [lo, hi]
+        int64_t lo = 0, hi = 63;
+        if constexpr (KEYS) {
+          if (my_row >= kv_limit) hi = -1;
+          if (p.causal) lo = my_row - p.causal_offset - col0;   // query >= key - offset
+        } else {
+          hi = kv_limit - 1 - col0;
+          if (p.causal) {
+            const int64_t c = my_row + p.causal_offset - col0;
+            if (c < hi) hi = c;
           }
-          pk[c >> 1] = pack2<kBf16>(pv[0], pv[1]);
-          dk[c >> 1] = pack2<kBf16>(dv[0], dv[1]);
         }
-        // 16-bit P and dS go back over the fp32 columns they came from (columns [c0/2, c0/2+16) were read already)
-        if constexpr (KEYS) tmem_st16(t_s + (uint32_t)(c0 >> 1), pk);
-        tmem_st16(t_dp + (uint32_t)(c0 >> 1), dk);
-      }
-      tc_wait_st();
-      tc_fence_before();
-      mbar_arrive(bar_p_full + 8 * half);
-    }
+        const bool edge = __any_sync(0xffffffffu, lo > 0 || hi < 63);
 
-    // ---- epilogue: accumulators -> global, one row per thread ------------------------------------------------
-    if (alive) {
-      bool have = w.steps > 0;
-      if (have) {
-        bool ok = mbar_wait(bar_acc_full, 0, abort_flag, wait_ns);
+        bool ok = mbar_wait(bar_s_full + 8 * half, (g + (uint32_t)j) & 1u, abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
-        if (!ok) have = false, alive = false;
+        if (!ok) { alive = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t sr[32], dr[32];
+          tmem_ld32(t_s + (uint32_t)c0, sr);
+          tmem_ld32(t_dp + (uint32_t)c0, dr);
+          tc_wait_ld();
+          uint32_t pk[16], dk[16];
+#pragma unroll
+          for (int c = 0; c < 32; c += 2) {
+            float pv[2], dv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int cc = c0 + c + e;
+              const float nl = KEYS ? nls[cc] : my_nl;
+              const float dl = KEYS ? dls[cc] : my_dl;
+              float pe = ex2_approx(fmaf(__uint_as_float(sr[c + e]), sl2, nl));
+              if (edge && (cc < lo || cc > hi)) pe = 0.f;
+              pv[e] = pe;
+              dv[e] = pe * (__uint_as_float(dr[c + e]) - dl);
+            }
+            pk[c >> 1] = pack2<kBf16>(pv[0], pv[1]);
+            dk[c >> 1] = pack2<kBf16>(dv[0], dv[1]);
+          }
+          // 16-bit P and dS go back over the fp32 columns they came from (columns [c0/2, c0/2+16) were read already)
+          if constexpr (KEYS) tmem_st16(t_s + (uint32_t)(c0 >> 1), pk);
+          tmem_st16(t_dp + (uint32_t)(c0 >> 1), dk);
+        }
+        tc_wait_st();
+        tc_fence_before();
+        mbar_arrive(bar_p_full + 8 * half);
+      }
+      if (!alive) break;
+
+      // ---- epilogue: accumulators -> global, one row per thread ----------------------------------------------
+      const bool have = w.steps > 0;
+      if (have) {
+        bool ok = mbar_wait(bar_acc_full, live & 1u, abort_flag, wait_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { alive = false; break; }
         tc_fence_after();
       }
-      if (alive) {
-        const int64_t rows_total = KEYS ? p.seq_kv : p.seq_q;
-        const bool row_valid = my_row < rows_total;
-        float* out0;
-        float* out1 = nullptr;
-        if constexpr (KEYS) {
-          const int64_t base = (((int64_t)w.b * (p.head_count / p.group) + (w.kvh - p.head_begin / p.group)) * p.seq_kv + my_row) * HD;
-          out0 = bp.dk + base;
-          out1 = bp.dv + base;
-        } else {
-          out0 = bp.dq + (((int64_t)w.b * p.head_count + (w.h - p.head_begin)) * p.seq_q + my_row) * HD;
-        }
-        {
-          // the two groups of row warps split the stores: dK | dV, or the two halves of dQ's columns
-          const int a = KEYS ? half : 0;
-          float* out = a == 0 ? out0 : out1;
-          const float f = a == 0 ? p.scale : 1.f;
-          const uint32_t t_acc = tmem_base + lane_bits + (uint32_t)(a == 0 ? C::kAcc0 : C::kAcc1);
-          const int c_begin = KEYS ? 0 : half * (HD / 2), c_end = KEYS ? HD : c_begin + HD / 2;
+      const int64_t rows_total = KEYS ? p.seq_kv : p.seq_q;
+      const bool row_valid = my_row < rows_total;
+      float* out0;
+      float* out1 = nullptr;
+      if constexpr (KEYS) {
+        const int64_t base = (((int64_t)w.b * (p.head_count / p.group) + (w.kvh - p.head_begin / p.group)) * p.seq_kv + my_row) * HD;
+        out0 = bp.dk + base;
+        out1 = bp.dv + base;
+      } else {
+        out0 = bp.dq + (((int64_t)w.b * p.head_count + (w.h - p.head_begin)) * p.seq_q + my_row) * HD;
+      }
+      {
+        // the two groups of row warps split the stores: dK | dV, or the two halves of dQ's columns
+        const int a = KEYS ? half : 0;
+        float* out = a == 0 ? out0 : out1;
+        const float f = a == 0 ? p.scale : 1.f;
+        const uint32_t t_acc = tmem_base + lane_bits + (uint32_t)(a == 0 ? C::kAcc0 : C::kAcc1);
+        const int c_begin = KEYS ? 0 : half * (HD / 2), c_end = KEYS ? HD : c_begin + HD / 2;
 #pragma unroll
-          for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-            uint32_t r[32];
-            if (have) {
-              tmem_ld32(t_acc + (uint32_t)c0, r);
-              tc_wait_ld();
-            } else {
+        for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+          uint32_t r[32];
+          if (have) {
+            tmem_ld32(t_acc + (uint32_t)c0, r);
+            tc_wait_ld();
+          } else {
 #pragma unroll
-              for (int c = 0; c < 32; ++c) r[c] = 0u;
-            }
-            if (row_valid) {
+            for (int c = 0; c < 32; ++c) r[c] = 0u;
+          }
+          if (row_valid) {
 #pragma unroll
-              for (int c = 0; c < 32; c += 8)
-                st_global_v8(out + c0 + c, __float_as_uint(__uint_as_float(r[c]) * f), __float_as_uint(__uint_as_float(r[c + 1]) * f),
-                             __float_as_uint(__uint_as_float(r[c + 2]) * f), __float_as_uint(__uint_as_float(r[c + 3]) * f),
-                             __float_as_uint(__uint_as_float(r[c + 4]) * f), __float_as_uint(__uint_as_float(r[c + 5]) * f),
-                             __float_as_uint(__uint_as_float(r[c + 6]) * f), __float_as_uint(__uint_as_float(r[c + 7]) * f));
-            }
+            for (int c = 0; c < 32; c += 8)
+              st_global_v8(out + c0 + c, __float_as_uint(__uint_as_float(r[c]) * f), __float_as_uint(__uint_as_float(r[c + 1]) * f),
+                           __float_as_uint(__uint_as_float(r[c + 2]) * f), __float_as_uint(__uint_as_float(r[c + 3]) * f),
+                           __float_as_uint(__uint_as_float(r[c + 4]) * f), __float_as_uint(__uint_as_float(r[c + 5]) * f),
+                           __float_as_uint(__uint_as_float(r[c + 6]) * f), __float_as_uint(__uint_as_float(r[c + 7]) * f));
           }
         }
+      }
+      if (have) {
+        // every lane's reads of the accumulators are complete: the next item's gradient products may overwrite them
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_acc_empty);
+        g += (uint32_t)w.steps;
+        ++live;
       }
     }
   }
@@ -496,10 +557,16 @@ cudaError_t launch_t(const BwdParams& bp, cudaStream_t stream, int* launches, co
   const int64_t items_q = (int64_t)sp.q_tiles * p.head_count * p.batch;
   const int64_t items_kv = (int64_t)sp.k_tiles * (p.head_count / p.group) * p.batch;
   if (items_q > 0x7fffffffll || items_kv > 0x7fffffffll) { *why = "work item count out of range"; return cudaErrorInvalidValue; }
-  kq<<<(unsigned)items_q, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, sp);
+  int dev = 0, sms = 0;
+  e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess || sms <= 0) { *why = "cannot read the SM count"; return e != cudaSuccess ? e : cudaErrorInvalidValue; }
+  sp.total_items = (int)items_q;
+  kq<<<(unsigned)(items_q < sms ? items_q : sms), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, sp);
   e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  kkv<<<(unsigned)items_kv, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, sp);
+  sp.total_items = (int)items_kv;
+  kkv<<<(unsigned)(items_kv < sms ? items_kv : sms), kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, sp);
   *launches += 2;
   return cudaGetLastError();
 }
