@@ -112,7 +112,7 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* tm,
 }
 
 // Untiled bulk copy global -> shared of `bytes` (a multiple of 16; both addresses 16-byte aligned), completion counted
-// in bytes on `bar`.  No multicast.
+// in bytes on `bar`; this CTA only.
 __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
