@@ -477,6 +477,7 @@ int aidn_sdpa_backward(aidn_sdpa_t h, const aidn_sdpa_bwd_args* a, void* cu_stre
     bp.dout_t = static_cast<char*>(a->fwd.workspace) +
                 align_up(a->fwd.batch * h->head_count * a->fwd.seq_q * (int64_t)sizeof(float), 256);
   bp.no_tcgen05 = h->d.path == AIDN_PATH_GENERIC ? 1 : 0;
+  bp.round_dout = 0;
   int launches = 0, used_tcgen05 = 0;
   cudaError_t e = aidn::launch_backward(bp, h->d.qkv_dtype, (cudaStream_t)cu_stream, &launches, &used_tcgen05);
   if (e != cudaSuccess) return fail_cuda(e, "backward");

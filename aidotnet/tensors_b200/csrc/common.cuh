@@ -185,6 +185,8 @@ struct BwdParams {
   float* delta;       // [B, Hc, Sq] scratch
   void* dout_t;       // scratch: dO in the input dtype, dense [B, Hc, Sq, D] (16-bit inputs with an fp32 dO), or null
   int32_t no_tcgen05; // 1: stay on the mma.sync / FFMA kernels (desc.path == AIDN_PATH_GENERIC)
+  int32_t round_dout; // set by the launcher: delta is summed from dO as rounded into dout_t (what the tensor-core
+                      // kernels multiply with), so that every row of dS sums to zero as it does in exact arithmetic
 };
 // *used_tcgen05 tells which family ran the dQ and dK / dV launches.
 cudaError_t launch_backward(const BwdParams& bp, int dtype, cudaStream_t stream, int* launches, int* used_tcgen05);

@@ -51,18 +51,23 @@ __global__ void __launch_bounds__(128) bwd_delta_kernel(const BwdParams bp) {
     const float4* o4 = reinterpret_cast<const float4*>(static_cast<const float*>(p.out) + ob);
     const float4* g4 = reinterpret_cast<const float4*>(static_cast<const float*>(bp.dout) + gb);
     for (int d4 = lane; d4 < p.head_dim / 4; d4 += 32) {
-      const float4 o = o4[d4], g = g4[d4];
-      acc += g.x * o.x + g.y * o.y + g.z * o.z + g.w * o.w;
+      const float4 o = o4[d4];
+      float4 g = g4[d4];
       if (gt) {
         T t4[4] = {from_float<T>(g.x), from_float<T>(g.y), from_float<T>(g.z), from_float<T>(g.w)};
         *reinterpret_cast<uint2*>(gt + 4 * d4) = *reinterpret_cast<const uint2*>(t4);
+        if (bp.round_dout) g = make_float4(to_float<T>(t4[0]), to_float<T>(t4[1]), to_float<T>(t4[2]), to_float<T>(t4[3]));
       }
+      acc += g.x * o.x + g.y * o.y + g.z * o.z + g.w * o.w;
     }
   } else {
     for (int d = lane; d < p.head_dim; d += 32) {
-      const float go = load_o<T>(bp.dout, gb + d, p.out_f32);
+      float go = load_o<T>(bp.dout, gb + d, p.out_f32);
+      if (gt) {
+        gt[d] = from_float<T>(go);   // the tensor-core dK / dV kernels stream dO in the input dtype
+        if (bp.round_dout) go = to_float<T>(gt[d]);
+      }
       acc += go * load_o<T>(p.out, ob + d, p.out_f32);
-      if (gt) gt[d] = from_float<T>(go);   // the tensor-core dK / dV kernels stream dO in the input dtype
     }
   }
 #pragma unroll
@@ -754,7 +759,15 @@ cudaError_t launch_bwd_t(const BwdParams& bp, cudaStream_t stream, int* launches
   const SdpaParams& p = bp.p;
   constexpr int PITCH = DMAX + 4;
   dim3 g0((unsigned)((p.seq_q + 3) / 4), (unsigned)p.head_count, (unsigned)p.batch);
-  bwd_delta_kernel<T><<<g0, 128, 0, stream>>>(bp);
+  {
+    // the tensor-core families multiply with dO in the input dtype: sum delta from the same rounded values
+    bool tensor_cores = false;
+    if constexpr (sizeof(T) == 2 && (DMAX == 64 || DMAX == 128))
+      tensor_cores = p.head_dim == DMAX && !p.block_table && mma_aligned(bp) && (bp.dout_t || !p.out_f32);
+    BwdParams b0 = bp;
+    b0.round_dout = tensor_cores ? 1 : 0;
+    bwd_delta_kernel<T><<<g0, 128, 0, stream>>>(b0);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   *used_tcgen05 = 0;

@@ -188,3 +188,22 @@ def test_backward_tensor_core_families(dtype, shape, causal):
         _check(dv, rv, dtype, f"dV {shape} path {path}")
         dq2, dk2, dv2 = _fwd_bwd(q, k, v, dout, dtype=dtype, causal=causal, bottom_right=True, kv_len=kv_len, path=path)
         assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+
+
+@pytest.mark.parametrize("path", [N.PATH_AUTO, N.PATH_GENERIC])
+def test_backward_single_visible_key_has_no_score_gradient(path):
+    """With one visible key the probabilities are exactly 1, so dS = dP - delta must cancel: dQ = dK = 0 and dV = the
+    column sum of dO.  The tensor-core kernels multiply with dO rounded to the input dtype; delta is summed from the
+    same rounded values, otherwise the difference of the two roundings accumulates over the queries into dK."""
+    B, H, Sq, Sk, D = 2, 2, 265, 239, 64
+    q, qf = gen((B, H, Sq, D), "bf16", 971)
+    k, kf = gen((B, H, Sk, D), "bf16", 972)
+    v, vf = gen((B, H, Sk, D), "bf16", 973)
+    dout, dof = gen((B, H, Sq, D), "f32", 974, scale=1.0)
+    kv_len = np.array([1, 1], np.int32)
+    dq, dk, dv = _fwd_bwd(q, k, v, dout, dtype="bf16", kv_len=kv_len, path=path)
+    assert float(dq.abs().max()) <= 1e-4 and float(dk.abs().max()) <= 1e-4
+    want = torch.from_numpy(dof).to(torch.bfloat16).to(torch.float32).sum(dim=2).numpy()   # [B, H, D]
+    got = dv.cpu().numpy()
+    assert np.abs(got[:, :, 0, :] - want).max() <= 2e-2 * np.abs(want).max()
+    assert np.abs(got[:, :, 1:, :]).max() == 0.0
