@@ -297,12 +297,13 @@ cudaError_t launch_t(const ProjGemm& g, cudaStream_t stream, int num_sms, int32_
   }
   if (!ok) { *why = "cuTensorMapEncodeTiled rejected a tensor (address or stride alignment)"; return cudaErrorInvalidValue; }
   GemmParams gp;
-  gp.row_tiles_per_batch = (int)((g.seq + kBM - 1) / kBM);
-  gp.row_tiles = (int)(g.batch * gp.row_tiles_per_batch);
+  const int64_t row_tiles_per_batch = (g.seq + kBM - 1) / kBM, col_tiles = (g.n / BN) * g.num_mats;
+  const int64_t total = g.batch * row_tiles_per_batch * col_tiles;
+  if (total <= 0 || total > 0x3fffffff || kGroupRows * col_tiles > 0x3fffffff) { *why = "tile count out of range"; return cudaErrorInvalidValue; }
+  gp.row_tiles_per_batch = (int)row_tiles_per_batch;
+  gp.row_tiles = (int)(g.batch * row_tiles_per_batch);
   gp.col_tiles_per_mat = (int)(g.n / BN);
-  gp.col_tiles = gp.col_tiles_per_mat * g.num_mats;
-  const int64_t total = (int64_t)gp.row_tiles * gp.col_tiles_per_mat * g.num_mats;
-  if (total <= 0 || total > 0x3fffffff) { *why = "tile count out of range"; return cudaErrorInvalidValue; }
+  gp.col_tiles = (int)col_tiles;
   gp.total_tiles = (int)total;
   gp.k_blocks = (int)((g.k + kBK - 1) / kBK);
   gp.seq = (int)g.seq;

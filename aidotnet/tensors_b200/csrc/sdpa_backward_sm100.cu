@@ -24,8 +24,8 @@
 // dV [256+D,256+2D).  Issue order  S(0) S(1) G(0) S(2) G(1) S(3) ...: UMMAs execute in issue order, so the scores of
 // half i+2, which overwrite P / dS of half i, cannot pass the gradient products G(i) that read them.
 //
-// Serves 16-bit inputs, head_dim 64 / 128, contiguous K / V, causal and length masks; everything else stays on the
-// kernels of sdpa_backward.cu.  Supersedes flash_attention_backward_deterministic_{dq,dkv} of the reference
+// Serves 16-bit inputs, head_dim 64 / 128, contiguous K / V, causal and length masks, and (MASKED instantiation) an
+// additive bias or a keep-mask read by the row threads; everything else stays on the kernels of sdpa_backward.cu.  Supersedes flash_attention_backward_deterministic_{dq,dkv} of the reference
 // (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/CudaAttentionKernels.cs:251-390), whose formulas it keeps.
 #include <cuda.h>
 
@@ -131,7 +131,7 @@ __device__ __forceinline__ int step_head(const Work& w, int j) { return KEYS ? w
 template <bool KEYS>
 __device__ __forceinline__ int step_tile(const Work& w, int j) { return KEYS ? w.first + j % w.count : j; }
 
-template <typename T, int HD, bool KEYS>
+template <typename T, int HD, bool KEYS, bool MASKED>
 __global__ void __launch_bounds__(kThreads, 1)
     sdpa_backward_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                                const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -363,6 +363,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int64_t col0 = (int64_t)step_tile<KEYS>(w, j) * kT + half * 64;   // first query (KEYS) or key of this half
         const float* nls = my_vec + (j & 1) * (2 * 64);
         const float* dls = nls + 64;
+        int64_t mask_base = 0;
+        if constexpr (MASKED)
+          mask_base = (int64_t)w.b * p.mask_stride[0] + (int64_t)(KEYS ? step_head<KEYS>(w, j) : w.h) * p.mask_stride[1];
         if constexpr (KEYS) {
           // the streamed queries' -lse*log2(e) and delta, one private copy per warp (no cross-warp barrier)
           const int h = step_head<KEYS>(w, j);
@@ -413,9 +416,21 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
               const int cc = c0 + c + e;
-              const float nl = KEYS ? nls[cc] : my_nl;
+              float nl = KEYS ? nls[cc] : my_nl;
               const float dl = KEYS ? dls[cc] : my_dl;
+              bool keep = true;
+              if constexpr (MASKED) {
+                // additive bias (after the scale) or keep-mask of this (query, key), as finish_logit() applies them
+                const int64_t qi = KEYS ? col0 + cc : my_row, kj = KEYS ? my_row : col0 + cc;
+                if (qi < p.seq_q && kj < p.seq_kv) {
+                  const int64_t idx = mask_base + qi * p.mask_stride[2] + kj * p.mask_stride[3];
+                  if (p.mask_kind == AIDN_MASK_KEEP_U8) keep = static_cast<const uint8_t*>(p.mask)[idx] != 0;
+                  else if (p.mask_kind == AIDN_MASK_KEEP_F32) keep = static_cast<const float*>(p.mask)[idx] != 0.0f;
+                  else nl = fmaf(static_cast<const float*>(p.mask)[idx], kLog2e, nl);
+                }
+              }
               float pe = ex2_approx(fmaf(__uint_as_float(sr[c + e]), sl2, nl));
+              if (!keep) pe = 0.f;
               if (edge && (cc < lo || cc > hi)) pe = 0.f;
               pv[e] = pe;
               dv[e] = pe * (__uint_as_float(dr[c + e]) - dl);
@@ -549,8 +564,9 @@ cudaError_t launch_t(const BwdParams& bp, cudaStream_t stream, int* launches, co
   sp.k_tiles = (int)((p.seq_kv + kT - 1) / kT);
   sp.do_head_off = bp.dout_t ? p.head_begin : 0;
   sp.wait_budget_ns = kWaitBudgetNs;
-  auto kq = sdpa_backward_sm100_kernel<T, HD, false>;
-  auto kkv = sdpa_backward_sm100_kernel<T, HD, true>;
+  const bool masked = p.mask_kind != AIDN_MASK_NONE;
+  auto kq = masked ? sdpa_backward_sm100_kernel<T, HD, false, true> : sdpa_backward_sm100_kernel<T, HD, false, false>;
+  auto kkv = masked ? sdpa_backward_sm100_kernel<T, HD, true, true> : sdpa_backward_sm100_kernel<T, HD, true, false>;
   e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) { *why = "cannot raise the dynamic shared memory limit"; return e; }
@@ -577,7 +593,8 @@ bool backward_sm100_supported(const BwdParams& bp, int dtype) {
   const SdpaParams& p = bp.p;
   if (dtype != AIDN_BF16 && dtype != AIDN_F16) return false;
   if (p.head_dim != 64 && p.head_dim != 128) return false;
-  if (p.block_table || p.mask_kind != AIDN_MASK_NONE || p.softcap > 0.f || !p.lse) return false;
+  if (p.block_table || p.softcap > 0.f || !p.lse) return false;
+  if (p.mask_kind != AIDN_MASK_NONE && !p.mask) return false;
   if (!bp.dout_t && p.out_f32) return false;   // dO must be available in the input dtype
   if (!aligned_bhs(p.q, p.qs, p.num_q_heads, p.batch, 16) || !aligned_bhs(p.k, p.ks, p.num_kv_heads, p.batch, 16) ||
       !aligned_bhs(p.v, p.vs, p.num_kv_heads, p.batch, 16))

@@ -207,3 +207,43 @@ def test_backward_single_visible_key_has_no_score_gradient(path):
     got = dv.cpu().numpy()
     assert np.abs(got[:, :, 0, :] - want).max() <= 2e-2 * np.abs(want).max()
     assert np.abs(got[:, :, 1:, :]).max() == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("kind", ["bias", "bias_broadcast", "keep_u8", "keep_f32"])
+@pytest.mark.parametrize("path", [N.PATH_AUTO, N.PATH_GENERIC])
+def test_backward_tensor_core_families_with_bias_and_masks(dtype, kind, path):
+    """16-bit inputs with an additive bias (per batch entry or shared, FlashAttentionBackward's attentionBias,
+    CudaBackend.cs:8580-8604) or a keep-mask: the row threads of the tcgen05 kernels read them per (query, key); the
+    mma.sync kernels (desc.path = generic) serve the same calls.  Several tiles per sequence, grouped-query heads,
+    a padded batch entry, causal on top of the mask."""
+    B, Hq, Hkv, Sq, Sk, D = 2, 4, 2, 200, 333, 128
+    q, qf = gen((B, Hq, Sq, D), dtype, 981)
+    k, kf = gen((B, Hkv, Sk, D), dtype, 982)
+    v, vf = gen((B, Hkv, Sk, D), dtype, 983)
+    dout, dof = gen((B, Hq, Sq, D), "f32", 984, scale=1.0)
+    kv_len = np.array([Sk, Sk - 50], np.int32)
+    rng = np.random.default_rng(985)
+    bias = keep = None
+    if kind == "bias":
+        m = rng.standard_normal((B, Hq, Sq, Sk)).astype(np.float32)
+        bias, mk = m, N.MASK_ADD_F32
+    elif kind == "bias_broadcast":
+        m = rng.standard_normal((1, Hq, Sq, Sk)).astype(np.float32)
+        bias, mk = m, N.MASK_ADD_F32
+    elif kind == "keep_u8":
+        keep = rng.random((B, 1, Sq, Sk)) < 0.7
+        keep[..., 0] = True
+        m, mk = keep.astype(np.uint8), N.MASK_KEEP_U8
+    else:
+        keep = rng.random((1, 1, Sq, Sk)) < 0.7
+        keep[..., 0] = True
+        m, mk = keep.astype(np.float32), N.MASK_KEEP_F32
+    info = {}
+    dq, dk, dv = _fwd_bwd(q, k, v, dout, dtype=dtype, causal=True, bottom_right=True, mask=torch.from_numpy(m).cuda(),
+                          mask_kind=mk, kv_len=kv_len, path=path, info=info)
+    assert info["path"] == (N.PATH_PREFILL_SM100 if path == N.PATH_AUTO else N.PATH_GENERIC)
+    rq, rk, rv, _, _ = O.sdpa_backward(qf, kf, vf, dof, causal=True, causal_offset=Sk - Sq, bias=bias, keep=keep, kv_len=kv_len)
+    _check(dq, rq, dtype, f"dQ {kind} path {path}")
+    _check(dk, rk, dtype, f"dK {kind} path {path}")
+    _check(dv, rv, dtype, f"dV {kind} path {path}")
