@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|c2bwdfull|c3bwd|mha|mhaq|qkvrope|qkvrope1|qkvrope70b|qkvrope32] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c2o16|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|c2bwdfull|c3bwd|mha|mhaq|qkvrope|qkvrope1|qkvrope70b|qkvrope32] [--impl reference]
 
 One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
 default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
@@ -31,6 +31,8 @@ WORKLOADS = {
     # name: (B, Hq, Hkv, Sq, Sk, D, causal, dtype, kind)
     "c2": dict(B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True, kind="prefill",
                name="llama_prefill_B4_H32_S2048_D128_causal_bf16"),
+    "c2o16": dict(B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True, kind="prefill", out16=True,
+                  name="llama_prefill_B4_H32_S2048_D128_causal_bf16_in_bf16_out"),
     "c3": dict(B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill",
                name="gqa_prefill_B2_Hq32_Hkv8_S8192_D128_causal_bf16"),
     "c5shard": dict(B=1, Hq=8, Hkv=1, Sq=32768, Sk=32768, D=128, causal=True, kind="prefill",
@@ -116,7 +118,7 @@ def algorithmic_bytes(w, kv_len=None):
     if w["kind"] == "decode":
         kv = 2 * w["Hkv"] * w["D"] * 2 * int(np.sum(kv_len))
         return kv + w["B"] * w["Hq"] * w["D"] * (2 + 4)
-    qo = w["B"] * w["Hq"] * w["Sq"] * w["D"] * (2 + 4)
+    qo = w["B"] * w["Hq"] * w["Sq"] * w["D"] * (2 + (2 if w.get("out16") else 4))
     return qo + 2 * w["B"] * w["Hkv"] * w["Sk"] * w["D"] * 2
 
 
@@ -399,8 +401,9 @@ class Runner:
         dev = torch.device("cuda", device_index)
         self.q, self.k, self.v, self.kv_len_host = make_inputs(w, dev, seed)
         self.kv_len = torch.from_numpy(self.kv_len_host).to(dev) if self.kv_len_host is not None else None
-        self.out = torch.empty((w["B"], w["Hq"], w["Sq"], w["D"]), dtype=torch.float32, device=dev)
-        self.h = N.Handle(device=device_index, qkv_dtype=N.BF16, out_dtype=N.F32, head_dim=w["D"], num_q_heads=w["Hq"],
+        out16 = bool(w.get("out16"))   # the reference's contract is an fp32 output; *o16 workloads keep the output in bf16
+        self.out = torch.empty((w["B"], w["Hq"], w["Sq"], w["D"]), dtype=torch.bfloat16 if out16 else torch.float32, device=dev)
+        self.h = N.Handle(device=device_index, qkv_dtype=N.BF16, out_dtype=N.BF16 if out16 else N.F32, head_dim=w["D"], num_q_heads=w["Hq"],
                           num_kv_heads=w["Hkv"], causal=w["causal"], causal_bottom_right=True,
                           max_batch=w["B"], max_seq_q=w["Sq"], max_seq_kv=w["Sk"], decode_chunk=decode_chunk)
         self.stream = torch.cuda.current_stream(dev).cuda_stream
