@@ -478,6 +478,7 @@ int aidn_sdpa_backward(aidn_sdpa_t h, const aidn_sdpa_bwd_args* a, void* cu_stre
                 align_up(a->fwd.batch * h->head_count * a->fwd.seq_q * (int64_t)sizeof(float), 256);
   bp.no_tcgen05 = h->d.path == AIDN_PATH_GENERIC ? 1 : 0;
   bp.round_dout = 0;
+  bp.expire = h->debug_mode == 3 ? 1 : 0;
   int launches = 0, used_tcgen05 = 0;
   cudaError_t e = aidn::launch_backward(bp, h->d.qkv_dtype, (cudaStream_t)cu_stream, &launches, &used_tcgen05);
   if (e != cudaSuccess) return fail_cuda(e, "backward");
@@ -759,7 +760,7 @@ int aidn_mha_forward(aidn_sdpa_t h, const aidn_mha_args* a, void* cu_stream) {
   auto gemm = [&](const char* what) -> int {
     if (tensor_route) {
       if (!aidn::proj_gemm_sm100_supported(g, &why)) return fail(AIDN_EUNSUPPORTED, "mha: %s", why);
-      e = aidn::launch_proj_gemm_sm100(g, stream, h->num_sms, h->status_dev, &why);
+      e = aidn::launch_proj_gemm_sm100(g, stream, h->num_sms, h->status_dev, &why, h->debug_mode == 3);
     } else {
       if (!aidn::proj_gemm_generic_supported(g, &why)) return fail(AIDN_EUNSUPPORTED, "mha: %s", why);
       e = aidn::launch_proj_gemm_generic(g, d.qkv_dtype, stream);

@@ -185,6 +185,7 @@ struct BwdParams {
   float* delta;       // [B, Hc, Sq] scratch
   void* dout_t;       // scratch: dO in the input dtype, dense [B, Hc, Sq, D] (16-bit inputs with an fp32 dO), or null
   int32_t no_tcgen05; // 1: stay on the mma.sync / FFMA kernels (desc.path == AIDN_PATH_GENERIC)
+  int32_t expire;     // test hook of the tcgen05 kernels: loads are withheld and every bounded wait gives up after 20 ms
   int32_t round_dout; // set by the launcher: delta is summed from dO as rounded into dout_t (what the tensor-core
                       // kernels multiply with), so that every row of dS sums to zero as it does in exact arithmetic
 };
@@ -240,8 +241,9 @@ struct ProjGemm {
   bool bf16;            // bf16 inputs, else fp16
 };
 bool proj_gemm_sm100_supported(const ProjGemm& g, const char** why);
+// expire: test hook - the producer withholds its loads and every bounded wait gives up after 20 ms.
 cudaError_t launch_proj_gemm_sm100(const ProjGemm& g, cudaStream_t stream, int num_sms, int32_t* status,
-                                   const char** why);
+                                   const char** why, bool expire = false);
 // The same contract in fp32 FFMA arithmetic for any sizes and for a / w of `dtype` (csrc/proj_gemm_generic.cu).
 bool proj_gemm_generic_supported(const ProjGemm& g, const char** why);
 cudaError_t launch_proj_gemm_generic(const ProjGemm& g, int dtype, cudaStream_t stream);

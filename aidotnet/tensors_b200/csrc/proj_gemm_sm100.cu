@@ -66,6 +66,7 @@ struct GemmParams {
   int32_t head_dim;
   int32_t out_f32;
   int32_t* status;
+  int32_t withhold_loads;        // test hook: the producer issues no loads, so that the bounded waits run out
   uint64_t wait_budget_ns;
 };
 
@@ -150,7 +151,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int s = (int)(kb_total % kStages);
         const uint32_t phase = (kb_total / kStages) & 1u;
         if (!mbar_wait(bar_empty + 8 * s, phase ^ 1u, abort_flag, wait_ns)) { alive = false; break; }
-        if (leader) {
+        if (leader && !gp.withhold_loads) {
           const uint32_t bar = bar_full + 8 * s;
           const uint32_t a_dst = smem_base + s * C::kStageBytes;
           const uint32_t b_dst = a_dst + C::kABytes;
@@ -276,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 template <int BN, bool BF16>
-cudaError_t launch_t(const ProjGemm& g, cudaStream_t stream, int num_sms, int32_t* status, const char** why) {
+cudaError_t launch_t(const ProjGemm& g, cudaStream_t stream, int num_sms, int32_t* status, const char** why, bool expire) {
   using C = GCfg<BN>;
   cudaError_t e = tmap::resolve_encode();
   if (e != cudaSuccess) { *why = "cuTensorMapEncodeTiled is not available from the driver"; return e; }
@@ -310,7 +311,8 @@ cudaError_t launch_t(const ProjGemm& g, cudaStream_t stream, int num_sms, int32_
   gp.head_dim = g.head_dim;
   gp.out_f32 = g.out_f32 ? 1 : 0;
   gp.status = status;
-  gp.wait_budget_ns = kWaitBudgetNs;
+  gp.withhold_loads = expire ? 1 : 0;
+  gp.wait_budget_ns = expire ? 20000000ull : kWaitBudgetNs;   // 20 ms in the time-out test
   auto kern = proj_gemm_sm100_kernel<BN, BF16>;
   e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) { *why = "cannot raise the dynamic shared memory limit"; return e; }
@@ -338,10 +340,10 @@ bool proj_gemm_sm100_supported(const ProjGemm& g, const char** why) {
 }
 
 cudaError_t launch_proj_gemm_sm100(const ProjGemm& g, cudaStream_t stream, int num_sms, int32_t* status,
-                                   const char** why) {
+                                   const char** why, bool expire) {
   const bool wide = g.n % 256 == 0;
-  if (g.bf16) return wide ? launch_t<256, true>(g, stream, num_sms, status, why) : launch_t<128, true>(g, stream, num_sms, status, why);
-  return wide ? launch_t<256, false>(g, stream, num_sms, status, why) : launch_t<128, false>(g, stream, num_sms, status, why);
+  if (g.bf16) return wide ? launch_t<256, true>(g, stream, num_sms, status, why, expire) : launch_t<128, true>(g, stream, num_sms, status, why, expire);
+  return wide ? launch_t<256, false>(g, stream, num_sms, status, why, expire) : launch_t<128, false>(g, stream, num_sms, status, why, expire);
 }
 
 }  // namespace aidn

@@ -71,6 +71,7 @@ struct BwdSm100Params {
   int32_t q_tiles, k_tiles;
   int32_t do_head_off;  // head coordinate of the dO tensor map = h - do_head_off
   int32_t total_items;
+  int32_t withhold_loads;   // test hook: the producer issues no loads, so that the bounded waits run out
   uint64_t wait_budget_ns;
 };
 
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t gs = g + (uint32_t)j;
         const int s = (int)(gs % C::kRing);
         if (!mbar_wait(bar_ring_empty + 8 * s, ((gs / C::kRing) & 1u) ^ 1u, abort_flag, wait_ns)) { alive = false; return; }
-        if (leader) {
+        if (leader && !bp.withhold_loads) {
           const uint32_t bar = bar_ring_full + 8 * s;
           const uint32_t u_dst = ring_smem + s * 2 * C::kTileBytes, w_dst = u_dst + C::kTileBytes;
           const int head = step_head<KEYS>(w, j), row = step_tile<KEYS>(w, j) * kT;
@@ -563,7 +564,8 @@ cudaError_t launch_t(const BwdParams& bp, cudaStream_t stream, int* launches, co
   sp.q_tiles = (int)((p.seq_q + kT - 1) / kT);
   sp.k_tiles = (int)((p.seq_kv + kT - 1) / kT);
   sp.do_head_off = bp.dout_t ? p.head_begin : 0;
-  sp.wait_budget_ns = kWaitBudgetNs;
+  sp.withhold_loads = bp.expire ? 1 : 0;
+  sp.wait_budget_ns = bp.expire ? 20000000ull : kWaitBudgetNs;   // 20 ms in the time-out test
   const bool masked = p.mask_kind != AIDN_MASK_NONE;
   auto kq = masked ? sdpa_backward_sm100_kernel<T, HD, false, true> : sdpa_backward_sm100_kernel<T, HD, false, false>;
   auto kkv = masked ? sdpa_backward_sm100_kernel<T, HD, true, true> : sdpa_backward_sm100_kernel<T, HD, true, false>;

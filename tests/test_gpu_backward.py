@@ -247,3 +247,40 @@ def test_backward_tensor_core_families_with_bias_and_masks(dtype, kind, path):
     _check(dq, rq, dtype, f"dQ {kind} path {path}")
     _check(dk, rk, dtype, f"dK {kind} path {path}")
     _check(dv, rv, dtype, f"dV {kind} path {path}")
+
+
+def test_backward_bounded_waits_expire_cleanly():
+    """Failure detection without a fault on the tcgen05 backward: with the test hook the producers withhold the streamed
+    tiles, the bounded waits (20 ms) run out in both launches, poll() reports AIDN_ETIMEOUT and the next backward on the
+    same handle is correct."""
+    B, H, S, D = 1, 2, 384, 128
+    q, qf = gen((B, H, S, D), "bf16", 991)
+    k, kf = gen((B, H, S, D), "bf16", 992)
+    v, vf = gen((B, H, S, D), "bf16", 993)
+    dout, dof = gen((B, H, S, D), "f32", 994, scale=1.0)
+    out = torch.zeros((B, H, S, D), device="cuda")
+    lse = torch.zeros((B, H, S), device="cuda")
+    dq, dk, dv = (torch.zeros((B, H, S, D), device="cuda") for _ in range(3))
+    h = N.Handle(device=0, qkv_dtype=N.BF16, head_dim=D, num_q_heads=H, num_kv_heads=H, causal=True, emit_lse=True)
+    stream = torch.cuda.current_stream().cuda_stream
+    common = dict(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), lse=lse.data_ptr(), batch=B, seq_q=S,
+                  seq_kv=S, stream=stream)
+    h.launch(**common)
+    nb = h.backward_workspace_bytes(B, S)
+    ws = torch.empty(nb, dtype=torch.uint8, device="cuda")
+    bwd = lambda: h.backward(dout=dout.data_ptr(), dq=dq.data_ptr(), dk=dk.data_ptr(), dv=dv.data_ptr(), workspace=ws.data_ptr(),
+                             workspace_bytes=nb, **common)
+    h.debug_set(None, 3)
+    bwd()
+    with pytest.raises(N.AidnError) as e:
+        h.poll(stream)
+    assert e.value.status == N.ETIMEOUT
+    h.debug_set(None, 0)
+    bwd()
+    h.poll(stream)
+    assert h.last_path == N.PATH_PREFILL_SM100
+    rq, rk, rv, _, _ = O.sdpa_backward(qf, kf, vf, dof, causal=True, causal_offset=0)
+    _check(dq, rq, "bf16", "dQ after a timed-out backward")
+    _check(dk, rk, "bf16", "dK after a timed-out backward")
+    _check(dv, rv, "bf16", "dV after a timed-out backward")
+    h.close()

@@ -283,3 +283,32 @@ def test_backend_mirror_exact_switch_and_small_heads():
         else:
             _check(got, O.mha_forward(_round(xf, "bf16"), *[_round(w, "bf16") for w in wfs], heads), "tensor route")
     be.Dispose()
+
+
+def test_mha_forward_bounded_waits_expire_cleanly():
+    """Failure detection without a fault: a test hook makes the producers of the projection GEMMs (and of the attention
+    kernel) withhold their loads, so every bounded wait (20 ms in this mode) runs out.  The kernels must unwind and free
+    TMEM, poll() must report AIDN_ETIMEOUT, and the next call on the same handle must be correct."""
+    B, S, heads, d = 2, 300, 2, 128
+    Dm = heads * d
+    x, xf, ws, wfs = _inputs(B, S, heads, d, "bf16", 5100)
+    out = torch.zeros((B, S, Dm), device="cuda")
+    h = N.Handle(device=0, qkv_dtype=N.BF16, out_dtype=N.BF16, head_dim=d, num_q_heads=heads, num_kv_heads=heads)
+    nb = h.mha_workspace_bytes(B, S, N.BF16, N.BF16)
+    wsb = torch.zeros(nb + 1024, dtype=torch.uint8, device="cuda")
+    base = _align(wsb.data_ptr())
+    stream = torch.cuda.current_stream().cuda_stream
+    call = lambda: h.mha_forward(input=x.data_ptr(), q_weight=ws[0].data_ptr(), k_weight=ws[1].data_ptr(),
+                                 v_weight=ws[2].data_ptr(), out_weight=ws[3].data_ptr(), out=out.data_ptr(), batch=B, seq=S,
+                                 input_dtype=N.BF16, weight_dtype=N.BF16, out_dtype=N.F32, workspace=base, workspace_bytes=nb,
+                                 stream=stream)
+    h.debug_set(None, 3)
+    call()
+    with pytest.raises(N.AidnError) as e:
+        h.poll(stream)
+    assert e.value.status == N.ETIMEOUT
+    h.debug_set(None, 0)
+    call()
+    h.poll(stream)
+    _check(out, O.mha_forward(xf, *wfs, heads), "call after a timed-out call")
+    h.close()
