@@ -4,6 +4,10 @@
 
 Objects go to ``aidotnet/tensors_b200/build/`` and the library to ``aidotnet/tensors_b200/lib/``; both are
 git-ignored.  The ptxas resource report of every kernel is kept in ``build/ptxas.log``.
+
+Development variants: ``build_variant("trace", ["-DAIDN_PREFILL_TRACE=1"])`` compiles the same sources with extra
+nvcc flags into ``lib/libaidotnet_sdpa_sm100.<name>.so`` (objects under ``build/<name>/``); ``native.load`` picks a
+variant when the environment variable ``AIDN_SDPA_LIB`` names its path.  The shipped library is the flag-less one.
 """
 from __future__ import annotations
 
@@ -43,10 +47,10 @@ def _deps_mtime() -> float:
     return max(os.path.getmtime(f) for f in files)
 
 
-def _compile(src: str, verbose: bool) -> str:
-    obj = os.path.join(BUILD, os.path.splitext(src)[0] + ".o")
+def _compile(src: str, verbose: bool, outdir: str = BUILD, extra=()) -> str:
+    obj = os.path.join(outdir, os.path.splitext(src)[0] + ".o")
     cmd = [_nvcc(), "-O3", "-std=c++17", *ARCH, "-lineinfo", "-ccbin", _host_cxx(), "-Xcompiler", "-fPIC,-fvisibility=hidden",
-           "-Xptxas", "-v", "--expt-relaxed-constexpr", "-c", os.path.join(CSRC, src), "-o", obj]
+           "-Xptxas", "-v", "--expt-relaxed-constexpr", *extra, "-c", os.path.join(CSRC, src), "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed for {src}:\n{r.stdout}\n{r.stderr}")
@@ -70,6 +74,28 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     return LIB
+
+
+def build_variant(name: str, flags, verbose: bool = False, only=None) -> str:
+    """Compiles the sources (or just those named in ``only``, linking the shipped build's objects for the rest) with
+    the extra nvcc ``flags`` into ``lib/libaidotnet_sdpa_sm100.<name>.so``."""
+    outdir = os.path.join(BUILD, name)
+    os.makedirs(outdir, exist_ok=True)
+    os.makedirs(LIBDIR, exist_ok=True)
+    lib = os.path.join(LIBDIR, f"libaidotnet_sdpa_sm100.{name}.so")
+    mine = [s for s in SOURCES if only is None or s in only]
+    if only is not None:
+        build()
+    with concurrent.futures.ThreadPoolExecutor(max_workers=len(mine)) as ex:
+        logs = list(ex.map(lambda s: _compile(s, verbose, outdir, tuple(flags)), mine))
+    with open(os.path.join(outdir, "ptxas.log"), "w") as f:
+        f.writelines(logs)
+    objs = [os.path.join(outdir if s in mine else BUILD, os.path.splitext(s)[0] + ".o") for s in SOURCES]
+    cmd = [_nvcc(), "-shared", *ARCH, "-ccbin", _host_cxx(), "-cudart", "static", "-o", lib, *objs, "-ldl", "-lpthread", "-lrt"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    return lib
 
 
 HOST_TEST_BIN = os.path.join(BUILD, "backend_tests")

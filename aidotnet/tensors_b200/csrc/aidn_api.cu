@@ -11,6 +11,7 @@
 #include <new>
 
 #include "common.cuh"
+#include "../../../include/aidn_sdpa_debug.h"
 
 namespace {
 
@@ -78,6 +79,7 @@ struct aidn_sdpa {
   int last_launches;
   float* debug;
   int debug_mode;
+  aidn::PrefillMapCache prefill_maps;   // tensor maps of the last tcgen05 prefill launch (see common.cuh)
 };
 
 namespace {
@@ -190,6 +192,7 @@ int aidn_sdpa_create(const aidn_sdpa_desc* desc, aidn_sdpa_t* out) {
   h->debug = nullptr;
   h->debug_mode = 0;
   h->num_sms = 0;
+  std::memset(&h->prefill_maps, 0, sizeof(h->prefill_maps));
   e = cudaDeviceGetAttribute(&h->num_sms, cudaDevAttrMultiProcessorCount, d.device);
   if (e == cudaSuccess) e = cudaMalloc(&h->status_dev, 4 * sizeof(int32_t));
   if (e == cudaSuccess) e = cudaMemset(h->status_dev, 0, 4 * sizeof(int32_t));
@@ -235,10 +238,8 @@ int64_t aidn_sdpa_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq_q, i
 int aidn_sdpa_last_path(aidn_sdpa_t h) { return h ? h->last_path : -1; }
 int aidn_sdpa_last_launch_count(aidn_sdpa_t h) { return h ? h->last_launches : -1; }
 
-// Diagnostic tap of the tcgen05 kernel (not part of the public header).  mode 1: CTA 0 writes its first score
-// tile, its un-normalised accumulator and the running (sum, max) into `buf`; mode 2: every CTA writes a timeline
-// of 16 globaltimer stamps.
-AIDN_API int aidn_sdpa_debug_set(aidn_sdpa_t h, float* buf, int mode) {
+// Test and development hook, declared in include/aidn_sdpa_debug.h.
+int aidn_sdpa_debug_set(aidn_sdpa_t h, float* buf, int mode) {
   if (!h) return AIDN_EINVAL;
   h->debug = buf;
   h->debug_mode = (buf || mode == 3) ? mode : 0;
@@ -316,6 +317,9 @@ int build_params(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* pg
     if (a->batch > 1 && pg->block_table_stride * pg->block_size < a->seq_kv && !a->kv_len)
       return fail(AIDN_EINVAL, "launch_paged: block_table_stride (%lld) holds fewer than seq_kv keys",
                   (long long)pg->block_table_stride);
+    // kv_len lives on the device and cannot be checked here: no key beyond what a table row can address is ever
+    // looked up, whatever kv_len[b] says (it would read the next sequence's row, or past the table)
+    if (a->batch > 1 && pg->block_table_stride * pg->block_size < p.seq_kv) p.seq_kv = pg->block_table_stride * pg->block_size;
     p.block_table = pg->block_table;
     p.bt_stride = pg->block_table_stride;
     p.block_size = pg->block_size;
@@ -385,7 +389,8 @@ int launch_common(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* p
     }
     e = aidn::launch_decode(p, d.qkv_dtype, chunk, nchunks, ws, stream, &launches);
   } else if (path == AIDN_PATH_PREFILL_SM100) {
-    e = aidn::launch_prefill_sm100(p, d.qkv_dtype, stream, h->status_dev + 1, h->num_sms, h->debug, h->debug_mode, &why);
+    e = aidn::launch_prefill_sm100(p, d.qkv_dtype, stream, h->status_dev + 1, h->num_sms, h->debug, h->debug_mode,
+                                   &h->prefill_maps, &why);
     launches = 1;
     if (e != cudaSuccess && why[0]) return fail(AIDN_ECUDA, "launch: %s (%s)", why, cudaGetErrorName(e));
   } else {
@@ -501,6 +506,13 @@ int aidn_sdpa_decode_noalloc(const aidn_sdpa_desc* desc, const aidn_sdpa_args* a
   if (!(d.softcap >= 0.f)) return fail(AIDN_EINVAL, "decode_noalloc: softcap must be >= 0");
   if (d.decode_chunk < 0 || (d.decode_chunk > 0 && d.decode_chunk % 8 != 0))
     return fail(AIDN_EINVAL, "decode_noalloc: decode_chunk must be 0 or a positive multiple of 8");
+  int cur = -1;
+  cudaError_t ce = cudaGetDevice(&cur);
+  if (ce != cudaSuccess) return fail_cuda(ce, "decode_noalloc: cudaGetDevice");
+  if (cur != d.device)
+    return fail(AIDN_EINVAL, "decode_noalloc: desc.device (%d) is not the current device (%d)", d.device, cur);
+  if (!aidn_sdpa_device_supported(d.device))
+    return fail(AIDN_EUNSUPPORTED, "decode_noalloc: device %d is not compute capability 10.x", d.device);
   aidn_sdpa tmp;  // on the stack: only the fields the chunk heuristic reads
   std::memset(&tmp, 0, sizeof(tmp));
   tmp.d = d;
@@ -509,6 +521,7 @@ int aidn_sdpa_decode_noalloc(const aidn_sdpa_desc* desc, const aidn_sdpa_args* a
   if (d.head_begin < 0 || tmp.head_count <= 0 || d.head_begin + tmp.head_count > d.num_q_heads ||
       d.head_begin % tmp.group != 0 || tmp.head_count % tmp.group != 0)
     return fail(AIDN_EINVAL, "decode_noalloc: the head shard must lie inside the tensor and cover whole KV groups");
+  if (tmp.head_count > 65535) return fail(AIDN_EINVAL, "decode_noalloc: more than 65535 heads in one shard");
   if (!a->q || !a->k || !a->v || !a->out) return fail(AIDN_EINVAL, "decode_noalloc: null tensor pointer");
   if (a->batch <= 0 || a->batch > 65535 || a->seq_kv <= 0) return fail(AIDN_EINVAL, "decode_noalloc: bad batch or seq_kv");
   if (a->seq_q != 1) return fail(AIDN_EUNSUPPORTED, "decode_noalloc: seq_q must be 1");
@@ -591,7 +604,8 @@ int aidn_qkv_rope_cache(const aidn_qkv_rope_args* a, void* cu_stream) {
     return fail(AIDN_EUNSUPPORTED, "qkv_rope_cache: heads * head_dim above %lld", (long long)aidn::qkv_rope_max_model());
   if ((uintptr_t)a->weights % 16 != 0 || (uintptr_t)a->input % 16 != 0)
     return fail(AIDN_EINVAL, "qkv_rope_cache: input and weights must be 16-byte aligned");
-  // per-device facts, looked up once: this entry point has no handle to keep them in
+  // per-device facts, looked up once: this entry point has no handle to keep them in.  Unsynchronised on purpose:
+  // two threads racing here write the same values (the lookups are idempotent), and g_sms is written last.
   static int g_sms[64] = {0};
   static int g_ok[64] = {0};
   int dev = -1;
@@ -684,6 +698,8 @@ int mha_check_handle(const aidn_sdpa* h) {
   if (d.emit_lse || d.softcap > 0.f || d.nccl_comm)
     return fail(AIDN_EUNSUPPORTED, "mha: the handle must not ask for log-sum-exp, softcap or a gather");
   if (d.mask_kind == AIDN_MASK_ADD_F32) return fail(AIDN_EUNSUPPORTED, "mha: the mask is a keep-mask (Tensor<bool>) or absent");
+  // desc.causal is honoured (causal self-attention without materialising the mask): an extension, the reference's
+  // MultiHeadAttentionForward expresses causality through its boolean mask only.
   return AIDN_OK;
 }
 }  // namespace

@@ -117,6 +117,7 @@ __device__ __forceinline__ float finish_logit(const SdpaParams& p, float s, int 
 }
 
 // Number of keys a batch entry can see before causal masking: min(seq_kv, kv_len[b]).
+// (With a block table the host has already capped seq_kv at the keys the table's rows can address.)
 __device__ __forceinline__ int64_t kv_limit_of(const SdpaParams& p, int b) {
   int64_t lim = p.seq_kv;
   if (p.kv_len) {
@@ -220,11 +221,25 @@ cudaError_t launch_qkv_rope_cache(const QkvRopeParams& p, int weight_dtype, int 
 cudaError_t launch_rope_interleaved(const float* in, const float* cosc, const float* sinc, float* out, int64_t rows,
                                     int head_dim, int seq_len, int start_position, cudaStream_t stream);
 
-struct PrefillPlan;  // opaque to callers of the sm100 prefill launcher
+// Per-handle memory of the tcgen05 prefill launcher: the four TMA tensor maps of the last launch, with the tensors
+// they were encoded for, and which kernel instantiations already had their shared-memory limit raised in the
+// handle's context.  A launch whose pointers, extents and strides match re-uses the maps; encoding happens on the host
+// only and is capture-safe either way.
+struct alignas(64) PrefillMapCache {
+  unsigned char maps[4][128];   // CUtensorMap images: q, k, v, out
+  struct Key {
+    const void* q; const void* k; const void* v; const void* out;
+    int64_t qs[3], ks[3], vs[3], os[3];
+    int64_t seq_q, kv_rows;
+    int32_t batch, kv_batch, num_q_heads, num_kv_heads, head_dim, kv_box, out_f32, dtype;
+  } key;
+  bool valid;
+  bool attr_set[8];             // by instantiation: (fp16 ? 4 : 0) + (head_dim 128 ? 2 : 0) + (masked ? 1 : 0)
+};
 bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why);
+// cache may be null (maps are then encoded on every call).
 cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t stream, int32_t* sched, int num_sms,
-                                 float* debug, int debug_mode, const char** why);
-cudaError_t prefill_sm100_prepare();  // one-time per-process function attribute setup
+                                 float* debug, int debug_mode, PrefillMapCache* cache, const char** why);
 
 // Projection GEMM of the fused multi-head-attention forward (csrc/proj_gemm_sm100.cu):
 // c[i][b, s, n] = sum_k a[b, s, k] * w[i][k, n] for up to three weight matrices that share a; column n lands at

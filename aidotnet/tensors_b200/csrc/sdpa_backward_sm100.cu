@@ -431,10 +431,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
               }
               float pe = ex2_approx(fmaf(__uint_as_float(sr[c + e]), sl2, nl));
-              if (!keep) pe = 0.f;
-              if (edge && (cc < lo || cc > hi)) pe = 0.f;
+              if (edge && (cc < lo || cc > hi)) keep = false;
+              // selected, not multiplied: a masked position stays 0 whatever its score or dP is (0 * NaN is NaN)
+              pe = keep ? pe : 0.f;
               pv[e] = pe;
-              dv[e] = pe * (__uint_as_float(dr[c + e]) - dl);
+              dv[e] = keep ? pe * (__uint_as_float(dr[c + e]) - dl) : 0.f;
             }
             pk[c >> 1] = pack2<kBf16>(pv[0], pv[1]);
             dk[c >> 1] = pack2<kBf16>(dv[0], dv[1]);

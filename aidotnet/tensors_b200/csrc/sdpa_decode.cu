@@ -764,25 +764,55 @@ cudaError_t launch_decode_t(const SdpaParams& p, int chunk, int nchunks, float* 
 constexpr int64_t kStaticScratchFloats = 4ll * 1024 * 1024;  // 16 MiB
 static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchFloats];
 
-constexpr int kMaxDevices = 64;
-float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+// The array has one address per CUDA context, not per device ordinal: a process may hold the primary context and a
+// context of its own making (the reference's backend creates one with cuCtxCreate) on the same GPU, and each has its
+// own copy of the library's device image.  The address is therefore looked up once per context and remembered under
+// the context's id (cuCtxGetId: unique for the life of the process, unlike the handle, which a later context may reuse).
+constexpr int kMaxContexts = 64;
+struct ScratchSlot {
+  unsigned long long ctx_id;
+  float* ptr;
+};
+ScratchSlot g_static_scratch[kMaxContexts] = {};
+int g_static_scratch_used = 0;
 std::mutex g_static_scratch_mutex;
 
-// In host code the array's name is only a stand-in; the device address has to be asked for, per device, with
-// that device current.
+typedef int (*CtxGetIdFn)(void*, unsigned long long*);   // CUresult cuCtxGetId(CUcontext, unsigned long long*)
+CtxGetIdFn ctx_get_id_fn() {
+  static CtxGetIdFn fn = nullptr;   // written under g_static_scratch_mutex
+  if (!fn) {
+    void* raw = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuCtxGetId", &raw, cudaEnableDefault, &qres) == cudaSuccess && raw &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<CtxGetIdFn>(raw);
+  }
+  return fn;
+}
+
+// In host code the array's name is only a stand-in; the device address has to be asked for with the context that
+// will run the kernel current.
 cudaError_t static_scratch_address(float** out) {
+  // binds the runtime to the caller's current context (or to the primary one when the thread has none)
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
   std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
-  if (!g_static_scratch_ptr[dev]) {
-    float* ptr = nullptr;
-    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_static_scratch);
-    if (e != cudaSuccess) return e;
-    g_static_scratch_ptr[dev] = ptr;
-  }
-  *out = g_static_scratch_ptr[dev];
+  unsigned long long id = 0;
+  CtxGetIdFn get = ctx_get_id_fn();
+  const bool have_id = get && get(nullptr, &id) == 0;   // a null context means the current one
+  if (have_id)
+    for (int i = 0; i < g_static_scratch_used; ++i)
+      if (g_static_scratch[i].ctx_id == id) {
+        *out = g_static_scratch[i].ptr;
+        return cudaSuccess;
+      }
+  float* ptr = nullptr;
+  e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_decode_static_scratch);
+  if (e != cudaSuccess) return e;
+  // without a context id (or with the table full) the address is simply looked up again on every call
+  if (have_id && g_static_scratch_used < kMaxContexts) g_static_scratch[g_static_scratch_used++] = {id, ptr};
+  *out = ptr;
   return cudaSuccess;
 }
 

@@ -76,7 +76,9 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaPar
       const int j = idx / DMAX, d = idx - j * DMAX;
       const int64_t key = j0 + j;
       const int64_t row = paged ? kv_rows[j] : key;
-      const bool ok = key < p.seq_kv && d < D && row >= 0;
+      // keys past this CTA's last visible key (padding beyond kv_len, a partly filled pool block, the causal
+      // future) are never read: their probability is 0, and 0 * (NaN or Inf left in unused memory) would be NaN
+      const bool ok = key < kend && d < D && row >= 0;
       Ks[j * PITCH + d] = ok ? to_float<T>(kb[row * p.ks[2] + d]) : 0.f;
       Vs[j * PITCH + d] = ok ? to_float<T>(vb[row * p.vs[2] + d]) : 0.f;
     }

@@ -3,7 +3,7 @@
 // arithmetic; a second instantiation adds softcap, additive bias and keep-masks read by the softmax warps.
 //
 // A work item is TWO 128-row query tiles that share one KV head, so every K/V tile fetched into shared
-// memory feeds two score MMAs and two P.V MMAs.  The two tiles are two query heads of the same GQA group at
+// memory feeds the score and P.V products of both.  The two tiles are two query heads of the same GQA group at
 // the same rows (group size even) or two consecutive row tiles of one head.  One CTA per SM walks a list of
 // work items ordered heaviest first (causal), drawing the next item from a global counter when it finishes one.
 //
@@ -11,17 +11,25 @@
 //   warps 4-7   softmax of tile 1  keeps the running max / sum, rescales O lazily, writes P (16-bit) back
 //                                  into the S columns; at the end normalises O, stages it 128 bytes per row in
 //                                  swizzled shared memory (one 4 KiB buffer per warp) and issues TMA stores
-//   warp  8     TMA producer + scheduler: Q tiles, then K0, V0, K1, V1, ... through a ring of smem slots
-//   warp  9     UMMA issuer (one lane): S_i = Q_i K^T (smem x smem), O_i += P_i V (TMEM x smem); owns TMEM
+//   warp  8     TMA producer + scheduler: Q tiles, then K and V sub-tiles of 64 keys through a ring of 8 slots, in the
+//               order the issuers need them (K(0), K(1), V(0), K(2), V(1), ...): three sub-tiles of look-ahead, which
+//               a TMA load under full load needs (2700 cycles from a slot's release to its data, measured)
+//   warps 9,10  UMMA issuers (one lane each): S = Q K^T (smem x smem), O += P V (TMEM x smem); issuer b handles the
+//               sub-tiles of parity b of both query tiles, the two take turns; warp 9 owns TMEM
 //
-// TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D); P_i aliases the first 64 columns
-// of S_i.  The issue order per KV tile j is  PV_0(j), QK_0(j+1), PV_1(j), QK_1(j+1): UMMAs execute in issue
-// order, so QK_i(j+1) overwriting S_i cannot pass PV_i(j) reading P_i, and while one tile waits for its
-// softmax the tensor core works on the other.  Because the softmax warps also run the epilogue, the loads
-// and first score MMAs of the next work item overlap the epilogue of the current one.  (Measured alternatives:
-// a separate epilogue warpgroup drains TMEM too slowly through plain stores and stalls the next item's first
-// P.V; a shared-memory transpose with plain stores loses to the tensor core's own shared-memory traffic; two
-// 64-byte staging buffers per warp with twice as many TMA stores were slower than one 128-byte buffer.)
+// Scores are produced and consumed in SUB-TILES of 64 keys, and every query tile has TWO score buffers in TMEM:
+//   S_i[b] at columns i*128 + b*64 (b = sub-tile index & 1), P_i[b] (16-bit) over the first 32 columns of S_i[b],
+//   O_0 at [256, 256+D), O_1 at [256+D, 256+2D).
+// The issuer runs the score product one sub-tile ahead of the softmax: right after P_i(u).V it issues Q_i.K(u+2)^T
+// into the buffer that P_i(u) is being read from (UMMAs execute in issue order), so when the softmax warps finish
+// sub-tile u the scores of u+1 are already waiting in the other buffer.  With a single 128-column score buffer per
+// tile the chain  softmax -> P.V -> next scores -> softmax  was the period of the loop (3500 cycles per 128 keys,
+// measured with clock stamps: 2000 softmax + 1030 UMMA issue-to-completion + 490 hand-offs) and left the tensor and
+// MUFU pipes 55-60 % busy; here the softmax warps go from one sub-tile straight to the next and the loop runs at
+// the rate of the slower of the two pipes.  N = 64 score UMMAs read more shared memory per flop than N = 128 ones
+// (the Q operand is re-read for every 64 keys); the trade is measured in profiles/.
+// Because the softmax warps also run the epilogue, the loads and first score UMMAs of the next work item overlap
+// the epilogue of the current one.
 //
 // Supersedes flash_attention_v2 / grouped_query_attention / scaled_dot_product_attention of the reference
 // (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/CudaAttentionKernels.cs:28-234, 527-646) and its
@@ -30,11 +38,18 @@
 // P rounded to 16 bit for the second MMA, O rescale skipped while the max moves little (:711-802).
 #include <cuda.h>
 
+#include <cstring>
 #include <type_traits>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "tensor_map.hpp"
+
+// Development builds (-DAIDN_PREFILL_TRACE=1) carry a per-item timeline and a value tap in the hot loops; the
+// library that ships is built without them, so they cost no registers or predicates there.
+#ifndef AIDN_PREFILL_TRACE
+#define AIDN_PREFILL_TRACE 0
+#endif
 
 namespace aidn {
 namespace {
@@ -42,35 +57,43 @@ namespace {
 using namespace ptx;
 
 constexpr int kBM = 128;           // rows per query tile
-constexpr int kBN = 128;           // keys per KV tile
+constexpr int kBS = 64;            // keys per score sub-tile: one softmax step, one K / V ring slot, one TMA box
 constexpr int kSoftmaxWarps = 8;   // 2 tiles x 4 warps
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
-constexpr int kThreads = 384;          // 3 warpgroups: softmax 0, softmax 1, {producer, UMMA issuer, 2 idle}
-// Per-thread registers after setmaxnreg.  8*32*216 + 4*32*72 == 384*168: the two figures must add up to what the CTA
+constexpr int kThreads = 384;          // 3 warpgroups: softmax 0, softmax 1, {producer, 2 UMMA issuers, 1 idle}
+// Per-thread registers after setmaxnreg.  8*32*184 + 4*32*136 == 384*168: the two figures must add up to what the CTA
 // was launched with - setmaxnreg.inc waits, without any bound, for registers that another warpgroup of the same CTA has
 // given up, and a sum above the launch allocation never becomes available.
-constexpr int kSoftmaxRegs = 216;
-constexpr int kOtherRegs = 72;
+#ifndef AIDN_SOFTMAX_REGS
+#define AIDN_SOFTMAX_REGS 184
+#endif
+#ifndef AIDN_OTHER_REGS
+#define AIDN_OTHER_REGS 136
+#endif
+constexpr int kSoftmaxRegs = AIDN_SOFTMAX_REGS;
+constexpr int kOtherRegs = AIDN_OTHER_REGS;
 constexpr int kStageBytesPerWarp = 4096;   // epilogue staging: 32 rows x 128 B (128-byte swizzle), one per softmax warp
 constexpr int kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8 between rescales
-constexpr int kSchedConsumers = kSoftmaxWarps + 1;
+constexpr int kSchedConsumers = kSoftmaxWarps + 2;   // softmax warps and the two UMMA issuers
 static_assert(kSoftmaxWarps * 32 * kSoftmaxRegs + 4 * 32 * kOtherRegs <= kThreads * 168,
               "setmaxnreg budget exceeds the registers the CTA is launched with");
-constexpr int kItemWords = 12;   // mailbox entry: item, b, kvh, n_max, then (h, t, n, valid) of both tiles
+constexpr int kItemWords = 14;   // mailbox entry: item, b, kvh, n_max, (h, t, n, valid) of both tiles, v_tail
 
 template <int HD>
 struct Cfg {
-  static constexpr int kTileBytes = kBN * HD * 2;         // one K or V tile == one Q tile
-  static constexpr int kStages = HD == 128 ? 4 : 6;       // K/V ring slots
+  static constexpr int kTileBytes = kBM * HD * 2;         // one Q tile
+  static constexpr int kSubBytes = kBS * HD * 2;          // one K or V sub-tile (64 keys): a ring slot
+  static constexpr int kStages = HD == 128 ? 8 : 12;      // K/V ring slots
   static constexpr int kHalves = HD / 64;                 // 64-element (128-byte) column blocks per tile
-  static constexpr int kHalfBytes = kBN * 128;            // 16 KiB
-  static constexpr int kStageOff = (2 + kStages) * kTileBytes;
+  static constexpr int kHalfBytes = kBM * 128;            // 16 KiB: one column block of a Q tile
+  static constexpr int kKvHalfBytes = kBS * 128;          // 8 KiB: one column block of a K / V sub-tile
+  static constexpr int kStageOff = 2 * kTileBytes + kStages * kSubBytes;
   static constexpr int kBarOff = kStageOff + kSoftmaxWarps * kStageBytesPerWarp;
-  // q_full[2] q_empty[2] kv_full[S] kv_empty[S] s_full[2] p_full[2] o_full[2] sched_full[2] sched_empty[2]
-  static constexpr int kNumBars = 14 + 2 * kStages;
-  static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // tmem ptr, abort flag, then the 2-slot item mailbox
+  // q_full[2] q_empty[2] kv_full[S] kv_empty[S] s_full[2][2] p_full[2][2] o_full[2] pv_done[2] sched_full[2] sched_empty[2]
+  static constexpr int kNumBars = 20 + 2 * kStages;
+  static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // issue lock, tmem ptr, abort flag, then the 2-slot item mailbox
   static constexpr int kMailOff = kMiscOff + 16;
   static constexpr int kSmemBytes = kMailOff + 2 * kItemWords * 4 + 1024 /*align slack*/;
   static constexpr int kOCol = 256;
@@ -85,22 +108,25 @@ struct PrefillParams {
   int32_t per_batch;       // work items per rank per batch entry
   int32_t total_items;
   int32_t* sched;          // [0] next-item counter, [1] finished-CTA counter; both zero between launches
-  float* debug;            // optional tap
-  int32_t debug_mode;      // 1: values of the first work item of CTA 0; 2: per-item timeline (16 x u64 per item);
-                           // 3: the producer withholds the Q tiles, so that the bounded waits run out (test hook)
+  float* debug;            // trace builds only: tap / timeline buffer
+  int32_t debug_mode;      // 3: the producer withholds the Q tiles, so that the bounded waits run out (test hook);
+                           // trace builds: 2 = per-item timeline (16 x u64 per item), 4 = per-step clock stamps of CTA 0
   uint64_t wait_budget_ns; // longest single wait before the CTA gives up
 };
 
 struct TileInfo {
   int h;          // q head
   int t;          // row tile index
-  int n;          // KV tiles to process (0 = none visible)
+  int n;          // 64-key score sub-tiles to process (0 = none visible)
   bool valid;     // tile exists
 };
 
 struct Item {
   TileInfo tile[2];
-  int b, kvh, n_max;
+  int b, kvh;
+  int n_max;      // sub-tiles of the longer tile = K and V sub-tiles the item streams
+  int v_tail;     // > 0: rows of the item's last V sub-tile that hold keys of the sequence; the rows after them are
+                  // cleared in shared memory before the P.V product (0 = nothing to clear)
 };
 
 // The producer decodes a work item once (two integer divisions and the tile counts) and hands the result to the
@@ -112,6 +138,7 @@ __device__ __forceinline__ void publish_item(volatile int* box, int item, const 
     box[4 + 4 * i] = it.tile[i].h; box[5 + 4 * i] = it.tile[i].t;
     box[6 + 4 * i] = it.tile[i].n; box[7 + 4 * i] = it.tile[i].valid ? 1 : 0;
   }
+  box[12] = it.v_tail;
   box[0] = item;
 }
 
@@ -123,6 +150,7 @@ __device__ __forceinline__ Item read_item(const volatile int* box) {
     it.tile[i].h = box[4 + 4 * i]; it.tile[i].t = box[5 + 4 * i];
     it.tile[i].n = box[6 + 4 * i]; it.tile[i].valid = box[7 + 4 * i] != 0;
   }
+  it.v_tail = box[12];
   return it;
 }
 
@@ -162,9 +190,15 @@ __device__ __forceinline__ Item decode_item(const PrefillParams& pp, int item) {
       }
       if (kend < 0) kend = 0;
     }
-    it.tile[i].n = (int)((kend + kBN - 1) / kBN);
+    it.tile[i].n = (int)((kend + kBS - 1) / kBS);
   }
   it.n_max = it.tile[0].n > it.tile[1].n ? it.tile[0].n : it.tile[1].n;
+  // Rows of the last V tile past the sequence's last key hold whatever the caller's buffer holds there (padding after
+  // kv_len, the unused tail of a pool block).  Their probabilities are 0, but 0 * NaN is NaN in the P.V product, so
+  // the UMMA warp clears them.  Rows past seq_kv of a contiguous tensor are zero-filled by TMA itself.
+  it.v_tail = 0;
+  if ((p.kv_len || p.block_table) && (int64_t)it.n_max * kBS > kv_limit)
+    it.v_tail = (int)(kv_limit - (int64_t)(it.n_max - 1) * kBS);
   return it;
 }
 
@@ -183,19 +217,21 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t q_smem = smem_base;                           // 2 tiles
-  const uint32_t kv_smem = smem_base + 2 * C::kTileBytes;      // kStages tiles
+  const uint32_t kv_smem = smem_base + 2 * C::kTileBytes;      // kStages sub-tiles
   const uint32_t stage_smem = smem_base + C::kStageOff;        // 8 warps x 4 KiB
   const uint32_t bars = smem_base + C::kBarOff;
   const uint32_t bar_q_full = bars;                            // [2]
   const uint32_t bar_q_empty = bars + 16;                      // [2]
   const uint32_t bar_kv_full = bars + 32;                      // [kStages]
   const uint32_t bar_kv_empty = bar_kv_full + 8 * C::kStages;  // [kStages]
-  const uint32_t bar_s_full = bar_kv_empty + 8 * C::kStages;   // [2]
-  const uint32_t bar_p_full = bar_s_full + 16;                 // [2]
-  const uint32_t bar_o_full = bar_p_full + 16;                 // [2]
-  const uint32_t bar_sched_full = bar_o_full + 16;             // [2]
+  const uint32_t bar_s_full = bar_kv_empty + 8 * C::kStages;   // [tile][buffer]
+  const uint32_t bar_p_full = bar_s_full + 32;                 // [tile][buffer]
+  const uint32_t bar_o_full = bar_p_full + 32;                 // [2]
+  const uint32_t bar_pv_done = bar_o_full + 16;                // [2] one phase per P.V product of the tile
+  const uint32_t bar_sched_full = bar_pv_done + 16;            // [2]
   const uint32_t bar_sched_empty = bar_sched_full + 16;        // [2]
   volatile int* mailbox = reinterpret_cast<volatile int*>(smem_gen + C::kMailOff);  // [2][kItemWords]
+  int* issue_turn = reinterpret_cast<int*>(smem_gen + C::kMiscOff);   // turns of the two UMMA issuers completed so far
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::kMiscOff + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::kMiscOff + 12);
 
@@ -205,18 +241,22 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ---- setup ---------------------------------------------------------------------------------------
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    *issue_turn = 0;
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar_q_full + 8 * i, 1);
-      mbar_init(bar_q_empty + 8 * i, 1);
-      mbar_init(bar_s_full + 8 * i, 1);
-      mbar_init(bar_p_full + 8 * i, 128);
+      mbar_init(bar_q_empty + 8 * i, 2);   // both issuers read a Q tile
       mbar_init(bar_o_full + 8 * i, 1);
+      mbar_init(bar_pv_done + 8 * i, 1);
       mbar_init(bar_sched_full + 8 * i, 1);
       mbar_init(bar_sched_empty + 8 * i, kSchedConsumers);
     }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(bar_s_full + 8 * i, 1);
+      mbar_init(bar_p_full + 8 * i, 4);   // one arrival per softmax warp of the tile
+    }
     for (int s = 0; s < C::kStages; ++s) {
       mbar_init(bar_kv_full + 8 * s, 1);
-      mbar_init(bar_kv_empty + 8 * s, 1);
+      mbar_init(bar_kv_empty + 8 * s, 1);   // a sub-tile is read by one issuer
     }
     fence_mbar_init();
   }
@@ -247,14 +287,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_bits + (uint32_t)(i * kBN);
+    const uint32_t t_s = tmem_base + lane_bits + (uint32_t)(i * 2 * kBS);
     const uint32_t t_o = tmem_base + lane_bits + (uint32_t)(C::kOCol + i * HD);
     const uint32_t my_stage = stage_smem + (uint32_t)(warp * kStageBytesPerWarp);
     // 128-byte staging rows under the 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
     const uint32_t my_row = my_stage + (uint32_t)(lane * 128);
     const uint32_t my_swz = (uint32_t)(lane & 7);
-    uint32_t s_cnt = 0, o_cnt = 0;   // completed phases of s_full/p_full and o_full of this tile
-    bool stores_in_flight = false;   // a TMA store of this warp may still be reading the staging buffer
+    uint32_t s_par = 0;                // bit b: parity of the next phase of s_full[tile][b]
+    uint32_t o_cnt = 0;                // completed phases of o_full
+    uint32_t pv_par = 0;               // parity of the next phase of pv_done (one per item with two or more sub-tiles)
+    bool stores_in_flight = false;     // a TMA store of this warp may still be reading the staging buffer
     bool alive = true;
 
     for (int seq = 0; alive; ++seq) {
@@ -274,6 +316,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const TileInfo ti = it.tile[i];
       if (!ti.valid) continue;
       const int b = it.b;
+#if AIDN_PREFILL_TRACE
       unsigned long long* trace = pp.debug_mode == 2
           ? reinterpret_cast<unsigned long long*>(pp.debug) + (size_t)item * 16 : nullptr;
       const bool tracer = trace && row_in_tile == 0;
@@ -285,7 +328,15 @@ __global__ void __launch_bounds__(kThreads, 1)
           trace[15] = ((unsigned long long)smid << 32) | (unsigned)it.n_max;
         }
       }
-      const bool tap = pp.debug_mode == 1 && blockIdx.x == 0 && seq == 0;
+      // per-step clock stamps (mode 4): CTA 0, the first 8 items, up to 32 steps, 16 slots per step
+      long long* steps = (((pp.debug_mode == 4) || (pp.debug_mode == 6 && i == 0)) && blockIdx.x == 0 && seq < 8 && row_in_tile == 0)
+          ? reinterpret_cast<long long*>(pp.debug) + (size_t)seq * 32 * 16 + 5 * i : nullptr;
+#define STEP_STAMP(j, slot) do { if (steps && (j) < 32) steps[(j) * 16 + (slot)] = clock64(); } while (0)
+#else
+      constexpr bool tracer = false;
+      unsigned long long* const trace = nullptr;
+#define STEP_STAMP(j, slot) do { } while (0)
+#endif
 
       const int64_t qrow = (int64_t)ti.t * kBM + row_in_tile;
       const int64_t kv_limit = kv_limit_of(p, b);
@@ -294,39 +345,36 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       float m = -INFINITY, l = 0.f;
 
-      for (int j = 0; j < ti.n; ++j) {
-        bool ok = mbar_wait(bar_s_full + 8 * i, s_cnt & 1u, abort_flag, wait_ns);
+      for (int u = 0; u < ti.n; ++u) {
+        const uint32_t buf = (uint32_t)(u & 1);
+        const uint32_t t_sb = t_s + buf * kBS;
+        const uint32_t bar_off = 8u * (uint32_t)(2 * i) + 8u * buf;
+        bool ok = mbar_wait(bar_s_full + bar_off, (s_par >> buf) & 1u, abort_flag, wait_ns);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
         tc_fence_after();
-        if (tracer && j == 0) trace[2 + 8 * i] = globaltimer_ns();
+        if (tracer && u == 0) trace[2 + 8 * i] = globaltimer_ns();
+        STEP_STAMP(u, 0);
 
-        uint32_t sr[128];
-        tmem_ld32(t_s + 0, sr + 0);
-        tmem_ld32(t_s + 32, sr + 32);
-        tmem_ld32(t_s + 64, sr + 64);
-        tmem_ld32(t_s + 96, sr + 96);
+        uint32_t sr[kBS];
+        tmem_ld32(t_sb + 0, sr + 0);
+        tmem_ld32(t_sb + 32, sr + 32);
         tc_wait_ld();
+        STEP_STAMP(u, 1);
         float* s = reinterpret_cast<float*>(sr);
 
-        if (tap && j == 0) {
-          float* dbg = pp.debug + (size_t)(i * kBM + row_in_tile) * kBN;
-#pragma unroll
-          for (int c = 0; c < kBN; ++c) dbg[c] = s[c];
-        }
-
-        const int64_t col0 = (int64_t)j * kBN;
+        const int64_t col0 = (int64_t)u * kBS;
         if constexpr (MASKED) {
           // scale -> softcap -> bias -> keep-mask, the order of the reference (CpuEngine.cs:27807-27816, 29218-29239)
           const float inv_cap = p.softcap > 0.f ? 1.f / p.softcap : 0.f;
           const int64_t mrow = qrow < p.seq_q ? qrow : p.seq_q - 1;   // rows past the end read a valid row
           const int64_t mbase = (int64_t)b * p.mask_stride[0] + (int64_t)ti.h * p.mask_stride[1] + mrow * p.mask_stride[2];
           const int64_t ms3 = p.mask_stride[3];
-          const bool full_tile = col0 + kBN <= p.seq_kv;
+          const bool full_tile = col0 + kBS <= p.seq_kv;
           const int kind = p.mask_kind;
           if (kind == AIDN_MASK_NONE) {
 #pragma unroll
-            for (int c = 0; c < kBN; ++c) {
+            for (int c = 0; c < kBS; ++c) {
               float val = s[c] * p.scale;
               if (p.softcap > 0.f) val = p.softcap * tanh_approx(val * inv_cap);
               s[c] = val;
@@ -335,11 +383,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint8_t* mp = static_cast<const uint8_t*>(p.mask) + mbase + col0 * ms3;
             const bool vec = ms3 == 1 && full_tile && ((reinterpret_cast<uintptr_t>(mp) & 15) == 0);
 #pragma unroll
-            for (int c0 = 0; c0 < kBN; c0 += 16) {
+            for (int c0 = 0; c0 < kBS; c0 += 16) {
               uint32_t w[4];
               if (vec) {
-                const uint4 u = *reinterpret_cast<const uint4*>(mp + c0);
-                w[0] = u.x; w[1] = u.y; w[2] = u.z; w[3] = u.w;
+                const uint4 u4 = *reinterpret_cast<const uint4*>(mp + c0);
+                w[0] = u4.x; w[1] = u4.y; w[2] = u4.z; w[3] = u4.w;
               } else {
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4) {
@@ -364,11 +412,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             const float* mp = static_cast<const float*>(p.mask) + mbase + col0 * ms3;
             const bool vec = ms3 == 1 && full_tile && ((reinterpret_cast<uintptr_t>(mp) & 15) == 0);
 #pragma unroll
-            for (int c0 = 0; c0 < kBN; c0 += 4) {
+            for (int c0 = 0; c0 < kBS; c0 += 4) {
               float mv[4];
               if (vec) {
-                const float4 u = *reinterpret_cast<const float4*>(mp + c0);
-                mv[0] = u.x; mv[1] = u.y; mv[2] = u.z; mv[3] = u.w;
+                const float4 u4 = *reinterpret_cast<const float4*>(mp + c0);
+                mv[0] = u4.x; mv[1] = u4.y; mv[2] = u4.z; mv[3] = u4.w;
               } else {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) mv[e] = (col0 + c0 + e < p.seq_kv) ? mp[(int64_t)(c0 + e) * ms3] : 0.f;
@@ -384,16 +432,16 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
-        if (col0 + kBN - 1 > kmax_row) {
+        if (col0 + kBS - 1 > kmax_row) {
           const int64_t lim = kmax_row - col0;  // columns > lim are masked (lim may be negative)
 #pragma unroll
-          for (int c = 0; c < kBN; ++c)
+          for (int c = 0; c < kBS; ++c)
             if (c > lim) s[c] = -INFINITY;
         }
 
         float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
 #pragma unroll
-        for (int c = 4; c < kBN; c += 4) {
+        for (int c = 4; c < kBS; c += 4) {
           mx0 = fmaxf(mx0, s[c]);
           mx1 = fmaxf(mx1, s[c + 1]);
           mx2 = fmaxf(mx2, s[c + 2]);
@@ -401,12 +449,26 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
         const float m_new = fmaxf(m, mx);
+        STEP_STAMP(u, 2);
 
-        if (j == 0) {
+        if (u == 0) {
           m = m_new;
         } else {
           const bool need = (m_new - m) * sl2 > kRescaleThreshold;
           if (__any_sync(0xffffffffu, need)) {
+            // O is rescaled in TMEM by the row's owner.  The P.V product of the previous sub-tile accumulates into
+            // the same columns and may still be running (the scores of this sub-tile were ready before it was even
+            // issued), so its completion is awaited first.  It is covered by the commit behind the score product
+            // that the issuer put right after it - the one for sub-tile u + 1, i.e. the other buffer's s_full, whose
+            // phase is only tested here, not consumed - or, when there is no sub-tile u + 1, by pv_done.
+            if (u + 1 < ti.n) {
+              ok = mbar_wait(bar_s_full + 8u * (uint32_t)(2 * i) + 8u * (buf ^ 1u), (s_par >> (buf ^ 1u)) & 1u, abort_flag, wait_ns);
+            } else {
+              ok = mbar_wait(bar_pv_done + 8 * i, pv_par, abort_flag, wait_ns);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { alive = false; break; }
+            tc_fence_after();
             float f;
             if (m_new == -INFINITY) f = 1.f;
             else if (m == -INFINITY) f = 0.f;
@@ -428,8 +490,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 
         const float neg_ms = (m == -INFINITY) ? 0.f : -m * sl2;
         float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+        // (Computing one exponential in 2, 4 or 8 on the FMA pipe instead - a cubic after the 1.5 * 2^23 rounding trick -
+        // was measured and is slower here, 6-10 %: with two softmax warps per scheduler the loop is bound by their
+        // instruction stream, not by the MUFU unit.)
 #pragma unroll
-        for (int c0 = 0; c0 < kBN; c0 += 32) {
+        for (int c0 = 0; c0 < kBS; c0 += 32) {
           uint32_t pk[16];
 #pragma unroll
           for (int c = 0; c < 32; c += 4) {
@@ -444,22 +509,28 @@ __global__ void __launch_bounds__(kThreads, 1)
             pk[c >> 1] = pack2<kBf16>(p0, p1);
             pk[(c >> 1) + 1] = pack2<kBf16>(p2, p3);
           }
-          tmem_st16(t_s + (c0 >> 1), pk);
+          tmem_st16(t_sb + (c0 >> 1), pk);
         }
         l += (ls0 + ls1) + (ls2 + ls3);
+        STEP_STAMP(u, 3);
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(bar_p_full + 8 * i);
-        ++s_cnt;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p_full + bar_off);   // one arrival per warp: 128 arrivals on one word serialise
+        STEP_STAMP(u, 4);
+        s_par ^= 1u << buf;
       }
       if (!alive) break;
+      if (ti.n >= 2) pv_par ^= 1u;   // the issuer signalled pv_done once for this item
       if (tracer) trace[3 + 8 * i] = globaltimer_ns();
 
       // ---- epilogue: O / l -> swizzled staging (128 B per row) -> TMA stores ------------------------------
       {
         const bool have_o = ti.n > 0;
         if (have_o) {
-          bool ok = mbar_wait(bar_o_full + 8 * i, o_cnt & 1u, abort_flag, wait_ns);
+          // the last two P.V products were issued by different warps: pv_done covers the second-to-last one
+          bool ok = ti.n < 2 || mbar_wait(bar_pv_done + 8 * i, pv_par ^ 1u, abort_flag, wait_ns);
+          ok = ok && mbar_wait(bar_o_full + 8 * i, o_cnt & 1u, abort_flag, wait_ns);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) { alive = false; break; }
           ++o_cnt;
@@ -479,11 +550,6 @@ __global__ void __launch_bounds__(kThreads, 1)
           } else {
 #pragma unroll
             for (int c = 0; c < 32; ++c) orr[c] = 0u;
-          }
-          if (tap) {
-            float* dbg = pp.debug + 2 * kBM * kBN + (size_t)(i * kBM + row_in_tile) * HD + c0;
-#pragma unroll
-            for (int c = 0; c < 32; ++c) dbg[c] = __uint_as_float(orr[c]);
           }
           // fp32 output: 32 columns fill the 128-byte row (one store per 32 columns); 16-bit output: 64 columns
           const int half = p.out_f32 ? 0 : ((c0 >> 5) & 1);
@@ -521,11 +587,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (row_valid && p.lse)
           p.lse[((int64_t)b * p.num_q_heads + ti.h) * p.seq_q + qrow] =
               (inv > 0.f) ? m * lse_scale + logf(l) : -INFINITY;
-        if (tap) {
-          float* dbg = pp.debug + 2 * kBM * kBN + 2 * kBM * HD + (size_t)(i * kBM + row_in_tile) * 2;
-          dbg[0] = l;
-          dbg[1] = m;
-        }
         if (tracer) trace[5 + 8 * i] = globaltimer_ns();
       }
     }
@@ -551,7 +612,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         Item it;
         if (item < pp.total_items) {
           it = decode_item(pp, item);
-          // Row pairs: the second tile runs one KV tile longer.  Alternating which softmax warpgroup gets it keeps
+          // Row pairs: the second tile runs two sub-tiles longer.  Alternating which softmax warpgroup gets it keeps
           // that lag from building up on one side from item to item.
           if (!pp.pair_heads && (seq & 1)) {
             const TileInfo t0 = it.tile[0];
@@ -565,9 +626,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           mbar_arrive(bar_sched_full + 8 * slot);
         }
         if (item >= pp.total_items) break;
+#if AIDN_PREFILL_TRACE
         unsigned long long* ptrace = pp.debug_mode == 2
             ? reinterpret_cast<unsigned long long*>(pp.debug) + (size_t)item * 16 : nullptr;
         if (ptrace && leader) ptrace[6] = globaltimer_ns();
+#else
+        unsigned long long* const ptrace = nullptr;
+#endif
         auto load_tile = [&](const CUtensorMap* tm, uint32_t dst, uint32_t bar, int row, int head) {
           if (leader) {
             mbar_expect_tx(bar, (uint32_t)C::kTileBytes);
@@ -582,55 +647,63 @@ __global__ void __launch_bounds__(kThreads, 1)
           load_tile(&tm_q, q_smem + i * C::kTileBytes, bar_q_full + 8 * i, it.tile[i].t * kBM, it.tile[i].h);
           ++q_uses[i];
         };
-        // Paged K/V: a key tile is 128 / block_size pool blocks, each fetched by its own TMA box (block_size rows)
-        // into its slice of the ring slot; the 128-byte swizzle is a function of the shared-memory address, so the
-        // slices compose into the same tile image as one 128-row box.  Lane i holds the pool block of slice i.
+        // Paged K/V: a sub-tile of 64 keys is 64 / block_size pool blocks, each fetched by its own TMA box (block_size
+        // rows) into its slice of the ring slot - the 128-byte swizzle is a function of the shared-memory address, so
+        // the slices compose into the same image as one 64-row box - or, with 128-token blocks, half of one block.
+        // Lane i holds the pool block of slice i.
         const bool paged = p.block_table != nullptr;
-        int32_t blk_cur = 0;
         int64_t last_blk = 0;
         if (paged) last_blk = (kv_limit_of(p, it.b) - 1) >> p.block_shift;
-        auto load_kv = [&](const CUtensorMap* tm, int key_tile, bool is_k) {
+        auto load_kv = [&](const CUtensorMap* tm, int key_sub) {
           const int s = (int)(t_load % C::kStages);
           const uint32_t phase = (t_load / C::kStages) & 1u;
           if (!mbar_wait(bar_kv_empty + 8 * s, phase ^ 1u, abort_flag, wait_ns)) { alive = false; return; }
+          const uint32_t dst = kv_smem + s * C::kSubBytes, bar = bar_kv_full + 8 * s;
+          if (leader) mbar_expect_tx(bar, (uint32_t)C::kSubBytes);
           if (!paged) {
-            load_tile(tm, kv_smem + s * C::kTileBytes, bar_kv_full + 8 * s, key_tile * kBN, it.kvh);
-          } else {
-            const int parts = kBN >> p.block_shift;
-            if (is_k) {   // the V tile of the same keys follows and reuses the entries
-              // Logical blocks past the sequence's last one repeat it: their keys are masked, the table has no entry
-              // for them, and what lands in shared memory only has to be finite.
-              int64_t lb = (int64_t)key_tile * parts + lane;
-              if (lb > last_blk) lb = last_blk;
-              blk_cur = 0;
-              if (lane < parts) {
-                blk_cur = __ldg(p.block_table + (int64_t)it.b * p.bt_stride + lb);
-                if ((blk_cur < 0 || blk_cur >= p.num_blocks) && p.status) atomicOr(p.status, kStatusBadBlock);
-              }
+            if (leader) {
+#pragma unroll
+              for (int hf = 0; hf < C::kHalves; ++hf)
+                tma_load_4d(dst + hf * C::kKvHalfBytes, tm, bar, hf * 64, key_sub * kBS, it.kvh, it.b);
             }
-            const uint32_t dst = kv_smem + s * C::kTileBytes, bar = bar_kv_full + 8 * s;
-            if (leader) mbar_expect_tx(bar, (uint32_t)C::kTileBytes);
+          } else {
+            const int rows = p.block_size < kBS ? p.block_size : kBS;   // rows per box
+            const int parts = kBS / rows;
+            // Logical blocks past the sequence's last one repeat it: their keys are masked and the table has no
+            // entry for them (the V rows among them are cleared before use, the K rows only feed masked scores).
+            const int64_t key = (int64_t)key_sub * kBS + (int64_t)lane * rows;
+            int64_t lb = key >> p.block_shift;
+            if (lb > last_blk) lb = last_blk;
+            int32_t blk = 0;
+            if (lane < parts) {
+              blk = __ldg(p.block_table + (int64_t)it.b * p.bt_stride + lb);
+              if ((blk < 0 || blk >= p.num_blocks) && p.status) atomicOr(p.status, kStatusBadBlock);
+            }
+            const int in_block = (int)(((int64_t)key_sub * kBS) & (int64_t)(p.block_size - 1));   // non-zero only for 128-token blocks
             for (int part = 0; part < parts; ++part) {
               // an entry outside the pool gives an out-of-range coordinate, which TMA fills with zeros
-              const int32_t phys = __shfl_sync(0xffffffffu, blk_cur, part);
+              const int32_t phys = __shfl_sync(0xffffffffu, blk, part);
               if (leader) {
 #pragma unroll
                 for (int hf = 0; hf < C::kHalves; ++hf)
-                  tma_load_4d(dst + hf * C::kHalfBytes + part * (p.block_size * 128), tm, bar, hf * 64,
-                              phys * p.block_size, it.kvh, 0);
+                  tma_load_4d(dst + hf * C::kKvHalfBytes + part * (rows * 128), tm, bar, hf * 64,
+                              phys * p.block_size + (parts == 1 ? in_block : 0), it.kvh, 0);
               }
             }
           }
           ++t_load;
         };
-        if (it.n_max > 0) {
+        // Ring order of an item with n sub-tiles: K(0), then K(u+1), V(u) for u = 0 .. n-2, then V(n-1) - the order in
+        // which the issuers need them (the score product runs two sub-tiles ahead of the P.V product).
+        const int n_sub = it.n_max;
+        if (n_sub > 0) {
           load_q(0);
-          if (alive) load_kv(&tm_k, 0, true);
+          if (alive) load_kv(&tm_k, 0);
           if (ptrace && leader) ptrace[0] = globaltimer_ns();
           if (alive) load_q(1);
-          for (int j = 0; j < it.n_max && alive; ++j) {
-            load_kv(&tm_v, j, false);
-            if (alive && j + 1 < it.n_max) load_kv(&tm_k, j + 1, true);
+          for (int u = 0; u < n_sub && alive; ++u) {
+            if (u + 1 < n_sub) load_kv(&tm_k, u + 1);
+            if (alive) load_kv(&tm_v, u);
           }
         }
         {
@@ -640,19 +713,37 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-  } else if (warp == kMmaWarp) {
-    // ========================================== UMMA issuer ==========================================
-    // The whole warp runs this role in lockstep and only the tcgen05 instructions themselves are issued by one
-    // elected lane: descriptors and addresses then stay warp-uniform (uniform registers), which a branch on
-    // lane == 0 around the role would prevent - every UMMA would first move its operands lane -> uniform.
+  } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+    // ========================================== UMMA issuers ==========================================
+    // Two issuer warps.  Issuer b owns score buffer b of BOTH query tiles, i.e. the sub-tiles u with (u & 1) == b:
+    // in its turn it issues P_0(u).V, Q_0.K(u+2)^T, P_1(u).V, Q_1.K(u+2)^T - 24 UMMAs, about 1300 cycles of tensor
+    // pipe - and then spends several hundred cycles on hand-offs (barrier tests, commits, the next turn's waits;
+    // tcgen05.mma issue blocks once a few instructions are queued, and an issuer shares its scheduler with two busy
+    // softmax warps).  The turns of the two issuers alternate, so one issuer's hand-offs run under the other's
+    // burst.  Measured alternatives: one issuer for everything (its hand-offs, 530 cycles per tile and sub-tile, sat
+    // between the bursts and idled the pipe half of the time) and one issuer per query tile (bursts of 12 UMMAs are
+    // shorter than the hand-offs between them).
+    // A counter in shared memory orders the turns (prologue of issuer 0, prologue of issuer 1, then sub-tile 0, 1,
+    // 2, ... of the item); it is what guarantees that the first P.V of a tile, which overwrites O, is queued before
+    // the second one, which accumulates.
+    // Each warp runs its role in lockstep and only the tcgen05 instructions themselves are issued by one elected
+    // lane: descriptors and addresses then stay warp-uniform (uniform registers), which a branch on lane == 0
+    // around the role would prevent - every UMMA would first move its operands lane -> uniform.
     {
+      const int b = warp - kMmaWarp;            // buffer / sub-tile parity owned by this issuer
       const bool leader = elect_one();
-      constexpr uint32_t idesc_qk = make_idesc(kBM, kBN, kBf16, false);
+      constexpr uint32_t idesc_qk = make_idesc(kBM, kBS, kBf16, false);
       constexpr uint32_t idesc_pv = make_idesc(kBM, HD, kBf16, true);
+      const uint32_t t_sc = tmem_base + (uint32_t)(b * kBS);            // S_0[b]; S_1[b] is 128 columns on
+      const uint32_t t_acc = tmem_base + (uint32_t)C::kOCol;            // O_0; O_1 is HD columns on
+      const uint64_t qdesc = make_smem_desc(q_smem, 16, 1024);          // Q_0; Q_1 is one tile on
+      constexpr uint64_t kQTile = (uint64_t)(C::kTileBytes >> 4);
+      volatile int* turn = issue_turn;
       bool alive = true;
-      uint32_t t_cons = 0;            // K/V tiles consumed so far (ring position)
-      uint32_t q_uses[2] = {0, 0};
-      uint32_t p_cnt[2] = {0, 0};
+      uint32_t t_cons = 0;            // K/V sub-tiles of earlier items (ring position)
+      uint32_t q_par = 0;             // bit i: parity of the next phase of q_full[i]
+      uint32_t p_par = 0;             // bit i: parity of the next phase of p_full[i][b]
+      int g = 0;                      // turns of earlier items
       for (int seq = 0; alive; ++seq) {
         int item;
         {
@@ -664,76 +755,160 @@ __global__ void __launch_bounds__(kThreads, 1)
         const Item it = read_item(mailbox + (seq & 1) * kItemWords);
         __syncwarp();
         if (leader) mbar_arrive(bar_sched_empty + 8 * (seq & 1));
-        unsigned long long* mtrace = pp.debug_mode == 2
+#if AIDN_PREFILL_TRACE
+        unsigned long long* mtrace = (pp.debug_mode == 2 && b == 0)
             ? reinterpret_cast<unsigned long long*>(pp.debug) + (size_t)item * 16 : nullptr;
         if (mtrace && leader) mtrace[7] = globaltimer_ns();
-        if (it.n_max == 0) continue;
+        long long* msteps = ((pp.debug_mode == 4 || pp.debug_mode == 6) && blockIdx.x == 0 && seq < 8 && leader)
+            ? reinterpret_cast<long long*>(pp.debug) + (size_t)seq * 32 * 16 + 10 : nullptr;
+#define MMA_STAMP(j, slot) do { if (msteps && (j) < 32) msteps[(j) * 16 + (slot)] = clock64(); } while (0)
+        // mode 6: the issuers' own phases in slots 5..9 of their sub-tiles (the tile-1 softmax columns are not written then)
+        long long* dsteps = (pp.debug_mode == 6 && blockIdx.x == 0 && seq < 8 && leader)
+            ? reinterpret_cast<long long*>(pp.debug) + (size_t)seq * 32 * 16 + 5 : nullptr;
+#define DET_STAMP(j, slot) do { if (dsteps && (j) < 32) dsteps[(j) * 16 + (slot)] = clock64(); } while (0)
+#else
+        unsigned long long* const mtrace = nullptr;
+#define MMA_STAMP(j, slot) do { } while (0)
+#define DET_STAMP(j, slot) do { } while (0)
+#endif
+        const int n_max = it.n_max;
+        if (n_max == 0) continue;
+        const int n0 = it.tile[0].n, n1 = it.tile[1].n;
+        // ring positions of the item's sub-tiles (the producer's order): K(0) at t0, K(s) at t0 + 2s - 1,
+        // V(u) at t0 + 2u + 2 except the last one, which follows K(n_max - 1) directly
+        const uint32_t t0 = t_cons;
+        t_cons = t0 + 2 * (uint32_t)n_max;
+        auto pos_k = [&](int sub) { return t0 + (uint32_t)(sub == 0 ? 0 : 2 * sub - 1); };
+        auto pos_v = [&](int sub) { return t0 + (uint32_t)(sub + 1 < n_max ? 2 * sub + 2 : 2 * n_max - 1); };
+        const int g0 = g;             // turn g0: prologue of issuer 0, g0 + 1: of issuer 1, g0 + 2 + u: sub-tile u
+        g = g0 + 2 + n_max;
         auto kv_slot = [&](uint32_t t) { return (int)(t % C::kStages); };
         auto kv_wait = [&](uint32_t t) {
           const int s = kv_slot(t);
           if (!mbar_wait(bar_kv_full + 8 * s, (t / C::kStages) & 1u, abort_flag, wait_ns)) alive = false;
-          return kv_smem + s * C::kTileBytes;
+          return kv_smem + s * C::kSubBytes;
         };
+        // the slot may be refilled when the products this warp has issued so far have read it
         auto kv_release = [&](uint32_t t) { if (leader) tc_commit(bar_kv_empty + 8 * kv_slot(t)); };
-        auto issue_qk = [&](int i, uint32_t kaddr, bool last_for_item) {
-          const uint32_t qaddr = q_smem + i * C::kTileBytes;
-          const uint32_t d = tmem_base + (uint32_t)(i * kBN);
+        auto wait_turn = [&](int my) {
+          uint32_t spins = 0;
+          while (*turn < my) {
+            if ((++spins & 63u) == 0u && (*abort_flag || spins > (1u << 22))) { alive = false; break; }
+          }
+        };
+        auto pass_turn = [&](int my) { if (leader) *turn = my + 1; };
+        // S_i[b] = Q_i . K(sub-tile s)^T, s & 1 == b; kaddr is the ring slot that holds the sub-tile
+        auto issue_qk = [&](int i, int s, uint32_t kaddr, int n_i, int pass_my) {
+          const uint64_t kdesc = make_smem_desc(kaddr, 16, 1024);
+          const uint64_t qd = qdesc + (uint64_t)i * kQTile;
+          const uint32_t d = t_sc + (uint32_t)(i * 2 * kBS);
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk) {
-            const uint32_t off = (uint32_t)((kk >> 2) * C::kHalfBytes + (kk & 3) * 32);
-            const uint64_t ad = make_smem_desc(qaddr + off, 16, 1024), bd = make_smem_desc(kaddr + off, 16, 1024);
-            if (leader) mma_ss(d, ad, bd, idesc_qk, kk > 0 ? 1u : 0u);
+            // 16 head-dim elements = 32 bytes inside the 128-byte swizzle row; 64 elements on, the next column block
+            const uint64_t qoff = (uint64_t)((kk >> 2) * (C::kHalfBytes >> 4) + (kk & 3) * 2);
+            const uint64_t koff = (uint64_t)((kk >> 2) * (C::kKvHalfBytes >> 4) + (kk & 3) * 2);
+            if (leader) mma_ss(d, qd + qoff, kdesc + koff, idesc_qk, kk > 0 ? 1u : 0u);
+            // The turn goes on while the last few UMMAs of the burst are still to be queued: the other issuer needs
+            // about that long to notice, and the tensor pipe has this burst's tail to run in the meantime.
+            if (pass_my >= 0 && kk == HD / 16 - 4) pass_turn(pass_my);
           }
           if (leader) {
-            tc_commit(bar_s_full + 8 * i);
-            if (last_for_item) tc_commit(bar_q_empty + 8 * i);   // the Q tile may be overwritten by the next item
+            tc_commit(bar_s_full + 8 * (2 * i + b));
+            // this issuer's last score product of the tile: its half of "the Q tile may be overwritten"
+            if (s + 2 >= n_i) tc_commit(bar_q_empty + 8 * i);
           }
         };
-        auto issue_pv = [&](int i, uint32_t vaddr, bool accumulate) {
-          const uint32_t d = tmem_base + (uint32_t)(C::kOCol + i * HD);
-          const uint32_t a = tmem_base + (uint32_t)(i * kBN);
+        // O_i (+)= P_i[b] . V(sub-tile u)
+        auto issue_pv = [&](int i, int u, uint32_t vaddr) {
+          const uint64_t vdesc = make_smem_desc(vaddr, C::kKvHalfBytes, 1024);
+          const uint32_t a = t_sc + (uint32_t)(i * 2 * kBS);
+          const uint32_t d = t_acc + (uint32_t)(i * HD);
 #pragma unroll
-          for (int kk = 0; kk < kBN / 16; ++kk) {
-            const uint64_t bd = make_smem_desc(vaddr + (uint32_t)(kk * 2048), C::kHalfBytes, 1024);
-            if (leader) mma_ts(d, a + (uint32_t)(kk * 8), bd, idesc_pv, (accumulate || kk > 0) ? 1u : 0u);
-          }
+          for (int kk = 0; kk < kBS / 16; ++kk)
+            if (leader) mma_ts(d, a + (uint32_t)(kk * 8), vdesc + (uint64_t)(kk * (2048 >> 4)), idesc_pv, (u > 0 || kk > 0) ? 1u : 0u);
         };
 
-        // S_i(0) = Q_i K_0^T
-        const uint32_t t0 = t_cons;   // ring index of K_0 of this item; V_j is t0 + 2j + 1, K_{j+1} is t0 + 2j + 2
-        const uint32_t kaddr = kv_wait(t0);
-        if (mtrace && leader) mtrace[14] = globaltimer_ns();
-        for (int i = 0; i < 2 && alive; ++i) {
-          if (it.tile[i].n == 0) continue;
-          if (!mbar_wait(bar_q_full + 8 * i, q_uses[i] & 1u, abort_flag, wait_ns)) { alive = false; break; }
-          if (mtrace && leader && i == 0) mtrace[8] = globaltimer_ns();
-          ++q_uses[i];
-          tc_fence_after();
-          issue_qk(i, kaddr, it.tile[i].n == 1);
-        }
-        if (!alive) break;
-        kv_release(t0);
-
-        for (int j = 0; j < it.n_max && alive; ++j) {
-          const uint32_t vaddr = kv_wait(t0 + 2 * j + 1);
-          uint32_t knext = 0;
-          const bool has_next = j + 1 < it.n_max;
-          if (alive && has_next) knext = kv_wait(t0 + 2 * j + 2);
+        // ---- prologue turn: score sub-tile b of both query tiles ----
+        {
+          uint32_t kaddr0 = 0;
+          if (b < n_max) kaddr0 = kv_wait(pos_k(b));
+          if (mtrace && leader) mtrace[14] = globaltimer_ns();
           for (int i = 0; i < 2 && alive; ++i) {
-            if (j >= it.tile[i].n) continue;
-            if (!mbar_wait(bar_p_full + 8 * i, p_cnt[i] & 1u, abort_flag, wait_ns)) { alive = false; break; }
-            ++p_cnt[i];
-            tc_fence_after();
-            issue_pv(i, vaddr, j > 0);
-            if (j + 1 < it.tile[i].n) issue_qk(i, knext, j + 2 == it.tile[i].n);
-            else if (leader) tc_commit(bar_o_full + 8 * i);
+            const int n_i = i ? n1 : n0;
+            if (n_i == 0) continue;
+            if (!mbar_wait(bar_q_full + 8 * i, (q_par >> i) & 1u, abort_flag, wait_ns)) { alive = false; break; }
+            q_par ^= 1u << i;
           }
-          if (alive) {
-            kv_release(t0 + 2 * j + 1);
-            if (has_next) kv_release(t0 + 2 * j + 2);
+          if (!alive) break;
+          if (mtrace && leader) mtrace[8] = globaltimer_ns();
+          tc_fence_after();
+          wait_turn(g0 + b);
+          if (!alive) break;
+          for (int i = 0; i < 2; ++i) {
+            const int n_i = i ? n1 : n0;
+            if (n_i > b) issue_qk(i, b, kaddr0, n_i, -1);
+            else if (n_i > 0 && leader) tc_commit(bar_q_empty + 8 * i);   // a single sub-tile: issuer 1 never reads this Q tile
           }
+          pass_turn(g0 + b);
+          if (b < n_max) kv_release(pos_k(b));
         }
-        t_cons = t0 + 2 * (uint32_t)it.n_max;
+
+        // ---- this issuer's sub-tiles ----
+        for (int u = b; u < n_max && alive; u += 2) {
+          const uint32_t tv = pos_v(u), tk = pos_k(u + 2);
+          const bool have_k = u + 2 < n_max;   // K(u + 2) exists (one of the query tiles needs its scores)
+          DET_STAMP(u, 0);
+          const uint32_t vaddr = kv_wait(tv);
+          uint32_t knext = 0;
+          if (have_k && alive) knext = kv_wait(tk);
+          if (!alive) break;
+          if (it.v_tail > 0 && u + 1 == n_max) {
+            // clear the rows of the item's last V sub-tile that lie past the sequence's last key (see decode_item)
+            const int chunks = (kBS - it.v_tail) * 8;   // 16-byte chunks per 64-column block
+#pragma unroll
+            for (int hf = 0; hf < C::kHalves; ++hf)
+              for (int c = lane; c < chunks; c += 32)
+                st_shared_v4(vaddr + (uint32_t)(hf * C::kKvHalfBytes + it.v_tail * 128 + c * 16), 0u, 0u, 0u, 0u);
+            fence_proxy_async_smem();
+            __syncwarp();
+          }
+          bool turn_mine = false;
+          DET_STAMP(u, 1);
+          for (int i = 0; i < 2 && alive; ++i) {
+            const int n_i = i ? n1 : n0;
+            if (u >= n_i) continue;
+            if (!mbar_wait(bar_p_full + 8 * (2 * i + b), (p_par >> i) & 1u, abort_flag, wait_ns)) { alive = false; break; }
+            p_par ^= 1u << i;
+            tc_fence_after();
+            if (!turn_mine) {
+              DET_STAMP(u, 2);
+              wait_turn(g0 + 2 + u);
+              if (!alive) break;
+              turn_mine = true;
+              DET_STAMP(u, 3);
+            }
+            MMA_STAMP(u, 2 * i);
+            issue_pv(i, u, vaddr);
+            // the last tile of the burst hands the turn on from inside its score product, or right here without one
+            const bool last_of_burst = i == 1 || u >= n1;
+            if (u + 2 < n_i) {
+              issue_qk(i, u + 2, knext, n_i, last_of_burst ? g0 + 2 + u : -1);
+            } else {
+              if (last_of_burst) pass_turn(g0 + 2 + u);
+              if (leader) {
+                // No further score product of this issuer will signal this P.V.  The second-to-last one of the tile
+                // is signalled for a late O rescale and for the epilogue, the last one hands O to the epilogue.
+                if (u + 2 == n_i) tc_commit(bar_pv_done + 8 * i);
+                else tc_commit(bar_o_full + 8 * i);
+              }
+            }
+            MMA_STAMP(u, 2 * i + 1);
+          }
+          if (!alive) break;
+          kv_release(tv);
+          if (have_k) kv_release(tk);
+          DET_STAMP(u, 4);
+        }
       }
     }
   }
@@ -784,32 +959,59 @@ bool aligned_bhs(const void* base, const int64_t* stride, int64_t H, int64_t B, 
 
 template <typename T, int HD, bool MASKED>
 cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, int num_sms, float* debug,
-                     int debug_mode, const char** why) {
+                     int debug_mode, PrefillMapCache* cache, const char** why) {
   using C = Cfg<HD>;
-  cudaError_t e = resolve_encode();
-  if (e != cudaSuccess) { *why = "cuTensorMapEncodeTiled is not available from the driver"; return e; }
   constexpr bool bf16 = !std::is_same_v<T, __half>;
-  const CUtensorMapDataType dt16 = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  const CUtensorMapSwizzle s128 = CU_TENSOR_MAP_SWIZZLE_128B;
-  CUtensorMap tq, tk, tv, to;
-  // output boxes are 128 bytes x 32 rows: 32 fp32 or 64 16-bit columns
-  const bool ok_o = p.out_f32
-      ? encode_bhsd(&to, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, s128, p.out, HD, p.seq_q, p.num_q_heads, p.batch, p.os, 32, 32)
-      : encode_bhsd(&to, dt16, 2, s128, p.out, HD, p.seq_q, p.num_q_heads, p.batch, p.os, 64, 32);
   // Paged pools are one "sequence" of num_blocks * block_size rows, fetched one block (box of block_size rows) at a time.
   const int64_t kv_rows = p.block_table ? (int64_t)p.num_blocks * p.block_size : p.seq_kv;
   const int kv_batch = p.block_table ? 1 : p.batch;
-  const int kv_box = p.block_table ? p.block_size : kBN;
-  if (!encode_bhsd(&tq, dt16, 2, s128, p.q, HD, p.seq_q, p.num_q_heads, p.batch, p.qs, 64, kBM) ||
-      !encode_bhsd(&tk, dt16, 2, s128, p.k, HD, kv_rows, p.num_kv_heads, kv_batch, p.ks, 64, kv_box) ||
-      !encode_bhsd(&tv, dt16, 2, s128, p.v, HD, kv_rows, p.num_kv_heads, kv_batch, p.vs, 64, kv_box) || !ok_o) {
-    *why = "cuTensorMapEncodeTiled rejected a tensor (address or stride alignment)";
-    return cudaErrorInvalidValue;
+  const int kv_box = p.block_table ? (p.block_size < kBS ? p.block_size : kBS) : kBS;
+  PrefillMapCache local;
+  PrefillMapCache* mc = cache ? cache : &local;
+  if (!cache) {
+    local.valid = false;
+    std::memset(local.attr_set, 0, sizeof(local.attr_set));
+  }
+  PrefillMapCache::Key key;
+  std::memset(&key, 0, sizeof(key));
+  key.q = p.q; key.k = p.k; key.v = p.v; key.out = p.out;
+  for (int i = 0; i < 3; ++i) { key.qs[i] = p.qs[i]; key.ks[i] = p.ks[i]; key.vs[i] = p.vs[i]; key.os[i] = p.os[i]; }
+  key.seq_q = p.seq_q; key.kv_rows = kv_rows;
+  key.batch = p.batch; key.kv_batch = kv_batch; key.num_q_heads = p.num_q_heads; key.num_kv_heads = p.num_kv_heads;
+  key.head_dim = HD; key.kv_box = kv_box; key.out_f32 = p.out_f32; key.dtype = bf16 ? AIDN_BF16 : AIDN_F16;
+  CUtensorMap* tq = reinterpret_cast<CUtensorMap*>(mc->maps[0]);
+  CUtensorMap* tk = reinterpret_cast<CUtensorMap*>(mc->maps[1]);
+  CUtensorMap* tv = reinterpret_cast<CUtensorMap*>(mc->maps[2]);
+  CUtensorMap* to = reinterpret_cast<CUtensorMap*>(mc->maps[3]);
+  cudaError_t e = cudaSuccess;
+  if (!mc->valid || std::memcmp(&mc->key, &key, sizeof(key)) != 0) {
+    mc->valid = false;
+    e = resolve_encode();
+    if (e != cudaSuccess) { *why = "cuTensorMapEncodeTiled is not available from the driver"; return e; }
+    const CUtensorMapDataType dt16 = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapSwizzle s128 = CU_TENSOR_MAP_SWIZZLE_128B;
+    // output boxes are 128 bytes x 32 rows: 32 fp32 or 64 16-bit columns
+    const bool ok_o = p.out_f32
+        ? encode_bhsd(to, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, s128, p.out, HD, p.seq_q, p.num_q_heads, p.batch, p.os, 32, 32)
+        : encode_bhsd(to, dt16, 2, s128, p.out, HD, p.seq_q, p.num_q_heads, p.batch, p.os, 64, 32);
+    if (!encode_bhsd(tq, dt16, 2, s128, p.q, HD, p.seq_q, p.num_q_heads, p.batch, p.qs, 64, kBM) ||
+        !encode_bhsd(tk, dt16, 2, s128, p.k, HD, kv_rows, p.num_kv_heads, kv_batch, p.ks, 64, kv_box) ||
+        !encode_bhsd(tv, dt16, 2, s128, p.v, HD, kv_rows, p.num_kv_heads, kv_batch, p.vs, 64, kv_box) || !ok_o) {
+      *why = "cuTensorMapEncodeTiled rejected a tensor (address or stride alignment)";
+      return cudaErrorInvalidValue;
+    }
+    mc->key = key;
+    mc->valid = true;
   }
   PrefillParams pp;
   pp.p = p;
+#if AIDN_PREFILL_TRACE
   pp.debug = debug;
   pp.debug_mode = (debug || debug_mode == 3) ? debug_mode : 0;
+#else
+  pp.debug = nullptr;
+  pp.debug_mode = debug_mode == 3 ? 3 : 0;
+#endif
   pp.wait_budget_ns = debug_mode == 3 ? 20000000ull : kWaitBudgetNs;   // 20 ms in the time-out test
   pp.sched = sched;
   pp.row_tiles = (int)((p.seq_q + kBM - 1) / kBM);
@@ -826,10 +1028,14 @@ cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
   if (total <= 0 || total > 0x3fffffff) { *why = "work item count out of range"; return cudaErrorInvalidValue; }
   pp.total_items = (int)total;
   auto kern = sdpa_prefill_sm100_kernel<T, HD, MASKED>;
-  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-  if (e != cudaSuccess) { *why = "cannot raise the dynamic shared memory limit"; return e; }
+  constexpr int inst = (bf16 ? 0 : 4) + (HD == 128 ? 2 : 0) + (MASKED ? 1 : 0);
+  if (!mc->attr_set[inst]) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (e != cudaSuccess) { *why = "cannot raise the dynamic shared memory limit"; return e; }
+    mc->attr_set[inst] = true;
+  }
   const unsigned grid = (unsigned)(total < num_sms ? total : num_sms);
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, pp);
+  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(*tq, *tk, *tv, *to, pp);
   return cudaGetLastError();
 }
 
@@ -840,7 +1046,7 @@ bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why) {
   if (p.head_dim != 64 && p.head_dim != 128) { *why = "tcgen05 prefill takes head_dim 64 or 128"; return false; }
   const int kv_batch = p.block_table ? 1 : p.batch;
   if (p.block_table) {
-    if (p.block_shift < 3 || p.block_size > kBN) {
+    if (p.block_shift < 3 || p.block_size > 128) {
       *why = "tcgen05 prefill reads paged K/V in blocks of 8, 16, 32, 64 or 128 tokens";
       return false;
     }
@@ -864,20 +1070,20 @@ bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why) {
 
 template <typename T, int HD>
 cudaError_t launch_m(const SdpaParams& p, cudaStream_t stream, int32_t* sched, int num_sms, float* debug, int debug_mode,
-                     const char** why) {
+                     PrefillMapCache* cache, const char** why) {
   if (p.mask_kind != AIDN_MASK_NONE || p.softcap > 0.f)
-    return launch_t<T, HD, true>(p, stream, sched, num_sms, debug, debug_mode, why);
-  return launch_t<T, HD, false>(p, stream, sched, num_sms, debug, debug_mode, why);
+    return launch_t<T, HD, true>(p, stream, sched, num_sms, debug, debug_mode, cache, why);
+  return launch_t<T, HD, false>(p, stream, sched, num_sms, debug, debug_mode, cache, why);
 }
 
 cudaError_t launch_prefill_sm100(const SdpaParams& p, int dtype, cudaStream_t stream, int32_t* sched, int num_sms,
-                                 float* debug, int debug_mode, const char** why) {
+                                 float* debug, int debug_mode, PrefillMapCache* cache, const char** why) {
   if (dtype == AIDN_BF16) {
-    if (p.head_dim == 128) return launch_m<__nv_bfloat16, 128>(p, stream, sched, num_sms, debug, debug_mode, why);
-    return launch_m<__nv_bfloat16, 64>(p, stream, sched, num_sms, debug, debug_mode, why);
+    if (p.head_dim == 128) return launch_m<__nv_bfloat16, 128>(p, stream, sched, num_sms, debug, debug_mode, cache, why);
+    return launch_m<__nv_bfloat16, 64>(p, stream, sched, num_sms, debug, debug_mode, cache, why);
   }
-  if (p.head_dim == 128) return launch_m<__half, 128>(p, stream, sched, num_sms, debug, debug_mode, why);
-  return launch_m<__half, 64>(p, stream, sched, num_sms, debug, debug_mode, why);
+  if (p.head_dim == 128) return launch_m<__half, 128>(p, stream, sched, num_sms, debug, debug_mode, cache, why);
+  return launch_m<__half, 64>(p, stream, sched, num_sms, debug, debug_mode, cache, why);
 }
 
 }  // namespace aidn

@@ -11,7 +11,8 @@ import os
 from typing import Optional, Sequence
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "lib", "libaidotnet_sdpa_sm100.so")
+# AIDN_SDPA_LIB selects a development variant of the library (see build.build_variant); unset = the shipped one.
+LIB_PATH = os.environ.get("AIDN_SDPA_LIB") or os.path.join(_HERE, "lib", "libaidotnet_sdpa_sm100.so")
 
 # aidn_status
 OK, EINVAL, EUNSUPPORTED, ECUDA, EWORKSPACE, ETIMEOUT, ENCCL = range(7)
@@ -29,6 +30,7 @@ EXPORTS = (
     "aidn_sdpa_decode_noalloc", "aidn_sdpa_launch_paged", "aidn_qkv_rope_cache", "aidn_rope_interleaved",
     "aidn_sdpa_backward", "aidn_sdpa_backward_workspace_bytes", "aidn_paged_kv_append", "aidn_mha_forward",
     "aidn_mha_workspace_bytes",
+    "aidn_sdpa_debug_set",   # include/aidn_sdpa_debug.h
 )
 
 

@@ -24,6 +24,18 @@
  *
  * Tensor layout is [B, H, S, D] with a unit stride on D; the B, H and S strides are explicit so that
  * permuted views ([B,S,H,D] storage, the single-sequence [S,Hkv,D] decode cache) need no copy.
+ *
+ * Threading (CudaBackend.cs:66, 5392: the reference serialises its launches under GpuDispatchLock): handles are
+ * independent of one another and create / destroy are thread-safe, but ONE handle is not re-entrant.  The persistent
+ * tcgen05 kernels keep their work-item counters and their status word in memory owned by the handle, so two launches
+ * of the same handle must not overlap on the GPU: issue them on one stream (or order them with events), do not replay
+ * a captured graph that contains a launch of the handle beside a live launch of it, and call aidn_sdpa_poll only when
+ * no launch of the handle is in flight on another stream.  Use one handle per stream.
+ *
+ * Padding: key / value rows that no query can see — rows at or past kv_len[b], the unused tail of the last pool block
+ * of a paged sequence, rows past seq_kv — may hold anything, NaN and Inf included: the forward kernels never let
+ * them reach the output.  aidn_sdpa_backward is the exception: K and V rows up to the end of the last 128-key tile
+ * that a sequence touches must be finite there (the reference zero-fills its buffers, CudaBackend.AllocateBuffer).
  */
 #ifndef AIDN_SDPA_H_
 #define AIDN_SDPA_H_
@@ -139,7 +151,9 @@ typedef struct {
 AIDN_API int aidn_sdpa_create(const aidn_sdpa_desc* desc, aidn_sdpa_t* out);
 /* Bytes of caller workspace a launch of this shape needs (0 for the prefill kernels); < 0 on error. */
 AIDN_API int64_t aidn_sdpa_workspace_bytes(aidn_sdpa_t h, int64_t batch, int64_t seq_q, int64_t seq_kv);
-/* Enqueues the attention forward on `cu_stream` (a CUstream / cudaStream_t).  Capture-safe, no allocation. */
+/* Enqueues the attention forward on `cu_stream` (a CUstream / cudaStream_t).  No allocation, no synchronisation; safe
+ * under stream capture once the handle has launched that kernel once outside capture (the first launch raises the
+ * kernel's shared-memory limit).  Launches of one handle must be stream-ordered (see "Threading" above). */
 AIDN_API int aidn_sdpa_launch(aidn_sdpa_t h, const aidn_sdpa_args* args, void* cu_stream);
 /* The same forward with K and V read through a block table (see aidn_paged_kv).  Decode (seq_q == 1, any batch,
  * per-sequence kv_len) is PagedAttentionDecode{,Gqa}; seq_q > 1 with desc.causal and causal_bottom_right = 0,
@@ -167,10 +181,12 @@ AIDN_API int aidn_sdpa_device_supported(int32_t device);
  * out (and lse / mask / kv_len) exactly as for aidn_sdpa_launch; `desc` is read on every call (path, max_*, nccl_comm
  * are ignored) and `args.workspace` is ignored.
  *   - Limit: batch * heads_in_shard * ceil(seq_kv / chunk) * (head_dim + 2) * 4 bytes must fit in 16 MiB, where
- *     chunk is desc.decode_chunk or the library's choice (at most 512 keys); a larger request returns
- *     AIDN_EWORKSPACE with the two sizes in aidn_sdpa_last_error().
- *   - The first call on each device looks up the array's device address (with that device current); make that
- *     first call outside any stream capture.
+ *     chunk is desc.decode_chunk or the library's choice: at most 1024 keys for 16-bit inputs with head_dim 64 / 128
+ *     and up to 16 query heads per KV head, at most 512 keys otherwise (fp32 inputs, head_dim 256, larger groups).  A
+ *     larger request returns AIDN_EWORKSPACE with the two sizes in aidn_sdpa_last_error().
+ *   - desc.device must be the current device.  The first call in each CUDA context looks up the array's device
+ *     address (the array has one copy per context: a process that uses the primary context and one created with
+ *     cuCtxCreate on the same GPU gets two); make that first call outside any stream capture.
  *   - All calls on a device share the one array and it keeps the previous call's contents.  Nothing has to be
  *     cleared between calls, because the combine kernel reads only the slots the partial kernel of the same call
  *     wrote, but two calls whose kernels overlap on the GPU (different streams, or two host threads) race on it:

@@ -16,7 +16,7 @@ def lib():
 
 
 def test_every_declared_symbol_is_exported(lib):
-    header = open(os.path.join(ROOT, "include", "aidn_sdpa.h")).read()
+    header = "".join(open(os.path.join(ROOT, "include", name)).read() for name in ("aidn_sdpa.h", "aidn_sdpa_debug.h"))
     declared = set(re.findall(r"AIDN_API\s+[\w\s\*]+?\b(aidn_\w+)\s*\(", header))
     assert len(declared) >= 13
     from aidotnet.tensors_b200 import native
