@@ -1,13 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the fused SDPA forward path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c2o16|c3|c3paged|c4|c4q|c4paged|c4gqa|c4gqatm|c4gqapaged|c5shard|c2bwd|c2bwdfull|c3bwd|mha|mhaq|qkvrope|qkvrope1|qkvrope70b|qkvrope32] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c1|c3|c5shard|c4|...] [--impl reference]
 
-One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The
-default workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out); the batched decode
-configuration (B64 H32 D128, kv_len in [512,4096]) is measured in the same run and reported under "decode".
-With N > 1 every rank runs the same per-GPU workload on its own head/batch shard of an N-times larger job
-(no collective on the data path; weak scaling).  Prints ONE JSON line on rank 0.
+One "step" is one pass of the attention forward over one synthetic batch of the named configuration.  The default
+workload is the Llama-style prefill (B4 H32 S2048 D128, causal, bf16 in, fp32 out), the configuration the metric is
+quoted on; the same run also measures, as objects of the same JSON line, the batched decode configuration ("decode":
+B64 H32 D128, kv_len in [512,4096]), the fp32 configuration ("c1"), the grouped-query prefill ("c3"), one GPU's shard
+of the long-context configuration ("c5shard") and the long-context job itself ("c5": B1 Hq64/Hkv8 S32768, whole on one
+GPU, or with --gpus N head-sharded over the N ranks with the all-gather of the output timed and checked).
+With N > 1 every rank also runs one copy of the default workload on its own shard of an N-times larger job (no
+collective on the data path; weak scaling).  Prints ONE JSON line on rank 0.
+
+Inputs come from one counter-based generator (aidotnet/tensors_b200/synth.py: Philox keyed by configuration, stream,
+batch entry and head) that the parity tests use too; after the timed region every workload compares a block of rows of
+what it computed with the CPU oracle ("checked").
 
 FLOPs are algorithmic: 4 * D * (visible query-key pairs), i.e. causal work is counted once, not doubled.
 Bytes for decode are the valid K and V rows plus Q and O, each once.
@@ -28,23 +35,29 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: (B, Hq, Hkv, Sq, Sk, D, causal, dtype, kind)
-    "c2": dict(B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True, kind="prefill",
+    # cfg = index of the baseline configuration (selects the generator's seed)
+    "c1": dict(cfg=1, B=1, Hq=8, Hkv=8, Sq=512, Sk=512, D=64, causal=False, kind="prefill", dtype="f32",
+               name="sdpa_fp32_B1_H8_S512_D64_noncausal"),
+    "c2": dict(cfg=2, B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True, kind="prefill",
                name="llama_prefill_B4_H32_S2048_D128_causal_bf16"),
-    "c2o16": dict(B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True, kind="prefill", out16=True,
+    "c2o16": dict(cfg=2, B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True, kind="prefill", out16=True,
                   name="llama_prefill_B4_H32_S2048_D128_causal_bf16_in_bf16_out"),
-    "c3": dict(B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill",
+    "c3": dict(cfg=3, B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill",
                name="gqa_prefill_B2_Hq32_Hkv8_S8192_D128_causal_bf16"),
-    "c5shard": dict(B=1, Hq=8, Hkv=1, Sq=32768, Sk=32768, D=128, causal=True, kind="prefill",
+    # one GPU's share of configuration 5: the 8 query heads of KV head 3
+    "c5shard": dict(cfg=5, B=1, Hq=8, Hkv=1, Sq=32768, Sk=32768, D=128, causal=True, kind="prefill",
+                    q_heads=list(range(24, 32)), kv_heads=[3],
                     name="long_context_shard_B1_Hq8_Hkv1_S32768_D128_causal_bf16"),
-    "c3paged": dict(B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill", block_size=16,
+    "c5": dict(cfg=5, B=1, Hq=64, Hkv=8, Sq=32768, Sk=32768, D=128, causal=True, kind="prefill",
+               name="long_context_B1_Hq64_Hkv8_S32768_D128_causal_bf16"),
+    "c3paged": dict(cfg=3, B=2, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True, kind="prefill", block_size=16,
                     name="paged_gqa_prefill_B2_Hq32_Hkv8_S8192_D128_block16_causal_bf16"),
     # attention backward (deterministic; tcgen05 dQ and dK/dV kernels for 16-bit inputs) on a quarter of the C2 shape
-    "c2bwd": dict(kind="bwd", B=1, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
+    "c2bwd": dict(cfg=2, kind="bwd", B=1, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
                   name="llama_backward_B1_H32_S2048_D128_causal_bf16"),
-    "c2bwdfull": dict(kind="bwd", B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
+    "c2bwdfull": dict(cfg=2, kind="bwd", B=4, Hq=32, Hkv=32, Sq=2048, Sk=2048, D=128, causal=True,
                       name="llama_backward_B4_H32_S2048_D128_causal_bf16"),
-    "c3bwd": dict(kind="bwd", B=1, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True,
+    "c3bwd": dict(cfg=3, kind="bwd", B=1, Hq=32, Hkv=8, Sq=8192, Sk=8192, D=128, causal=True,
                   name="gqa_backward_B1_Hq32_Hkv8_S8192_D128_causal_bf16"),
     # the in-library caller of the attention path: Q/K/V projections + attention + output projection in one call
     "mha": dict(kind="mha", B=4, S=2048, heads=32, D=128, name="mha_forward_B4_S2048_dmodel4096_H32_bf16"),
@@ -58,24 +71,24 @@ WORKLOADS = {
                      name="qkv_rope_cache_T1_Hq32_Hkv8_D128_bf16_weights"),
     "qkvrope32": dict(kind="gemv", tokens=1, heads=64, kv_heads=64, D=64, weight="f32", cache_rows=1 << 12,
                       name="qkv_rope_cache_T1_H64_D64_fp32_weights_reference_contract"),
-    "c4q": dict(B=16, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
+    "c4q": dict(cfg=4, B=16, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
                 name="batched_decode_quarter_B16_H32_D128_kvlen512-4096_bf16"),
-    "c4": dict(B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
+    "c4": dict(cfg=4, B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
                name="batched_decode_B64_H32_D128_kvlen512-4096_bf16"),
     # the same decode step over a paged pool [blocks, 16, Hkv, D] with a shuffled block table (the serving layout)
-    "c4paged": dict(B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode", block_size=16,
+    "c4paged": dict(cfg=4, B=64, Hq=32, Hkv=32, Sq=1, Sk=4096, D=128, causal=False, kind="decode", block_size=16,
                     name="paged_decode_B64_H32_D128_block16_kvlen512-4096_bf16"),
-    "c4gqa": dict(B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
+    "c4gqa": dict(cfg=4, B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode",
                   name="gqa_decode_B64_Hq32_Hkv8_D128_kvlen512-4096_bf16"),
-    "c4gqatm": dict(B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode", token_major=True,
+    "c4gqatm": dict(cfg=4, B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode", token_major=True,
                     name="gqa_decode_token_major_cache_B64_Hq32_Hkv8_D128_kvlen512-4096_bf16"),
-    "c4gqapaged": dict(B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode", block_size=16,
+    "c4gqapaged": dict(cfg=4, B=64, Hq=32, Hkv=8, Sq=1, Sk=4096, D=128, causal=False, kind="decode", block_size=16,
                        name="paged_gqa_decode_B64_Hq32_Hkv8_D128_block16_kvlen512-4096_bf16"),
 }
-# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each,
-# see profiles/).  Prefill C2 was captured directly.  Decode was captured on the B=16 quarter of C4 (525.5 MB of
-# traffic for 520.1 MB of algorithmic bytes); every (batch, head) streams its own keys once, so traffic grows in
-# proportion to the bytes streamed and a full-size launch is that ratio times its own algorithmic bytes.
+# DRAM traffic per launch of the dominant kernel (dram__bytes_read.sum + dram__bytes_write.sum, one ncu capture each; the
+# summaries are under profiles/).  Decode was captured on the B=16 quarter of C4 (525.5 MB of traffic for 520.1 MB of
+# algorithmic bytes); every (batch, head) streams its own keys once, so traffic grows in proportion to the bytes
+# streamed and a full-size launch is that ratio times its own algorithmic bytes.
 NCU_TRAFFIC_BYTES = {"c2": 651.5e6, "c4q": 525.5e6}
 NCU_DECODE_TRAFFIC_RATIO = 525.5 / 520.1
 
@@ -184,16 +197,47 @@ class ClockSampler:
                 "samples": len(inside), "note": note}
 
 
-def make_inputs(w, device, seed):
-    g = torch.Generator(device=device).manual_seed(seed)
-    mk = lambda *s: (torch.randn(s, generator=g, device=device) * 0.5).to(torch.bfloat16)
-    q = mk(w["B"], w["Hq"], w["Sq"], w["D"])
-    k = mk(w["B"], w["Hkv"], w["Sk"], w["D"])
-    v = mk(w["B"], w["Hkv"], w["Sk"], w["D"])
-    kv_len = None
-    if w["kind"] == "decode":
-        kv_len = np.random.Generator(np.random.Philox(seed)).integers(512, w["Sk"] + 1, w["B"]).astype(np.int32)
-    return q, k, v, kv_len
+def make_inputs(w, device, rank=0, q_heads=None, kv_heads=None):
+    """Q, K, V of the workload from the shared generator (streams 0, 1, 2 of its configuration; `rank` offsets the
+    batch index of the stream so that the copies of a weak-scaling run differ).  q_heads / kv_heads: global head
+    indices when only a shard of the heads is materialised."""
+    from aidotnet.tensors_b200 import synth
+    dt = w.get("dtype", "bf16")
+    scale = 1.0 if dt == "f32" else 0.5
+    q_heads = q_heads if q_heads is not None else w.get("q_heads")
+    kv_heads = kv_heads if kv_heads is not None else w.get("kv_heads")
+    cfg = w["cfg"] + 16 * rank
+    q = synth.tensor(cfg, synth.STREAM_Q, (w["B"], len(q_heads) if q_heads else w["Hq"], w["Sq"], w["D"]), dt, scale, q_heads)
+    k = synth.tensor(cfg, synth.STREAM_K, (w["B"], len(kv_heads) if kv_heads else w["Hkv"], w["Sk"], w["D"]), dt, scale, kv_heads)
+    v = synth.tensor(cfg, synth.STREAM_V, (w["B"], len(kv_heads) if kv_heads else w["Hkv"], w["Sk"], w["D"]), dt, scale, kv_heads)
+    kv_len = synth.lengths(cfg, w["B"], 512, w["Sk"]) if w["kind"] == "decode" else None
+    return q.to(device), k.to(device), v.to(device), kv_len
+
+
+def oracle_check(w, q, k, v, out, kv_len=None, rows=64, b=None, h=None):
+    """Compares `rows` query rows of one (batch entry, head) of `out` with the CPU oracle on the same inputs (read
+    back from the device).  Returns {"checked": bool, "max_abs": float, ...}; tolerance as in the parity tests."""
+    from oracle import sdpa_oracle as O
+    B, Hq, Sq, D = out.shape
+    b = B - 1 if b is None else b
+    h = Hq - 1 if h is None else h
+    group = Hq // k.shape[1]
+    kvh = h // group
+    r1 = Sq
+    r0 = max(0, r1 - rows)
+    qf = q[b:b + 1, h:h + 1, r0:r1].float().cpu().numpy()
+    kf = k[b:b + 1, kvh:kvh + 1].float().cpu().numpy()
+    vf = v[b:b + 1, kvh:kvh + 1].float().cpu().numpy()
+    kv = None if kv_len is None else np.asarray(kv_len[b:b + 1], np.int32)
+    off = (k.shape[2] - Sq + r0) if w["causal"] else 0
+    ref = O.sdpa(qf, kf, vf, causal=w["causal"], causal_offset=off, kv_len=kv)
+    got = out[b:b + 1, h:h + 1, r0:r1].float().cpu().numpy()
+    err = np.abs(got - ref)
+    if w.get("dtype", "bf16") == "f32":
+        rel = float(err.max() / max(np.abs(ref).max(), 1e-30))
+        return {"checked": bool(np.isfinite(got).all() and rel <= 1e-5), "rel": rel, "rows": [int(r0), int(r1)], "b": b, "h": h}
+    ok = bool(np.isfinite(got).all() and err.max() <= 2e-2 and err.mean() <= 2e-3)
+    return {"checked": ok, "max_abs": float(err.max()), "mean_abs": float(err.mean()), "rows": [int(r0), int(r1)], "b": b, "h": h}
 
 
 def run_gemv(args, w, pk):
@@ -268,7 +312,7 @@ def run_bwd(args, w, pk):
     (five matrix products: S, dP, dV, dQ, dK), causal pairs counted once."""
     from aidotnet.tensors_b200 import native as N
     dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    q, k, v, _ = make_inputs(w, dev, 5)
+    q, k, v, _ = make_inputs(w, dev)
     B, Hq, Hkv, Sq, Sk, D = w["B"], w["Hq"], w["Hkv"], w["Sq"], w["Sk"], w["D"]
     out = torch.empty((B, Hq, Sq, D), device=dev)
     lse = torch.empty((B, Hq, Sq), device=dev)
@@ -394,18 +438,40 @@ def run_mha(args, w, pk):
 class Runner:
     """One workload bound to one handle of the C ABI; `step()` enqueues one forward pass."""
 
-    def __init__(self, w, device_index, seed, decode_chunk=0):
+    def __init__(self, w, device_index, rank=0, decode_chunk=0, shard=None, nccl_comm=None):
+        """shard = (head_begin, head_count): the handle computes that head range of the FULL tensors of `w`; only the
+        shard's heads of Q / K / V are filled in (the rest is never read)."""
         from aidotnet.tensors_b200 import native as N
         self.N = N
         self.w = w
         dev = torch.device("cuda", device_index)
-        self.q, self.k, self.v, self.kv_len_host = make_inputs(w, dev, seed)
+        self.dev = dev
+        dt = w.get("dtype", "bf16")
+        self.dtype = dt
+        if shard is None:
+            self.q, self.k, self.v, self.kv_len_host = make_inputs(w, dev, rank)
+        else:
+            hb, hc = shard
+            group = w["Hq"] // w["Hkv"]
+            qh = list(range(hb, hb + hc))
+            kh = list(range(hb // group, (hb + hc) // group))
+            qs, ks, vs, _ = make_inputs(w, dev, 0, qh, kh)
+            self.q = torch.zeros((w["B"], w["Hq"], w["Sq"], w["D"]), dtype=qs.dtype, device=dev)
+            self.k = torch.zeros((w["B"], w["Hkv"], w["Sk"], w["D"]), dtype=ks.dtype, device=dev)
+            self.v = torch.zeros_like(self.k)
+            self.q[:, hb:hb + hc] = qs
+            self.k[:, kh[0]:kh[-1] + 1] = ks
+            self.v[:, kh[0]:kh[-1] + 1] = vs
+            self.kv_len_host = None
+            del qs, ks, vs
         self.kv_len = torch.from_numpy(self.kv_len_host).to(dev) if self.kv_len_host is not None else None
         out16 = bool(w.get("out16"))   # the reference's contract is an fp32 output; *o16 workloads keep the output in bf16
-        self.out = torch.empty((w["B"], w["Hq"], w["Sq"], w["D"]), dtype=torch.bfloat16 if out16 else torch.float32, device=dev)
-        self.h = N.Handle(device=device_index, qkv_dtype=N.BF16, out_dtype=N.BF16 if out16 else N.F32, head_dim=w["D"], num_q_heads=w["Hq"],
-                          num_kv_heads=w["Hkv"], causal=w["causal"], causal_bottom_right=True,
-                          max_batch=w["B"], max_seq_q=w["Sq"], max_seq_kv=w["Sk"], decode_chunk=decode_chunk)
+        self.out = torch.zeros((w["B"], self.q.shape[1], w["Sq"], w["D"]), dtype=torch.bfloat16 if out16 else torch.float32, device=dev)
+        adt = {"bf16": N.BF16, "f16": N.F16, "f32": N.F32}[dt]
+        self.h = N.Handle(device=device_index, qkv_dtype=adt, out_dtype=N.BF16 if out16 else N.F32, head_dim=w["D"],
+                          num_q_heads=self.q.shape[1], num_kv_heads=self.k.shape[1], causal=w["causal"], causal_bottom_right=True,
+                          max_batch=w["B"], max_seq_q=w["Sq"], max_seq_kv=w["Sk"], decode_chunk=decode_chunk,
+                          head_begin=shard[0] if shard else 0, head_count=shard[1] if shard else 0, nccl_comm=nccl_comm)
         self.stream = torch.cuda.current_stream(dev).cuda_stream
         self.launches = 0
         self.paged = {}
@@ -418,7 +484,7 @@ class Runner:
         if bs:
             # Scatter the logical blocks of every sequence over one shared pool [blocks, bs, Hkv, D].
             nb = w["B"] * w["Sk"] // bs
-            perm = torch.randperm(nb, generator=torch.Generator().manual_seed(seed & 0x7fffffff))
+            perm = torch.randperm(nb, generator=torch.Generator().manual_seed(w["cfg"]))
             for name in ("k", "v"):
                 logical = getattr(self, name).permute(0, 2, 1, 3).reshape(nb, bs, w["Hkv"], w["D"])
                 pool = torch.empty_like(logical)
@@ -428,44 +494,55 @@ class Runner:
             self.paged = dict(block_table=self.table.data_ptr(), block_table_stride=w["Sk"] // bs, block_size=bs,
                               num_blocks=nb)
 
-    def step(self, q=None, k=None, v=None, out=None, stream=None):
+    def step(self, q=None, k=None, v=None, out=None, stream=None, gather=False):
         q = self.q if q is None else q
         k = self.k if k is None else k
         v = self.v if v is None else v
         out = self.out if out is None else out
         self.h.launch(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), batch=self.w["B"],
                       seq_q=self.w["Sq"], seq_kv=self.w["Sk"], stream=self.stream if stream is None else stream,
-                      kv_len=self.kv_len.data_ptr() if self.kv_len is not None else None, **self.paged)
+                      kv_len=self.kv_len.data_ptr() if self.kv_len is not None else None, gather_output=gather, **self.paged)
         self.launches += self.h.last_launch_count
 
-    def time_steps(self, steps, warmup, sampler=None, dist=None):
+    def time_steps(self, steps, warmup, sampler=None, dist=None, repeats=1, gather=False):
+        """W warm-up steps, then `repeats` loops of exactly `steps` steps, every step bracketed by CUDA events on the
+        launching stream.  Returns (seconds of the FIRST loop, launches in it, per-step milliseconds of all loops)."""
         for _ in range(warmup):
-            self.step()
+            self.step(gather=gather)
         torch.cuda.synchronize()
-        if dist is not None:
-            dist.barrier()
+        per_step = []
+        first = None
+        first_launches = 0
+        for r in range(repeats):
+            if dist is not None:
+                dist.barrier()
+                torch.cuda.synchronize()
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+            l0 = self.launches
+            if sampler and r == 0:
+                sampler.mark_begin()
+            ev[0].record()
+            for i in range(steps):
+                self.step(gather=gather)
+                ev[i + 1].record()
             torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        l0 = self.launches
-        if sampler:
-            sampler.mark_begin()
-        e0.record()
-        for _ in range(steps):
-            self.step()
-        e1.record()
-        torch.cuda.synchronize()
+            if dist is not None:
+                dist.barrier()
+                torch.cuda.synchronize()
+            if r == 0:
+                first = ev[0].elapsed_time(ev[steps]) / 1e3
+                first_launches = self.launches - l0
+            per_step += [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
         if sampler:
             sampler.mark_end()
-        if dist is not None:
-            dist.barrier()
-            torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / 1e3, self.launches - l0
+        return first, first_launches, per_step
 
-    def time_e2e(self, steps, warmup):
+    def time_e2e(self, steps, warmup, copy_only=False):
         """The same C-ABI call with HOST buffers: every step copies its pinned Q/K/V in and its output back inside the
         timed region.  The three phases run on three streams over two sets of device buffers, so the host->device copy
         of step i+1 and the device->host copy of step i-1 overlap the kernel of step i (what a caller that streams
-        requests through the library would do); every step still moves all of its bytes."""
+        requests through the library would do); every step still moves all of its bytes.  copy_only: the same copies
+        on the same streams without the kernel - the ceiling the host link sets for this pipeline."""
         dev = self.q.device
         hq, hk, hv = (t.cpu().pin_memory() for t in (self.q, self.k, self.v))
         din = [tuple(torch.empty_like(t) for t in (self.q, self.k, self.v)) for _ in range(2)]
@@ -486,7 +563,8 @@ class Runner:
             with torch.cuda.stream(s_c):
                 s_c.wait_event(in_ready[b])
                 s_c.wait_event(out_free[b])              # step i-2's output has left this output buffer
-                self.step(*din[b], out=dout[b], stream=s_c.cuda_stream)
+                if not copy_only:
+                    self.step(*din[b], out=dout[b], stream=s_c.cuda_stream)
                 comp_done[b].record(s_c)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(comp_done[b])
@@ -508,6 +586,18 @@ class Runner:
         d2h = hout[0].numel() * hout[0].element_size()
         return e0.elapsed_time(e1) / 1e3, h2d, d2h
 
+    def check(self, **kw):
+        torch.cuda.synchronize()
+        return oracle_check(self.w, self.q, self.k, self.v, self.out, self.kv_len_host, **kw)
+
+
+def step_stats(per_step_ms, sm_mhz=None):
+    a = np.asarray(per_step_ms, np.float64)
+    st = {"n": int(a.size), "median_ms": float(np.median(a)), "p95_ms": float(np.percentile(a, 95)), "min_ms": float(a.min())}
+    if sm_mhz:
+        st["median_ms_x_sm_mhz"] = float(np.median(a) * sm_mhz)
+    return st
+
 
 def cpu_reference_time(w, threads, passes=1, sample_batch=None):
     """Times the CPU restatement of the reference path (faithful mode: full-width GEMMs, KV broadcast copy)."""
@@ -519,12 +609,13 @@ def cpu_reference_time(w, threads, passes=1, sample_batch=None):
     kv = None
     if w["kind"] == "decode":
         kv = np.random.Generator(np.random.Philox(7)).integers(512, w["Sk"] + 1, B).astype(np.int32)
-    t0 = time.perf_counter()
+    times = []
     for _ in range(passes):
+        t0 = time.perf_counter()
         O.sdpa(q, k, v, causal=w["causal"], kv_len=kv, faithful=True, threads=threads)
-    dt = (time.perf_counter() - t0) / passes
+        times.append(time.perf_counter() - t0)
     ws = dict(w, B=B)
-    return dt, algorithmic_flops(ws, kv), algorithmic_bytes(ws, kv)
+    return times, algorithmic_flops(ws, kv), algorithmic_bytes(ws, kv)
 
 
 def host_threads():
@@ -536,41 +627,147 @@ def host_threads():
 
 
 def run_reference_arm(args, w):
-    """`--impl reference`: the reference's CPU attention path (C++ restatement; the .NET original cannot run here)."""
+    """`--impl reference`: the reference's CPU attention path (C++ restatement; the .NET original cannot run here) on
+    the whole workload, every step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = host_threads()
-    sample_batch = 1
-    times = []
-    for i in range(args.warmup + args.steps):
-        dt, fl, by = cpu_reference_time(w, threads, 1, sample_batch)
-        if i >= args.warmup:
-            times.append(dt)
+    times, fl, by = cpu_reference_time(w, threads, args.warmup + args.steps)
+    times = times[args.warmup:]
     ms = float(np.mean(times)) * 1e3
     value = (fl / 1e12) / (ms / 1e3) if w["kind"] == "prefill" else (by / 1e9) / (ms / 1e3)
     unit = "TFLOP/s" if w["kind"] == "prefill" else "GB/s"
-    sample = f"batch entry 0 of the workload ({sample_batch} of {w['B']} batch entries) per step"
+    sample = "the whole workload (all %d batch entries) per step" % w["B"]
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic", "config": {"workload": w["name"], "sample": sample},
         "cpu_baseline": {"value": value, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "per_step": step_stats([t * 1e3 for t in times]), "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def side_workload(key, local, pk, steps, dist=None, world=1):
+    """One of the other baseline configurations, measured in the default run: kernel-only value, roofline, check."""
+    w = WORKLOADS[key]
+    r = Runner(w, local)
+    secs, launches, per = r.time_steps(steps, 3, None, dist, repeats=2)
+    if dist is not None:
+        t = torch.tensor([secs], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        secs = float(t.item())
+    fl, by = algorithmic_flops(w, r.kv_len_host), algorithmic_bytes(w, r.kv_len_host)
+    tf = fl / 1e12 / (secs / steps)
+    f32 = w.get("dtype") == "f32"
+    # fp32 inputs run FFMA arithmetic: no measured peak exists for it, the nominal one is 148 SMs x 128 lanes x 2 x 1.965 GHz
+    peak = 74.4 if f32 else pk["bf16"]
+    obj = {"workload": w["name"], "value": tf * world, "unit": "TFLOP/s", "per_gpu": tf, "ms_per_step": secs / steps * 1e3,
+           "steps": steps, "per_step": step_stats(per), "gpu_launches": launches, "tokens_per_s": w["B"] * w["Sq"] * world / (secs / steps),
+           "roofline": {"bound": "fp32 FFMA (0.5 GFLOP, latency-bound; reported, not a target)" if f32 else "tensor",
+                        "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                        "traffic": ncu_traffic(key, w, by), "traffic_unit": "bytes per launch (ncu)", "algorithmic": fl,
+                        "algorithmic_unit": "FLOP per launch", "algorithmic_bytes": by,
+                        "peak_source": "nominal fp32 FFMA" if f32 else pk["source"] + " (burst)"},
+           "check": r.check()}
+    del r
+    torch.cuda.empty_cache()
+    return obj
+
+
+def long_context_job(local, rank, world, pk, steps, dist):
+    """Configuration 5 as one job: B1, 64 query heads over 8 KV heads, S 32768, causal.  One GPU runs all of it; N ranks
+    take `sharding.plan(N, 1, 64, 8)` - whole KV groups, so K/V are never duplicated and the computation needs no
+    collective.  Timed twice: the kernel alone, and the same launch with gather_output = 1, i.e. followed on the same
+    stream by the library's ncclAllGather that leaves the full [1, 64, S, D] output on every rank."""
+    from aidotnet.tensors_b200 import nccl_util, sharding
+    w = WORKLOADS["c5"]
+    fl, by = algorithmic_flops(w), algorithmic_bytes(w)
+    if world == 1:
+        r = Runner(w, local)
+        secs, launches, per = r.time_steps(steps, 2, None, None, repeats=1)
+        tf = fl / 1e12 / (secs / steps)
+        obj = {"workload": w["name"], "ranks": 1, "heads_per_rank": 64, "value": tf, "unit": "TFLOP/s", "per_gpu": tf,
+               "ms_per_step": secs / steps * 1e3, "steps": steps, "per_step": step_stats(per), "gpu_launches": launches,
+               "tokens_per_s": w["Sq"] / (secs / steps),
+               "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16"], "unit": "TFLOP/s", "frac": tf / pk["bf16"],
+                            "traffic": None, "algorithmic": fl, "algorithmic_unit": "FLOP per launch",
+                            "peak_source": pk["source"] + " (burst)"},
+               "gather": None, "check": r.check(h=37)}
+        del r
+        torch.cuda.empty_cache()
+        return obj
+    plan = sharding.plan(world, w["B"], w["Hq"], w["Hkv"])
+    if not sharding.gatherable(plan):
+        return {"workload": w["name"], "ranks": world, "skipped": "8 KV groups do not split evenly over %d ranks" % world}
+    sh = plan[rank]
+    comm = nccl_util.create_comm(rank, world)
+    r = Runner(w, local, shard=(sh.head_begin, sh.head_count), nccl_comm=comm)
+    secs, launches, per = r.time_steps(steps, 2, None, dist, repeats=1)
+    gsecs, _, gper = r.time_steps(steps, 2, None, dist, repeats=1, gather=True)
+    t = torch.tensor([secs, gsecs], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs, gsecs = float(t[0].item()), float(t[1].item())
+    # every rank checks (a) a row block of its own shard against the CPU oracle and (b) a row block of a REMOTE rank's
+    # heads in the gathered output against a local recomputation from regenerated inputs
+    torch.cuda.synchronize()
+    own = oracle_check(w, r.q, r.k, r.v, r.out, None, rows=32, h=sh.head_begin + sh.head_count - 1)
+    other = plan[(rank + 1) % world]
+    group = w["Hq"] // w["Hkv"]
+    rows = 128
+    r0 = w["Sq"] - rows
+    qh = list(range(other.head_begin, other.head_begin + other.head_count))
+    kh = list(range(other.head_begin // group, (other.head_begin + other.head_count) // group))
+    dev = torch.device("cuda", local)
+    qo, ko, vo, _ = make_inputs(w, dev, 0, qh, kh)
+    from aidotnet.tensors_b200 import native as N
+    h2 = N.Handle(device=local, qkv_dtype=N.BF16, head_dim=w["D"], num_q_heads=len(qh), num_kv_heads=len(kh), causal=True,
+                  causal_bottom_right=False, causal_offset=r0)
+    o2 = torch.empty((1, len(qh), rows, w["D"]), device=dev)
+    q_rows = qo[:, :, r0:].contiguous()
+    h2.launch(q=q_rows.data_ptr(), k=ko.data_ptr(), v=vo.data_ptr(), out=o2.data_ptr(), batch=1, seq_q=rows, seq_kv=w["Sk"],
+              stream=r.stream)
+    torch.cuda.synchronize()
+    remote_diff = float((o2 - r.out[:, other.head_begin:other.head_begin + other.head_count, r0:]).abs().max())
+    remote_ok = bool(remote_diff <= 1e-6)   # the same kernel on the same rows and keys: expected bit-identical
+    flags = torch.tensor([int(own["checked"]), int(remote_ok)], device="cuda")
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    h2.close()
+    per_rank_fl = fl / world
+    tf = per_rank_fl / 1e12 / (secs / steps)
+    out_bytes = w["Hq"] * w["Sq"] * w["D"] * 4
+    gather_ms = max(gsecs - secs, 0.0) / steps * 1e3
+    recv = out_bytes * (world - 1) / world
+    obj = {"workload": w["name"], "ranks": world, "heads_per_rank": sh.head_count, "value": tf * world, "unit": "TFLOP/s",
+           "per_gpu": tf, "ms_per_step": secs / steps * 1e3, "steps": steps, "per_step": step_stats(per), "gpu_launches": launches,
+           "scaling": "strong (one fixed job split over the ranks); efficiency = (N=1 ms_per_step) / (N x this ms_per_step)",
+           "tokens_per_s": w["Sq"] / (secs / steps),
+           "roofline": {"bound": "tensor", "achieved": tf, "peak": pk["bf16"], "unit": "TFLOP/s", "frac": tf / pk["bf16"],
+                        "traffic": None, "algorithmic": per_rank_fl, "algorithmic_unit": "FLOP per launch and rank",
+                        "peak_source": pk["source"] + " (burst)"},
+           "gather": {"ms_per_step_with_gather": gsecs / steps * 1e3, "gather_ms": gather_ms, "per_step": step_stats(gper),
+                      "bytes_received_per_rank": recv, "nvlink_gbs_per_rank": (recv / 1e9) / (gather_ms / 1e3) if gather_ms > 0 else None,
+                      "nvlink_reference_gbs": 770.0, "collective": "ncclAllGather, in place, on the kernel's stream"},
+           "gather_ok": bool(flags[1].item() == 1), "gather_check": {"rows": [r0, r0 + rows], "remote_heads": [qh[0], qh[-1]], "max_abs_diff_rank0": remote_diff},
+           "check": dict(own, all_ranks=bool(flags[0].item() == 1))}
+    del r
+    nccl_util.destroy_comm(comm)
+    torch.cuda.empty_cache()
+    return obj
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode / c1 / c3 / c5 objects of the default run")
+    ap.add_argument("--repeats", type=int, default=10, help="loops of --steps steps timed for the per-step statistics")
     ap.add_argument("--decode-chunk", type=int, default=0, help="keys per split of the decode kernel (0 = library's choice)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -607,10 +804,10 @@ def main():
     if sampler:
         sampler.start()
 
-    runner = Runner(w, local, 0xA1D00000 + 2 + rank, args.decode_chunk)
+    runner = Runner(w, local, rank, args.decode_chunk)
     kvh = runner.kv_len_host
     fl, by = algorithmic_flops(w, kvh), algorithmic_bytes(w, kvh)
-    secs, launches = runner.time_steps(args.steps, args.warmup, sampler, dist)
+    secs, launches, per = runner.time_steps(args.steps, args.warmup, sampler, dist, repeats=max(1, args.repeats))
     if dist is not None:
         t = torch.tensor([secs], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -621,65 +818,83 @@ def main():
     per_gpu = (fl / 1e12 if prefill else by / 1e9) / per_step
     value = per_gpu * world
     peak = pk["bf16"] if prefill else pk["hbm"]
+    check = runner.check()
 
-    e2e_secs, h2d, d2h = runner.time_e2e(max(3, min(args.steps, 20)), 2)
     e2e_steps = max(3, min(args.steps, 20))
+    e2e_secs, h2d, d2h = runner.time_e2e(e2e_steps, 2)
+    copy_secs, _, _ = runner.time_e2e(e2e_steps, 2, copy_only=True)
     if dist is not None:
-        t = torch.tensor([e2e_secs], device="cuda")
+        t = torch.tensor([e2e_secs, copy_secs], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_secs = float(t.item())
+        e2e_secs, copy_secs = float(t[0].item()), float(t[1].item())
     e2e_value = (fl / 1e12 if prefill else by / 1e9) / (e2e_secs / e2e_steps) * world
 
-    decode_obj = None
-    if prefill and not args.no_decode:
+    extra = {}
+    if args.workload == "c2" and not args.no_decode:
         wd = WORKLOADS["c4"]
-        rd = Runner(wd, local, 0xA1D00004 + rank)
-        dsecs, dl = rd.time_steps(max(10, args.steps // 2), 3, None, dist)
-        dsteps = max(10, args.steps // 2)
+        rd = Runner(wd, local, rank)
+        dsteps = max(10, args.steps)
+        dsecs, dl, dper = rd.time_steps(dsteps, 3, None, dist, repeats=2)
         if dist is not None:
             t = torch.tensor([dsecs], device="cuda")
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             dsecs = float(t.item())
         dby = algorithmic_bytes(wd, rd.kv_len_host)
         gbs = dby / 1e9 / (dsecs / dsteps)
-        decode_obj = {"workload": wd["name"], "value": gbs * world, "unit": "GB/s", "ms_per_step": dsecs / dsteps * 1e3,
-                      "tokens_per_s": wd["B"] * world / (dsecs / dsteps), "gpu_launches": dl,
-                      "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s",
-                                   "frac": gbs / pk["hbm"], "traffic": ncu_traffic("c4", wd, dby),
-                                   "traffic_unit": "bytes per launch (ncu, B=16 capture scaled by the bytes streamed)", "algorithmic": dby,
-                                   "algorithmic_unit": "bytes per launch", "peak_source": pk["source"]}}
+        extra["decode"] = {"workload": wd["name"], "value": gbs * world, "unit": "GB/s", "ms_per_step": dsecs / dsteps * 1e3,
+                           "steps": dsteps, "per_step": step_stats(dper), "tokens_per_s": wd["B"] * world / (dsecs / dsteps), "gpu_launches": dl,
+                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm"], "unit": "GB/s",
+                                        "frac": gbs / pk["hbm"], "traffic": ncu_traffic("c4", wd, dby),
+                                        "traffic_unit": "bytes per launch (ncu, B=16 capture scaled by the bytes streamed)", "algorithmic": dby,
+                                        "algorithmic_unit": "bytes per launch", "peak_source": pk["source"]},
+                           "check": rd.check()}
         del rd
+        torch.cuda.empty_cache()
+        side_steps = max(5, min(args.steps, 20))
+        for key in ("c1", "c3", "c5shard"):
+            extra[key] = side_workload(key, local, pk, side_steps, dist, world)
+        del runner.q, runner.k, runner.v
+        torch.cuda.empty_cache()
+        extra["c5"] = long_context_job(local, rank, world, pk, 5 if world == 1 else 10, dist)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = host_threads()
-        dt, cfl, cby = cpu_reference_time(w, threads, 1, 1 if prefill else None)
+        # one warm-up pass, then two timed passes over the whole workload (all batch entries), as the reference arm does
+        times, cfl, cby = cpu_reference_time(w, threads, 3)
+        dt = float(np.mean(times[1:]))
         cpu = {"value": (cfl / 1e12 if prefill else cby / 1e9) / dt, "unit": "TFLOP/s" if prefill else "GB/s",
                "cores": threads, "kind": "port",
-               "sample": ("batch entry 0 of the workload (1 of %d batch entries), one pass" % w["B"]) if prefill
-               else "the full workload, one pass"}
+               "sample": "the whole workload (all %d batch entries), mean of two passes after one warm-up pass" % w["B"]}
 
     if rank == 0:
+        mhz = clocks.get("sm_mhz") if clocks else None
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s" if prefill else "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "scaling": "weak", "vs_baseline": None, "dtype": w.get("dtype", "bf16"), "data": "synthetic",
             "config": {"workload": w["name"], "per_gpu": "one copy of the workload per GPU (batch x head shard of an N-fold job)",
                        "l2": "inputs+outputs larger than the 126 MB L2; no flush",
-                       "flop_convention": "4*D*visible(q,k) pairs (causal counted once)"},
+                       "flop_convention": "4*D*visible(q,k) pairs (causal counted once)",
+                       "inputs": "synth.py, seed 0xA1D00000 + configuration, streams Q/K/V = 0/1/2"},
             "per_gpu": per_gpu, "pct_of_measured_bf16_peak": (100.0 * per_gpu / pk["bf16"]) if prefill else None,
             "tokens_per_s": w["B"] * w["Sq"] * world / per_step,
+            "per_step": dict(step_stats(per, mhz), loops=max(1, args.repeats), note="value and ms_per_step are the first loop of --steps steps"),
             "roofline": {"bound": "tensor" if prefill else "hbm", "achieved": per_gpu, "peak": peak,
                          "unit": "TFLOP/s" if prefill else "GB/s", "frac": per_gpu / peak,
                          "traffic": ncu_traffic(args.workload, w, by), "traffic_unit": "bytes per launch (ncu)",
                          "algorithmic": fl if prefill else by, "algorithmic_unit": "FLOP per launch" if prefill else "bytes per launch",
-                         "peak_source": pk["source"] + (" (burst)" if prefill else "")},
+                         "algorithmic_bytes": by, "peak_source": pk["source"] + (" (burst)" if prefill else "")},
+            "check": check, "checked": bool(check["checked"]),
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s" if prefill else "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_secs / e2e_steps * 1e3,
-                    "pipeline": "host->device copy, kernel and device->host copy on three streams over two buffer sets"},
-            "gpu_launches": launches, "clocks": clocks, "decode": decode_obj,
+                    "copy_only_ms": copy_secs / e2e_steps * 1e3, "frac_of_copy_only": copy_secs / e2e_secs,
+                    "pipeline": "host->device copy, kernel and device->host copy on three streams over two buffer sets; "
+                                "copy_only_ms = the same copies without the kernel (max over ranks)"},
+            "gpu_launches": launches, "clocks": clocks,
         }
+        line.update(extra)
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
