@@ -24,6 +24,31 @@ def gen(shape, dtype: str, seed: int, scale: float = 0.5):
     return t.cuda(), t.to(torch.float32).numpy()
 
 
+# Guard words around every buffer a launch writes (output, log-sum-exp, workspace): a kernel that stores outside its
+# buffer is caught here.  The host-side stand-in for a memory checker (compare-sanitizer is not available where these
+# tests run); the reference guards its own launches on the host too (Engines/DirectGpu/GpuKernelGuards.cs:10-70).
+GUARD = 256
+CANARY = 1232.0   # exactly representable in fp32, fp16 and bf16
+
+
+def guarded(shape, dtype, device, fill=float("nan")):
+    """A tensor of `shape` inside a larger allocation with GUARD canary elements on either side.  Returns (flat, body)."""
+    n = int(np.prod(shape))
+    flat = torch.full((n + 2 * GUARD,), CANARY, dtype=dtype, device=device)
+    body = flat[GUARD:GUARD + n].view(shape)
+    body.fill_(fill)
+    return flat, body
+
+
+def check_guards(flat, what):
+    head, tail = flat[:GUARD], flat[-GUARD:]
+    if flat.dtype == torch.uint8:
+        ok = bool((head == 0xA5).all()) and bool((tail == 0xA5).all())
+    else:
+        ok = bool((head == CANARY).all()) and bool((tail == CANARY).all())
+    assert ok, f"{what}: a kernel wrote outside its buffer (guard words changed)"
+
+
 def run_gpu(q, k, v, *, dtype: str, out_dtype: str = "f32", causal=False, bottom_right=True, causal_offset=0,
             softcap=0.0, mask=None, mask_kind=N.MASK_NONE, kv_len=None, want_lse=False, path=N.PATH_AUTO,
             scale=0.0, decode_chunk=0, k_stride=None, v_stride=None, seq_kv=None, num_kv_heads=None,
@@ -33,9 +58,14 @@ def run_gpu(q, k, v, *, dtype: str, out_dtype: str = "f32", causal=False, bottom
     Hkv = num_kv_heads if num_kv_heads is not None else k.shape[1]
     Sk = seq_kv if seq_kv is not None else k.shape[2]
     dev = q.device.index or 0
+    guards = []
     if out is None:
-        out = torch.full((B, Hq, Sq, D), float("nan"), dtype=TORCH_DT[out_dtype], device=q.device)
-    lse = torch.full((B, Hq, Sq), float("nan"), dtype=torch.float32, device=q.device) if want_lse else None
+        flat, out = guarded((B, Hq, Sq, D), TORCH_DT[out_dtype], q.device)
+        guards.append((flat, "output"))
+    lse = None
+    if want_lse:
+        flat, lse = guarded((B, Hq, Sq), torch.float32, q.device)
+        guards.append((flat, "log-sum-exp"))
     mask_stride = (0, 0, 0, 0)
     mt = None
     if mask is not None:
@@ -50,7 +80,9 @@ def run_gpu(q, k, v, *, dtype: str, out_dtype: str = "f32", causal=False, bottom
                  head_begin=head_begin, head_count=head_count)
     stream = torch.cuda.current_stream().cuda_stream
     nbytes = h.workspace_bytes(B, Sq, Sk)
-    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    ws_flat = torch.full((max(nbytes, 16) + 2 * GUARD,), 0xA5, dtype=torch.uint8, device=q.device)
+    ws = ws_flat[GUARD:GUARD + max(nbytes, 16)]
+    guards.append((ws_flat, "workspace"))
     h.launch(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), batch=B, seq_q=Sq, seq_kv=Sk,
              stream=stream, lse=lse.data_ptr() if lse is not None else None,
              mask=mt.data_ptr() if mt is not None else None, mask_stride=mask_stride,
@@ -58,6 +90,8 @@ def run_gpu(q, k, v, *, dtype: str, out_dtype: str = "f32", causal=False, bottom
              workspace=ws.data_ptr() if nbytes > 0 else None, workspace_bytes=nbytes)
     if poll:
         h.poll(stream)
+        for flat, what in guards:
+            check_guards(flat, what)
     info = dict(path=h.last_path, launches=h.last_launch_count)
     h.close()
     return out, lse, info
@@ -83,6 +117,33 @@ def compare_lse(lse: torch.Tensor, ref: np.ndarray, dtype: str, what: str = ""):
     assert np.array_equal(np.isneginf(got), inf_ref), f"{what}: -inf pattern of LSE differs"
     tol = 1e-4 if dtype == "f32" else 2e-2   # the reference's own half-precision LSE bar is 0.02
     assert np.abs(got[~inf_ref] - ref[~inf_ref]).max(initial=0.0) <= tol, f"{what}: LSE mismatch"
+
+
+def gen_config(config: int, stream: int, shape, dtype: str, scale: float = 0.5, heads=None):
+    """Inputs of a baseline configuration from the generator the benchmark uses (aidotnet/tensors_b200/synth.py):
+    (device tensor, fp32 numpy view of the same rounded values)."""
+    from aidotnet.tensors_b200 import synth
+    t = synth.tensor(config, stream, shape, dtype, scale, heads)
+    return t.cuda(), t.to(torch.float32).numpy()
+
+
+def reference_rows(qf, kf, vf, b, h, rows, *, causal_offset=0, scale=None):
+    """float64 attention output for an arbitrary set of query rows of one (batch entry, head): the textbook
+    formulation, used where the rows are scattered (the C++ oracle takes contiguous row blocks).  Causal with the
+    given offset; K / V of the head's KV group."""
+    Hq, Hkv = qf.shape[1], kf.shape[1]
+    kvh = h // (Hq // Hkv)
+    D = qf.shape[-1]
+    scale = 1.0 / np.sqrt(D) if scale is None else scale
+    rows = np.asarray(rows)
+    qs = qf[b, h, rows].astype(np.float64)
+    s = qs @ kf[b, kvh].astype(np.float64).T * scale
+    key = np.arange(kf.shape[2])[None, :]
+    s = np.where(key <= rows[:, None] + causal_offset, s, -np.inf)
+    s -= s.max(axis=1, keepdims=True)
+    p = np.exp(s)
+    p /= p.sum(axis=1, keepdims=True)
+    return p @ vf[b, kvh].astype(np.float64)
 
 
 def oracle_rows(qf, kf, vf, r0, r1, *, causal, causal_offset, **kw):
