@@ -105,6 +105,10 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         [DllImport(Lib)] public static extern long aidn_sdpa_workspace_bytes(IntPtr handle, long batch, long seqQ, long seqKv);
         [DllImport(Lib)] public static extern int aidn_sdpa_launch(IntPtr handle, ref AidnSdpaArgs args, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_sdpa_launch_paged(IntPtr handle, ref AidnSdpaArgs args, ref AidnPagedKv paged, IntPtr cuStream);
+        /// <summary>Batched decode without a handle or a workspace (split-KV partials in a 16 MiB array inside the
+        /// library): for a backend that may not allocate device memory where it decodes.  First call per context
+        /// outside stream capture; concurrent calls on one device share the array and must be stream-ordered.</summary>
+        [DllImport(Lib)] public static extern int aidn_sdpa_decode_noalloc(ref AidnSdpaDesc desc, ref AidnSdpaArgs args, IntPtr cuStream);
         [DllImport(Lib)] public static extern int aidn_paged_kv_append(IntPtr newKeys, IntPtr newValues, IntPtr keyPool, IntPtr valuePool, IntPtr blockTable, long startPosition, long tokens, int blockSize, int numBlocks, long rowBytes, IntPtr cuStream);
         [DllImport(Lib)] public static extern long aidn_sdpa_backward_workspace_bytes(IntPtr handle, long batch, long seqQ);
         [DllImport(Lib)] public static extern int aidn_sdpa_backward(IntPtr handle, ref AidnSdpaBwdArgs args, IntPtr cuStream);
