@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -30,6 +31,35 @@ int fail_cuda(cudaError_t e, const char* what) {
 }
 
 inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+// AIDOTNET_KERNEL_LAUNCH_CHECK=1, the reference's own debugging switch (CudaBackend.cs:5381-5421): every entry point
+// then synchronises the stream right after its launches and reports a device error, or a bounded wait that gave up, as
+// the failure of THAT call instead of some later one.  Skipped while the stream is being captured.  Read once.
+bool launch_check_enabled() {
+  static const bool on = [] {
+    const char* v = std::getenv("AIDOTNET_KERNEL_LAUNCH_CHECK");
+    return v && v[0] == '1' && v[1] == 0;
+  }();
+  return on;
+}
+
+int post_launch_check(cudaStream_t stream, const char* what, int32_t* status_dev) {
+  if (!launch_check_enabled()) return AIDN_OK;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return AIDN_OK;
+  }
+  cudaError_t e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail(AIDN_ECUDA, "[LAUNCH-FAULT] %s: %s (%s)", what, cudaGetErrorString(e), cudaGetErrorName(e));
+  if (status_dev) {
+    int32_t st = 0;
+    e = cudaMemcpy(&st, status_dev, sizeof(st), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return fail_cuda(e, "launch check: status read");
+    if (st & aidn::kStatusTimeout) return fail(AIDN_ETIMEOUT, "[LAUNCH-FAULT] %s: a kernel gave up a bounded wait (status word 0x%x)", what, st);
+  }
+  return AIDN_OK;
+}
 
 size_t elem_size(int dtype) { return dtype == AIDN_F32 ? 4 : 2; }
 
@@ -426,7 +456,7 @@ int launch_common(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* p
       return fail(AIDN_ENCCL, "launch: ncclAllGather failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?");
     h->last_launches += 1;
   }
-  return AIDN_OK;
+  return post_launch_check(stream, "aidn_sdpa_launch", h->status_dev);
 }
 
 }  // namespace
@@ -489,7 +519,7 @@ int aidn_sdpa_backward(aidn_sdpa_t h, const aidn_sdpa_bwd_args* a, void* cu_stre
   if (e != cudaSuccess) return fail_cuda(e, "backward");
   h->last_path = used_tcgen05 ? AIDN_PATH_PREFILL_SM100 : AIDN_PATH_GENERIC;
   h->last_launches = launches;
-  return AIDN_OK;
+  return post_launch_check((cudaStream_t)cu_stream, "aidn_sdpa_backward", h->status_dev);
 }
 
 // Decode for callers that cannot allocate device memory (no handle, no workspace): see include/aidn_sdpa.h.
@@ -576,7 +606,7 @@ int aidn_sdpa_decode_noalloc(const aidn_sdpa_desc* desc, const aidn_sdpa_args* a
   int launches = 0;
   cudaError_t e = aidn::launch_decode_static(p, d.qkv_dtype, chunk, nchunks, (cudaStream_t)cu_stream, &launches);
   if (e != cudaSuccess) return fail_cuda(e, "decode_noalloc");
-  return AIDN_OK;
+  return post_launch_check((cudaStream_t)cu_stream, "aidn_sdpa_decode_noalloc", nullptr);
 }
 
 int aidn_qkv_rope_cache(const aidn_qkv_rope_args* a, void* cu_stream) {
@@ -632,7 +662,7 @@ int aidn_qkv_rope_cache(const aidn_qkv_rope_args* a, void* cu_stream) {
   int launches = 0;
   e = aidn::launch_qkv_rope_cache(p, a->weight_dtype, sms, (cudaStream_t)cu_stream, &launches);
   if (e != cudaSuccess) return fail_cuda(e, "qkv_rope_cache");
-  return AIDN_OK;
+  return post_launch_check((cudaStream_t)cu_stream, "aidn_qkv_rope_cache", nullptr);
 }
 
 int aidn_rope_interleaved(const float* input, const float* cosine, const float* sine, float* output, int64_t rows,
@@ -809,7 +839,7 @@ int aidn_mha_forward(aidn_sdpa_t h, const aidn_mha_args* a, void* cu_stream) {
   rc = gemm("mha: output projection");
   if (rc != AIDN_OK) return rc;
   h->last_launches = launches;
-  return AIDN_OK;
+  return post_launch_check(stream, "aidn_mha_forward", h->status_dev);
 }
 
 static int cast_common(int kind, const void* src, void* dst, int64_t n, void* cu_stream) {

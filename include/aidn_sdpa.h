@@ -32,6 +32,10 @@
  * a captured graph that contains a launch of the handle beside a live launch of it, and call aidn_sdpa_poll only when
  * no launch of the handle is in flight on another stream.  Use one handle per stream.
  *
+ * Debugging: with AIDOTNET_KERNEL_LAUNCH_CHECK=1 in the environment (the reference's own switch, CudaBackend.cs:5381-5421)
+ * every entry point synchronises its stream after launching and returns a device error or an expired bounded wait as
+ * its own status ("[LAUNCH-FAULT] ..." in aidn_sdpa_last_error()).  Off by default; ignored during stream capture.
+ *
  * Padding: key / value rows that no query can see — rows at or past kv_len[b], the unused tail of the last pool block
  * of a paged sequence, rows past seq_kv — may hold anything, NaN and Inf included: the forward kernels never let
  * them reach the output.  aidn_sdpa_backward is the exception: K and V rows up to the end of the last 128-key tile
@@ -270,7 +274,9 @@ AIDN_API int aidn_rope_interleaved(const float* input, const float* cosine, cons
  *     generic attention kernel in fp32 arithmetic; with an fp32 handle this meets the 1e-4 bound of the reference's own
  *     tests of the fused call (tests/AiDotNet.Tensors.Tests/Engines/MultiHeadAttentionForwardTests.cs:123).
  * The handle gives heads, head_dim and the mask kind (none or a keep-mask broadcastable to [B, H, S, S]; a fully masked
- * row gives zeros, CpuEngine.MultiHeadAttention.cs:481-485); it must have out_dtype == qkv_dtype,
+ * row gives zeros, CpuEngine.MultiHeadAttention.cs:481-485; a handle created with desc.causal = 1 additionally applies
+ * the causal rule without a materialised mask - an extension, the reference expresses causality through the mask); it
+ * must have out_dtype == qkv_dtype,
  * num_kv_heads == num_q_heads, all heads, no log-sum-exp, softcap or additive bias (else AIDN_EUNSUPPORTED). */
 typedef struct {
   const void* input;        /* [batch, seq, heads*head_dim], input_dtype                                         */

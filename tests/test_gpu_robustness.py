@@ -144,3 +144,40 @@ def test_a_launch_allocates_nothing(kind):
     assert torch.cuda.memory_allocated() == alloc0 and torch.cuda.memory_reserved() == reserved0
     assert free1 == free0, f"device memory changed across 100 launches: {free0} -> {free1}"
     h.close()
+
+
+def test_launch_check_switch_reports_a_failure_at_the_call_that_caused_it():
+    """AIDOTNET_KERNEL_LAUNCH_CHECK=1 (the reference's switch, CudaBackend.cs:5381-5421): the launch itself returns the
+    expired bounded wait that normally only aidn_sdpa_poll reports.  The failure is provoked with the test hook that
+    withholds the producer's loads (20 ms budget, no fault); the variable is read once per process, hence the child."""
+    import os
+    import subprocess
+    import sys
+    code = r'''
+import torch
+from aidotnet.tensors_b200 import native as N
+from tests._harness import gen
+q, _ = gen((1, 4, 256, 128), "bf16", 1); k, _ = gen((1, 2, 256, 128), "bf16", 2); v = k.clone()
+out = torch.zeros((1, 4, 256, 128), device="cuda")
+h = N.Handle(device=0, qkv_dtype=N.BF16, head_dim=128, num_q_heads=4, num_kv_heads=2, causal=True)
+st = torch.cuda.current_stream().cuda_stream
+go = lambda: h.launch(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), batch=1, seq_q=256, seq_kv=256, stream=st)
+go()                                  # a healthy launch passes the check
+h.debug_set(None, 3)
+try:
+    go()
+    raise SystemExit("the launch did not report the expired wait")
+except N.AidnError as e:
+    assert e.status == N.ETIMEOUT and "LAUNCH-FAULT" in e.message, (e.status, e.message)
+h.debug_set(None, 0)
+try:
+    h.poll(st)                        # clears the status word
+except N.AidnError:
+    pass
+go(); h.poll(st)
+print("launch check ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, AIDOTNET_KERNEL_LAUNCH_CHECK="1", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300, env=env, cwd=root)
+    assert r.returncode == 0 and "launch check ok" in r.stdout, f"stdout:\n{r.stdout}\nstderr:\n{r.stderr[-2000:]}"
