@@ -821,12 +821,16 @@ def main():
     check = runner.check()
 
     e2e_steps = max(3, min(args.steps, 20))
-    e2e_secs, h2d, d2h = runner.time_e2e(e2e_steps, 2)
+    # measured twice, around the copy-only run: with several ranks sharing the host's memory the first pass also pays
+    # for bringing the pinned buffers in; the lower of the two (each the max over ranks) is reported, both are printed
+    e2e_a, h2d, d2h = runner.time_e2e(e2e_steps, 2)
     copy_secs, _, _ = runner.time_e2e(e2e_steps, 2, copy_only=True)
+    e2e_b, _, _ = runner.time_e2e(e2e_steps, 2)
     if dist is not None:
-        t = torch.tensor([e2e_secs, copy_secs], device="cuda")
+        t = torch.tensor([e2e_a, copy_secs, e2e_b], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_secs, copy_secs = float(t[0].item()), float(t[1].item())
+        e2e_a, copy_secs, e2e_b = float(t[0].item()), float(t[1].item()), float(t[2].item())
+    e2e_secs = min(e2e_a, e2e_b)
     e2e_value = (fl / 1e12 if prefill else by / 1e9) / (e2e_secs / e2e_steps) * world
 
     extra = {}
@@ -889,6 +893,7 @@ def main():
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s" if prefill else "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_secs / e2e_steps * 1e3,
+                    "ms_per_step_runs": [e2e_a / e2e_steps * 1e3, e2e_b / e2e_steps * 1e3],
                     "copy_only_ms": copy_secs / e2e_steps * 1e3, "frac_of_copy_only": copy_secs / e2e_secs,
                     "pipeline": "host->device copy, kernel and device->host copy on three streams over two buffer sets; "
                                 "copy_only_ms = the same copies without the kernel (max over ranks)"},
