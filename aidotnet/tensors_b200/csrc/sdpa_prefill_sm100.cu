@@ -110,7 +110,8 @@ struct PrefillParams {
   int32_t* sched;          // [0] next-item counter, [1] finished-CTA counter; both zero between launches
   float* debug;            // trace builds only: tap / timeline buffer
   int32_t debug_mode;      // 3: the producer withholds the Q tiles, so that the bounded waits run out (test hook);
-                           // trace builds: 2 = per-item timeline (16 x u64 per item), 4 = per-step clock stamps of CTA 0
+                           // trace builds: 2 = per-item timeline (16 x u64 per item), 4 / 6 = per-step clock stamps of CTA 0,
+                           // 7 = SM clock and wall-clock time at the start and end of every CTA
   uint64_t wait_budget_ns; // longest single wait before the CTA gives up
 };
 
@@ -274,6 +275,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_ptr_smem;
+#if AIDN_PREFILL_TRACE
+  // mode 7: SM clock and wall-clock time at the start and end of every CTA (4 x u64 per CTA): the effective SM clock
+  if (pp.debug_mode == 7 && threadIdx.x == 0) {
+    unsigned long long* cl = reinterpret_cast<unsigned long long*>(pp.debug) + 4 * blockIdx.x;
+    cl[0] = (unsigned long long)clock64();
+    cl[1] = globaltimer_ns();
+  }
+#endif
 
   // Plain: scores stay raw and the scale is folded into the exponent (one FMA).  Masked: scores are scaled first
   // (softcap and bias act on scaled logits), so the exponent only needs log2(e).
@@ -937,6 +946,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       __threadfence();
     }
   }
+#if AIDN_PREFILL_TRACE
+  if (pp.debug_mode == 7 && threadIdx.x == 0) {
+    unsigned long long* cl = reinterpret_cast<unsigned long long*>(pp.debug) + 4 * blockIdx.x;
+    cl[2] = (unsigned long long)clock64();
+    cl[3] = globaltimer_ns();
+  }
+#endif
   if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
