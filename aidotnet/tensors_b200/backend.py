@@ -123,7 +123,7 @@ class CudaBackend:
 
     def _run(self, h: N.Handle, *, query, key, value, output, batch, seqQ, seqK, scale, lse=None, mask=None,
              mask_stride=(0, 0, 0, 0), kv_len=None, q_stride=None, k_stride=None, v_stride=None, o_stride=None,
-             block_table=None, block_table_stride=0, block_size=0, num_blocks=0):
+             block_table=None, block_table_stride=0, block_size=0, num_blocks=0, weights=None):
         ws, ws_bytes = self._workspace(h.workspace_bytes(batch, seqQ, seqK))
         h.launch(q=query.Handle, k=key.Handle, v=value.Handle, out=output.Handle, batch=batch, seq_q=seqQ, seq_kv=seqK,
                  stream=self.stream.cuda_stream, lse=lse.Handle if lse is not None else None,
@@ -131,9 +131,21 @@ class CudaBackend:
                  kv_len=kv_len.Handle if kv_len is not None else None, q_stride=q_stride, k_stride=k_stride,
                  v_stride=v_stride, o_stride=o_stride, scale=scale, workspace=ws, workspace_bytes=ws_bytes,
                  block_table=block_table.Handle if block_table is not None else None,
-                 block_table_stride=block_table_stride, block_size=block_size, num_blocks=num_blocks)
+                 block_table_stride=block_table_stride, block_size=block_size, num_blocks=num_blocks,
+                 weights=weights.Handle if weights is not None else None)
         self.launch_count += h.last_launch_count
         self.last_path = h.last_path
+
+    @staticmethod
+    def _check_weights(attentionWeights: Optional[GpuBuffer], weightsSize: int) -> None:
+        """The optional ``attentionWeights`` buffer receives the fp32 probabilities [batch, heads, seqQ, seqK]
+        (``CudaBackend.cs:8340-8349`` checks its size the same way)."""
+        if attentionWeights is None:
+            return
+        if attentionWeights.dtype != torch.float32:
+            raise ValueError("attentionWeights must be an fp32 buffer")
+        if attentionWeights.Size < weightsSize:
+            raise ValueError("Attention tensor buffers are smaller than the requested dimensions.")
 
     # -- IDirectGpuBackend attention methods ----------------------------------------------------------------
     def ScaledDotProductAttention(self, query: GpuBuffer, key: GpuBuffer, value: GpuBuffer, output: GpuBuffer,
@@ -154,8 +166,7 @@ class CudaBackend:
         weightsSize = batch * numHeads * seqQ * seqK
         if query.Size < querySize or key.Size < keyValueSize or value.Size < keyValueSize or output.Size < querySize:
             raise ValueError("Attention tensor buffers are smaller than the requested dimensions.")
-        if attentionWeights is not None:
-            raise NotImplementedError("the weight-returning call is not served by the sm_100a library")
+        self._check_weights(attentionWeights, weightsSize)
         mask_kind, mask_stride = N.MASK_NONE, (0, 0, 0, 0)
         if mask is not None:
             if mask.Size < seqQ * seqK:
@@ -169,7 +180,7 @@ class CudaBackend:
                          num_q_heads=numHeads, num_kv_heads=kvHeads, causal=bool(isCausal), causal_bottom_right=True,
                          mask_kind=mask_kind, softcap=float(softcap))
         self._run(h, query=query, key=key, value=value, output=output, batch=batch, seqQ=seqQ, seqK=seqK,
-                  scale=float(scale), mask=mask, mask_stride=mask_stride, kv_len=kvLengths)
+                  scale=float(scale), mask=mask, mask_stride=mask_stride, kv_len=kvLengths, weights=attentionWeights)
 
     def FlashAttention(self, query: GpuBuffer, key: GpuBuffer, value: GpuBuffer, output: GpuBuffer,
                        mask: Optional[GpuBuffer], batch: int, numHeads: int, seqLen: int, headDim: int, scale: float,
@@ -208,13 +219,12 @@ class CudaBackend:
         self._check_dims(batch, numQHeads, seqQ, seqK, headDim)
         if numKVHeads <= 0 or numQHeads % numKVHeads != 0:
             raise ValueError("numQHeads must be divisible by numKVHeads")
-        if attentionWeights is not None:
-            raise NotImplementedError("the weight-returning call is not served by the sm_100a library")
+        self._check_weights(attentionWeights, batch * numQHeads * seqQ * seqK)
         h = self._handle(qkv_dtype=_DTYPE[query.dtype], out_dtype=_DTYPE[output.dtype], head_dim=headDim,
                          num_q_heads=numQHeads, num_kv_heads=numKVHeads, causal=bool(isCausal),
                          causal_bottom_right=False, causal_offset=0)
         self._run(h, query=query, key=key, value=value, output=output, batch=batch, seqQ=seqQ, seqK=seqK,
-                  scale=float(scale))
+                  scale=float(scale), weights=attentionWeights)
 
     def FlashDecode(self, q: GpuBuffer, k: GpuBuffer, v: GpuBuffer, heads: int, kvHeads: int, headDim: int,
                     seqLen: int, scale: float, splits: int = 0) -> GpuBuffer:

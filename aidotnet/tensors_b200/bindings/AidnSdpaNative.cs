@@ -39,6 +39,7 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         public IntPtr workspace;
         public long workspace_bytes;
         public int gather_output;
+        public IntPtr weights;     // [B, Hq, Sq, Sk] fp32 probabilities on request, or zero
     }
 
     /// <summary>Paged K/V: the block pool of DevicePagedKVCache ([MaxBlocks, BlockSize, KvHeads, HeadDim]) and the

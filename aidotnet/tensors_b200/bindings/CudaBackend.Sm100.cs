@@ -96,9 +96,11 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
             IGpuBuffer output, IGpuBuffer? attentionWeights, IGpuBuffer? mask,
             int batch, int numHeads, int seqQ, int seqK, int headDim, float scale, bool isCausal, float softcap, int kvHeads)
         {
-            // The weights-returning call stays on the reference's kernel (it needs the [B,H,Sq,Sk] probabilities).
-            if (attentionWeights is not null || !Sm100Usable() || headDim > 256 || headDim % 8 != 0) return false;
+            if (!Sm100Usable() || headDim > 256 || headDim % 8 != 0) return false;
             long weightsSize = (long)batch * numHeads * seqQ * seqK;       // long: the int product overflows from S = 8192 on
+            // the [B,H,Sq,Sk] probabilities on request (CudaBackend.cs:8343-8356): args.weights selects the fp32 kernel
+            if (attentionWeights is not null && attentionWeights.Size < weightsSize)
+                throw new ArgumentException("The attention-weights buffer is too small.", nameof(attentionWeights));
             if (mask is not null && mask.Size < (long)seqQ * seqK)
                 throw new ArgumentException("The attention mask must contain at least seqQ * seqK elements.", nameof(mask));
             var k = new Sm100Key((int)AidnDtype.F32, (int)AidnDtype.F32, headDim, numHeads, kvHeads, isCausal, true, 0,
@@ -107,6 +109,7 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
             {
                 q = query.Handle, k = key.Handle, v = value.Handle, @out = output.Handle,
                 mask = mask?.Handle ?? IntPtr.Zero, batch = batch, seq_q = seqQ, seq_kv = seqK, scale = scale,
+                weights = attentionWeights?.Handle ?? IntPtr.Zero,
             };
             // the maskMode rule of CudaBackend.cs:8355: a full [B,H,Sq,Sk] mask, else one [Sq,Sk] plane for all
             if (mask is not null)
@@ -151,13 +154,16 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
             IGpuBuffer? attentionWeights, int batch, int numQHeads, int numKVHeads, int seqQ, int seqK, int headDim, float scale,
             bool isCausal)
         {
-            if (attentionWeights is not null || !Sm100Usable() || headDim > 256 || headDim % 8 != 0) return false;
+            if (!Sm100Usable() || headDim > 256 || headDim % 8 != 0) return false;
+            if (attentionWeights is not null && attentionWeights.Size < (long)batch * numQHeads * seqQ * seqK)
+                throw new ArgumentException("The attention-weights buffer is too small.", nameof(attentionWeights));
             var k = new Sm100Key((int)AidnDtype.F32, (int)AidnDtype.F32, headDim, numQHeads, numKVHeads, isCausal, false, 0,
                 (int)AidnMaskKind.None, false, 0f, 0);
             var args = new AidnSdpaArgs
             {
                 q = query.Handle, k = key.Handle, v = value.Handle, @out = output.Handle,
                 batch = batch, seq_q = seqQ, seq_kv = seqK, scale = scale,
+                weights = attentionWeights?.Handle ?? IntPtr.Zero,               // CudaBackend.cs:8731-8732
             };
             if (seqQ == 1) Sm100AttachWorkspace(Sm100Handle(k), ref args);
             Sm100Launch(Sm100Handle(k), ref args);

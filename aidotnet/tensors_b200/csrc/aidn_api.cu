@@ -317,6 +317,7 @@ int build_params(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* pg
   p.v = a->v;
   p.out = a->out;
   p.lse = d.emit_lse ? a->lse : nullptr;
+  p.weights = a->weights;
   p.mask = d.mask_kind != AIDN_MASK_NONE ? a->mask : nullptr;
   p.mask_kind = d.mask_kind;
   p.kv_len = a->kv_len;
@@ -392,6 +393,14 @@ int launch_common(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* p
 
   int path = d.path;
   if (path == AIDN_PATH_AUTO) path = decode_ok ? AIDN_PATH_DECODE : (prefill_ok ? AIDN_PATH_PREFILL_SM100 : AIDN_PATH_GENERIC);
+  if (p.weights) {
+    // the probabilities are written by the fp32 kernel only
+    if (d.path != AIDN_PATH_AUTO && d.path != AIDN_PATH_GENERIC)
+      return fail(AIDN_EUNSUPPORTED, "launch: attention weights are produced by the generic kernel (desc.path AUTO or GENERIC)");
+    if ((uintptr_t)p.weights % 4 != 0) return fail(AIDN_EINVAL, "launch: weights must be 4-byte aligned");
+    if (pg) return fail(AIDN_EUNSUPPORTED, "launch: attention weights over paged K/V are not defined");
+    path = AIDN_PATH_GENERIC;
+  }
   if (path == AIDN_PATH_DECODE && !decode_ok)
     return fail(AIDN_EUNSUPPORTED,
                 "launch: decode kernel needs seq_q == 1, head_dim 64/128 (256 for 16-bit) and 16-byte aligned Q/K/V rows");
@@ -496,6 +505,7 @@ int aidn_sdpa_backward(aidn_sdpa_t h, const aidn_sdpa_bwd_args* a, void* cu_stre
   const int rc = build_params(h, &a->fwd, a->paged, bp.p);
   if (rc != AIDN_OK) return rc;
   bp.p.lse = a->fwd.lse;   // read here, whatever desc.emit_lse says
+  bp.p.weights = nullptr;
   const int64_t need = aidn_sdpa_backward_workspace_bytes(h, a->fwd.batch, a->fwd.seq_q);
   if (!a->fwd.workspace || a->fwd.workspace_bytes < need)
     return fail(AIDN_EWORKSPACE, "backward: workspace of %lld bytes, need %lld", (long long)a->fwd.workspace_bytes, (long long)need);

@@ -24,6 +24,7 @@ struct SdpaParams {
   const void* v;
   void* out;
   float* lse;
+  float* weights;   // [B, Hq, Sq, Sk] fp32 probabilities, or null (generic kernel only)
   const void* mask;
   const int32_t* kv_len;
   int64_t mask_stride[4];

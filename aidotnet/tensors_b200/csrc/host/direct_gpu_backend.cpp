@@ -85,7 +85,8 @@ void CudaBackend::ScaledDotProductAttention(const GpuBuffer& query, const GpuBuf
   const int64_t weightsSize = (int64_t)batch * numHeads * seqQ * seqK;
   if (query.Size < querySize || key.Size < keyValueSize || value.Size < keyValueSize || output.Size < querySize)
     throw std::invalid_argument("Attention tensor buffers are smaller than the requested dimensions.");
-  if (attentionWeights) throw std::runtime_error("the weight-returning call is not served by the sm_100a library");
+  if (attentionWeights && (attentionWeights->Size < weightsSize || attentionWeights->Dtype != AIDN_F32))
+    throw std::invalid_argument("The attention-weights buffer is too small.");   // CudaBackend.cs:8343-8344
   if (mask && mask->Size < (int64_t)seqQ * seqK)
     throw std::invalid_argument("The attention mask must contain at least seqQ * seqK elements.");
   aidn_sdpa_desc d = base_desc(device_, query, output, headDim, numHeads, kvHeads);
@@ -97,6 +98,7 @@ void CudaBackend::ScaledDotProductAttention(const GpuBuffer& query, const GpuBuf
   std::memset(&a, 0, sizeof(a));
   a.q = query.Handle; a.k = key.Handle; a.v = value.Handle; a.out = output.Handle;
   a.batch = batch; a.seq_q = seqQ; a.seq_kv = seqK; a.scale = scale;
+  a.weights = attentionWeights ? static_cast<float*>(attentionWeights->Handle) : nullptr;
   if (mask) {
     a.mask = mask->Handle;
     const bool full = mask->Size >= weightsSize;   // maskMode rule, CudaBackend.cs:8355
@@ -168,7 +170,8 @@ void CudaBackend::GroupedQueryAttention(const GpuBuffer& query, const GpuBuffer&
     throw std::invalid_argument("Attention dimensions must be positive.");
   if (numKVHeads <= 0 || numQHeads % numKVHeads != 0)
     throw std::invalid_argument("numQHeads must be divisible by numKVHeads");
-  if (attentionWeights) throw std::runtime_error("the weight-returning call is not served by the sm_100a library");
+  if (attentionWeights && (attentionWeights->Size < (int64_t)batch * numQHeads * seqQ * seqK || attentionWeights->Dtype != AIDN_F32))
+    throw std::invalid_argument("The attention-weights buffer is too small.");
   aidn_sdpa_desc d = base_desc(device_, query, output, headDim, numQHeads, numKVHeads);
   d.causal = isCausal ? 1 : 0;
   d.causal_bottom_right = 0;                 // CudaAttentionKernels.cs:598 (top-left)
@@ -176,6 +179,7 @@ void CudaBackend::GroupedQueryAttention(const GpuBuffer& query, const GpuBuffer&
   std::memset(&a, 0, sizeof(a));
   a.q = query.Handle; a.k = key.Handle; a.v = value.Handle; a.out = output.Handle;
   a.batch = batch; a.seq_q = seqQ; a.seq_kv = seqK; a.scale = scale;
+  a.weights = attentionWeights ? static_cast<float*>(attentionWeights->Handle) : nullptr;   // CudaBackend.cs:8731-8732
   Run(Handle(d), a);
 }
 

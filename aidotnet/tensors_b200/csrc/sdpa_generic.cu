@@ -150,6 +150,52 @@ __global__ void __launch_bounds__(kWarps * 32) sdpa_generic_kernel(const SdpaPar
     __syncwarp();
   }
 
+  // Probabilities on request (the reference's `out attentionWeights`; its GQA kernel writes them the same way, from
+  // the final row statistics: CUDA/Kernels/CudaAttentionKernels.cs:628-642): a second pass over the keys recomputes
+  // every logit and stores exp(logit - max) / sum.  Masked positions and fully masked rows give exact zeros.
+  if (p.weights) {
+    for (int64_t j0 = 0; j0 < p.seq_kv; j0 += kBN) {
+      __syncthreads();
+      const bool live = j0 < kend;   // tiles past the last visible key only need their zeros written
+      if (live) {   // (the host refuses weights together with a block table, so keys are rows of K here)
+        for (int idx = tid; idx < kBN * DMAX; idx += kWarps * 32) {
+          const int j = idx / DMAX, d = idx - j * DMAX;
+          const int64_t key = j0 + j;
+          Ks[j * PITCH + d] = (key < kend && d < D) ? to_float<T>(kb[key * p.ks[2] + d]) : 0.f;
+        }
+        __syncthreads();
+      }
+      float s[kRowsPerWarp] = {0.f, 0.f, 0.f, 0.f};
+      if (live) {
+        const float4* krow = reinterpret_cast<const float4*>(Ks + lane * PITCH);
+#pragma unroll 4
+        for (int d4 = 0; d4 < DMAX / 4; ++d4) {
+          const float4 kv = krow[d4];
+#pragma unroll
+          for (int r = 0; r < kRowsPerWarp; ++r) {
+            const float4 qv = reinterpret_cast<const float4*>(Qs + (warp * kRowsPerWarp + r) * PITCH)[d4];
+            s[r] = fmaf(qv.x, kv.x, s[r]);
+            s[r] = fmaf(qv.y, kv.y, s[r]);
+            s[r] = fmaf(qv.z, kv.z, s[r]);
+            s[r] = fmaf(qv.w, kv.w, s[r]);
+          }
+        }
+      }
+      const int64_t key = j0 + lane;
+#pragma unroll
+      for (int r = 0; r < kRowsPerWarp; ++r) {
+        const int64_t row = row0 + warp * kRowsPerWarp + r;
+        if (row >= p.seq_q || key >= p.seq_kv) continue;
+        float w = 0.f;
+        if (live && l[r] > 0.f) {
+          const float val = finish_logit(p, s[r] * p.scale, b, h, row, key, kv_limit);
+          if (val != -INFINITY) w = softmax_exp<T>(val - m[r]) / l[r];
+        }
+        p.weights[(((int64_t)b * p.num_q_heads + h) * p.seq_q + row) * p.seq_kv + key] = w;
+      }
+    }
+  }
+
   report_bad_block(p, bad_block);
 #pragma unroll
   for (int r = 0; r < kRowsPerWarp; ++r) {

@@ -53,7 +53,7 @@ class SdpaArgs(ctypes.Structure):
         ("kv_len", ctypes.c_void_p), ("batch", ctypes.c_int64), ("seq_q", ctypes.c_int64), ("seq_kv", ctypes.c_int64),
         ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3), ("v_stride", ctypes.c_int64 * 3),
         ("o_stride", ctypes.c_int64 * 3), ("scale", ctypes.c_float), ("workspace", ctypes.c_void_p),
-        ("workspace_bytes", ctypes.c_int64), ("gather_output", ctypes.c_int32),
+        ("workspace_bytes", ctypes.c_int64), ("gather_output", ctypes.c_int32), ("weights", ctypes.c_void_p),
     ]
 
 
@@ -210,7 +210,7 @@ class Handle:
                kv_len: Optional[int] = None, q_stride=None, k_stride=None, v_stride=None, o_stride=None,
                scale: float = 0.0, workspace: Optional[int] = None, workspace_bytes: int = 0,
                gather_output: bool = False, block_table: Optional[int] = None, block_table_stride: int = 0,
-               block_size: int = 0, num_blocks: int = 0) -> None:
+               block_size: int = 0, num_blocks: int = 0, weights: Optional[int] = None) -> None:
         """Enqueues one forward.  With ``block_table`` (a device int32 array) ``k`` / ``v`` are the paged pools
         ``[num_blocks, block_size, Hkv, D]`` and the call goes through ``aidn_sdpa_launch_paged``."""
         a = SdpaArgs()
@@ -219,6 +219,7 @@ class Handle:
         a.batch, a.seq_q, a.seq_kv = batch, seq_q, seq_kv
         a.q_stride, a.k_stride, a.v_stride, a.o_stride = _arr3(q_stride), _arr3(k_stride), _arr3(v_stride), _arr3(o_stride)
         a.scale, a.workspace, a.workspace_bytes, a.gather_output = scale, workspace, workspace_bytes, int(gather_output)
+        a.weights = weights
         if block_table is not None:
             pg = PagedKv()
             pg.block_table, pg.block_table_stride = block_table, block_table_stride

@@ -133,6 +133,12 @@ typedef struct {
   int64_t workspace_bytes;
   int32_t gather_output;  /* 1: after the kernel, ncclAllGather the head shards of `out` in place on the same
                              stream (batch == 1 or per-batch-entry group call); needs desc.nccl_comm      */
+  float* weights;         /* NULL, or [B, Hq, Sq, Sk] dense fp32: receives the attention probabilities, the
+                             `out attentionWeights` of IEngine.ScaledDotProductAttention (IEngine.cs:4133-4140):
+                             0 at masked positions, an all-zero row where every key is masked.  The call then runs
+                             on the fp32 FFMA kernel whatever the input dtype, with a second pass over the keys -
+                             sized for the training-time shapes that ask for weights, not for long prefill; the
+                             buffer is B*Hq*Sq*Sk*4 bytes, counted in 64 bits.                              */
 } aidn_sdpa_args;
 
 /* Paged K/V (the vLLM-style pool of Engines/DirectGpu/DevicePagedKVCache.cs:10-18): args.k / args.v are the key and

@@ -52,7 +52,7 @@ def check_guards(flat, what):
 def run_gpu(q, k, v, *, dtype: str, out_dtype: str = "f32", causal=False, bottom_right=True, causal_offset=0,
             softcap=0.0, mask=None, mask_kind=N.MASK_NONE, kv_len=None, want_lse=False, path=N.PATH_AUTO,
             scale=0.0, decode_chunk=0, k_stride=None, v_stride=None, seq_kv=None, num_kv_heads=None,
-            head_begin=0, head_count=0, out=None, poll=True):
+            head_begin=0, head_count=0, out=None, poll=True, want_weights=False):
     """q [B,Hq,Sq,D], k/v [B,Hkv,Sk,D] CUDA tensors (dense unless strides are given).  Returns (out, lse, handle info)."""
     B, Hq, Sq, D = q.shape
     Hkv = num_kv_heads if num_kv_heads is not None else k.shape[1]
@@ -66,6 +66,11 @@ def run_gpu(q, k, v, *, dtype: str, out_dtype: str = "f32", causal=False, bottom
     if want_lse:
         flat, lse = guarded((B, Hq, Sq), torch.float32, q.device)
         guards.append((flat, "log-sum-exp"))
+    weights = None
+    if want_weights:   # pre-filled with NaN: every element has to be written, zeros included
+        flat, weights = guarded((B, Hq, Sq, Sk), torch.float32, q.device)
+        weights.fill_(float("nan"))
+        guards.append((flat, "attention weights"))
     mask_stride = (0, 0, 0, 0)
     mt = None
     if mask is not None:
@@ -87,12 +92,13 @@ def run_gpu(q, k, v, *, dtype: str, out_dtype: str = "f32", causal=False, bottom
              stream=stream, lse=lse.data_ptr() if lse is not None else None,
              mask=mt.data_ptr() if mt is not None else None, mask_stride=mask_stride,
              kv_len=klt.data_ptr() if klt is not None else None, k_stride=k_stride, v_stride=v_stride, scale=scale,
-             workspace=ws.data_ptr() if nbytes > 0 else None, workspace_bytes=nbytes)
+             workspace=ws.data_ptr() if nbytes > 0 else None, workspace_bytes=nbytes,
+             weights=weights.data_ptr() if weights is not None else None)
     if poll:
         h.poll(stream)
         for flat, what in guards:
             check_guards(flat, what)
-    info = dict(path=h.last_path, launches=h.last_launch_count)
+    info = dict(path=h.last_path, launches=h.last_launch_count, weights=weights)
     h.close()
     return out, lse, info
 

@@ -63,12 +63,14 @@ struct RefOpts {
   const std::vector<float>* keep = nullptr;   // [B,H,Sq,Sk] float mask, 0 = masked
   const std::vector<float>* bias = nullptr;   // [B or 1,H,Sq,Sk]
   bool bias_has_batch = true;
+  std::vector<double>* weights = nullptr;     // receives the [B,H,Sq,Sk] probabilities when set
 };
 static void reference(const std::vector<float>& q, const std::vector<float>& k, const std::vector<float>& v, int B,
                       int Hq, int Hkv, int Sq, int Sk, int D, const RefOpts& o, std::vector<double>& out,
                       std::vector<double>& lse, std::function<size_t(int, int, int, int)> kv_index = nullptr) {
   out.assign((size_t)B * Hq * Sq * D, 0.0);
   lse.assign((size_t)B * Hq * Sq, 0.0);
+  if (o.weights) o.weights->assign((size_t)B * Hq * Sq * Sk, 0.0);
   const int g = Hq / Hkv;
   if (!kv_index) kv_index = [=](int b, int kh, int j, int d) { return (((size_t)b * Hkv + kh) * Sk + j) * D + d; };
   std::vector<double> s(Sk);
@@ -95,6 +97,8 @@ static void reference(const std::vector<float>& q, const std::vector<float>& k, 
         }
         for (int j = 0; j < Sk; ++j) { s[j] = std::exp(s[j] - mx); sum += s[j]; }
         lse[((size_t)b * Hq + h) * Sq + i] = mx + std::log(sum);
+        if (o.weights)
+          for (int j = 0; j < Sk; ++j) (*o.weights)[(((size_t)b * Hq + h) * Sq + i) * Sk + j] = s[j] / sum;
         for (int d = 0; d < D; ++d) {
           double acc = 0;
           for (int j = 0; j < Sk; ++j) acc += s[j] / sum * v[kv_index(b, h / g, j, d)];
@@ -147,6 +151,27 @@ int main() {
     o.keep = &mask;
     reference(q, k, v, B, H, H, Sq, Sk, D, o, ref, lse);
     EXPECT(max_abs_diff(dout.download(), ref) <= 2e-5, "masked output mismatch %g", max_abs_diff(dout.download(), ref));
+
+    // :946-955, :1046-1060 the probabilities on request, with and without the mask, 2e-5
+    std::printf("attention weights on request\n");
+    std::vector<double> wref;
+    o.weights = &wref;
+    DeviceArray dw((int64_t)B * H * Sq * Sk);
+    backend.ScaledDotProductAttention(dq.buf, dk.buf, dv.buf, dout.buf, &dw.buf, &dm.buf, B, H, Sq, Sk, D, 0.75f, false);
+    backend.Synchronize();
+    reference(q, k, v, B, H, H, Sq, Sk, D, o, ref, lse);
+    EXPECT(max_abs_diff(dw.download(), wref) <= 2e-5, "masked weights mismatch %g", max_abs_diff(dw.download(), wref));
+    EXPECT(max_abs_diff(dout.download(), ref) <= 2e-5, "output beside weights mismatch %g", max_abs_diff(dout.download(), ref));
+    o.keep = nullptr;
+    backend.ScaledDotProductAttention(dq.buf, dk.buf, dv.buf, dout.buf, &dw.buf, nullptr, B, H, Sq, Sk, D, 0.75f, false);
+    backend.Synchronize();
+    reference(q, k, v, B, H, H, Sq, Sk, D, o, ref, lse);
+    EXPECT(max_abs_diff(dw.download(), wref) <= 2e-5, "weights mismatch %g", max_abs_diff(dw.download(), wref));
+    DeviceArray tiny((int64_t)4);
+    bool threw = false;
+    try { backend.ScaledDotProductAttention(dq.buf, dk.buf, dv.buf, dout.buf, &tiny.buf, nullptr, B, H, Sq, Sk, D, 0.75f, false); }
+    catch (const std::invalid_argument&) { threw = true; }
+    EXPECT(threw, "a short weights buffer was accepted%s", "");
   }
   {  // :962-1003 ScaledDotProductAttention_LogitSoftcap_MatchesCpu
     std::printf("logit softcap\n");
