@@ -235,7 +235,7 @@ struct alignas(64) PrefillMapCache {
     int32_t batch, kv_batch, num_q_heads, num_kv_heads, head_dim, kv_box, out_f32, dtype;
   } key;
   bool valid;
-  bool attr_set[8];             // by instantiation: (fp16 ? 4 : 0) + (head_dim 128 ? 2 : 0) + (masked ? 1 : 0)
+  bool attr_set[16];            // by instantiation: (epilogue warpgroup ? 8 : 0) + (fp16 ? 4 : 0) + (head_dim 128 ? 2 : 0) + (masked ? 1 : 0)
 };
 bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why);
 // cache may be null (maps are then encoded on every call).

@@ -9,8 +9,11 @@
 //
 //   warps 0-3   softmax of tile 0: thread t owns row t of the tile (TMEM lane == row), reads S from TMEM,
 //   warps 4-7   softmax of tile 1  keeps the running max / sum, rescales O lazily, writes P (16-bit) back
-//                                  into the S columns; at the end normalises O, stages it 128 bytes per row in
-//                                  swizzled shared memory (one 4 KiB buffer per warp) and issues TMA stores
+//                                  into the S columns; at the end either runs the epilogue of its tile itself or
+//                                  hands 1 / sum to the epilogue warps and goes on to the next item (struct Roles)
+//   warps 12-15 epilogue (four-warpgroup layout only): read O_i out of TMEM (releasing it to the next item's first
+//               P.V product), normalise, stage 128 bytes per row in swizzled shared memory (4 KiB boxes) and issue
+//               TMA stores
 //   warp  8     TMA producer + scheduler: Q tiles, then K and V sub-tiles of 64 keys through a ring of 8 slots, in the
 //               order the issuers need them (K(0), K(1), V(0), K(2), V(1), ...): three sub-tiles of look-ahead, which
 //               a TMA load under full load needs (2700 cycles from a slot's release to its data, measured)
@@ -28,8 +31,9 @@
 // MUFU pipes 55-60 % busy; here the softmax warps go from one sub-tile straight to the next and the loop runs at
 // the rate of the slower of the two pipes.  N = 64 score UMMAs read more shared memory per flop than N = 128 ones
 // (the Q operand is re-read for every 64 keys); the trade is measured in profiles/.
-// Because the softmax warps also run the epilogue, the loads and first score UMMAs of the next work item overlap
-// the epilogue of the current one.
+// With the softmax warps running the epilogue, an item of two equally long tiles costs its loop plus 4.5 us of
+// hand-over (o_full wait 0.6, epilogue 2.6, restart 1.2 us; per-item timeline), during which the tensor pipe idles;
+// a fourth warpgroup takes the epilogue over for such items.
 //
 // Supersedes flash_attention_v2 / grouped_query_attention / scaled_dot_product_attention of the reference
 // (src/AiDotNet.Tensors/Engines/DirectGpu/CUDA/Kernels/CudaAttentionKernels.cs:28-234, 527-646) and its
@@ -61,24 +65,38 @@ constexpr int kBS = 64;            // keys per score sub-tile: one softmax step,
 constexpr int kSoftmaxWarps = 8;   // 2 tiles x 4 warps
 constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
-constexpr int kThreads = 384;          // 3 warpgroups: softmax 0, softmax 1, {producer, 2 UMMA issuers, 1 idle}
-// Per-thread registers after setmaxnreg.  8*32*184 + 4*32*136 == 384*168: the two figures must add up to what the CTA
-// was launched with - setmaxnreg.inc waits, without any bound, for registers that another warpgroup of the same CTA has
-// given up, and a sum above the launch allocation never becomes available.
-#ifndef AIDN_SOFTMAX_REGS
-#define AIDN_SOFTMAX_REGS 184
-#endif
-#ifndef AIDN_OTHER_REGS
-#define AIDN_OTHER_REGS 136
-#endif
-constexpr int kSoftmaxRegs = AIDN_SOFTMAX_REGS;
-constexpr int kOtherRegs = AIDN_OTHER_REGS;
-constexpr int kStageBytesPerWarp = 4096;   // epilogue staging: 32 rows x 128 B (128-byte swizzle), one per softmax warp
+constexpr int kEpilogueWarp = 12;      // warps 12-15: warp 12 + j reads TMEM lanes 32 j .. 32 j + 31, like softmax warp j
+constexpr int kEpilogueWarps = 4;
+constexpr int kStageBytes = 32768;     // epilogue staging: 32-row x 128-byte boxes (128-byte swizzle) of 4 KiB
 constexpr int kTmemCols = 512;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units: P stays below 2^8 between rescales
-constexpr int kSchedConsumers = kSoftmaxWarps + 2;   // softmax warps and the two UMMA issuers
-static_assert(kSoftmaxWarps * 32 * kSoftmaxRegs + 4 * 32 * kOtherRegs <= kThreads * 168,
-              "setmaxnreg budget exceeds the registers the CTA is launched with");
+
+// Two role layouts, chosen by the host per launch.
+//   EPI = false: 3 warpgroups (384 threads); the softmax warps run the epilogue of their own tile (one 4 KiB staging
+//                buffer per warp).  Best when the two tiles of an item differ in length (row pairs under a causal mask:
+//                the second tile runs two sub-tiles longer): the warpgroup that finishes first stores its tile under
+//                the other's last sub-tiles and then starts the next item - where it gets the longer tile - ahead of it.
+//   EPI = true:  4 warpgroups (512 threads); warps 12-15 run the epilogue (two 4 KiB staging buffers per warp) and the
+//                softmax warps go straight on to the next item.  Best when both tiles end together (head pairs of a GQA
+//                group, no causal mask): measured +4 % on B2 Hq32/Hkv8 S8192 and on B1 Hq8/Hkv1 S32768, -1 % on the
+//                row pairs of B4 H32 S2048, which therefore keep the first layout.
+// Per-thread registers after setmaxnreg: 8*32*184 + 4*32*136 == 384*168 and 8*32*176 + 8*32*80 == 512*128 - the figures
+// must add up to what the CTA was launched with: setmaxnreg.inc waits, without any bound, for registers that another
+// warpgroup of the same CTA has given up, and a sum above the launch allocation never becomes available.
+template <bool EPI>
+struct Roles {
+  static constexpr int kThreads = EPI ? 512 : 384;
+  static constexpr int kSoftmaxRegs = EPI ? 176 : 184;
+  static constexpr int kOtherRegs = EPI ? 80 : 136;
+  static constexpr int kOtherWarps = EPI ? 8 : 4;
+  static constexpr int kStoreWarps = EPI ? kEpilogueWarps : kSoftmaxWarps;   // warps that stage and store O
+  static constexpr int kStageBufs = EPI ? 2 : 1;                             // 4 KiB staging buffers per storing warp
+  // consumers of the item mailbox: softmax warps, the two UMMA issuers, epilogue warps
+  static constexpr int kSchedConsumers = kSoftmaxWarps + 2 + (EPI ? kEpilogueWarps : 0);
+  static_assert(kSoftmaxWarps * 32 * kSoftmaxRegs + kOtherWarps * 32 * kOtherRegs <= kThreads * (EPI ? 128 : 168),
+                "setmaxnreg budget exceeds the registers the CTA is launched with");
+  static_assert(kStoreWarps * kStageBufs * 4096 == kStageBytes, "staging memory");
+};
 constexpr int kItemWords = 14;   // mailbox entry: item, b, kvh, n_max, (h, t, n, valid) of both tiles, v_tail
 
 template <int HD>
@@ -90,12 +108,15 @@ struct Cfg {
   static constexpr int kHalfBytes = kBM * 128;            // 16 KiB: one column block of a Q tile
   static constexpr int kKvHalfBytes = kBS * 128;          // 8 KiB: one column block of a K / V sub-tile
   static constexpr int kStageOff = 2 * kTileBytes + kStages * kSubBytes;
-  static constexpr int kBarOff = kStageOff + kSoftmaxWarps * kStageBytesPerWarp;
+  static constexpr int kBarOff = kStageOff + kStageBytes;
   // q_full[2] q_empty[2] kv_full[S] kv_empty[S] s_full[2][2] p_full[2][2] o_full[2] pv_done[2] sched_full[2] sched_empty[2]
-  static constexpr int kNumBars = 20 + 2 * kStages;
+  // stats_full[2] stats_empty[2] o_empty[2]
+  static constexpr int kNumBars = 26 + 2 * kStages;
   static constexpr int kMiscOff = kBarOff + kNumBars * 8;  // issue lock, tmem ptr, abort flag, then the 2-slot item mailbox
   static constexpr int kMailOff = kMiscOff + 16;
-  static constexpr int kSmemBytes = kMailOff + 2 * kItemWords * 4 + 1024 /*align slack*/;
+  static constexpr int kStatsOff = kMailOff + 2 * kItemWords * 4;   // 1 / row sum of both tiles: [2][128] floats
+  static constexpr int kSmemBytes = kStatsOff + 2 * kBM * 4 + 1024 /*align slack*/;
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory of one CTA");
   static constexpr int kOCol = 256;
 };
 
@@ -203,14 +224,80 @@ __device__ __forceinline__ Item decode_item(const PrefillParams& pp, int item) {
   return it;
 }
 
+// Epilogue warps: O_i / l of one tile, 32 rows per warp: TMEM -> registers -> swizzled staging (128 bytes per row) -> TMA
+// stores.  `n_stores` counts this warp's stores; store k stages through buffer k & 1.  `bar_o_empty` gets one arrival
+// per warp as soon as the tile's last tcgen05.ld has completed.
+template <int HD, bool kBf16>
+__device__ __forceinline__ void store_o_tile(const SdpaParams& p, const CUtensorMap* tm_o, uint32_t t_o, bool have_o,
+                                             float inv, uint32_t my_stage, uint32_t& n_stores, int lane, int row0,
+                                             int h, int b, uint32_t bar_o_empty) {
+  // 128-byte staging rows under the 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+  const uint32_t my_swz = (uint32_t)(lane & 7);
+  const bool box_valid = row0 < p.seq_q;
+#pragma unroll
+  for (int c0 = 0; c0 < HD; c0 += 32) {
+    uint32_t orr[32];
+    if (have_o) {
+      tmem_ld32(t_o + c0, orr);
+      tc_wait_ld();
+      if (c0 + 32 == HD) {
+        // O_i is in registers: the next item's first P.V product may overwrite it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_o_empty);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 32; ++c) orr[c] = 0u;
+    }
+    // fp32 output: 32 columns fill the 128-byte row (one store per 32 columns); 16-bit output: 64 columns
+    const int half = p.out_f32 ? 0 : ((c0 >> 5) & 1);
+    const uint32_t buf = my_stage + (n_stores & 1u) * 4096u;
+    const uint32_t my_row = buf + (uint32_t)(lane * 128);
+    if (half == 0 && n_stores >= 2u) {
+      // the store before the previous one used this buffer and must have finished reading it
+      if (lane == 0) bulk_wait_read1();
+      __syncwarp();
+    }
+    if (p.out_f32) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        st_shared_v4(my_row + (((uint32_t)c ^ my_swz) << 4),
+                     __float_as_uint(__uint_as_float(orr[4 * c]) * inv),
+                     __float_as_uint(__uint_as_float(orr[4 * c + 1]) * inv),
+                     __float_as_uint(__uint_as_float(orr[4 * c + 2]) * inv),
+                     __float_as_uint(__uint_as_float(orr[4 * c + 3]) * inv));
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        st_shared_v4(my_row + (((uint32_t)(half * 4 + c) ^ my_swz) << 4),
+                     pack2<kBf16>(__uint_as_float(orr[8 * c]) * inv, __uint_as_float(orr[8 * c + 1]) * inv),
+                     pack2<kBf16>(__uint_as_float(orr[8 * c + 2]) * inv, __uint_as_float(orr[8 * c + 3]) * inv),
+                     pack2<kBf16>(__uint_as_float(orr[8 * c + 4]) * inv, __uint_as_float(orr[8 * c + 5]) * inv),
+                     pack2<kBf16>(__uint_as_float(orr[8 * c + 6]) * inv, __uint_as_float(orr[8 * c + 7]) * inv));
+    }
+    if (p.out_f32 || half == 1) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      // the store is counted (and its group committed) whether or not the box lies inside the tensor
+      if (lane == 0) {
+        if (box_valid) tma_store_4d(tm_o, buf, p.out_f32 ? c0 : c0 - 32, row0, h, b);
+        bulk_commit();
+      }
+      ++n_stores;
+    }
+  }
+}
+
 // MASKED: the softmax warps also apply softcap, an additive bias or a keep-mask read from global memory (one row
 // per thread); the plain variant carries none of that code.
-template <typename T, int HD, bool MASKED>
-__global__ void __launch_bounds__(kThreads, 1)
+template <typename T, int HD, bool MASKED, bool EPI>
+__global__ void __launch_bounds__(Roles<EPI>::kThreads, 1)
     sdpa_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
                               const PrefillParams pp) {
   using C = Cfg<HD>;
+  using R = Roles<EPI>;
   constexpr bool kBf16 = !std::is_same_v<T, __half>;
   const SdpaParams& p = pp.p;
 
@@ -219,7 +306,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t q_smem = smem_base;                           // 2 tiles
   const uint32_t kv_smem = smem_base + 2 * C::kTileBytes;      // kStages sub-tiles
-  const uint32_t stage_smem = smem_base + C::kStageOff;        // 8 warps x 4 KiB
+  const uint32_t stage_smem = smem_base + C::kStageOff;        // 4 KiB boxes: 2 per epilogue warp, or 1 per softmax warp
   const uint32_t bars = smem_base + C::kBarOff;
   const uint32_t bar_q_full = bars;                            // [2]
   const uint32_t bar_q_empty = bars + 16;                      // [2]
@@ -231,6 +318,10 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t bar_pv_done = bar_o_full + 16;                // [2] one phase per P.V product of the tile
   const uint32_t bar_sched_full = bar_pv_done + 16;            // [2]
   const uint32_t bar_sched_empty = bar_sched_full + 16;        // [2]
+  const uint32_t bar_stats_full = bar_sched_empty + 16;        // [2] the softmax warps of a tile have written its 1 / row sums
+  const uint32_t bar_stats_empty = bar_stats_full + 16;        // [2] the epilogue warps have read them
+  const uint32_t bar_o_empty = bar_stats_empty + 16;           // [2] the epilogue warps have read O_i out of TMEM
+  volatile float* stats = reinterpret_cast<volatile float*>(smem_gen + C::kStatsOff);   // [2][kBM]
   volatile int* mailbox = reinterpret_cast<volatile int*>(smem_gen + C::kMailOff);  // [2][kItemWords]
   int* issue_turn = reinterpret_cast<int*>(smem_gen + C::kMiscOff);   // turns of the two UMMA issuers completed so far
   uint32_t* tmem_ptr_smem = reinterpret_cast<uint32_t*>(smem_gen + C::kMiscOff + 8);
@@ -249,7 +340,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(bar_o_full + 8 * i, 1);
       mbar_init(bar_pv_done + 8 * i, 1);
       mbar_init(bar_sched_full + 8 * i, 1);
-      mbar_init(bar_sched_empty + 8 * i, kSchedConsumers);
+      mbar_init(bar_sched_empty + 8 * i, R::kSchedConsumers);
+      mbar_init(bar_stats_full + 8 * i, 4);    // one arrival per softmax warp of the tile
+      mbar_init(bar_stats_empty + 8 * i, kEpilogueWarps);
+      mbar_init(bar_o_empty + 8 * i, kEpilogueWarps);
     }
     for (int i = 0; i < 4; ++i) {
       mbar_init(bar_s_full + 8 * i, 1);
@@ -291,21 +385,22 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (warp < kSoftmaxWarps) {
     // =================================== softmax / epilogue ===================================
-    setmaxnreg_inc<kSoftmaxRegs>();
+    setmaxnreg_inc<R::kSoftmaxRegs>();
     const int i = warp >> 2;
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
     const uint32_t t_s = tmem_base + lane_bits + (uint32_t)(i * 2 * kBS);
     const uint32_t t_o = tmem_base + lane_bits + (uint32_t)(C::kOCol + i * HD);
-    const uint32_t my_stage = stage_smem + (uint32_t)(warp * kStageBytesPerWarp);
-    // 128-byte staging rows under the 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+    uint32_t s_par = 0;                // bit b: parity of the next phase of s_full[tile][b]
+    uint32_t pv_par = 0;               // parity of the next phase of pv_done (one per item with two or more sub-tiles)
+    uint32_t handed = 0;               // EPI: row statistics handed to the epilogue warps so far
+    uint32_t o_cnt = 0;                // !EPI: completed phases of o_full
+    bool stores_in_flight = false;     // !EPI: a TMA store of this warp may still be reading the staging buffer
+    // !EPI: one 4 KiB staging buffer per softmax warp; 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+    const uint32_t my_stage = stage_smem + (uint32_t)(warp * 4096);
     const uint32_t my_row = my_stage + (uint32_t)(lane * 128);
     const uint32_t my_swz = (uint32_t)(lane & 7);
-    uint32_t s_par = 0;                // bit b: parity of the next phase of s_full[tile][b]
-    uint32_t o_cnt = 0;                // completed phases of o_full
-    uint32_t pv_par = 0;               // parity of the next phase of pv_done (one per item with two or more sub-tiles)
-    bool stores_in_flight = false;     // a TMA store of this warp may still be reading the staging buffer
     bool alive = true;
 
     for (int seq = 0; alive; ++seq) {
@@ -533,77 +628,94 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (ti.n >= 2) pv_par ^= 1u;   // the issuer signalled pv_done once for this item
       if (tracer) trace[3 + 8 * i] = globaltimer_ns();
 
-      // ---- epilogue: O / l -> swizzled staging (128 B per row) -> TMA stores ------------------------------
-      {
-        const bool have_o = ti.n > 0;
-        if (have_o) {
-          // the last two P.V products were issued by different warps: pv_done covers the second-to-last one
-          bool ok = ti.n < 2 || mbar_wait(bar_pv_done + 8 * i, pv_par ^ 1u, abort_flag, wait_ns);
-          ok = ok && mbar_wait(bar_o_full + 8 * i, o_cnt & 1u, abort_flag, wait_ns);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) { alive = false; break; }
-          ++o_cnt;
-          tc_fence_after();
-        }
-        if (tracer) trace[4 + 8 * i] = globaltimer_ns();
-        const bool row_valid = qrow < p.seq_q;
+      if constexpr (EPI) {
+        // ---- hand the row to the epilogue warps: 1 / l through shared memory, the log-sum-exp straight to memory ----
+        bool ok = mbar_wait(bar_stats_empty + 8 * i, (handed & 1u) ^ 1u, abort_flag, wait_ns);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { alive = false; break; }
+        ++handed;
         const float inv = (l > 0.f && m != -INFINITY) ? 1.f / l : 0.f;
-        const int row0 = ti.t * kBM + quarter * 32;   // first row of this warp's 32-row box
-        const bool box_valid = row0 < p.seq_q;
-#pragma unroll
-        for (int c0 = 0; c0 < HD; c0 += 32) {
-          uint32_t orr[32];
-          if (have_o) {
-            tmem_ld32(t_o + c0, orr);
-            tc_wait_ld();
-          } else {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) orr[c] = 0u;
-          }
-          // fp32 output: 32 columns fill the 128-byte row (one store per 32 columns); 16-bit output: 64 columns
-          const int half = p.out_f32 ? 0 : ((c0 >> 5) & 1);
-          if (half == 0 && stores_in_flight) {
-            if (lane == 0) bulk_wait_read0();
-            __syncwarp();
-          }
-          if (p.out_f32) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              st_shared_v4(my_row + (((uint32_t)c ^ my_swz) << 4),
-                           __float_as_uint(__uint_as_float(orr[4 * c]) * inv),
-                           __float_as_uint(__uint_as_float(orr[4 * c + 1]) * inv),
-                           __float_as_uint(__uint_as_float(orr[4 * c + 2]) * inv),
-                           __float_as_uint(__uint_as_float(orr[4 * c + 3]) * inv));
-          } else {
-#pragma unroll
-            for (int c = 0; c < 4; ++c)
-              st_shared_v4(my_row + (((uint32_t)(half * 4 + c) ^ my_swz) << 4),
-                           pack2<kBf16>(__uint_as_float(orr[8 * c]) * inv, __uint_as_float(orr[8 * c + 1]) * inv),
-                           pack2<kBf16>(__uint_as_float(orr[8 * c + 2]) * inv, __uint_as_float(orr[8 * c + 3]) * inv),
-                           pack2<kBf16>(__uint_as_float(orr[8 * c + 4]) * inv, __uint_as_float(orr[8 * c + 5]) * inv),
-                           pack2<kBf16>(__uint_as_float(orr[8 * c + 6]) * inv, __uint_as_float(orr[8 * c + 7]) * inv));
-          }
-          if (p.out_f32 || half == 1) {
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0 && box_valid) {
-              tma_store_4d(&tm_o, my_stage, p.out_f32 ? c0 : c0 - 32, row0, ti.h, b);
-              bulk_commit();
-            }
-            stores_in_flight = true;
-          }
-        }
-        if (row_valid && p.lse)
+        stats[i * kBM + row_in_tile] = inv;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_stats_full + 8 * i);
+        if (qrow < p.seq_q && p.lse)
           p.lse[((int64_t)b * p.num_q_heads + ti.h) * p.seq_q + qrow] =
               (inv > 0.f) ? m * lse_scale + logf(l) : -INFINITY;
-        if (tracer) trace[5 + 8 * i] = globaltimer_ns();
+      } else {
+        // ---- epilogue: O / l -> swizzled staging (128 B per row) -> TMA stores ------------------------------
+        {
+          const bool have_o = ti.n > 0;
+          if (have_o) {
+            // the last two P.V products were issued by different warps: pv_done covers the second-to-last one
+            bool ok = ti.n < 2 || mbar_wait(bar_pv_done + 8 * i, pv_par ^ 1u, abort_flag, wait_ns);
+            ok = ok && mbar_wait(bar_o_full + 8 * i, o_cnt & 1u, abort_flag, wait_ns);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { alive = false; break; }
+            ++o_cnt;
+            tc_fence_after();
+          }
+          if (tracer) trace[4 + 8 * i] = globaltimer_ns();
+          const bool row_valid = qrow < p.seq_q;
+          const float inv = (l > 0.f && m != -INFINITY) ? 1.f / l : 0.f;
+          const int row0 = ti.t * kBM + quarter * 32;   // first row of this warp's 32-row box
+          const bool box_valid = row0 < p.seq_q;
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 32) {
+            uint32_t orr[32];
+            if (have_o) {
+              tmem_ld32(t_o + c0, orr);
+              tc_wait_ld();
+            } else {
+#pragma unroll
+              for (int c = 0; c < 32; ++c) orr[c] = 0u;
+            }
+            // fp32 output: 32 columns fill the 128-byte row (one store per 32 columns); 16-bit output: 64 columns
+            const int half = p.out_f32 ? 0 : ((c0 >> 5) & 1);
+            if (half == 0 && stores_in_flight) {
+              if (lane == 0) bulk_wait_read0();
+              __syncwarp();
+            }
+            if (p.out_f32) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                st_shared_v4(my_row + (((uint32_t)c ^ my_swz) << 4),
+                             __float_as_uint(__uint_as_float(orr[4 * c]) * inv),
+                             __float_as_uint(__uint_as_float(orr[4 * c + 1]) * inv),
+                             __float_as_uint(__uint_as_float(orr[4 * c + 2]) * inv),
+                             __float_as_uint(__uint_as_float(orr[4 * c + 3]) * inv));
+            } else {
+#pragma unroll
+              for (int c = 0; c < 4; ++c)
+                st_shared_v4(my_row + (((uint32_t)(half * 4 + c) ^ my_swz) << 4),
+                             pack2<kBf16>(__uint_as_float(orr[8 * c]) * inv, __uint_as_float(orr[8 * c + 1]) * inv),
+                             pack2<kBf16>(__uint_as_float(orr[8 * c + 2]) * inv, __uint_as_float(orr[8 * c + 3]) * inv),
+                             pack2<kBf16>(__uint_as_float(orr[8 * c + 4]) * inv, __uint_as_float(orr[8 * c + 5]) * inv),
+                             pack2<kBf16>(__uint_as_float(orr[8 * c + 6]) * inv, __uint_as_float(orr[8 * c + 7]) * inv));
+            }
+            if (p.out_f32 || half == 1) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0 && box_valid) {
+                tma_store_4d(&tm_o, my_stage, p.out_f32 ? c0 : c0 - 32, row0, ti.h, b);
+                bulk_commit();
+              }
+              stores_in_flight = true;
+            }
+          }
+          if (row_valid && p.lse)
+            p.lse[((int64_t)b * p.num_q_heads + ti.h) * p.seq_q + qrow] =
+                (inv > 0.f) ? m * lse_scale + logf(l) : -INFINITY;
+          if (tracer) trace[5 + 8 * i] = globaltimer_ns();
+        }
       }
     }
-    // staging memory must outlive the bulk stores that read it
-    if (lane == 0) bulk_wait_all();
-    __syncwarp();
+    if constexpr (!EPI) {
+      // staging memory must outlive the bulk stores that read it
+      if (lane == 0) bulk_wait_all();
+      __syncwarp();
+    }
   } else {
-    setmaxnreg_dec<kOtherRegs>();
+    setmaxnreg_dec<R::kOtherRegs>();
   }
 
   if (warp == kProducerWarp) {
@@ -752,6 +864,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint32_t t_cons = 0;            // K/V sub-tiles of earlier items (ring position)
       uint32_t q_par = 0;             // bit i: parity of the next phase of q_full[i]
       uint32_t p_par = 0;             // bit i: parity of the next phase of p_full[i][b]
+      uint32_t oe_par = 3;            // bit i: parity to test on o_empty[i] before the tile's next first P.V product
       int g = 0;                      // turns of earlier items
       for (int seq = 0; alive; ++seq) {
         int item;
@@ -888,6 +1001,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (u >= n_i) continue;
             if (!mbar_wait(bar_p_full + 8 * (2 * i + b), (p_par >> i) & 1u, abort_flag, wait_ns)) { alive = false; break; }
             p_par ^= 1u << i;
+            if (EPI && u == 0) {
+              // this product overwrites O_i: the epilogue warps must have read the previous item's out of TMEM
+              if (!mbar_wait(bar_o_empty + 8 * i, (oe_par >> i) & 1u, abort_flag, wait_ns)) { alive = false; break; }
+              oe_par ^= 1u << i;
+            }
             tc_fence_after();
             if (!turn_mine) {
               DET_STAMP(u, 2);
@@ -919,6 +1037,76 @@ __global__ void __launch_bounds__(kThreads, 1)
           DET_STAMP(u, 4);
         }
       }
+    }
+  }
+
+  if constexpr (EPI) {
+    if (warp >= kEpilogueWarp) {
+      // ============================================ epilogue ============================================
+      // O_i / l -> staging -> TMA stores, off the softmax warps' path: the first P.V product of the next item (which
+      // overwrites O_i) waits for o_empty[i], i.e. only for the tcgen05.ld's of the tile, not for the stores.
+      const int quarter = warp - kEpilogueWarp;
+      const int row_in_tile = quarter * 32 + lane;
+      const uint32_t lane_bits = (uint32_t)(quarter * 32) << 16;
+      const uint32_t my_stage = stage_smem + (uint32_t)(quarter * 2 * 4096);
+      uint32_t st_par = 0;               // bit i: parity of the next phase of stats_full[i]
+      uint32_t of_par = 0;               // bit i: parity of the next phase of o_full[i]
+      uint32_t pv_par = 0;               // bit i: parity of the next phase of pv_done[i]
+      uint32_t n_stores = 0;             // TMA stores issued by this warp
+      bool alive = true;
+      for (int seq = 0; alive; ++seq) {
+        int item;
+        {
+          const int slot = seq & 1;
+          bool ok = mbar_wait(bar_sched_full + 8 * slot, (uint32_t)((seq >> 1) & 1), abort_flag, wait_ns);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          item = mailbox[slot * kItemWords];
+        }
+        if (item >= pp.total_items) break;
+        const Item it = read_item(mailbox + (seq & 1) * kItemWords);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_sched_empty + 8 * (seq & 1));
+#if AIDN_PREFILL_TRACE
+        unsigned long long* trace = pp.debug_mode == 2
+            ? reinterpret_cast<unsigned long long*>(pp.debug) + (size_t)item * 16 : nullptr;
+        const bool tracer = trace && row_in_tile == 0;
+#else
+        constexpr bool tracer = false;
+        unsigned long long* const trace = nullptr;
+#endif
+        for (int i = 0; i < 2 && alive; ++i) {
+          const TileInfo ti = it.tile[i];
+          if (!ti.valid) continue;
+          bool ok = mbar_wait(bar_stats_full + 8 * i, (st_par >> i) & 1u, abort_flag, wait_ns);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) { alive = false; break; }
+          st_par ^= 1u << i;
+          const float inv = stats[i * kBM + row_in_tile];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_stats_empty + 8 * i);
+          const bool have_o = ti.n > 0;
+          if (have_o) {
+            // the last two P.V products were issued by different warps: pv_done covers the second-to-last one
+            if (ti.n >= 2) {
+              ok = mbar_wait(bar_pv_done + 8 * i, (pv_par >> i) & 1u, abort_flag, wait_ns);
+              pv_par ^= 1u << i;
+            }
+            ok = ok && mbar_wait(bar_o_full + 8 * i, (of_par >> i) & 1u, abort_flag, wait_ns);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { alive = false; break; }
+            of_par ^= 1u << i;
+            tc_fence_after();
+          }
+          if (tracer) trace[4 + 8 * i] = globaltimer_ns();
+          store_o_tile<HD, kBf16>(p, &tm_o, tmem_base + lane_bits + (uint32_t)(C::kOCol + i * HD), have_o, inv, my_stage,
+                                     n_stores, lane, ti.t * kBM + quarter * 32, ti.h, it.b, bar_o_empty + 8 * i);
+          if (tracer) trace[5 + 8 * i] = globaltimer_ns();
+        }
+      }
+      // staging memory must outlive the bulk stores that read it
+      if (lane == 0) bulk_wait_all();
+      __syncwarp();
     }
   }
 
@@ -973,8 +1161,8 @@ bool aligned_bhs(const void* base, const int64_t* stride, int64_t H, int64_t B, 
   return true;
 }
 
-template <typename T, int HD, bool MASKED>
-cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, int num_sms, float* debug,
+template <typename T, int HD, bool MASKED, bool EPI>
+cudaError_t launch_e(const SdpaParams& p, cudaStream_t stream, int32_t* sched, int num_sms, float* debug,
                      int debug_mode, PrefillMapCache* cache, const char** why) {
   using C = Cfg<HD>;
   constexpr bool bf16 = !std::is_same_v<T, __half>;
@@ -1043,15 +1231,15 @@ cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
   const int64_t total = (int64_t)pp.ranks * pp.items_per_rank;
   if (total <= 0 || total > 0x3fffffff) { *why = "work item count out of range"; return cudaErrorInvalidValue; }
   pp.total_items = (int)total;
-  auto kern = sdpa_prefill_sm100_kernel<T, HD, MASKED>;
-  constexpr int inst = (bf16 ? 0 : 4) + (HD == 128 ? 2 : 0) + (MASKED ? 1 : 0);
+  auto kern = sdpa_prefill_sm100_kernel<T, HD, MASKED, EPI>;
+  constexpr int inst = (EPI ? 8 : 0) + (bf16 ? 0 : 4) + (HD == 128 ? 2 : 0) + (MASKED ? 1 : 0);
   if (!mc->attr_set[inst]) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
     if (e != cudaSuccess) { *why = "cannot raise the dynamic shared memory limit"; return e; }
     mc->attr_set[inst] = true;
   }
   const unsigned grid = (unsigned)(total < num_sms ? total : num_sms);
-  kern<<<grid, kThreads, C::kSmemBytes, stream>>>(*tq, *tk, *tv, *to, pp);
+  kern<<<grid, Roles<EPI>::kThreads, C::kSmemBytes, stream>>>(*tq, *tk, *tv, *to, pp);
   return cudaGetLastError();
 }
 
@@ -1082,6 +1270,15 @@ bool prefill_sm100_supported(const SdpaParams& p, int dtype, const char** why) {
   }
   if (p.seq_q > 0x7fffff00ll || p.seq_kv > 0x7fffff00ll) { *why = "sequence too long"; return false; }
   return true;
+}
+
+// The epilogue warpgroup pays when both tiles of an item end together: head pairs, or row pairs without a causal mask.
+template <typename T, int HD, bool MASKED>
+cudaError_t launch_t(const SdpaParams& p, cudaStream_t stream, int32_t* sched, int num_sms, float* debug,
+                     int debug_mode, PrefillMapCache* cache, const char** why) {
+  const bool epi = (p.group % 2 == 0) || !p.causal;
+  if (epi) return launch_e<T, HD, MASKED, true>(p, stream, sched, num_sms, debug, debug_mode, cache, why);
+  return launch_e<T, HD, MASKED, false>(p, stream, sched, num_sms, debug, debug_mode, cache, why);
 }
 
 template <typename T, int HD>

@@ -128,6 +128,8 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* tm, uint32_t src
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the bulk stores committed by this thread have finished READING shared memory (it may be reused).
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Same, but the most recently committed group may still be reading (two staging buffers used alternately).
+__device__ __forceinline__ void bulk_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 // Makes generic-proxy writes to shared memory visible to the async proxy (TMA) of this CTA.
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

@@ -89,7 +89,7 @@ WORKLOADS = {
 # summaries are under profiles/).  Decode was captured on the B=16 quarter of C4 (525.5 MB of traffic for 520.1 MB of
 # algorithmic bytes); every (batch, head) streams its own keys once, so traffic grows in proportion to the bytes
 # streamed and a full-size launch is that ratio times its own algorithmic bytes.
-NCU_TRAFFIC_BYTES = {"c2": 646.8e6, "c3": 653.6e6, "c5shard": 167.9e6, "c4q": 525.5e6}
+NCU_TRAFFIC_BYTES = {"c2": 646.8e6, "c3": 690.8e6, "c5shard": 168.2e6, "c4q": 525.5e6}
 NCU_DECODE_TRAFFIC_RATIO = 525.5 / 520.1
 
 
