@@ -241,6 +241,55 @@ def test_prefill_sm100_padding_and_dtype_out():
     compare(out, O.sdpa(q2f, kf, vf, causal=True, causal_offset=0), "bf16")
 
 
+ROLE_LAYOUT_CASES = [
+    # B, Hq, Hkv, Sq, Sk, D, causal, out dtype, what it selects
+    (4, 8, 2, 1536, 1536, 128, True, "f32"),    # head pairs: epilogue warpgroup; 192 items, several per CTA
+    (4, 8, 2, 1536, 1536, 128, True, "bf16"),   # ... one staging buffer per 64 columns
+    (3, 6, 6, 1100, 1100, 128, False, "f32"),   # row pairs without a causal mask: epilogue warpgroup, ragged last tile
+    (3, 6, 6, 1100, 1100, 128, True, "f32"),    # row pairs under a causal mask: the softmax warps run the epilogue
+    (2, 12, 4, 900, 900, 64, True, "bf16"),     # odd group (3): row pairs; head_dim 64
+    (2, 8, 4, 700, 300, 128, True, "f32"),      # Sq > Sk, bottom-right: the first row tiles see no key at all
+]
+
+
+@pytest.mark.parametrize("case", ROLE_LAYOUT_CASES)
+def test_prefill_sm100_both_role_layouts_many_items_per_cta(case):
+    """The kernel has two role layouts (softmax warps or a fourth warpgroup run the epilogue) chosen by item shape.
+    Shapes with more work items than SMs, so that every hand-over between consecutive items of a CTA is exercised
+    (O released to the next item's first P.V product, row sums passed through shared memory, both staging buffers),
+    with ragged lengths, tiles without any visible key, 16-bit and fp32 output, and LSE."""
+    B, Hq, Hkv, Sq, Sk, D, causal, odt = case
+    q, qf = gen((B, Hq, Sq, D), "bf16", 131)
+    k, kf = gen((B, Hkv, Sk, D), "bf16", 132)
+    v, vf = gen((B, Hkv, Sk, D), "bf16", 133)
+    kv = np.array([Sk, max(1, Sk // 3), 0, Sk - 7][:B], np.int32)     # full, short, empty, ragged
+    out, lse, info = run_gpu(q, k, v, dtype="bf16", out_dtype=odt, causal=causal, kv_len=_t(kv, torch.int32),
+                             want_lse=True, path=N.PATH_PREFILL_SM100)
+    assert info["path"] == N.PATH_PREFILL_SM100
+    ref, rlse, _ = O.sdpa(qf, kf, vf, causal=causal, kv_len=kv, want_lse=True)
+    compare(out, ref, "bf16", f"role layouts {case}")
+    compare_lse(lse, rlse, "bf16")
+    # twice on one handle: scheduler counters, cached tensor maps and barrier phases start over
+    again, _, _ = run_gpu(q, k, v, dtype="bf16", out_dtype=odt, causal=causal, kv_len=_t(kv, torch.int32),
+                          path=N.PATH_PREFILL_SM100)
+    assert torch.equal(again, out)
+
+
+def test_prefill_sm100_masked_instantiation_on_both_layouts():
+    """Softcap + additive bias (the MASKED instantiation) with head pairs (epilogue warpgroup) and with row pairs."""
+    for Hq, Hkv in ((8, 2), (3, 3)):
+        B, S, D = 2, 640, 128
+        q, qf = gen((B, Hq, S, D), "bf16", 141)
+        k, kf = gen((B, Hkv, S, D), "bf16", 142)
+        v, vf = gen((B, Hkv, S, D), "bf16", 143)
+        bias = np.random.default_rng(3).standard_normal((B, Hq, S, S)).astype(np.float32)
+        out, lse, info = run_gpu(q, k, v, dtype="bf16", causal=True, softcap=3.0, mask=_t(bias), mask_kind=N.MASK_ADD_F32,
+                                 want_lse=True, path=N.PATH_PREFILL_SM100)
+        ref, rlse, _ = O.sdpa(qf, kf, vf, causal=True, softcap=3.0, mask=bias, mask_kind=O.MASK_ADD_F32, want_lse=True)
+        compare(out, ref, "bf16", f"masked, Hq {Hq} Hkv {Hkv}")
+        compare_lse(lse, rlse, "bf16")
+
+
 def test_prefill_sm100_head_shard_matches_full():
     """A head shard (multi-GPU partition) computes exactly the rows of the full call."""
     B, Hq, Hkv, S, D = 1, 8, 4, 384, 128
