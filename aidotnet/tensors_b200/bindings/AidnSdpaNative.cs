@@ -40,6 +40,8 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         public long workspace_bytes;
         public int gather_output;
         public IntPtr weights;     // [B, Hq, Sq, Sk] fp32 probabilities on request, or zero
+        public int peer_count;     // fused gather: other devices' output tensors, mapped with aidn_peer_open
+        public IntPtr peer_out0, peer_out1, peer_out2, peer_out3, peer_out4, peer_out5, peer_out6, peer_out7;
     }
 
     /// <summary>Paged K/V: the block pool of DevicePagedKVCache ([MaxBlocks, BlockSize, KvHeads, HeadDim]) and the
@@ -110,6 +112,11 @@ namespace AiDotNet.Tensors.Engines.DirectGpu.CUDA
         /// library): for a backend that may not allocate device memory where it decodes.  First call per context
         /// outside stream capture; concurrent calls on one device share the array and must be stream-ordered.</summary>
         [DllImport(Lib)] public static extern int aidn_sdpa_decode_noalloc(ref AidnSdpaDesc desc, ref AidnSdpaArgs args, IntPtr cuStream);
+        /// <summary>Peer mappings for AidnSdpaArgs.peer_out (fused gather of a head-sharded prefill): the 64-byte IPC
+        /// handle and offset of a device allocation, and its mapping into another process of the same node.</summary>
+        [DllImport(Lib)] public static extern int aidn_peer_export(IntPtr devPtr, byte[] handle64, out long offset);
+        [DllImport(Lib)] public static extern int aidn_peer_open(byte[] handle64, out IntPtr basePtr);
+        [DllImport(Lib)] public static extern int aidn_peer_close(IntPtr basePtr);
         [DllImport(Lib)] public static extern int aidn_paged_kv_append(IntPtr newKeys, IntPtr newValues, IntPtr keyPool, IntPtr valuePool, IntPtr blockTable, long startPosition, long tokens, int blockSize, int numBlocks, long rowBytes, IntPtr cuStream);
         [DllImport(Lib)] public static extern long aidn_sdpa_backward_workspace_bytes(IntPtr handle, long batch, long seqQ);
         [DllImport(Lib)] public static extern int aidn_sdpa_backward(IntPtr handle, ref AidnSdpaBwdArgs args, IntPtr cuStream);

@@ -318,6 +318,12 @@ int build_params(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* pg
   p.out = a->out;
   p.lse = d.emit_lse ? a->lse : nullptr;
   p.weights = a->weights;
+  if (a->peer_count < 0 || a->peer_count > AIDN_MAX_PEERS) return fail(AIDN_EINVAL, "launch: peer_count out of range");
+  p.peer_count = a->peer_count;
+  for (int i = 0; i < a->peer_count; ++i) {
+    if (!a->peer_out[i]) return fail(AIDN_EINVAL, "launch: peer_out[%d] is null", i);
+    p.peer_out[i] = a->peer_out[i];
+  }
   p.mask = d.mask_kind != AIDN_MASK_NONE ? a->mask : nullptr;
   p.mask_kind = d.mask_kind;
   p.kv_len = a->kv_len;
@@ -400,6 +406,12 @@ int launch_common(aidn_sdpa_t h, const aidn_sdpa_args* a, const aidn_paged_kv* p
     if ((uintptr_t)p.weights % 4 != 0) return fail(AIDN_EINVAL, "launch: weights must be 4-byte aligned");
     if (pg) return fail(AIDN_EUNSUPPORTED, "launch: attention weights over paged K/V are not defined");
     path = AIDN_PATH_GENERIC;
+  }
+  if (p.peer_count > 0) {
+    // the stores to the other devices are issued by the tcgen05 kernel's epilogue
+    if (path != AIDN_PATH_PREFILL_SM100 || !prefill_ok)
+      return fail(AIDN_EUNSUPPORTED, "launch: peer_out needs the tcgen05 prefill kernel (16-bit inputs, head_dim 64 or 128)");
+    if (a->gather_output) return fail(AIDN_EINVAL, "launch: peer_out and gather_output are two ways to the same result");
   }
   if (path == AIDN_PATH_DECODE && !decode_ok)
     return fail(AIDN_EUNSUPPORTED,
@@ -857,6 +869,51 @@ static int cast_common(int kind, const void* src, void* dst, int64_t n, void* cu
   if (n < 0 || (n > 0 && (!src || !dst))) return fail(AIDN_EINVAL, "cast: bad argument");
   cudaError_t e = aidn::launch_cast(kind, src, dst, n, (cudaStream_t)cu_stream);
   if (e != cudaSuccess) return fail_cuda(e, "cast");
+  return AIDN_OK;
+}
+
+int aidn_peer_export(const void* dev_ptr, void* handle64, int64_t* offset) {
+  g_err[0] = 0;
+  if (!dev_ptr || !handle64 || !offset) return fail(AIDN_EINVAL, "peer_export: null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle size");
+  // the handle names a whole allocation: find its base
+  typedef int (*GetRangeFn)(unsigned long long*, size_t*, unsigned long long);   // CUresult cuMemGetAddressRange_v2
+  static GetRangeFn get_range = nullptr;
+  if (!get_range) {
+    void* raw = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &raw, cudaEnableDefault, &qres) != cudaSuccess || !raw ||
+        qres != cudaDriverEntryPointSuccess)
+      return fail(AIDN_ECUDA, "peer_export: cuMemGetAddressRange is not available from the driver");
+    get_range = reinterpret_cast<GetRangeFn>(raw);
+  }
+  unsigned long long base = 0;
+  size_t size = 0;
+  if (get_range(&base, &size, (unsigned long long)(uintptr_t)dev_ptr) != 0)
+    return fail(AIDN_EINVAL, "peer_export: not a device allocation");
+  cudaIpcMemHandle_t hdl;
+  cudaError_t e = cudaIpcGetMemHandle(&hdl, reinterpret_cast<void*>((uintptr_t)base));
+  if (e != cudaSuccess) return fail_cuda(e, "peer_export");
+  std::memcpy(handle64, &hdl, 64);
+  *offset = (int64_t)((uintptr_t)dev_ptr - (uintptr_t)base);
+  return AIDN_OK;
+}
+
+int aidn_peer_open(const void* handle64, void** base) {
+  g_err[0] = 0;
+  if (!handle64 || !base) return fail(AIDN_EINVAL, "peer_open: null argument");
+  cudaIpcMemHandle_t hdl;
+  std::memcpy(&hdl, handle64, 64);
+  cudaError_t e = cudaIpcOpenMemHandle(base, hdl, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail_cuda(e, "peer_open");
+  return AIDN_OK;
+}
+
+int aidn_peer_close(void* base) {
+  g_err[0] = 0;
+  if (!base) return fail(AIDN_EINVAL, "peer_close: null argument");
+  cudaError_t e = cudaIpcCloseMemHandle(base);
+  if (e != cudaSuccess) return fail_cuda(e, "peer_close");
   return AIDN_OK;
 }
 

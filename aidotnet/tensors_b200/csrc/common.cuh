@@ -25,6 +25,8 @@ struct SdpaParams {
   void* out;
   float* lse;
   float* weights;   // [B, Hq, Sq, Sk] fp32 probabilities, or null (generic kernel only)
+  void* peer_out[8];   // other devices' `out` tensors, mapped here (tcgen05 prefill only)
+  int32_t peer_count;
   const void* mask;
   const int32_t* kv_len;
   int64_t mask_stride[4];

@@ -136,6 +136,12 @@ struct PrefillParams {
   uint64_t wait_budget_ns; // longest single wait before the CTA gives up
 };
 
+// Tensor maps of the other devices' output tensors (fused gather): every output box is stored to each of them too.
+struct alignas(64) PeerMaps {
+  CUtensorMap maps[AIDN_MAX_PEERS];
+  int32_t count;
+};
+
 struct TileInfo {
   int h;          // q head
   int t;          // row tile index
@@ -228,9 +234,9 @@ __device__ __forceinline__ Item decode_item(const PrefillParams& pp, int item) {
 // stores.  `n_stores` counts this warp's stores; store k stages through buffer k & 1.  `bar_o_empty` gets one arrival
 // per warp as soon as the tile's last tcgen05.ld has completed.
 template <int HD, bool kBf16>
-__device__ __forceinline__ void store_o_tile(const SdpaParams& p, const CUtensorMap* tm_o, uint32_t t_o, bool have_o,
-                                             float inv, uint32_t my_stage, uint32_t& n_stores, int lane, int row0,
-                                             int h, int b, uint32_t bar_o_empty) {
+__device__ __forceinline__ void store_o_tile(const SdpaParams& p, const CUtensorMap* tm_o, const PeerMaps& pm, uint32_t t_o,
+                                             bool have_o, float inv, uint32_t my_stage, uint32_t& n_stores, int lane,
+                                             int row0, int h, int b, uint32_t bar_o_empty) {
   // 128-byte staging rows under the 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
   const uint32_t my_swz = (uint32_t)(lane & 7);
   const bool box_valid = row0 < p.seq_q;
@@ -281,7 +287,10 @@ __device__ __forceinline__ void store_o_tile(const SdpaParams& p, const CUtensor
       __syncwarp();
       // the store is counted (and its group committed) whether or not the box lies inside the tensor
       if (lane == 0) {
-        if (box_valid) tma_store_4d(tm_o, buf, p.out_f32 ? c0 : c0 - 32, row0, h, b);
+        if (box_valid) {
+          tma_store_4d(tm_o, buf, p.out_f32 ? c0 : c0 - 32, row0, h, b);
+          for (int r = 0; r < pm.count; ++r) tma_store_4d(&pm.maps[r], buf, p.out_f32 ? c0 : c0 - 32, row0, h, b);
+        }
         bulk_commit();
       }
       ++n_stores;
@@ -295,7 +304,7 @@ template <typename T, int HD, bool MASKED, bool EPI>
 __global__ void __launch_bounds__(Roles<EPI>::kThreads, 1)
     sdpa_prefill_sm100_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-                              const PrefillParams pp) {
+                              const __grid_constant__ PeerMaps pm, const PrefillParams pp) {
   using C = Cfg<HD>;
   using R = Roles<EPI>;
   constexpr bool kBf16 = !std::is_same_v<T, __half>;
@@ -697,6 +706,7 @@ __global__ void __launch_bounds__(Roles<EPI>::kThreads, 1)
               __syncwarp();
               if (lane == 0 && box_valid) {
                 tma_store_4d(&tm_o, my_stage, p.out_f32 ? c0 : c0 - 32, row0, ti.h, b);
+                for (int r = 0; r < pm.count; ++r) tma_store_4d(&pm.maps[r], my_stage, p.out_f32 ? c0 : c0 - 32, row0, ti.h, b);
                 bulk_commit();
               }
               stores_in_flight = true;
@@ -1099,7 +1109,7 @@ __global__ void __launch_bounds__(Roles<EPI>::kThreads, 1)
             tc_fence_after();
           }
           if (tracer) trace[4 + 8 * i] = globaltimer_ns();
-          store_o_tile<HD, kBf16>(p, &tm_o, tmem_base + lane_bits + (uint32_t)(C::kOCol + i * HD), have_o, inv, my_stage,
+          store_o_tile<HD, kBf16>(p, &tm_o, pm, tmem_base + lane_bits + (uint32_t)(C::kOCol + i * HD), have_o, inv, my_stage,
                                      n_stores, lane, ti.t * kBM + quarter * 32, ti.h, it.b, bar_o_empty + 8 * i);
           if (tracer) trace[5 + 8 * i] = globaltimer_ns();
         }
@@ -1207,6 +1217,26 @@ cudaError_t launch_e(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
     mc->key = key;
     mc->valid = true;
   }
+  // Fused gather: the same box geometry over the other devices' output tensors.  (Encoded per launch: a handful of
+  // microseconds against a launch that is long enough to be sharded.)
+  PeerMaps pm;
+  std::memset(&pm, 0, sizeof(pm));
+  pm.count = p.peer_count;
+  for (int r = 0; r < p.peer_count; ++r) {
+    const CUtensorMapDataType dt16 = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    if (!aligned_bhs(p.peer_out[r], p.os, p.num_q_heads, p.batch, p.out_f32 ? 4 : 2, 16)) {
+      *why = "peer_out must be 16-byte aligned like out";
+      return cudaErrorInvalidValue;
+    }
+    e = resolve_encode();
+    if (e != cudaSuccess) { *why = "cuTensorMapEncodeTiled is not available from the driver"; return e; }
+    const bool ok = p.out_f32
+        ? encode_bhsd(&pm.maps[r], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, CU_TENSOR_MAP_SWIZZLE_128B, p.peer_out[r], HD, p.seq_q,
+                      p.num_q_heads, p.batch, p.os, 32, 32)
+        : encode_bhsd(&pm.maps[r], dt16, 2, CU_TENSOR_MAP_SWIZZLE_128B, p.peer_out[r], HD, p.seq_q, p.num_q_heads, p.batch,
+                      p.os, 64, 32);
+    if (!ok) { *why = "cuTensorMapEncodeTiled rejected a peer output tensor"; return cudaErrorInvalidValue; }
+  }
   PrefillParams pp;
   pp.p = p;
 #if AIDN_PREFILL_TRACE
@@ -1239,7 +1269,7 @@ cudaError_t launch_e(const SdpaParams& p, cudaStream_t stream, int32_t* sched, i
     mc->attr_set[inst] = true;
   }
   const unsigned grid = (unsigned)(total < num_sms ? total : num_sms);
-  kern<<<grid, Roles<EPI>::kThreads, C::kSmemBytes, stream>>>(*tq, *tk, *tv, *to, pp);
+  kern<<<grid, Roles<EPI>::kThreads, C::kSmemBytes, stream>>>(*tq, *tk, *tv, *to, pm, pp);
   return cudaGetLastError();
 }
 

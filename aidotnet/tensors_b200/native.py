@@ -29,7 +29,7 @@ EXPORTS = (
     "aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32",
     "aidn_sdpa_decode_noalloc", "aidn_sdpa_launch_paged", "aidn_qkv_rope_cache", "aidn_rope_interleaved",
     "aidn_sdpa_backward", "aidn_sdpa_backward_workspace_bytes", "aidn_paged_kv_append", "aidn_mha_forward",
-    "aidn_mha_workspace_bytes",
+    "aidn_mha_workspace_bytes", "aidn_peer_export", "aidn_peer_open", "aidn_peer_close",
     "aidn_sdpa_debug_set",   # include/aidn_sdpa_debug.h
 )
 
@@ -54,6 +54,7 @@ class SdpaArgs(ctypes.Structure):
         ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3), ("v_stride", ctypes.c_int64 * 3),
         ("o_stride", ctypes.c_int64 * 3), ("scale", ctypes.c_float), ("workspace", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_int64), ("gather_output", ctypes.c_int32), ("weights", ctypes.c_void_p),
+        ("peer_count", ctypes.c_int32), ("peer_out", ctypes.c_void_p * 8),
     ]
 
 
@@ -131,6 +132,12 @@ def load() -> ctypes.CDLL:
     lib.aidn_sdpa_last_error.restype = ctypes.c_char_p
     lib.aidn_sdpa_device_supported.argtypes = [ctypes.c_int32]
     lib.aidn_sdpa_device_supported.restype = ctypes.c_int
+    lib.aidn_peer_export.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]
+    lib.aidn_peer_export.restype = ctypes.c_int
+    lib.aidn_peer_open.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]
+    lib.aidn_peer_open.restype = ctypes.c_int
+    lib.aidn_peer_close.argtypes = [ctypes.c_void_p]
+    lib.aidn_peer_close.restype = ctypes.c_int
     for name in ("aidn_cast_f32_to_bf16", "aidn_cast_f32_to_f16", "aidn_cast_bf16_to_f32", "aidn_cast_f16_to_f32"):
         fn = getattr(lib, name)
         fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
@@ -210,7 +217,8 @@ class Handle:
                kv_len: Optional[int] = None, q_stride=None, k_stride=None, v_stride=None, o_stride=None,
                scale: float = 0.0, workspace: Optional[int] = None, workspace_bytes: int = 0,
                gather_output: bool = False, block_table: Optional[int] = None, block_table_stride: int = 0,
-               block_size: int = 0, num_blocks: int = 0, weights: Optional[int] = None) -> None:
+               block_size: int = 0, num_blocks: int = 0, weights: Optional[int] = None,
+               peer_out: Sequence[int] = ()) -> None:
         """Enqueues one forward.  With ``block_table`` (a device int32 array) ``k`` / ``v`` are the paged pools
         ``[num_blocks, block_size, Hkv, D]`` and the call goes through ``aidn_sdpa_launch_paged``."""
         a = SdpaArgs()
@@ -220,6 +228,9 @@ class Handle:
         a.q_stride, a.k_stride, a.v_stride, a.o_stride = _arr3(q_stride), _arr3(k_stride), _arr3(v_stride), _arr3(o_stride)
         a.scale, a.workspace, a.workspace_bytes, a.gather_output = scale, workspace, workspace_bytes, int(gather_output)
         a.weights = weights
+        a.peer_count = len(peer_out)
+        for i, ptr in enumerate(peer_out):
+            a.peer_out[i] = ptr
         if block_table is not None:
             pg = PagedKv()
             pg.block_table, pg.block_table_stride = block_table, block_table_stride

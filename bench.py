@@ -494,21 +494,26 @@ class Runner:
             self.paged = dict(block_table=self.table.data_ptr(), block_table_stride=w["Sk"] // bs, block_size=bs,
                               num_blocks=nb)
 
-    def step(self, q=None, k=None, v=None, out=None, stream=None, gather=False):
+    def step(self, q=None, k=None, v=None, out=None, stream=None, gather=False, peer_out=()):
         q = self.q if q is None else q
         k = self.k if k is None else k
         v = self.v if v is None else v
         out = self.out if out is None else out
         self.h.launch(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=out.data_ptr(), batch=self.w["B"],
                       seq_q=self.w["Sq"], seq_kv=self.w["Sk"], stream=self.stream if stream is None else stream,
-                      kv_len=self.kv_len.data_ptr() if self.kv_len is not None else None, gather_output=gather, **self.paged)
+                      kv_len=self.kv_len.data_ptr() if self.kv_len is not None else None, gather_output=gather,
+                      peer_out=peer_out, **self.paged)
         self.launches += self.h.last_launch_count
 
-    def time_steps(self, steps, warmup, sampler=None, dist=None, repeats=1, gather=False):
+    def time_steps(self, steps, warmup, sampler=None, dist=None, repeats=1, gather=False, peer_out=(), after_step=None):
         """W warm-up steps, then `repeats` loops of exactly `steps` steps, every step bracketed by CUDA events on the
-        launching stream.  Returns (seconds of the FIRST loop, launches in it, per-step milliseconds of all loops)."""
+        launching stream.  Returns (seconds of the FIRST loop, launches in it, per-step milliseconds of all loops).
+        `after_step` is enqueued behind every step inside the timed region (the rank synchronisation of the fused
+        gather)."""
         for _ in range(warmup):
-            self.step(gather=gather)
+            self.step(gather=gather, peer_out=peer_out)
+            if after_step:
+                after_step()
         torch.cuda.synchronize()
         per_step = []
         first = None
@@ -523,7 +528,9 @@ class Runner:
                 sampler.mark_begin()
             ev[0].record()
             for i in range(steps):
-                self.step(gather=gather)
+                self.step(gather=gather, peer_out=peer_out)
+                if after_step:
+                    after_step()
                 ev[i + 1].record()
             torch.cuda.synchronize()
             if dist is not None:
@@ -730,9 +737,39 @@ def long_context_job(local, rank, world, pk, steps, dist):
     h2.launch(q=q_rows.data_ptr(), k=ko.data_ptr(), v=vo.data_ptr(), out=o2.data_ptr(), batch=1, seq_q=rows, seq_kv=w["Sk"],
               stream=r.stream)
     torch.cuda.synchronize()
-    remote_diff = float((o2 - r.out[:, other.head_begin:other.head_begin + other.head_count, r0:]).abs().max())
+
+    def remote_block_diff():
+        return float((o2 - r.out[:, other.head_begin:other.head_begin + other.head_count, r0:]).abs().max())
+
+    remote_diff = remote_block_diff()
     remote_ok = bool(remote_diff <= 1e-6)   # the same kernel on the same rows and keys: expected bit-identical
-    flags = torch.tensor([int(own["checked"]), int(remote_ok)], device="cuda")
+    # Third timing: the gather fused into the kernel.  Every rank maps the other ranks' output tensors (CUDA IPC) and
+    # the epilogue stores each output tile to all of them; a one-element all-reduce behind every launch is the rank
+    # synchronisation after which the gathered tensor is complete everywhere (inside the timed region).
+    from aidotnet.tensors_b200.peer import PeerTensor
+    fused = None
+    fused_ok = False
+    fused_diff = None
+    try:
+        r.out[:, other.head_begin:other.head_begin + other.head_count].zero_()   # what the NCCL gather left there
+        torch.cuda.synchronize()
+        dist.barrier()
+        peers = PeerTensor(r.out, dist)
+        token = torch.zeros(1, device="cuda")
+        fsecs, _, fper = r.time_steps(steps, 2, None, dist, repeats=1, peer_out=peers.others,
+                                      after_step=lambda: dist.all_reduce(token))
+        fused = [fsecs, fper]
+        torch.cuda.synchronize()
+        dist.barrier()
+        fused_diff = remote_block_diff()
+        fused_ok = bool(fused_diff <= 1e-6)
+        peers.close()
+    except Exception as exc:   # the mapping is host plumbing outside the C ABI's hot path: report, do not fail the line
+        fused = str(exc)
+    t = torch.tensor([fused[0] if isinstance(fused, list) else 0.0], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    fsecs = float(t[0].item())
+    flags = torch.tensor([int(own["checked"]), int(remote_ok), int(fused_ok)], device="cuda")
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     h2.close()
     per_rank_fl = fl / world
@@ -750,6 +787,11 @@ def long_context_job(local, rank, world, pk, steps, dist):
            "gather": {"ms_per_step_with_gather": gsecs / steps * 1e3, "gather_ms": gather_ms, "per_step": step_stats(gper),
                       "bytes_received_per_rank": recv, "nvlink_gbs_per_rank": (recv / 1e9) / (gather_ms / 1e3) if gather_ms > 0 else None,
                       "nvlink_reference_gbs": 770.0, "collective": "ncclAllGather, in place, on the kernel's stream"},
+           "fused_gather": ({"ms_per_step": fsecs / steps * 1e3, "extra_ms": max(fsecs - secs, 0.0) / steps * 1e3,
+                             "per_step": step_stats(fused[1]),
+                             "how": "peer_out: the kernel's TMA stores write every tile to all ranks; one-element all-reduce per step as the rank barrier"}
+                            if isinstance(fused, list) else {"unavailable": fused}),
+           "fused_gather_ok": bool(flags[2].item() == 1), "fused_gather_max_abs_diff_rank0": fused_diff,
            "gather_ok": bool(flags[1].item() == 1), "gather_check": {"rows": [r0, r0 + rows], "remote_heads": [qh[0], qh[-1]], "max_abs_diff_rank0": remote_diff},
            "check": dict(own, all_ranks=bool(flags[0].item() == 1))}
     del r

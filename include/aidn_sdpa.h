@@ -139,7 +139,17 @@ typedef struct {
                              on the fp32 FFMA kernel whatever the input dtype, with a second pass over the keys -
                              sized for the training-time shapes that ask for weights, not for long prefill; the
                              buffer is B*Hq*Sq*Sk*4 bytes, counted in 64 bits.                              */
+  int32_t peer_count;     /* 0, or the number of entries of peer_out (at most AIDN_MAX_PEERS)                     */
+  void* peer_out[8];      /* Fused gather of a head-sharded prefill (tcgen05 kernel only): peer_out[i] is the `out`
+                             tensor of another device - same shape, strides and dtype - mapped into this device's
+                             address space (aidn_peer_open).  Every output tile is stored to `out` and to each
+                             peer_out[i] by the kernel's own TMA stores, while the other tiles are still being
+                             computed: the all-gather of NcclComm.AllGather (CUDA/NcclComm.cs:106-110) costs no
+                             second pass.  A device's tensor is complete when EVERY rank's launch has completed:
+                             synchronise the ranks (a barrier or a tiny collective on the stream) before reading.
+                             Not together with gather_output.                                                 */
 } aidn_sdpa_args;
+#define AIDN_MAX_PEERS 8
 
 /* Paged K/V (the vLLM-style pool of Engines/DirectGpu/DevicePagedKVCache.cs:10-18): args.k / args.v are the key and
  * value pools [num_blocks, block_size, Hkv, D]; key t of batch entry b is row
@@ -307,6 +317,15 @@ AIDN_API int aidn_mha_forward(aidn_sdpa_t h, const aidn_mha_args* args, void* cu
 
 /* dtype staging (IDirectGpuBackend.cs:1890 ConvertToFp16, :1911 ConvertToFp32; bf16 rounding per
  * NumericOperations/BFloat16.cs:65-84: round-to-nearest-even, NaN keeps its top payload bits plus the quiet bit). */
+/* Peer mappings for aidn_sdpa_args.peer_out, between processes of one node (one process per GPU).
+ * aidn_peer_export: the 64-byte CUDA IPC handle of the allocation that holds `dev_ptr`, and the offset of dev_ptr in
+ * it (the allocation must come from cudaMalloc, as torch's default allocator's blocks do).  aidn_peer_open: maps an
+ * exported allocation of ANOTHER process into the current device's address space (peer access is enabled on
+ * demand) and returns its base; the tensor is at base + offset.  aidn_peer_close unmaps it. */
+AIDN_API int aidn_peer_export(const void* dev_ptr, void* handle64, int64_t* offset);
+AIDN_API int aidn_peer_open(const void* handle64, void** base);
+AIDN_API int aidn_peer_close(void* base);
+
 AIDN_API int aidn_cast_f32_to_bf16(const float* src, void* dst, int64_t n, void* cu_stream);
 AIDN_API int aidn_cast_f32_to_f16(const float* src, void* dst, int64_t n, void* cu_stream);
 AIDN_API int aidn_cast_bf16_to_f32(const void* src, float* dst, int64_t n, void* cu_stream);
