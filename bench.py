@@ -789,6 +789,10 @@ def long_context_job(local, rank, world, pk, steps, dist):
                       "nvlink_reference_gbs": 770.0, "collective": "ncclAllGather, in place, on the kernel's stream"},
            "fused_gather": ({"ms_per_step": fsecs / steps * 1e3, "extra_ms": max(fsecs - secs, 0.0) / steps * 1e3,
                              "per_step": step_stats(fused[1]),
+                             "bytes_sent_per_rank": out_bytes / world * (world - 1),
+                             "target_ms": max(per_rank_fl / (pk["bf16"] * 1e12), (out_bytes / world * (world - 1)) / 770e9) * 1e3,
+                             "frac_of_target": max(per_rank_fl / (pk["bf16"] * 1e12), (out_bytes / world * (world - 1)) / 770e9) / (fsecs / steps),
+                             "target": "the slower of FLOP / measured bf16 peak and bytes sent / 770 GB/s (measured peer copy)",
                              "how": "peer_out: the kernel's TMA stores write every tile to all ranks; one-element all-reduce per step as the rank barrier"}
                             if isinstance(fused, list) else {"unavailable": fused}),
            "fused_gather_ok": bool(flags[2].item() == 1), "fused_gather_max_abs_diff_rank0": fused_diff,
