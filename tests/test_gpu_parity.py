@@ -290,6 +290,53 @@ def test_prefill_sm100_masked_instantiation_on_both_layouts():
         compare_lse(lse, rlse, "bf16")
 
 
+@pytest.mark.parametrize("case", [(1, 8, 4, 640, 128, "f32", True), (2, 6, 6, 500, 64, "bf16", True), (1, 4, 4, 384, 128, "f32", False)])
+def test_prefill_sm100_peer_out_on_one_device(case):
+    """args.peer_out (the fused gather of a head-sharded launch) with the "other ranks" played by further tensors on
+    the same device: every output box has to arrive in `out` and in each of them, through both role layouts, with
+    guard words around every tensor intact.  (Across two devices: tests/test_gpu_multi.py.)"""
+    from tests._harness import guarded, check_guards, TORCH_DT
+    B, Hq, Hkv, S, D, odt, causal = case
+    q, _ = gen((B, Hq, S, D), "bf16", 151)
+    k, _ = gen((B, Hkv, S, D), "bf16", 152)
+    v, _ = gen((B, Hkv, S, D), "bf16", 153)
+    full, _, _ = run_gpu(q, k, v, dtype="bf16", out_dtype=odt, causal=causal, path=N.PATH_PREFILL_SM100)
+    flats, bodies = zip(*(guarded((B, Hq, S, D), TORCH_DT[odt], q.device, fill=0.0) for _ in range(4)))
+    stream = torch.cuda.current_stream().cuda_stream
+    half = Hq // 2
+    for hb in (0, half):   # two "ranks", one after the other
+        h = N.Handle(device=0, qkv_dtype=N.BF16, out_dtype=N.F32 if odt == "f32" else N.BF16, head_dim=D, num_q_heads=Hq,
+                     num_kv_heads=Hkv, causal=causal, head_begin=hb, head_count=half, path=N.PATH_PREFILL_SM100)
+        h.launch(q=q.data_ptr(), k=k.data_ptr(), v=v.data_ptr(), out=bodies[0].data_ptr(), batch=B, seq_q=S, seq_kv=S,
+                 stream=stream, peer_out=[t.data_ptr() for t in bodies[1:]])
+        h.poll(stream)
+        assert h.last_launch_count == 1
+        h.close()
+    for flat, body in zip(flats, bodies):
+        check_guards(flat, "a gathered output tensor")
+        assert torch.equal(body, full)
+
+
+def test_peer_out_is_refused_where_no_kernel_serves_it():
+    q, _ = gen((1, 4, 256, 128), "f32", 161, 1.0)
+    out = torch.zeros((1, 4, 256, 128), device="cuda")
+    other = torch.zeros_like(out)
+    stream = torch.cuda.current_stream().cuda_stream
+    h = N.Handle(device=0, qkv_dtype=N.F32, head_dim=128, num_q_heads=4, num_kv_heads=4)
+    with pytest.raises(N.AidnError) as e:   # fp32 inputs run on the FFMA kernel
+        h.launch(q=q.data_ptr(), k=q.data_ptr(), v=q.data_ptr(), out=out.data_ptr(), batch=1, seq_q=256, seq_kv=256,
+                 stream=stream, peer_out=[other.data_ptr()])
+    assert e.value.status == N.EUNSUPPORTED
+    h.close()
+    qb = q.to(torch.bfloat16)
+    h = N.Handle(device=0, qkv_dtype=N.BF16, head_dim=128, num_q_heads=4, num_kv_heads=4)
+    with pytest.raises(N.AidnError) as e:   # a null entry
+        h.launch(q=qb.data_ptr(), k=qb.data_ptr(), v=qb.data_ptr(), out=out.data_ptr(), batch=1, seq_q=256, seq_kv=256,
+                 stream=stream, peer_out=[other.data_ptr(), 0])
+    assert e.value.status == N.EINVAL
+    h.close()
+
+
 def test_prefill_sm100_head_shard_matches_full():
     """A head shard (multi-GPU partition) computes exactly the rows of the full call."""
     B, Hq, Hkv, S, D = 1, 8, 4, 384, 128
