@@ -758,7 +758,9 @@ def long_context_job(local, rank, world, pk, steps, dist):
         token = torch.zeros(1, device="cuda")
         fsecs, _, fper = r.time_steps(steps, 2, None, dist, repeats=1, peer_out=peers.others,
                                       after_step=lambda: dist.all_reduce(token))
-        fused = [fsecs, fper]
+        # and without the per-step barrier (ranks synchronised only around the loop): what the stores themselves cost
+        nsecs, _, _ = r.time_steps(steps, 2, None, dist, repeats=1, peer_out=peers.others)
+        fused = [fsecs, fper, nsecs]
         torch.cuda.synchronize()
         dist.barrier()
         fused_diff = remote_block_diff()
@@ -766,9 +768,9 @@ def long_context_job(local, rank, world, pk, steps, dist):
         peers.close()
     except Exception as exc:   # the mapping is host plumbing outside the C ABI's hot path: report, do not fail the line
         fused = str(exc)
-    t = torch.tensor([fused[0] if isinstance(fused, list) else 0.0], device="cuda")
+    t = torch.tensor([fused[0], fused[2]] if isinstance(fused, list) else [0.0, 0.0], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    fsecs = float(t[0].item())
+    fsecs, nsecs = float(t[0].item()), float(t[1].item())
     flags = torch.tensor([int(own["checked"]), int(remote_ok), int(fused_ok)], device="cuda")
     dist.all_reduce(flags, op=dist.ReduceOp.MIN)
     h2.close()
@@ -788,6 +790,7 @@ def long_context_job(local, rank, world, pk, steps, dist):
                       "bytes_received_per_rank": recv, "nvlink_gbs_per_rank": (recv / 1e9) / (gather_ms / 1e3) if gather_ms > 0 else None,
                       "nvlink_reference_gbs": 770.0, "collective": "ncclAllGather, in place, on the kernel's stream"},
            "fused_gather": ({"ms_per_step": fsecs / steps * 1e3, "extra_ms": max(fsecs - secs, 0.0) / steps * 1e3,
+                             "ms_per_step_without_step_barrier": nsecs / steps * 1e3,
                              "per_step": step_stats(fused[1]),
                              "bytes_sent_per_rank": out_bytes / world * (world - 1),
                              "target_ms": max(per_rank_fl / (pk["bf16"] * 1e12), (out_bytes / world * (world - 1)) / 770e9) * 1e3,
