@@ -8,11 +8,51 @@ communicator bootstrap of ``NcclComm`` (``CUDA/NcclComm.cs:43-97``): a few bytes
 from __future__ import annotations
 
 import ctypes
-from typing import List
+from typing import Callable, List, Tuple
 
 import torch
 
 from . import native as N
+
+
+def exchange_mappings(dist, local_pointer: int, export: Callable[[int], Tuple[bytes, int]],
+                      open_mapping: Callable[[bytes], int], close_mapping: Callable[[int], None]) -> Tuple[List[int], List[int]]:
+    """The exchange itself, independent of CUDA: returns (pointers by rank, bases this rank has mapped).
+
+    Every rank takes part in both collectives whatever happens to it locally, and all ranks then agree on the outcome:
+    a rank that raised on its own would leave the others waiting in a collective.  On failure everything this rank
+    mapped is unmapped again and every rank raises the same ``RuntimeError``."""
+    rank, world = dist.get_rank(), dist.get_world_size()
+    mine, problem = None, None
+    try:
+        mine = export(local_pointer)
+    except Exception as exc:   # noqa: BLE001 - whatever the export raised is reported by all ranks
+        problem = f"rank {rank}: {exc}"
+    everyone: List = [None] * world
+    dist.all_gather_object(everyone, mine)
+    bases: List[int] = []
+    pointers: List[int] = []
+    if problem is None and all(e is not None for e in everyone):
+        try:
+            for r, (handle, offset) in enumerate(everyone):
+                if r == rank:
+                    pointers.append(local_pointer)
+                    continue
+                base = open_mapping(handle)
+                bases.append(base)
+                pointers.append(base + offset)
+        except Exception as exc:   # noqa: BLE001
+            problem = f"rank {rank}: {exc}"
+    elif problem is None:
+        problem = f"rank {rank}: another rank could not export its tensor"
+    verdicts: List = [None] * world
+    dist.all_gather_object(verdicts, problem)
+    failed = [v for v in verdicts if v is not None]
+    if failed:
+        for base in bases:
+            close_mapping(base)
+        raise RuntimeError("peer mapping failed: " + "; ".join(failed))
+    return pointers, bases
 
 
 class PeerTensor:
@@ -24,41 +64,25 @@ class PeerTensor:
         self.tensor = tensor
         self.rank, self.world = dist.get_rank(), dist.get_world_size()
         lib = N.load()
-        # Every rank takes part in both exchanges whatever happens to it locally, and all ranks then agree on the
-        # outcome: a rank that raised on its own would leave the others waiting in a collective.
-        mine, problem = None, None
-        try:
+
+        def export(ptr: int) -> Tuple[bytes, int]:
             handle = (ctypes.c_ubyte * 64)()
             offset = ctypes.c_int64(0)
-            N.check(lib.aidn_peer_export(ctypes.c_void_p(tensor.data_ptr()), handle, ctypes.byref(offset)))
-            mine = (bytes(handle), int(offset.value))
-        except N.AidnError as exc:
-            problem = f"rank {self.rank}: {exc}"
-        everyone: List = [None] * self.world
-        dist.all_gather_object(everyone, mine)
+            N.check(lib.aidn_peer_export(ctypes.c_void_p(ptr), handle, ctypes.byref(offset)))
+            return bytes(handle), int(offset.value)
+
+        def open_mapping(handle: bytes) -> int:
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(handle)
+            base = ctypes.c_void_p()
+            N.check(lib.aidn_peer_open(buf, ctypes.byref(base)))
+            return int(base.value)
+
         self._bases: List[int] = []
-        self.pointers: List[int] = []
-        if problem is None and all(e is not None for e in everyone):
-            try:
-                for r, (hbytes, off) in enumerate(everyone):
-                    if r == self.rank:
-                        self.pointers.append(tensor.data_ptr())
-                        continue
-                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(hbytes)
-                    base = ctypes.c_void_p()
-                    N.check(lib.aidn_peer_open(buf, ctypes.byref(base)))
-                    self._bases.append(base.value)
-                    self.pointers.append(base.value + off)
-            except N.AidnError as exc:
-                problem = f"rank {self.rank}: {exc}"
-        elif problem is None:
-            problem = f"rank {self.rank}: another rank could not export its tensor"
-        verdicts: List = [None] * self.world
-        dist.all_gather_object(verdicts, problem)
-        failed = [v for v in verdicts if v is not None]
-        if failed:
-            self.close()
-            raise RuntimeError("peer mapping failed: " + "; ".join(failed))
+        self.pointers, self._bases = exchange_mappings(dist, tensor.data_ptr(), export, open_mapping, self._close_one)
+
+    @staticmethod
+    def _close_one(base: int) -> None:
+        N.load().aidn_peer_close(ctypes.c_void_p(base))
 
     @property
     def others(self) -> List[int]:
@@ -66,7 +90,6 @@ class PeerTensor:
         return [p for r, p in enumerate(self.pointers) if r != self.rank]
 
     def close(self) -> None:
-        lib = N.load()
         for base in self._bases:
-            lib.aidn_peer_close(ctypes.c_void_p(base))
+            self._close_one(base)
         self._bases = []

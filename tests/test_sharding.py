@@ -79,3 +79,51 @@ def test_two_rank_head_shards_gathered_equal_full(tmp_path):
     mp.spawn(_worker, args=(2, _free_port(), q, k, v, out_path), nprocs=2, join=True)
     full = O.sdpa(q, k, v, causal=True)
     assert np.array_equal(np.load(out_path), full[0])
+
+
+def _peer_worker(rank, world, port, scenario, out_dir):
+    """The host side of the fused gather (peer.exchange_mappings) with the three library calls replaced by fakes."""
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    from aidotnet.tensors_b200.peer import exchange_mappings
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    closed = []
+
+    def export(ptr):
+        if scenario == "export_fails_on_1" and rank == 1:
+            raise RuntimeError("no handle for this allocation")
+        return bytes([rank]) * 64, 16 * rank
+
+    def open_mapping(handle):
+        if scenario == "open_fails_on_0" and rank == 0:
+            raise RuntimeError("cannot map")
+        return 0x100000 * (1 + handle[0])
+
+    result = None
+    try:
+        pointers, bases = exchange_mappings(dist, 0xABC000 + rank, export, open_mapping, closed.append)
+        result = ("ok", pointers, bases)
+    except RuntimeError as exc:
+        result = ("error", str(exc), list(closed))
+    np.save(os.path.join(out_dir, f"peer{rank}.npy"), np.array([repr(result)]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("scenario", ["fine", "export_fails_on_1", "open_fails_on_0"])
+def test_peer_mapping_exchange_agrees_on_success_and_failure(tmp_path, scenario):
+    """Two gloo ranks: on success every rank holds the other's tensor at base + offset; a failure on ONE rank makes
+    BOTH raise the same error (nobody is left waiting in a collective) and unmaps what had been mapped."""
+    import torch.multiprocessing as mp
+    mp.spawn(_peer_worker, args=(2, _free_port(), scenario, str(tmp_path)), nprocs=2, join=True)
+    res = [eval(str(np.load(tmp_path / f"peer{r}.npy")[0])) for r in range(2)]
+    if scenario == "fine":
+        assert res[0] == ("ok", [0xABC000, 0x200000 + 16], [0x200000])
+        assert res[1] == ("ok", [0x100000 + 0, 0xABC001], [0x100000])
+    elif scenario == "export_fails_on_1":
+        assert res[0][0] == res[1][0] == "error"
+        assert "rank 1: no handle" in res[0][1] and "rank 1: no handle" in res[1][1]
+    else:
+        assert res[0][0] == res[1][0] == "error" and "rank 0: cannot map" in res[1][1]
+        assert res[1][2] == [0x100000]      # rank 1 had mapped rank 0's tensor and let go of it again
+
