@@ -768,6 +768,25 @@ def long_context_job(local, rank, world, pk, steps, dist):
         peers.close()
     except Exception as exc:   # the mapping is host plumbing outside the C ABI's hot path: report, do not fail the line
         fused = str(exc)
+    # The same pair with a 16-bit output tensor (half the bytes to send): kernel alone, then fused.
+    out16 = None
+    if isinstance(fused, list):
+        try:
+            r16 = Runner(dict(w, out16=True), local, shard=(sh.head_begin, sh.head_count))
+            k16, _, _ = r16.time_steps(steps, 2, None, dist, repeats=1)
+            peers16 = PeerTensor(r16.out, dist)
+            token16 = torch.zeros(1, device="cuda")
+            f16, _, _ = r16.time_steps(steps, 2, None, dist, repeats=1, peer_out=peers16.others,
+                                       after_step=lambda: dist.all_reduce(token16))
+            torch.cuda.synchronize()
+            dist.barrier()
+            peers16.close()
+            out16 = [k16, f16]
+            del r16
+        except Exception as exc:
+            out16 = str(exc)
+    t16 = torch.tensor(out16 if isinstance(out16, list) else [0.0, 0.0], device="cuda")
+    dist.all_reduce(t16, op=dist.ReduceOp.MAX)
     t = torch.tensor([fused[0], fused[2]] if isinstance(fused, list) else [0.0, 0.0], device="cuda")
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     fsecs, nsecs = float(t[0].item()), float(t[1].item())
@@ -798,6 +817,10 @@ def long_context_job(local, rank, world, pk, steps, dist):
                              "target": "the slower of FLOP / measured bf16 peak and bytes sent / 770 GB/s (measured peer copy)",
                              "how": "peer_out: the kernel's TMA stores write every tile to all ranks; one-element all-reduce per step as the rank barrier"}
                             if isinstance(fused, list) else {"unavailable": fused}),
+           "fused_gather_out16": ({"kernel_ms_per_step": float(t16[0].item()) / steps * 1e3,
+                                   "fused_ms_per_step": float(t16[1].item()) / steps * 1e3,
+                                   "bytes_sent_per_rank": out_bytes / 2 / world * (world - 1)}
+                                  if isinstance(out16, list) else {"unavailable": out16}),
            "fused_gather_ok": bool(flags[2].item() == 1), "fused_gather_max_abs_diff_rank0": fused_diff,
            "gather_ok": bool(flags[1].item() == 1), "gather_check": {"rows": [r0, r0 + rows], "remote_heads": [qh[0], qh[-1]], "max_abs_diff_rank0": remote_diff},
            "check": dict(own, all_ranks=bool(flags[0].item() == 1))}
