@@ -45,6 +45,62 @@ def test_struct_layout_matches_header():
     assert ctypes.sizeof(native.MhaArgs) == f6
 
 
+def test_field_offsets_match_header():
+    """Field by field: every member of the ctypes mirrors sits at the offset the C compiler gives the member of the same
+    name in the header (a swapped or missing field with an unchanged total size would pass the size check above)."""
+    import subprocess
+    import tempfile
+    from aidotnet.tensors_b200 import native
+    pairs = [("aidn_sdpa_desc", native.SdpaDesc), ("aidn_sdpa_args", native.SdpaArgs), ("aidn_paged_kv", native.PagedKv),
+             ("aidn_qkv_rope_args", native.QkvRopeArgs), ("aidn_sdpa_bwd_args", native.SdpaBwdArgs),
+             ("aidn_mha_args", native.MhaArgs)]
+    lines = ['#include "aidn_sdpa.h"', "#include <stddef.h>", "#include <stdio.h>", "int main(){"]
+    expected = []
+    for cname, mirror in pairs:
+        for fname, _ in mirror._fields_:
+            lines.append(f'printf("%zu\\n", offsetof({cname}, {fname}));')
+            expected.append((cname, fname, getattr(mirror, fname).offset))
+    lines.append("return 0;}")
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "t.c")
+        open(c, "w").write("\n".join(lines) + "\n")
+        exe = os.path.join(d, "t")
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
+        got = list(map(int, subprocess.check_output([exe]).split()))
+    assert len(got) == len(expected)
+    for (cname, fname, off), g in zip(expected, got):
+        assert off == g, f"{cname}.{fname}: ctypes offset {off}, header offset {g}"
+
+
+def test_csharp_binding_lists_the_same_fields_in_the_same_order():
+    """The P/Invoke structs cannot be compiled here (no .NET toolchain), so they are checked as text: every struct of
+    bindings/AidnSdpaNative.cs names the fields of its ctypes mirror in the same order (`@out` = out; a C array member
+    may be spelled as numbered fields)."""
+    import re
+    from aidotnet.tensors_b200 import native
+    text = open(os.path.join(ROOT, "aidotnet", "tensors_b200", "bindings", "AidnSdpaNative.cs")).read()
+    pairs = [("AidnSdpaDesc", native.SdpaDesc), ("AidnSdpaArgs", native.SdpaArgs), ("AidnPagedKv", native.PagedKv),
+             ("AidnQkvRopeArgs", native.QkvRopeArgs), ("AidnSdpaBwdArgs", native.SdpaBwdArgs), ("AidnMhaArgs", native.MhaArgs)]
+    for cs_name, mirror in pairs:
+        m = re.search(r"struct\s+" + cs_name + r"\s*\{(.*?)\n    \}", text, re.S)
+        assert m, f"{cs_name} not found in the C# binding"
+        names = []
+        for line in m.group(1).split("\n"):
+            line = line.split("//")[0].strip()
+            if not line.startswith("public"):
+                continue
+            decl = line.rstrip(";").split()
+            body = " ".join(decl[2:]) if decl[1] != "fixed" else " ".join(decl[3:])
+            for item in body.split(","):
+                name = item.strip().lstrip("@")
+                name = re.sub(r"\[.*\]$", "", name)
+                name = re.sub(r"\d+$", "", name) if re.fullmatch(r"[a-z_]+\d", name) and name[:-1] + "0" in body else name
+                if name and (not names or names[-1] != name):
+                    names.append(name)
+        expected = [f for f, _ in mirror._fields_]
+        assert names == expected, f"{cs_name}: C# lists {names}, the C ABI has {expected}"
+
+
 def test_validation_without_gpu():
     from aidotnet.tensors_b200 import native as N
     N.load()
