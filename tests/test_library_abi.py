@@ -101,6 +101,15 @@ def test_csharp_binding_lists_the_same_fields_in_the_same_order():
         assert names == expected, f"{cs_name}: C# lists {names}, the C ABI has {expected}"
 
 
+def test_csharp_binding_declares_every_entry_point():
+    """Every exported entry point has a DllImport in the C# binding (the debug hook of aidn_sdpa_debug.h excepted:
+    it is for this repository's tests)."""
+    from aidotnet.tensors_b200 import native
+    text = open(os.path.join(ROOT, "aidotnet", "tensors_b200", "bindings", "AidnSdpaNative.cs")).read()
+    missing = [n for n in native.EXPORTS if n != "aidn_sdpa_debug_set" and f"extern" in text and f" {n}(" not in text]
+    assert not missing, f"no DllImport for {missing}"
+
+
 def test_validation_without_gpu():
     from aidotnet.tensors_b200 import native as N
     N.load()
